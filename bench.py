@@ -1,0 +1,400 @@
+#!/usr/bin/env python
+"""Benchmark of the convolution hot path: forward + backward (dX, dW, db) + gradient all-reduce (N > 1) + SGD step
+of one convolution layer on synthetic data, one process per GPU.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload alexnet_conv1|caffenet_conv2|lenet_conv1]
+    python bench.py --impl reference ...      # the reference's own CPU code (oracle/_ref) on the host cores
+
+Prints ONE JSON line (rank 0).  `value` is whole-job images/s with inputs resident in HBM; `e2e` is the same metric
+through the host-buffer C-ABI calls (pinned host memory, copies inside the timed region); `roofline` describes the
+slowest of the three contraction passes against the 3xTF32 tensor roofline; `cpu_baseline` is the reference CPU path
+timed on this box's host cores in the same run.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "conv_fwd_bwd_images_per_sec"
+WORKLOADS = {
+    # BASELINE config 2: AlexNet conv1, batch 256 per GPU, X ~ N(0,1), W ~ N(0,0.01), bias 0, dY ~ N(0,1)
+    "alexnet_conv1": dict(B=256, D=3, n=227, o=96, k=11, s=4, p=0, g=1, x="normal", bias="zero"),
+    # BASELINE config 3 geometry: CaffeNet conv2 (grouped), post-ReLU inputs
+    "caffenet_conv2": dict(B=256, D=96, n=27, o=256, k=5, s=1, p=2, g=2, x="relu", bias="one"),
+    # BASELINE config 1: LeNet conv1
+    "lenet_conv1": dict(B=64, D=1, n=28, o=20, k=5, s=1, p=0, g=1, x="uniform", bias="normal"),
+}
+SOLVER = dict(base_lr=0.01, momentum=0.9, weight_decay=0.0005)  # caffenet solver values; lr kept small on purpose
+
+
+def out_size(w):
+    return (w["n"] + 2 * w["p"] - w["k"]) // w["s"] + 1
+
+
+def gemm_flops(w):
+    m = out_size(w)
+    return 2.0 * w["o"] * (w["k"] ** 2 * w["D"] // w["g"]) * m * m * w["B"]
+
+
+def synth(w, seed):
+    rng = np.random.default_rng(seed)
+    m = out_size(w)
+    B, D, n, o, k, g = w["B"], w["D"], w["n"], w["o"], w["k"], w["g"]
+    if w["x"] == "uniform":
+        X = rng.random((B, D, n, n), dtype=np.float32)
+    else:
+        X = rng.standard_normal((B, D, n, n), dtype=np.float32)
+        if w["x"] == "relu":
+            np.maximum(X, 0, out=X)
+    W = (0.01 * rng.standard_normal((o, D // g, k, k))).astype(np.float32)
+    bias = {"zero": np.zeros(o, np.float32), "one": np.ones(o, np.float32),
+            "normal": (0.01 * rng.standard_normal(o)).astype(np.float32)}[w["bias"]]
+    dY = rng.standard_normal((B, o, m, m), dtype=np.float32)
+    return X, W, bias, dY
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(bf16_tflops=p["bf16_tflops"], bf16_tflops_sustained=p.get("bf16_tflops_sustained"),
+                    hbm_gbs=p["hbm_gbs"], source="measured (MEASURED_PEAKS.json)")
+    return dict(bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, hbm_gbs=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index):
+        self.idx = device_index
+        self.lines = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                                          "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line)
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], None, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9 or f[0] != str(self.idx):
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax = float(f[2])
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": smax, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+def cpu_reference_time(w, iters, warmup, with_update):
+    """(images/s, cores, kind, sample) of the reference CPU path on this host; falls back to the C port."""
+    from oracle import build as obuild, pyoracle
+    X, W, bias, dY = synth(w, 1234)
+    ref = pyoracle.reference()
+    if ref is not None:
+        parts = ref.default_partitions(w["B"])
+        per_group = []
+        g = w["g"]
+        Dg, og = w["D"] // g, w["o"] // g
+        for gi in range(g):  # the reference bridge has no group concept: one bridge per channel slice
+            Xs = np.ascontiguousarray(X[:, gi * Dg:(gi + 1) * Dg])
+            Ws = np.ascontiguousarray(W[gi * og:(gi + 1) * og])
+            bs = np.ascontiguousarray(bias[gi * og:(gi + 1) * og])
+            dYs = np.ascontiguousarray(dY[:, gi * og:(gi + 1) * og])
+            per_group.append(ref.conv_time(Xs, Ws, bs, dYs, w["k"], w["s"], w["p"], parts, True, warmup, iters)[0])
+        sec = sum(per_group)
+        return dict(value=w["B"] / sec, unit="images/s", cores=parts, kind="reference",
+                    sample="%d fwd+bwd passes over the full %d-image batch (median), %d batch partitions x 1 BLAS thread, "
+                           "hardware_concurrency %d, %s" % (iters, w["B"], parts, ref.hardware_concurrency(),
+                                                            ref.blas_config()),
+                    seconds_per_step=sec)
+    obuild.build_port()
+    port = pyoracle.port()
+    nb = max(1, min(w["B"], 8))
+    Xs, dYs = X[:nb].copy(), dY[:nb].copy()
+    t0 = time.perf_counter()
+    port.conv_forward(Xs, W, bias, w["k"], w["s"], w["p"], w["g"])
+    port.conv_backward(Xs, W, dYs, w["k"], w["s"], w["p"], w["g"])
+    sec = time.perf_counter() - t0
+    return dict(value=nb / sec, unit="images/s", cores=os.cpu_count(), kind="port",
+                sample="1 fwd+bwd pass over %d images (plain-C restatement, OpenMP)" % nb, seconds_per_step=sec)
+
+
+def run_reference_arm(args, w, rank, world):
+    if rank != 0:
+        return
+    from oracle import pyoracle
+    ref = pyoracle.reference()
+    X, W, bias, dY = synth(w, 1234)
+    if ref is None:
+        base = cpu_reference_time(w, max(1, args.steps), max(0, args.warmup), True)
+        ms = base["seconds_per_step"] * 1e3
+        val = base["value"]
+        cpu = base
+    else:
+        parts = ref.default_partitions(w["B"])
+        g = w["g"]
+        Dg, og = w["D"] // g, w["o"] // g
+        handles = []
+        for gi in range(g):
+            h = ref.conv_create(w["B"], Dg, w["n"], og, w["k"], w["s"], w["p"], True, parts, True,
+                                SOLVER["base_lr"], SOLVER["momentum"], SOLVER["weight_decay"])
+            ref.lib.cctref_conv_set_model(h, pyoracle._p(np.ascontiguousarray(W[gi * og:(gi + 1) * og])),
+                                          pyoracle._p(np.ascontiguousarray(bias[gi * og:(gi + 1) * og])))
+            ref.lib.cctref_conv_load(h, pyoracle._p(np.ascontiguousarray(X[:, gi * Dg:(gi + 1) * Dg])),
+                                     pyoracle._p(np.ascontiguousarray(dY[:, gi * og:(gi + 1) * og])))
+            handles.append(h)
+        def step():
+            for h in handles:
+                ref.lib.cctref_conv_step(h, 1)
+        for _ in range(args.warmup):
+            step()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            step()
+        sec = (time.perf_counter() - t0) / args.steps
+        for h in handles:
+            ref.conv_destroy(h)
+        ms, val = sec * 1e3, w["B"] / sec
+        cpu = dict(value=val, unit="images/s", cores=parts, kind="reference",
+                   sample="each step = forward + backward + SGD update of the reference's ParallelizedBridge over one "
+                          "%d-image batch (%d of the job's %d images), %d partitions x 1 BLAS thread, "
+                          "hardware_concurrency %d, %s" % (w["B"], w["B"], w["B"] * world, parts,
+                                                           ref.hardware_concurrency(), ref.blas_config()))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "images/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": config_of(args, w, world), "tflops": 3 * gemm_flops(w) / (ms * 1e-3) / 1e12,
+        "cpu_baseline": cpu,
+        "e2e": {"value": val, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def config_of(args, w, world):
+    return {"workload": args.workload, "batch_per_gpu": w["B"], "global_batch": w["B"] * world,
+            "in": "%dx%dx%d" % (w["D"], w["n"], w["n"]), "filters": "%d x %dx%d stride %d pad %d groups %d" %
+            (w["o"], w["k"], w["k"], w["s"], w["p"], w["g"]),
+            "step": "forward + backward (dX, dW, db) + gradient all-reduce (N>1) + SGD momentum step",
+            "l2": "inputs larger than L2 (X + dY per step exceed 126 MB)" if
+            4 * w["B"] * (w["D"] * w["n"] ** 2 + w["o"] * out_size(w) ** 2) > 126e6 else "L2 flushed between steps",
+            "parallelism": "dp%d" % world}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="alexnet_conv1", choices=sorted(WORKLOADS))
+    ap.add_argument("--algo", type=int, default=0, help="0 auto, 1 SIMT fp32, 2 tcgen05 3xTF32")
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    w = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, w, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from caffecontroll_b200 import capi
+    from caffecontroll_b200.bridge import Context
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    stream = torch.cuda.current_stream()
+    ctx = Context(local_rank, stream=stream.cuda_stream)
+    lib = ctx.lib
+
+    B, D, n, o, k, g = w["B"], w["D"], w["n"], w["o"], w["k"], w["g"]
+    m = out_size(w)
+    X, W, bias, dY = synth(w, 1000 * (rank + 1))
+    nw = W.size
+    tX, tdY = torch.from_numpy(X).to(dev), torch.from_numpy(dY).to(dev)
+    tY = torch.empty((B, o, m, m), device=dev)
+    tdX = torch.empty_like(tX)
+    params = torch.cat([torch.from_numpy(W).reshape(-1), torch.from_numpy(bias)]).to(dev)   # W | bias
+    grads = torch.zeros_like(params)                                                          # dW | db
+    hist = torch.zeros_like(params)
+    pW, pb = params.data_ptr(), params.data_ptr() + 4 * nw
+    pdW, pdb = grads.data_ptr(), grads.data_ptr() + 4 * nw
+    phW, phb = hist.data_ptr(), hist.data_ptr() + 4 * nw
+
+    desc = capi.ConvDesc(B, D, n, o, k, w["s"], w["p"], g, 1, args.algo)
+    plan = C.c_void_p()
+    capi.check(lib.cct_conv_plan_create(ctx.h, C.byref(desc), C.byref(plan)), "cct_conv_plan_create", ctx.h)
+    algo = C.c_int()
+    lib.cct_conv_plan_algo(plan, C.byref(algo))
+    vp = C.c_void_p
+    lr = SOLVER["base_lr"]
+
+    def step():
+        capi.check(lib.cct_conv_forward(plan, vp(tX.data_ptr()), vp(pW), vp(pb), vp(tY.data_ptr()), 0), "forward", ctx.h)
+        capi.check(lib.cct_conv_backward(plan, vp(tX.data_ptr()), vp(pW), vp(tdY.data_ptr()), vp(tdX.data_ptr()),
+                                         vp(pdW), vp(pdb)), "backward", ctx.h)
+        if world > 1:
+            dist.all_reduce(grads)  # SUM over partitions, as ParallelizedBridge does on the host
+        # weights: lr_mult 1, decay_mult 1; bias: lr_mult 2, decay_mult 0 (CaffeNet's blobs_lr / weight_decay)
+        capi.check(lib.cct_sgd_step(ctx.h, nw, vp(pW), vp(pdW), vp(phW), lr, SOLVER["momentum"],
+                                    SOLVER["weight_decay"]), "sgd W", ctx.h)
+        capi.check(lib.cct_sgd_step(ctx.h, o, vp(pb), vp(pdb), vp(phb), 2 * lr, SOLVER["momentum"], 0.0), "sgd b", ctx.h)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+
+    # Per-kernel durations: same steps again with CUDA events around each kernel group on the launching stream.
+    lib.cct_conv_plan_enable_timing(plan, 1)
+    acc = np.zeros(5)
+    prof_steps = min(args.steps, 10)
+    for _ in range(prof_steps):
+        step()
+        t5 = (C.c_float * 5)()
+        capi.check(lib.cct_conv_plan_last_timings(plan, t5), "timings", ctx.h)
+        acc += np.array(list(t5))
+    lib.cct_conv_plan_enable_timing(plan, 0)
+    clocks = sampler.stop() if rank == 0 else None
+    k_ms = acc / prof_steps
+    F = gemm_flops(w)
+    passes = {"forward": k_ms[0], "wgrad": k_ms[1], "dgrad": k_ms[3]}
+    peaks = load_peaks()
+    tensor_peak = peaks["bf16_tflops"] / 2.0 / 3.0  # TF32 = 1/2 bf16 rate; 3 MMAs per product
+    dom = max(passes, key=lambda x: passes[x])
+    ach = F / (passes[dom] * 1e-3) / 1e12 if passes[dom] > 0 else 0.0
+    n_phase = w["s"] ** 2
+    roofline = {
+        "bound": "tensor", "kernel": {"forward": "gather_conv_kernel", "dgrad": "gather_conv_kernel (x%d stride phases)" % n_phase,
+                                      "wgrad": "wgrad_kernel"}[dom] if algo.value == 2 else "simt_%s" % dom,
+        "pass": dom, "achieved": ach, "peak": tensor_peak, "unit": "TFLOP/s", "frac": ach / tensor_peak,
+        "traffic": None,
+        "peak_source": "%s: bf16 burst %.1f TFLOP/s / 2 (TF32 rate) / 3 (3xTF32) — of measured" %
+                       (peaks["source"], peaks["bf16_tflops"]),
+        "flops_per_launch": F, "ms_per_launch": passes[dom],
+        "timing": "CUDA events around each kernel group on the launching stream, mean of %d steps run right after the "
+                  "timed region" % prof_steps,
+        "passes_ms": {"forward": k_ms[0], "wgrad": k_ms[1], "wgrad_reduce": k_ms[2], "dgrad": k_ms[3],
+                      "forward_repack": k_ms[4]},
+        "passes_tflops": {p: (F / (v * 1e-3) / 1e12 if v > 0 else None) for p, v in passes.items()},
+    }
+
+    # End to end through the host-buffer C-ABI calls: pinned host memory, copies inside the timed region.
+    hX, hW, hb, hdY = (torch.from_numpy(a).pin_memory() for a in (X, W, bias, dY))
+    hY = torch.empty((B, o, m, m)).pin_memory()
+    hdX, hdW, hdb = torch.empty(X.shape).pin_memory(), torch.empty(W.shape).pin_memory(), torch.empty(o).pin_memory()
+
+    def e2e_step():
+        capi.check(lib.cct_conv_forward_host(plan, vp(hX.data_ptr()), vp(hW.data_ptr()), vp(hb.data_ptr()),
+                                             vp(hY.data_ptr()), 0), "forward_host", ctx.h)
+        capi.check(lib.cct_conv_backward_host(plan, None, None, vp(hdY.data_ptr()), vp(hdX.data_ptr()),
+                                              vp(hdW.data_ptr()), vp(hdb.data_ptr())), "backward_host", ctx.h)
+        return float(hdb[0])  # the step's result is read on the host
+
+    e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.e2e_steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_s = (time.perf_counter() - t0) / args.e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    h2d = 4 * (X.size + W.size + bias.size + dY.size)
+    d2h = 4 * (hY.numel() + X.size + W.size + bias.size)
+
+    lib.cct_conv_plan_destroy(plan)
+    if rank == 0:
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            cpu = cpu_reference_time(w, 3, 1, False)
+            cpu.pop("seconds_per_step", None)
+        launches_per_step = (2 + 2 + 2 * n_phase + 2) if algo.value == 2 else (1 + 3 + 2)
+        line = {
+            "metric": METRIC, "value": world * B / (ms_step * 1e-3), "unit": "images/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": dict(config_of(args, w, world), algo={1: "simt_fp32", 2: "tcgen05_3xtf32"}[algo.value]),
+            "tflops": world * 3 * F / (ms_step * 1e-3) / 1e12,
+            "roofline": roofline, "cpu_baseline": cpu,
+            "e2e": {"value": world * B / e2e_s, "unit": "images/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3, "steps": args.e2e_steps},
+            "clocks": clocks, "gpu_launches": launches_per_step * args.steps,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    ctx.close()
+
+
+if __name__ == "__main__":
+    main()

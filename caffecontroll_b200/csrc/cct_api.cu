@@ -1,0 +1,351 @@
+// Context, memory and convolution-plan entry points of include/cct_b200.h.
+#include <cstdio>
+#include <new>
+
+#include "cct_internal.h"
+
+struct cct_conv_plan {
+  cct_ctx* ctx = nullptr;
+  cct_conv_desc desc{};
+  ConvGeom G{};
+  int algo = CCT_ALGO_SIMT_FP32;
+  UmmaPlan* umma = nullptr;
+  // Device staging for the host-buffer entry points, allocated on first use.
+  float *sX = nullptr, *sW = nullptr, *sb = nullptr, *sY = nullptr, *sdY = nullptr, *sdX = nullptr, *sdW = nullptr,
+        *sdb = nullptr;
+  size_t staging_bytes = 0;
+  bool staged_forward = false;  // sX / sW hold what the last cct_conv_forward_host uploaded
+  PhaseTimer timer;
+};
+
+namespace {
+
+int geom_from_desc(const cct_conv_desc* d, ConvGeom* G) {
+  if (!d) return CCT_ERR_INVALID;
+  if (d->batch <= 0 || d->in_depth <= 0 || d->in_size <= 0 || d->out_depth <= 0 || d->kernel <= 0 || d->stride <= 0 ||
+      d->pad < 0 || d->groups <= 0)
+    return CCT_ERR_INVALID;
+  if (d->in_depth % d->groups || d->out_depth % d->groups) return CCT_ERR_INVALID;
+  if (d->in_size + 2 * d->pad < d->kernel) return CCT_ERR_INVALID;
+  G->B = d->batch; G->D = d->in_depth; G->n = d->in_size; G->o = d->out_depth;
+  G->k = d->kernel; G->s = d->stride; G->p = d->pad; G->g = d->groups;
+  G->m = (d->in_size + 2 * d->pad - d->kernel) / d->stride + 1;
+  G->Dg = d->in_depth / d->groups;
+  G->og = d->out_depth / d->groups;
+  G->bias = d->bias_term != 0;
+  // 32-bit index arithmetic inside the kernels: keep every tensor below 2^31 elements.
+  const double lim = 2147483647.0;
+  if ((double)G->B * G->D * G->n * G->n > lim || (double)G->B * G->o * G->m * G->m > lim) return CCT_ERR_UNSUPPORTED;
+  return CCT_OK;
+}
+
+int ensure_staging(cct_conv_plan* p) {
+  if (p->sX) return CCT_OK;
+  cct_ctx* ctx = p->ctx;
+  const ConvGeom& G = p->G;
+  const size_t nx = (size_t)G.B * G.D * G.n * G.n, ny = (size_t)G.B * G.o * G.m * G.m,
+               nw = (size_t)G.o * G.Dg * G.k * G.k;
+  float** slots[] = {&p->sX, &p->sW, &p->sb, &p->sY, &p->sdY, &p->sdX, &p->sdW, &p->sdb};
+  const size_t counts[] = {nx, nw, (size_t)G.o, ny, ny, nx, nw, (size_t)G.o};
+  for (int i = 0; i < 8; ++i) {
+    CCT_CUDA(ctx, cudaMalloc((void**)slots[i], counts[i] * sizeof(float)));
+    p->staging_bytes += counts[i] * sizeof(float);
+  }
+  return CCT_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int cct_device_count(int* count) {
+  if (!count) return CCT_ERR_INVALID;
+  return cudaGetDeviceCount(count) == cudaSuccess ? CCT_OK : CCT_ERR_CUDA;
+}
+
+static int ctx_create_common(int device_id, cudaStream_t stream, bool make_stream, cct_ctx** out) {
+  if (!out) return CCT_ERR_INVALID;
+  *out = nullptr;
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || device_id < 0 || device_id >= count) return CCT_ERR_CUDA;
+  cct_ctx* ctx = new (std::nothrow) cct_ctx();
+  if (!ctx) return CCT_ERR_NOMEM;
+  ctx->device = device_id;
+  cudaError_t e = cudaSetDevice(device_id);
+  cudaDeviceProp prop;
+  if (e == cudaSuccess) e = cudaGetDeviceProperties(&prop, device_id);
+  if (e == cudaSuccess && prop.major != 10) {
+    std::fprintf(stderr, "cct_b200: device %d is sm_%d%d; this library contains sm_100a code only\n", device_id,
+                 prop.major, prop.minor);
+    delete ctx;
+    return CCT_ERR_UNSUPPORTED;
+  }
+  if (e == cudaSuccess) {
+    ctx->sm_count = prop.multiProcessorCount;
+    if (make_stream) {
+      e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+      ctx->owns_stream = true;
+    } else {
+      ctx->stream = stream;
+    }
+  }
+  int* hs = nullptr;
+  if (e == cudaSuccess) e = cudaHostAlloc((void**)&hs, sizeof(int), cudaHostAllocMapped);
+  if (e == cudaSuccess) {
+    *hs = 0;
+    ctx->status_host = hs;
+    e = cudaHostGetDevicePointer((void**)&ctx->status_dev, hs, 0);
+  }
+  if (e != cudaSuccess) {
+    std::fprintf(stderr, "cct_b200: context creation failed: %s\n", cudaGetErrorString(e));
+    if (hs) cudaFreeHost(hs);
+    if (ctx->owns_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return CCT_ERR_CUDA;
+  }
+  *out = ctx;
+  return CCT_OK;
+}
+
+int cct_ctx_create(int device_id, cct_ctx** out) { return ctx_create_common(device_id, nullptr, true, out); }
+
+int cct_ctx_create_on_stream(int device_id, void* cuda_stream, cct_ctx** out) {
+  return ctx_create_common(device_id, (cudaStream_t)cuda_stream, false, out);
+}
+
+int cct_ctx_destroy(cct_ctx* ctx) {
+  if (!ctx) return CCT_ERR_INVALID;
+  cudaSetDevice(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
+  if (ctx->status_host) cudaFreeHost((void*)ctx->status_host);
+  delete ctx;
+  return CCT_OK;
+}
+
+int cct_sync(cct_ctx* ctx) {
+  if (!ctx) return CCT_ERR_INVALID;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  CCT_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (*ctx->status_host != 0) {
+    char buf[96];
+    std::snprintf(buf, sizeof buf, "device-side bounded wait gave up (status word 0x%x)", *ctx->status_host);
+    ctx->last_error = buf;
+    *ctx->status_host = 0;
+    return CCT_ERR_TIMEOUT;
+  }
+  return CCT_OK;
+}
+
+const char* cct_last_error_string(cct_ctx* ctx) { return ctx ? ctx->last_error.c_str() : "null context"; }
+
+int cct_malloc(cct_ctx* ctx, size_t bytes, void** dptr) {
+  if (!ctx || !dptr) return CCT_ERR_INVALID;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  CCT_CUDA(ctx, cudaMalloc(dptr, bytes ? bytes : 1));
+  return CCT_OK;
+}
+
+int cct_free(cct_ctx* ctx, void* dptr) {
+  if (!ctx) return CCT_ERR_INVALID;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  CCT_CUDA(ctx, cudaFree(dptr));
+  return CCT_OK;
+}
+
+int cct_malloc_host(cct_ctx* ctx, size_t bytes, void** hptr) {
+  if (!ctx || !hptr) return CCT_ERR_INVALID;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  CCT_CUDA(ctx, cudaHostAlloc(hptr, bytes ? bytes : 1, cudaHostAllocDefault));
+  return CCT_OK;
+}
+
+int cct_free_host(cct_ctx* ctx, void* hptr) {
+  if (!ctx) return CCT_ERR_INVALID;
+  CCT_CUDA(ctx, cudaFreeHost(hptr));
+  return CCT_OK;
+}
+
+static int copy_common(cct_ctx* ctx, void* dst, const void* src, size_t bytes, cudaMemcpyKind kind) {
+  if (!ctx || ((!dst || !src) && bytes)) return CCT_ERR_INVALID;
+  if (!bytes) return CCT_OK;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  CCT_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, kind, ctx->stream));
+  return CCT_OK;
+}
+
+int cct_memcpy_h2d(cct_ctx* ctx, void* dst, const void* src, size_t bytes) {
+  return copy_common(ctx, dst, src, bytes, cudaMemcpyHostToDevice);
+}
+int cct_memcpy_d2h(cct_ctx* ctx, void* dst, const void* src, size_t bytes) {
+  return copy_common(ctx, dst, src, bytes, cudaMemcpyDeviceToHost);
+}
+int cct_memcpy_d2d(cct_ctx* ctx, void* dst, const void* src, size_t bytes) {
+  return copy_common(ctx, dst, src, bytes, cudaMemcpyDeviceToDevice);
+}
+
+int cct_memset(cct_ctx* ctx, void* dptr, int byte_value, size_t bytes) {
+  if (!ctx || (!dptr && bytes)) return CCT_ERR_INVALID;
+  if (!bytes) return CCT_OK;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  CCT_CUDA(ctx, cudaMemsetAsync(dptr, byte_value, bytes, ctx->stream));
+  return CCT_OK;
+}
+
+int cct_conv_out_size(const cct_conv_desc* desc, int* out_size) {
+  ConvGeom G;
+  const int rc = geom_from_desc(desc, &G);
+  if (rc != CCT_OK || !out_size) return rc != CCT_OK ? rc : CCT_ERR_INVALID;
+  *out_size = G.m;
+  return CCT_OK;
+}
+
+int cct_conv_plan_create(cct_ctx* ctx, const cct_conv_desc* desc, cct_conv_plan** out) {
+  if (!ctx || !out) return CCT_ERR_INVALID;
+  *out = nullptr;
+  ConvGeom G;
+  const int rc = geom_from_desc(desc, &G);
+  if (rc != CCT_OK) {
+    ctx->last_error = "invalid convolution descriptor";
+    return rc;
+  }
+  int algo = desc->algo;
+  if (algo == CCT_ALGO_AUTO) algo = umma_supported(G) ? CCT_ALGO_UMMA_3XTF32 : CCT_ALGO_SIMT_FP32;
+  if (algo != CCT_ALGO_SIMT_FP32 && algo != CCT_ALGO_UMMA_3XTF32) return CCT_ERR_INVALID;
+  if (algo == CCT_ALGO_UMMA_3XTF32 && !umma_supported(G)) {
+    ctx->last_error = "shape not supported by the tcgen05 path";
+    return CCT_ERR_UNSUPPORTED;
+  }
+  cct_conv_plan* p = new (std::nothrow) cct_conv_plan();
+  if (!p) return CCT_ERR_NOMEM;
+  p->ctx = ctx;
+  p->desc = *desc;
+  p->G = G;
+  p->algo = algo;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (algo == CCT_ALGO_UMMA_3XTF32) {
+    const int rc2 = umma_plan_create(ctx, G, &p->umma);
+    if (rc2 != CCT_OK) {
+      delete p;
+      return rc2;
+    }
+  }
+  *out = p;
+  return CCT_OK;
+}
+
+int cct_conv_plan_destroy(cct_conv_plan* plan) {
+  if (!plan) return CCT_ERR_INVALID;
+  cct_ctx* ctx = plan->ctx;
+  cudaSetDevice(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  if (plan->umma) umma_plan_destroy(ctx, plan->umma);
+  for (cudaEvent_t e : plan->timer.ev)
+    if (e) cudaEventDestroy(e);
+  float* slots[] = {plan->sX, plan->sW, plan->sb, plan->sY, plan->sdY, plan->sdX, plan->sdW, plan->sdb};
+  for (float* s : slots)
+    if (s) cudaFree(s);
+  delete plan;
+  return CCT_OK;
+}
+
+int cct_conv_plan_algo(const cct_conv_plan* plan, int* algo) {
+  if (!plan || !algo) return CCT_ERR_INVALID;
+  *algo = plan->algo;
+  return CCT_OK;
+}
+
+int cct_conv_plan_workspace_bytes(const cct_conv_plan* plan, size_t* bytes) {
+  if (!plan || !bytes) return CCT_ERR_INVALID;
+  *bytes = (plan->umma ? umma_plan_workspace_bytes(plan->umma) : 0) + plan->staging_bytes;
+  return CCT_OK;
+}
+
+int cct_conv_plan_enable_timing(cct_conv_plan* plan, int enable) {
+  if (!plan) return CCT_ERR_INVALID;
+  cct_ctx* ctx = plan->ctx;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  PhaseTimer& t = plan->timer;
+  if (enable && !t.ev[0])
+    for (cudaEvent_t& e : t.ev) CCT_CUDA(ctx, cudaEventCreate(&e));
+  t.enabled = enable != 0;
+  for (bool& h : t.have) h = false;
+  return CCT_OK;
+}
+
+int cct_conv_plan_last_timings(cct_conv_plan* plan, float ms[5]) {
+  if (!plan || !ms) return CCT_ERR_INVALID;
+  cct_ctx* ctx = plan->ctx;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  CCT_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  for (int i = 0; i < PhaseTimer::kSlots; ++i) {
+    ms[i] = 0.f;
+    if (plan->timer.have[i]) CCT_CUDA(ctx, cudaEventElapsedTime(&ms[i], plan->timer.ev[2 * i], plan->timer.ev[2 * i + 1]));
+  }
+  return CCT_OK;
+}
+
+int cct_conv_forward(cct_conv_plan* plan, const float* X, const float* W, const float* bias, float* Y, int relu) {
+  if (!plan || !X || !W || !Y) return CCT_ERR_INVALID;
+  cct_ctx* ctx = plan->ctx;
+  if (plan->G.bias && !bias) return CCT_ERR_INVALID;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (plan->algo == CCT_ALGO_UMMA_3XTF32) return umma_conv_forward(ctx, plan->umma, X, W, bias, Y, relu, &plan->timer);
+  return simt_conv_forward(ctx, plan->G, X, W, bias, Y, relu, &plan->timer);
+}
+
+int cct_conv_backward(cct_conv_plan* plan, const float* X, const float* W, const float* dY, float* dX, float* dW,
+                      float* db) {
+  if (!plan || !X || !W || !dY || !dW) return CCT_ERR_INVALID;
+  cct_ctx* ctx = plan->ctx;
+  if (plan->G.bias && !db) return CCT_ERR_INVALID;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (plan->algo == CCT_ALGO_UMMA_3XTF32) return umma_conv_backward(ctx, plan->umma, X, W, dY, dX, dW, db, &plan->timer);
+  return simt_conv_backward(ctx, plan->G, X, W, dY, dX, dW, db, &plan->timer);
+}
+
+int cct_conv_forward_host(cct_conv_plan* plan, const float* hX, const float* hW, const float* hbias, float* hY,
+                          int relu) {
+  if (!plan || !hX || !hW || !hY) return CCT_ERR_INVALID;
+  cct_ctx* ctx = plan->ctx;
+  const ConvGeom& G = plan->G;
+  if (G.bias && !hbias) return CCT_ERR_INVALID;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  int rc = ensure_staging(plan);
+  if (rc != CCT_OK) return rc;
+  const size_t nx = (size_t)G.B * G.D * G.n * G.n, ny = (size_t)G.B * G.o * G.m * G.m,
+               nw = (size_t)G.o * G.Dg * G.k * G.k;
+  CCT_CUDA(ctx, cudaMemcpyAsync(plan->sX, hX, nx * 4, cudaMemcpyHostToDevice, ctx->stream));
+  CCT_CUDA(ctx, cudaMemcpyAsync(plan->sW, hW, nw * 4, cudaMemcpyHostToDevice, ctx->stream));
+  if (G.bias) CCT_CUDA(ctx, cudaMemcpyAsync(plan->sb, hbias, (size_t)G.o * 4, cudaMemcpyHostToDevice, ctx->stream));
+  rc = cct_conv_forward(plan, plan->sX, plan->sW, plan->sb, plan->sY, relu);
+  if (rc != CCT_OK) return rc;
+  CCT_CUDA(ctx, cudaMemcpyAsync(hY, plan->sY, ny * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  plan->staged_forward = true;
+  return cct_sync(ctx);
+}
+
+int cct_conv_backward_host(cct_conv_plan* plan, const float* hX, const float* hW, const float* hdY, float* hdX,
+                           float* hdW, float* hdb) {
+  if (!plan || !hdY || !hdW) return CCT_ERR_INVALID;
+  cct_ctx* ctx = plan->ctx;
+  const ConvGeom& G = plan->G;
+  if (G.bias && !hdb) return CCT_ERR_INVALID;
+  if ((!hX || !hW) && !plan->staged_forward) return CCT_ERR_INVALID;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  int rc = ensure_staging(plan);
+  if (rc != CCT_OK) return rc;
+  const size_t nx = (size_t)G.B * G.D * G.n * G.n, ny = (size_t)G.B * G.o * G.m * G.m,
+               nw = (size_t)G.o * G.Dg * G.k * G.k;
+  if (hX) CCT_CUDA(ctx, cudaMemcpyAsync(plan->sX, hX, nx * 4, cudaMemcpyHostToDevice, ctx->stream));
+  if (hW) CCT_CUDA(ctx, cudaMemcpyAsync(plan->sW, hW, nw * 4, cudaMemcpyHostToDevice, ctx->stream));
+  CCT_CUDA(ctx, cudaMemcpyAsync(plan->sdY, hdY, ny * 4, cudaMemcpyHostToDevice, ctx->stream));
+  rc = cct_conv_backward(plan, plan->sX, plan->sW, plan->sdY, hdX ? plan->sdX : nullptr, plan->sdW, plan->sdb);
+  if (rc != CCT_OK) return rc;
+  if (hdX) CCT_CUDA(ctx, cudaMemcpyAsync(hdX, plan->sdX, nx * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  CCT_CUDA(ctx, cudaMemcpyAsync(hdW, plan->sdW, nw * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  if (G.bias) CCT_CUDA(ctx, cudaMemcpyAsync(hdb, plan->sdb, (size_t)G.o * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  return cct_sync(ctx);
+}
+
+}  // extern "C"

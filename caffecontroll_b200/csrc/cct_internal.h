@@ -1,0 +1,71 @@
+// Internal declarations shared by the translation units behind include/cct_b200.h.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string>
+
+#include "../../include/cct_b200.h"
+
+struct cct_ctx {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  bool owns_stream = false;
+  int sm_count = 148;
+  // One word in mapped pinned host memory that kernels set when a bounded wait runs out; read by cct_sync().
+  volatile int* status_host = nullptr;
+  int* status_dev = nullptr;
+  std::string last_error;
+};
+
+#define CCT_CUDA(ctx, call)                                                                   \
+  do {                                                                                        \
+    cudaError_t e__ = (call);                                                                 \
+    if (e__ != cudaSuccess) {                                                                 \
+      (ctx)->last_error = std::string(#call) + ": " + cudaGetErrorString(e__);                \
+      return e__ == cudaErrorMemoryAllocation ? CCT_ERR_NOMEM : CCT_ERR_CUDA;                 \
+    }                                                                                         \
+  } while (0)
+
+#define CCT_CHECK_LAUNCH(ctx) CCT_CUDA(ctx, cudaGetLastError())
+
+// Optional per-kernel-group timing with CUDA events on the context's stream (measurement only).
+struct PhaseTimer {
+  static constexpr int kSlots = 5;  // 0 forward, 1 wgrad, 2 wgrad reduce, 3 dgrad (with its repacking), 4 forward repack
+  bool enabled = false;
+  cudaEvent_t ev[2 * kSlots] = {};
+  bool have[kSlots] = {};
+  void begin(int slot, cudaStream_t s) {
+    if (enabled) cudaEventRecord(ev[2 * slot], s);
+  }
+  void end(int slot, cudaStream_t s) {
+    if (enabled) {
+      cudaEventRecord(ev[2 * slot + 1], s);
+      have[slot] = true;
+    }
+  }
+};
+
+// Geometry of one convolution layer, resolved once per plan.
+struct ConvGeom {
+  int B, D, n, o, k, s, p, g;
+  int m;       // output size
+  int Dg, og;  // per-group depths
+  int bias;
+};
+
+// ---- SIMT fp32 path (conv_simt.cu) ----
+int simt_conv_forward(cct_ctx* ctx, const ConvGeom& G, const float* X, const float* W, const float* bias, float* Y,
+                      int relu, PhaseTimer* t);
+int simt_conv_backward(cct_ctx* ctx, const ConvGeom& G, const float* X, const float* W, const float* dY, float* dX,
+                       float* dW, float* db, PhaseTimer* t);
+
+// ---- tcgen05 3xTF32 path (conv_umma.cu) ----
+struct UmmaPlan;  // opaque: tables, packed weights, split-K scratch
+int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out);
+void umma_plan_destroy(cct_ctx* ctx, UmmaPlan* p);
+size_t umma_plan_workspace_bytes(const UmmaPlan* p);
+bool umma_supported(const ConvGeom& G);
+int umma_conv_forward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W, const float* bias, float* Y,
+                      int relu, PhaseTimer* t);
+int umma_conv_backward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W, const float* dY, float* dX,
+                       float* dW, float* db, PhaseTimer* t);

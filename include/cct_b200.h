@@ -1,0 +1,147 @@
+/* cct_b200.h — C ABI of the B200 (sm_100a) convolution hot path for Caffe con Troll.
+ *
+ * This is the drop-in boundary: everything above it (the C++ bridge mirror in caffecontroll_b200/host/, the
+ * Python binding in caffecontroll_b200/capi.py, or a DeviceDriver subclass inside the reference tree) speaks
+ * plain pointers and sizes.  All tensors are fp32, NCHW, dense — the layout of the reference's
+ * LogicalCube<float, Layout_CRDB> (src/LogicalCube_impl.hxx:217-219).  Unless a function says "host", every
+ * data pointer is a device pointer on the context's device, owned by the caller.
+ *
+ * Every function returns CCT_OK (0) or a CCT_ERR_* code and never aborts; the reference's convention
+ * ("functions return void, on error assert(false)", src/sched/DeviceDriver.h:48-51) is re-created by the
+ * bridge adaptor on top.  Work is enqueued on the context's stream; cct_sync() waits for it and reports
+ * device-side failures (a bounded wait that ran out).  A context may be used from any host thread, one
+ * caller at a time (the reference runs each bridge call on a fresh std::thread: src/bridges/PhysicalStratum.h:43-70).
+ */
+#ifndef CCT_B200_H
+#define CCT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  CCT_OK = 0,
+  CCT_ERR_INVALID = 1,     /* bad argument / shape */
+  CCT_ERR_CUDA = 2,        /* a CUDA runtime call failed; see cct_last_error_string */
+  CCT_ERR_NOMEM = 3,
+  CCT_ERR_TIMEOUT = 4,     /* a bounded device-side wait gave up */
+  CCT_ERR_UNSUPPORTED = 5
+};
+
+/* Which arithmetic runs the three contractions. */
+enum {
+  CCT_ALGO_AUTO = 0,       /* tcgen05 3xTF32 where the shape allows, else SIMT fp32 */
+  CCT_ALGO_SIMT_FP32 = 1,  /* direct convolution in fp32 FMA (exact fp32 products) */
+  CCT_ALGO_UMMA_3XTF32 = 2 /* implicit GEMM on tcgen05/TMEM, each operand split hi+lo in TF32, 3 MMAs */
+};
+
+typedef struct cct_ctx cct_ctx;
+typedef struct cct_conv_plan cct_conv_plan;
+
+/* ---- context, memory, sync: replaces DeviceDriver::{malloc,free,memcpy,memset,device_sync,set_device_id}
+ *      (src/sched/DeviceDriver.h:56-120) and GPUDriver's per-call cublasCreate/Destroy
+ *      (src/sched/DeviceDriver_GPU.cu:1601-1620): a context is created once and reused. ---- */
+int cct_ctx_create(int device_id, cct_ctx** out);
+/* Same, but enqueue on a stream the caller owns (a cudaStream_t passed as void*; NULL = legacy default stream). */
+int cct_ctx_create_on_stream(int device_id, void* cuda_stream, cct_ctx** out);
+int cct_ctx_destroy(cct_ctx* ctx);
+int cct_sync(cct_ctx* ctx);
+const char* cct_last_error_string(cct_ctx* ctx);
+int cct_device_count(int* count);
+
+int cct_malloc(cct_ctx* ctx, size_t bytes, void** dptr);
+int cct_free(cct_ctx* ctx, void* dptr);
+int cct_malloc_host(cct_ctx* ctx, size_t bytes, void** hptr); /* pinned host memory */
+int cct_free_host(cct_ctx* ctx, void* hptr);
+int cct_memcpy_h2d(cct_ctx* ctx, void* dst, const void* src, size_t bytes); /* stream-ordered */
+int cct_memcpy_d2h(cct_ctx* ctx, void* dst, const void* src, size_t bytes); /* stream-ordered */
+int cct_memcpy_d2d(cct_ctx* ctx, void* dst, const void* src, size_t bytes);
+int cct_memset(cct_ctx* ctx, void* dptr, int byte_value, size_t bytes);
+/* DeviceDriver::sconstant_initialize (src/sched/DeviceDriver.h:236, DeviceDriver_GPU.cu:1189-1200). */
+int cct_fill_f32(cct_ctx* ctx, float* dptr, size_t count, float value);
+
+/* ---- the convolution bridge: replaces ConvolutionBridge::forward/backward
+ *      (src/bridges/ConvolutionBridge_impl.hxx:294-500, 551-773) together with the driver entry points they
+ *      call: lower_cube, sgemm, forward_bias, backward_bias, inverse_lower_cube
+ *      (src/sched/DeviceDriver.h:122-190; GPU versions src/sched/DeviceDriver_GPU.cu:205-228, 670-786, 1059-1139)
+ *      and Connector::remap_output (src/Connector_impl_Lowering_type1.hxx:92-128), which has no counterpart
+ *      here because outputs are produced directly in [b][o][r][c] order. ---- */
+typedef struct cct_conv_desc {
+  int batch;      /* B: images per call (one partition of the mini-batch) */
+  int in_depth;   /* D */
+  int in_size;    /* n: square input, as the reference requires (src/sched/DeviceDriver_CPU.cpp:137-140) */
+  int out_depth;  /* o: number of filters */
+  int kernel;     /* k */
+  int stride;     /* s */
+  int pad;        /* p */
+  int groups;     /* g: D and o must be multiples of g; filter tensor is [o][D/g][k][k] */
+  int bias_term;  /* 0: no bias (bias/db pointers ignored) */
+  int algo;       /* CCT_ALGO_* */
+} cct_conv_desc;
+
+int cct_conv_plan_create(cct_ctx* ctx, const cct_conv_desc* desc, cct_conv_plan** out);
+int cct_conv_plan_destroy(cct_conv_plan* plan);
+/* m = (n + 2p - k)/s + 1 (src/DeepNet.h:112-115). */
+int cct_conv_out_size(const cct_conv_desc* desc, int* out_size);
+/* The algorithm the plan resolved to (CCT_ALGO_SIMT_FP32 or CCT_ALGO_UMMA_3XTF32). */
+int cct_conv_plan_algo(const cct_conv_plan* plan, int* algo);
+/* Bytes of scratch memory the plan owns (packed weight splits, split-K partial sums). */
+int cct_conv_plan_workspace_bytes(const cct_conv_plan* plan, size_t* bytes);
+
+/* Y[b][o][r][c] = bias[o] + sum_{d,kr,kc} W[o][d][kr][kc] * X[b][d][r*s-p+kr][c*s-p+kc]   (zero outside X).
+ * relu != 0 additionally clamps Y at 0 (the ReLU bridge that follows every CaffeNet convolution,
+ * src/kernels/relu.hxx:17-26, folded into the epilogue). */
+int cct_conv_forward(cct_conv_plan* plan, const float* X, const float* W, const float* bias, float* Y, int relu);
+
+/* dW, db are overwritten (beta = 0, src/bridges/ConvolutionBridge_impl.hxx:619-621); dX is written only when
+ * dX != NULL (needs_to_calc_backward_grad, src/bridges/AbstractBridge.h; the first convolution of a net skips it,
+ * src/DeepNet.h:1108-1110).  dY is not modified (the reference's CPU path permutes it in place, :604). */
+int cct_conv_backward(cct_conv_plan* plan, const float* X, const float* W, const float* dY, float* dX, float* dW,
+                      float* db);
+
+/* Host-buffer forms of the two calls above, for callers that keep cubes in host memory as the reference's
+ * ParallelizedBridge does (src/bridges/ParallelizedBridge_impl.hxx:538-671, 686-738, 779-830, 895-910,
+ * 1071-1122): inputs are copied to plan-owned device buffers, the kernels run, results are copied back, and the
+ * call returns after the results have landed.  Pinned host memory (cct_malloc_host) makes the copies asynchronous.
+ * cct_conv_backward_host accepts hX == NULL and/or hW == NULL, meaning "the copy staged by the last
+ * cct_conv_forward_host on this plan" (the reference keeps the input cube on the device between the two passes). */
+int cct_conv_forward_host(cct_conv_plan* plan, const float* hX, const float* hW, const float* hbias, float* hY,
+                          int relu);
+int cct_conv_backward_host(cct_conv_plan* plan, const float* hX, const float* hW, const float* hdY, float* hdX,
+                           float* hdW, float* hdb);
+
+/* Per-kernel device times of the plan's most recent forward and backward call, for measurement: when enabled,
+ * CUDA events are recorded around each kernel group on the context's stream.  ms[0] forward contraction,
+ * ms[1] weight(+bias)-gradient contraction, ms[2] its split reduction, ms[3] data-gradient contraction(s),
+ * ms[4] weight repacking (all calls).  The getter synchronises the stream.  No counterpart in the reference
+ * (its Report objects hold host wall-clock: src/Report.h:13-91). */
+int cct_conv_plan_enable_timing(cct_conv_plan* plan, int enable);
+int cct_conv_plan_last_timings(cct_conv_plan* plan, float ms[5]);
+
+/* ---- adjacent layers whose backward masks feed the convolution backward ---- */
+/* DeviceDriver::maxpool_forward / maxpool_backward (src/sched/DeviceDriver_CPU.cpp:369-421): windows k x k,
+ * stride s, no padding, clipped at the border, output size (n-k)/s+1 by floor; idx = int32 offset h*n+w of the
+ * first maximum inside the (n x n) plane; backward zero-fills dX and adds dY at idx. */
+int cct_maxpool_forward(cct_ctx* ctx, const float* X, float* Y, int32_t* idx, int planes, int n, int k, int s);
+int cct_maxpool_backward(cct_ctx* ctx, const float* dY, const int32_t* idx, float* dX, int planes, int n, int k,
+                         int s);
+/* ReLU bridge (src/kernels/relu.hxx:17-43). */
+int cct_relu_forward(cct_ctx* ctx, const float* X, float* Y, size_t count);
+int cct_relu_backward(cct_ctx* ctx, const float* X, const float* dY, float* dX, size_t count);
+/* ReLUBridge::backward after MaxPoolingBridge::backward in one pass: given the convolution output A (pre- or
+ * post-ReLU: only its sign is used), the pooling indices and the gradient of the pooled tensor,
+ *   dA[plane][h][w] = (A > 0) * sum over windows (ph,pw) covering (h,w) with idx == h*n+w of dP[plane][ph][pw]. */
+int cct_pool_relu_backward(cct_ctx* ctx, const float* A, const int32_t* idx, const float* dP, float* dA, int planes,
+                           int n, int k, int s);
+
+/* ---- parameter update: SGDGradientUpdater::update (src/algorithms/GradientUpdater.h:154-193) as one kernel:
+ *      g += lambda*w (if lambda != 0);  h = lr*g + momentum*h;  w -= h. ---- */
+int cct_sgd_step(cct_ctx* ctx, size_t count, float* w, float* g, float* h, float lr, float momentum, float lambda);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CCT_B200_H */

@@ -126,6 +126,7 @@ class Reference:
         L.cctref_conv_forward.argtypes = [C.c_void_p, _fp, _fp]
         L.cctref_conv_backward.argtypes = [C.c_void_p, _fp, _fp, _fp, _fp, C.c_int]
         L.cctref_conv_load.argtypes = [C.c_void_p, _fp, _fp]
+        L.cctref_conv_step.argtypes = [C.c_void_p, C.c_int]
         L.cctref_conv_time.restype = C.c_double
         L.cctref_conv_time.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_double)]
         L.cctref_maxpool.argtypes = [C.c_int] * 5 + [_fp, _fp, _ip, _fp, _fp]

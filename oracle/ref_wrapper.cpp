@@ -154,6 +154,14 @@ double cctref_conv_time(void* hv, int warmup, int iters, double* fwd_s, double* 
   return tt[tt.size() / 2];
 }
 
+// One training step on whatever the cubes hold: forward, backward and (do_update != 0) the reference's SGD update.
+void cctref_conv_step(void* hv, int do_update) {
+  ConvHandle* h = (ConvHandle*)hv;
+  h->bridge->set_update_model_gradients(do_update != 0);
+  h->bridge->forward();
+  h->bridge->backward();
+}
+
 // Fill the bridge's cubes for timing without going through forward()/backward() copies.
 void cctref_conv_load(void* hv, const float* X, const float* dY) {
   ConvHandle* h = (ConvHandle*)hv;

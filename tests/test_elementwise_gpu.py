@@ -1,0 +1,95 @@
+"""GPU tests of the memory-bound companions (pooling / ReLU masks, SGD step, fill): integer and copy work is
+compared bit-exactly, fp32 sums that follow the oracle's order too."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+from caffecontroll_b200.bridge import LogicalCube
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "conv_golden.npz")
+
+
+def _cube(ctx, arr):
+    return LogicalCube.from_numpy(ctx, arr)
+
+
+@pytest.mark.parametrize("shape", [(2, 3, 13, 3, 2), (2, 3, 10, 4, 2), (1, 2, 27, 3, 2), (3, 1, 7, 2, 1), (1, 1, 9, 3, 3)])
+def test_pool_and_relu_masks_match_oracle_bitwise(ctx, port, shape):
+    from caffecontroll_b200 import capi
+    B, D, n, k, s = shape
+    m = (n - k) // s + 1
+    rng = np.random.default_rng(21)
+    A = rng.standard_normal((B, D, n, n), dtype=np.float32)
+    A[0, 0, :3, :3] = 1.5  # ties: the first maximum must win
+    dP = rng.standard_normal((B, D, m, m), dtype=np.float32)
+    Yr, idxr = port.maxpool_forward(A, k, s)
+    dAr = port.maxpool_backward(dP, idxr, n)
+    lib = ctx.lib
+    cA, cdP = _cube(ctx, A), _cube(ctx, dP)
+    cY, cidx = LogicalCube(ctx, m, m, D, B), LogicalCube(ctx, m, m, D, B, np.int32)
+    cdA, cdA2, cR, cdR = (LogicalCube(ctx, n, n, D, B) for _ in range(4))
+    vp = C.c_void_p
+    capi.check(lib.cct_maxpool_forward(ctx.h, vp(cA.ptr), vp(cY.ptr), vp(cidx.ptr), B * D, n, k, s), "pool fwd", ctx.h)
+    capi.check(lib.cct_maxpool_backward(ctx.h, vp(cdP.ptr), vp(cidx.ptr), vp(cdA.ptr), B * D, n, k, s), "pool bwd", ctx.h)
+    capi.check(lib.cct_pool_relu_backward(ctx.h, vp(cA.ptr), vp(cidx.ptr), vp(cdP.ptr), vp(cdA2.ptr), B * D, n, k, s),
+               "pool+relu bwd", ctx.h)
+    capi.check(lib.cct_relu_forward(ctx.h, vp(cA.ptr), vp(cR.ptr), A.size), "relu fwd", ctx.h)
+    capi.check(lib.cct_relu_backward(ctx.h, vp(cA.ptr), vp(cdA.ptr), vp(cdR.ptr), A.size), "relu bwd", ctx.h)
+    ctx.sync()
+    assert np.array_equal(cY.download(), Yr)
+    assert np.array_equal(cidx.download(), idxr)
+    assert np.array_equal(cdA.download(), dAr)
+    assert np.array_equal(cR.download(), port.relu_forward(A))
+    assert np.array_equal(cdR.download(), port.relu_backward(A, dAr))
+    assert np.array_equal(cdA2.download(), port.relu_backward(A, dAr))
+    for c in (cA, cdP, cY, cidx, cdA, cdA2, cR, cdR):
+        c.free()
+
+
+def test_masks_match_committed_reference_fixtures(ctx):
+    from caffecontroll_b200 import capi
+    z = np.load(GOLDEN)
+    lib, vp = ctx.lib, C.c_void_p
+    for name in ("pool3s2", "pool4s2"):
+        B, D, n, k, s = (int(v) for v in z[name + "/shape"])
+        m = (n - k) // s + 1
+        cA, cdP = _cube(ctx, z[name + "/A"]), _cube(ctx, z[name + "/dP"])
+        cY, cidx, cdA = LogicalCube(ctx, m, m, D, B), LogicalCube(ctx, m, m, D, B, np.int32), LogicalCube(ctx, n, n, D, B)
+        capi.check(lib.cct_maxpool_forward(ctx.h, vp(cA.ptr), vp(cY.ptr), vp(cidx.ptr), B * D, n, k, s), "pool fwd", ctx.h)
+        capi.check(lib.cct_pool_relu_backward(ctx.h, vp(cA.ptr), vp(cidx.ptr), vp(cdP.ptr), vp(cdA.ptr), B * D, n, k, s),
+                   "pool+relu bwd", ctx.h)
+        ctx.sync()
+        assert np.array_equal(cY.download(), z[name + "/Y"])
+        assert np.array_equal(cidx.download(), z[name + "/idx"])
+        assert np.array_equal(cdA.download(), z[name + "/dA_pool_relu"])
+        for c in (cA, cdP, cY, cidx, cdA):
+            c.free()
+
+
+def test_sgd_step_matches_oracle_bitwise(ctx, port):
+    from caffecontroll_b200 import capi
+    rng = np.random.default_rng(22)
+    n = 100003
+    w, g, h = (rng.standard_normal(n).astype(np.float32) for _ in range(3))
+    cw, cg, ch = _cube(ctx, w), _cube(ctx, g), _cube(ctx, h)
+    for lam in (0.0005, 0.0):
+        capi.check(ctx.lib.cct_sgd_step(ctx.h, n, C.c_void_p(cw.ptr), C.c_void_p(cg.ptr), C.c_void_p(ch.ptr), 0.01, 0.9,
+                                        lam), "sgd", ctx.h)
+        port.sgd_update(w, g, h, 0.01, 0.9, lam)
+    ctx.sync()
+    assert np.array_equal(cw.download().ravel(), w)
+    assert np.array_equal(cg.download().ravel(), g)
+    assert np.array_equal(ch.download().ravel(), h)
+
+
+def test_fill_and_empty_sizes(ctx):
+    from caffecontroll_b200 import capi
+    c = LogicalCube(ctx, 5, 7, 3, 2)
+    c.reset_cube(-2.5)
+    assert np.all(c.download() == np.float32(-2.5))
+    assert ctx.lib.cct_fill_f32(ctx.h, None, 0, 1.0) == capi.CCT_OK
+    assert ctx.lib.cct_memset(ctx.h, None, 0, 0) == capi.CCT_OK
+    c.free()
