@@ -7,7 +7,7 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libcct_b200.so")
+LIB_PATH = os.environ.get("CCT_B200_LIB") or os.path.join(HERE, "libcct_b200.so")
 
 CCT_OK, CCT_ERR_INVALID, CCT_ERR_CUDA, CCT_ERR_NOMEM, CCT_ERR_TIMEOUT, CCT_ERR_UNSUPPORTED = range(6)
 ALGO_AUTO, ALGO_SIMT_FP32, ALGO_UMMA_3XTF32 = 0, 1, 2

@@ -22,6 +22,7 @@
 // the fill of the next stage overlaps the MMAs.  Every mbarrier wait is bounded: when it runs out the thread sets
 // the context's status word, stops waiting on anything else, and the kernel still frees its tensor memory.
 #include <algorithm>
+#include <cstdlib>
 #include <vector>
 
 #include "cct_internal.h"
@@ -34,6 +35,11 @@ constexpr int kBlockK = 32;  // fp32 per k-block: one 128-byte swizzled row
 constexpr int kMaxStages = 4;
 constexpr int kATileBytes = kTileM * 128;
 constexpr int kSmemLimit = 227 * 1024;
+#ifdef CCT_DBG
+#define DBG(P, bit) ((P).dbg & (bit))
+#else
+#define DBG(P, bit) 0
+#endif
 constexpr int kPadTap = 0x4000;  // tap coordinate that fails every bounds test (marks padding rows of a table)
 
 // One entry per reduction index of a gathered operand: element offset from the pixel's tap origin and the tap's
@@ -213,6 +219,7 @@ struct GatherParams {
   int n, n_pad, k_pad;     // real / padded output channels per virtual group, padded reduction length
   int relu;
   int* status;
+  int dbg;
 };
 
 __global__ void __launch_bounds__(kThreads, 1) gather_conv_kernel(const __grid_constant__ GatherParams P) {
@@ -225,7 +232,6 @@ __global__ void __launch_bounds__(kThreads, 1) gather_conv_kernel(const __grid_c
   const int vg = blockIdx.y;
   const int grp = vg / P.tiles_per_group, ntile = vg % P.tiles_per_group;
   const uint32_t ncols = tmem_cols(P.n_pad);
-  if (*reinterpret_cast<volatile int*>(P.status) != 0) return;  // an earlier wait gave up: do not pile up behind it
 
   if (tid == 0) {
     for (int s = 0; s < L.stages; ++s) mbar_init(bar0 + 8u * s, 1);
@@ -276,13 +282,13 @@ __global__ void __launch_bounds__(kThreads, 1) gather_conv_kernel(const __grid_c
       for (int e = 0; e < 4; ++e) {
         const Tap t = tp[c * 4 + e];
         const bool ok = (unsigned)(iy0 + t.dy) < (unsigned)P.in_lim && (unsigned)(ix0 + t.dx) < (unsigned)P.in_lim;
-        v[e] = ok ? __ldg(in_px + t.off) : 0.f;
+        v[e] = (ok && !DBG(P, 1)) ? __ldg(in_px + t.off) : 0.f;
       }
       const uint32_t o = swz(row, half * 4 + c);
-      store_split4(a_hi + o, a_lo + o, v);
+      if (!DBG(P, 8)) store_split4(a_hi + o, a_lo + o, v);
     }
     // B: packed weights, already split; n_pad rows x 8 chunks, hi and lo.
-    for (int i = tid; i < P.n_pad * 8; i += kThreads) {
+    for (int i = tid; i < P.n_pad * 8 && !DBG(P, 2); i += kThreads) {
       const int r = i >> 3, q = i & 7;
       const size_t g = (size_t)r * P.k_pad + kb * kBlockK + q * 4;
       const float4 h = *reinterpret_cast<const float4*>(wh + g);
@@ -291,11 +297,11 @@ __global__ void __launch_bounds__(kThreads, 1) gather_conv_kernel(const __grid_c
       st_shared_v4(b_hi + o, h.x, h.y, h.z, h.w);
       st_shared_v4(b_lo + o, l.x, l.y, l.z, l.w);
     }
-    fence_proxy_async_smem();
+    if (!DBG(P, 16)) fence_proxy_async_smem();
     __syncthreads();
     if (tid == 0) {
       tc_fence_after();
-      issue_stage(tmem_d, a_hi, a_lo, b_hi, b_lo, idesc, kb == 0);
+      if (!DBG(P, 4)) issue_stage(tmem_d, a_hi, a_lo, b_hi, b_lo, idesc, kb == 0);
       umma_commit(bar0 + 8u * s);
     }
   }
@@ -359,6 +365,7 @@ struct WgradParams {
   int n_real, n_pad;
   int kblocks_total, kblocks_per_split;
   int* status;
+  int dbg;
 };
 constexpr int kOnesTap = 0x2000;
 
@@ -372,7 +379,6 @@ __global__ void __launch_bounds__(kThreads, 1) wgrad_kernel(const __grid_constan
   const int mtile = blockIdx.x, split = blockIdx.y, vg = blockIdx.z;
   const int grp = vg / P.tiles_per_group, ntile = vg % P.tiles_per_group;
   const uint32_t ncols = tmem_cols(P.n_pad);
-  if (*reinterpret_cast<volatile int*>(P.status) != 0) return;  // an earlier wait gave up: do not pile up behind it
 
   if (tid == 0) {
     for (int s = 0; s < L.stages; ++s) mbar_init(bar0 + 8u * s, 1);
@@ -438,25 +444,25 @@ __global__ void __launch_bounds__(kThreads, 1) wgrad_kernel(const __grid_constan
         } else {
           const bool in = ok[e] && (unsigned)(iy0[e] + tap[i].dy) < (unsigned)P.n &&
                           (unsigned)(ix0[e] + tap[i].dx) < (unsigned)P.n;
-          v[e] = in ? __ldg(xg + xoff[e] + tap[i].off) : 0.f;
+          v[e] = (in && !DBG(P, 1)) ? __ldg(xg + xoff[e] + tap[i].off) : 0.f;
         }
       }
       const uint32_t o = swz(r0 + 32 * i, q);
-      store_split4(a_hi + o, a_lo + o, v);
+      if (!DBG(P, 8)) store_split4(a_hi + o, a_lo + o, v);
     }
     // B: rows = output channels, columns = the same pixels.
-    for (int j = r0; j < P.n_pad; j += 32) {
+    for (int j = r0; j < P.n_pad && !DBG(P, 2); j += 32) {
       float v[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) v[e] = (ok[e] && j < P.n_real) ? __ldg(dyg + dyoff[e] + (long long)j * P.mm) : 0.f;
       const uint32_t o = swz(j, q);
       store_split4(b_hi + o, b_lo + o, v);
     }
-    fence_proxy_async_smem();
+    if (!DBG(P, 16)) fence_proxy_async_smem();
     __syncthreads();
     if (tid == 0) {
       tc_fence_after();
-      issue_stage(tmem_d, a_hi, a_lo, b_hi, b_lo, idesc, it == 0);
+      if (!DBG(P, 4)) issue_stage(tmem_d, a_hi, a_lo, b_hi, b_lo, idesc, it == 0);
       umma_commit(bar0 + 8u * s);
     }
   }
@@ -546,6 +552,16 @@ __global__ void pack_dgrad_kernel(const float* __restrict__ W, float* __restrict
     hi[t] = h;
     lo[t] = l;
   }
+}
+
+// Measurement knobs of debug builds (-DCCT_DBG): a bit mask from the environment that removes one pipeline part.
+int dbg_knobs() {
+#ifdef CCT_DBG
+  const char* e = getenv("CCT_DBG_KNOBS");
+  return e ? atoi(e) : 0;
+#else
+  return 0;
+#endif
 }
 
 int round_up(int v, int a) { return (v + a - 1) / a * a; }
@@ -731,6 +747,7 @@ size_t umma_plan_workspace_bytes(const UmmaPlan* p) { return p->bytes; }
 
 int umma_conv_forward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W, const float* bias, float* Y,
                       int relu, PhaseTimer* t) {
+  if (*ctx->status_host != 0) return CCT_ERR_TIMEOUT;  // an earlier bounded wait gave up: do not pile up behind it
   const ConvGeom& G = p->G;
   const int vgroups = G.g * p->f_tiles;
   t->begin(4, ctx->stream);
@@ -755,6 +772,7 @@ int umma_conv_forward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W,
   P.n = p->f_n; P.n_pad = p->f_npad; P.k_pad = p->f_kpad;
   P.relu = relu;
   P.status = ctx->status_dev;
+  P.dbg = dbg_knobs();
   dim3 grid((P.n_pix + kTileM - 1) / kTileM, vgroups);
   t->begin(0, ctx->stream);
   gather_conv_kernel<<<grid, kThreads, smem_bytes(P.n_pad), ctx->stream>>>(P);
@@ -765,6 +783,7 @@ int umma_conv_forward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W,
 
 int umma_conv_backward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W, const float* dY, float* dX,
                        float* dW, float* db, PhaseTimer* t) {
+  if (*ctx->status_host != 0) return CCT_ERR_TIMEOUT;
   const ConvGeom& G = p->G;
   // ---- weight + bias gradient
   {
@@ -779,6 +798,7 @@ int umma_conv_backward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W
     P.n_real = p->f_n; P.n_pad = p->f_npad;
     P.kblocks_total = p->w_kblocks_total; P.kblocks_per_split = p->w_kblocks_per_split;
     P.status = ctx->status_dev;
+    P.dbg = dbg_knobs();
     const int vgroups = G.g * p->f_tiles;
     dim3 grid(p->w_mtiles, p->w_splits, vgroups);
     t->begin(1, ctx->stream);
@@ -823,6 +843,7 @@ int umma_conv_backward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W
       P.n = p->d_n; P.n_pad = p->d_npad; P.k_pad = ph.k_pad;
       P.relu = 0;
       P.status = ctx->status_dev;
+      P.dbg = dbg_knobs();
       dim3 grid((P.n_pix + kTileM - 1) / kTileM, vgroups);
       gather_conv_kernel<<<grid, kThreads, smem_bytes(P.n_pad), ctx->stream>>>(P);
       CCT_CHECK_LAUNCH(ctx);
