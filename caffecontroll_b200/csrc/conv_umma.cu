@@ -25,6 +25,8 @@
 #include <cstdlib>
 #include <vector>
 
+#include <cuda.h>
+
 #include "cct_internal.h"
 
 namespace {
@@ -199,155 +201,291 @@ __host__ __device__ inline uint32_t tmem_cols(int n_pad) {
 }
 
 // ------------------------------------------------------------------------------ gather kernel (forward, dgrad)
+//
+// Persistent, warp-specialised: one CTA per SM walks over (channel tile, 128-pixel tile) pairs.
+//   warps 0-7   producers: thread = one pixel of the tile = one TMEM lane.  Per k-block a thread gathers its 32
+//               lowered values, splits them hi/lo and writes them with tcgen05.st into the A stage in tensor memory
+//               (warps 0-3 take even k-blocks, warps 4-7 odd ones; both sets cover all 128 lanes).
+//   warp 8      one thread issues the MMAs: A from tensor memory, B from shared memory.
+//   warp 9      one thread streams the pre-split weight tiles (B) into shared memory with TMA (128-byte swizzle).
+//   warps 10-13 epilogue: tcgen05.ld the finished accumulator, add bias / clamp, store NCHW (or depth-to-space for
+//               the strided data gradient); overlaps the next tile's MMAs when two accumulators fit.
+// Tensor memory (512 columns): [accumulator(s) | A stages of 64 columns: 32 hi + 32 lo].
+constexpr int kProducerWarps = 8;
+constexpr int kMmaWarp = 8, kTmaWarp = 9, kEpiWarp0 = 10, kEpiWarps = 4;
+constexpr int kGatherThreads = (kEpiWarp0 + kEpiWarps) * 32;  // 448
+constexpr int kMaxAStages = 4, kMaxBStages = 8, kMaxAccBufs = 2;
+
+struct ColEnt {  // one accumulator column -> where it lands in the output
+  int off;       // element offset from the pixel's output origin
+  short cy, cx;  // displacement of the output pixel (depth-to-space), for the bounds test
+};
+
 struct GatherParams {
   const float* in;    // gathered tensor: X (forward) or dY (data gradient)
   float* out;         // Y or dX
-  const float* w_hi;  // packed B operand [vgroups][n_pad][k_pad], tf32-rounded part
-  const float* w_lo;  // remainder part
   const Tap* taps;    // [k_pad]
+  const ColEnt* cols; // [n_pad]
   const float* bias;  // indexed by output channel, or null
   int n_pix, q_h, q_w;                 // pixels = batch * q_h * q_w
   int iy_mul, iy_add, ix_mul, ix_add;  // tap origin in the gathered tensor: iy0 = qy*iy_mul + iy_add
   int in_lim;                          // gathered tensor is in_lim x in_lim per channel
   long long in_batch_stride;
   int in_group_stride;   // elements between the channel blocks of consecutive groups
-  int tiles_per_group;   // virtual groups per real group (output-channel tiles)
-  int oy_mul, oy_add, ox_mul, ox_add;  // output pixel: oy = qy*oy_mul + oy_add
+  int tiles_per_group;   // virtual groups per real group (channel tiles)
+  int oy_mul, oy_add, ox_mul, ox_add;  // output origin of a pixel: oy0 = qy*oy_mul + oy_add
+  int out_lim, check_out;              // output plane is out_lim x out_lim; check_out: columns may fall outside
   int out_pitch, out_plane;
   long long out_batch_stride;
-  int out_group_channels;  // output channels per real group
-  int n, n_pad, k_pad;     // real / padded output channels per virtual group, padded reduction length
+  int out_group_channels, out_tile_channels;  // output channels per real group / per channel tile
+  int n, n_pad, k_pad;     // real / padded accumulator columns per virtual group, padded reduction length
+  int n_pix_tiles, total_tiles;
+  int a_stages, b_stages, acc_bufs;
+  int lo_row_offset;       // first row of the "lo" half inside the packed-weight tensor map
   int relu;
   int* status;
   int dbg;
 };
 
-__global__ void __launch_bounds__(kThreads, 1) gather_conv_kernel(const __grid_constant__ GatherParams P) {
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(tmap), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]^T.
+__device__ __forceinline__ void umma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+      :
+      : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+struct GatherSmem {
+  uint32_t b_stage_bytes, taps_off, cols_off, bars_off, total;
+};
+__host__ __device__ inline GatherSmem gather_smem(int n_pad, int k_pad, int b_stages) {
+  GatherSmem L;
+  L.b_stage_bytes = 2u * (uint32_t)n_pad * 128u;
+  L.taps_off = (uint32_t)b_stages * L.b_stage_bytes;
+  L.cols_off = L.taps_off + (uint32_t)k_pad * 8u;
+  L.bars_off = (L.cols_off + (uint32_t)n_pad * 8u + 15u) & ~15u;
+  L.total = L.bars_off + 8u * (2 * kMaxAStages + 2 * kMaxBStages + 2 * kMaxAccBufs) + 16u;
+  return L;
+}
+
+__global__ void __launch_bounds__(kGatherThreads, 1)
+    gather_conv_kernel(const __grid_constant__ GatherParams P, const __grid_constant__ CUtensorMap w_map) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const SmemLayout L = smem_layout(P.n_pad);
-  const uint32_t bar0 = base + (uint32_t)L.stages * L.stage_bytes;  // mma_done[stage]
-  const uint32_t tmem_slot = bar0 + 8u * kMaxStages;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const GatherSmem L = gather_smem(P.n_pad, P.k_pad, P.b_stages);
+  const uint32_t bars = base + L.bars_off;
+  const uint32_t a_full = bars, a_empty = a_full + 8u * kMaxAStages, b_full = a_empty + 8u * kMaxAStages,
+                 b_empty = b_full + 8u * kMaxBStages, acc_full = b_empty + 8u * kMaxBStages,
+                 acc_empty = acc_full + 8u * kMaxAccBufs, tmem_slot = acc_empty + 8u * kMaxAccBufs;
+  Tap* s_taps = reinterpret_cast<Tap*>(base_ptr + L.taps_off);
+  ColEnt* s_cols = reinterpret_cast<ColEnt*>(base_ptr + L.cols_off);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int vg = blockIdx.y;
-  const int grp = vg / P.tiles_per_group, ntile = vg % P.tiles_per_group;
-  const uint32_t ncols = tmem_cols(P.n_pad);
 
+  for (int i = tid; i < P.k_pad; i += kGatherThreads) s_taps[i] = P.taps[i];
+  for (int i = tid; i < P.n_pad; i += kGatherThreads) s_cols[i] = P.cols[i];
   if (tid == 0) {
-    for (int s = 0; s < L.stages; ++s) mbar_init(bar0 + 8u * s, 1);
+    for (int s = 0; s < kMaxAStages; ++s) { mbar_init(a_full + 8u * s, 128); mbar_init(a_empty + 8u * s, 1); }
+    for (int s = 0; s < kMaxBStages; ++s) { mbar_init(b_full + 8u * s, 1); mbar_init(b_empty + 8u * s, 1); }
+    for (int s = 0; s < kMaxAccBufs; ++s) { mbar_init(acc_full + 8u * s, 1); mbar_init(acc_empty + 8u * s, 128); }
     fence_mbar_init();
   }
-  if (warp == 0) tmem_alloc(tmem_slot, ncols);
+  if (warp == 0) tmem_alloc(tmem_slot, 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  uint32_t tmem_d;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_d) : "r"(tmem_slot));
-
-  // This thread's A row = one output pixel of the tile.
-  const int row = tid & 127, half = tid >> 7;
-  const int pix = blockIdx.x * kTileM + row;
-  const bool pix_ok = pix < P.n_pix;
-  int b = 0, qy = 0, qx = 0;
-  if (pix_ok) {
-    const int per_img = P.q_h * P.q_w;
-    b = pix / per_img;
-    const int r = pix - b * per_img;
-    qy = r / P.q_w;
-    qx = r - qy * P.q_w;
-  }
-  const int iy0 = pix_ok ? qy * P.iy_mul + P.iy_add : -kPadTap * 2;
-  const int ix0 = qx * P.ix_mul + P.ix_add;
-  const float* in_px = P.in + (long long)b * P.in_batch_stride + (long long)grp * P.in_group_stride +
-                       (long long)iy0 * P.in_lim + ix0;
-  if (!pix_ok) in_px = P.in;
-  const float* wh = P.w_hi + (size_t)vg * P.n_pad * P.k_pad;
-  const float* wl = P.w_lo + (size_t)vg * P.n_pad * P.k_pad;
-  const uint32_t idesc = make_idesc(P.n_pad);
+  uint32_t tmem_base;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+  const uint32_t a_col0 = (uint32_t)(P.acc_bufs * P.n_pad);
   const int kblocks = P.k_pad / kBlockK;
   bool failed = false;
 
-  for (int kb = 0; kb < kblocks; ++kb) {
-    const int s = kb % L.stages, use = kb / L.stages;
-    const uint32_t st = base + (uint32_t)s * L.stage_bytes;
-    const uint32_t a_hi = st, a_lo = st + kATileBytes, b_hi = st + 2 * kATileBytes, b_lo = b_hi + L.b_tile_bytes;
-    if (use > 0) mbar_wait(bar0 + 8u * s, (uint32_t)(use - 1) & 1u, failed, P.status, 0x1);
-
-    // A: 4 chunks of 4 reduction indices for this thread's pixel.
-    const Tap* tp = P.taps + kb * kBlockK + half * 16;
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      float v[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const Tap t = tp[c * 4 + e];
-        const bool ok = (unsigned)(iy0 + t.dy) < (unsigned)P.in_lim && (unsigned)(ix0 + t.dx) < (unsigned)P.in_lim;
-        v[e] = (ok && !DBG(P, 1)) ? __ldg(in_px + t.off) : 0.f;
+  if (warp < kProducerWarps) {
+    // ------------------------------------------------------------------ producers
+    const int group = warp >> 2, quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + a_col0;
+    int it = 0;
+    for (int t = blockIdx.x; t < P.total_tiles; t += gridDim.x) {
+      const int vg = t / P.n_pix_tiles, ptile = t - vg * P.n_pix_tiles;
+      const int grp = vg / P.tiles_per_group;
+      const int pix = ptile * kTileM + row;
+      const bool pix_ok = pix < P.n_pix;
+      int b = 0, qy = 0, qx = 0;
+      if (pix_ok) {
+        const int per_img = P.q_h * P.q_w;
+        b = pix / per_img;
+        const int r = pix - b * per_img;
+        qy = r / P.q_w;
+        qx = r - qy * P.q_w;
       }
-      const uint32_t o = swz(row, half * 4 + c);
-      if (!DBG(P, 8)) store_split4(a_hi + o, a_lo + o, v);
-    }
-    // B: packed weights, already split; n_pad rows x 8 chunks, hi and lo.
-    for (int i = tid; i < P.n_pad * 8 && !DBG(P, 2); i += kThreads) {
-      const int r = i >> 3, q = i & 7;
-      const size_t g = (size_t)r * P.k_pad + kb * kBlockK + q * 4;
-      const float4 h = *reinterpret_cast<const float4*>(wh + g);
-      const float4 l = *reinterpret_cast<const float4*>(wl + g);
-      const uint32_t o = swz(r, q);
-      st_shared_v4(b_hi + o, h.x, h.y, h.z, h.w);
-      st_shared_v4(b_lo + o, l.x, l.y, l.z, l.w);
-    }
-    if (!DBG(P, 16)) fence_proxy_async_smem();
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after();
-      if (!DBG(P, 4)) issue_stage(tmem_d, a_hi, a_lo, b_hi, b_lo, idesc, kb == 0);
-      umma_commit(bar0 + 8u * s);
-    }
-  }
-  {
-    const int last = kblocks - 1;
-    mbar_wait(bar0 + 8u * (last % L.stages), (uint32_t)(last / L.stages) & 1u, failed, P.status, 0x2);
-  }
-  tc_fence_after();
-
-  // Epilogue: warp w reads TMEM lanes 32*(w%4).., 16 columns at a time; warps 0-3 take even chunks, 4-7 odd ones.
-  {
-    const int erow = (warp & 3) * 32 + lane;
-    const int epix = blockIdx.x * kTileM + erow;
-    const bool eok = epix < P.n_pix && !failed;
-    int eb = 0, ey = 0, ex = 0;
-    if (epix < P.n_pix) {
-      const int per_img = P.q_h * P.q_w;
-      eb = epix / per_img;
-      const int r = epix - eb * per_img;
-      ey = r / P.q_w;
-      ex = r - ey * P.q_w;
-    }
-    const int ch0 = grp * P.out_group_channels + ntile * P.n;
-    float* op = P.out + (long long)eb * P.out_batch_stride + (long long)ch0 * P.out_plane +
-                (long long)(ey * P.oy_mul + P.oy_add) * P.out_pitch + (ex * P.ox_mul + P.ox_add);
-    const int chunks = P.n_pad / 16;
-    for (int c = warp >> 2; c < chunks; c += 2) {
-      float v[16];
-      tmem_ld16(tmem_d + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(c * 16), v);
-      if (eok) {
+      const int iy0 = pix_ok ? qy * P.iy_mul + P.iy_add : -2 * kPadTap;
+      const int ix0 = qx * P.ix_mul + P.ix_add;
+      const float* in_px = pix_ok ? P.in + (long long)b * P.in_batch_stride + (long long)grp * P.in_group_stride +
+                                        (long long)iy0 * P.in_lim + ix0
+                                  : P.in;
+      for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        if ((it & 1) != group) continue;
+        const int sa = it % P.a_stages, use = it / P.a_stages;
+        if (use > 0) mbar_wait(a_empty + 8u * sa, (uint32_t)(use - 1) & 1u, failed, P.status, 0x10);
+        tc_fence_after();
+        const Tap* tp = s_taps + kb * kBlockK;
+        const uint32_t st_addr = lane_addr + (uint32_t)(sa * 64);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int ch = c * 16 + j;
-          if (ch < P.n) {
-            float y = v[j];
-            if (P.bias) y += __ldg(P.bias + ch0 + ch);
-            if (P.relu) y = fmaxf(y, 0.f);
-            op[(long long)ch * P.out_plane] = y;
+        for (int h = 0; h < 2; ++h) {
+          float v[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const Tap tap = tp[h * 16 + e];
+            const bool ok =
+                (unsigned)(iy0 + tap.dy) < (unsigned)P.in_lim && (unsigned)(ix0 + tap.dx) < (unsigned)P.in_lim;
+            v[e] = (ok && !DBG(P, 1)) ? __ldg(in_px + tap.off) : 0.f;
+          }
+          uint32_t hi[16], lo[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            float fh, fl;
+            split_tf32(v[e], fh, fl);
+            hi[e] = __float_as_uint(fh);
+            lo[e] = __float_as_uint(fl);
+          }
+          tmem_st16(st_addr + (uint32_t)(h * 16), hi);
+          tmem_st16(st_addr + 32u + (uint32_t)(h * 16), lo);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(a_full + 8u * sa);
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ------------------------------------------------------------------ MMA issue
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(P.n_pad);
+      int it = 0, tile_iter = 0;
+      for (int t = blockIdx.x; t < P.total_tiles; t += gridDim.x, ++tile_iter) {
+        const int buf = tile_iter % P.acc_bufs, ause = tile_iter / P.acc_bufs;
+        if (ause > 0) mbar_wait(acc_empty + 8u * buf, (uint32_t)(ause - 1) & 1u, failed, P.status, 0x20);
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * P.n_pad);
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int sa = it % P.a_stages, sb = it % P.b_stages;
+          mbar_wait(a_full + 8u * sa, (uint32_t)(it / P.a_stages) & 1u, failed, P.status, 0x40);
+          mbar_wait(b_full + 8u * sb, (uint32_t)(it / P.b_stages) & 1u, failed, P.status, 0x80);
+          tc_fence_after();
+          const uint32_t b_hi = base + (uint32_t)sb * L.b_stage_bytes, b_lo = b_hi + (uint32_t)P.n_pad * 128u;
+          const uint64_t dbh = make_desc(b_hi), dbl = make_desc(b_lo);
+          const uint32_t a_hi = tmem_base + a_col0 + (uint32_t)(sa * 64), a_lo = a_hi + 32u;
+          if (!DBG(P, 4)) {
+#pragma unroll
+            for (int j = 0; j < kBlockK / 8; ++j) {
+              const uint64_t adv = (uint64_t)(j * 2);
+              umma_tf32_ts(d_tmem, a_lo + (uint32_t)(j * 8), dbh + adv, idesc, (kb == 0 && j == 0) ? 0u : 1u);
+              umma_tf32_ts(d_tmem, a_hi + (uint32_t)(j * 8), dbl + adv, idesc, 1u);
+              umma_tf32_ts(d_tmem, a_hi + (uint32_t)(j * 8), dbh + adv, idesc, 1u);
+            }
+          }
+          umma_commit(a_empty + 8u * sa);
+          umma_commit(b_empty + 8u * sb);
+        }
+        umma_commit(acc_full + 8u * buf);
+      }
+    }
+  } else if (warp == kTmaWarp) {
+    // ------------------------------------------------------------------ weight tiles by TMA
+    if (lane == 0) {
+      int it = 0;
+      for (int t = blockIdx.x; t < P.total_tiles; t += gridDim.x) {
+        const int vg = t / P.n_pix_tiles;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int sb = it % P.b_stages, use = it / P.b_stages;
+          if (use > 0) mbar_wait(b_empty + 8u * sb, (uint32_t)(use - 1) & 1u, failed, P.status, 0x100);
+          const uint32_t b_hi = base + (uint32_t)sb * L.b_stage_bytes, b_lo = b_hi + (uint32_t)P.n_pad * 128u;
+          mbar_expect_tx(b_full + 8u * sb, L.b_stage_bytes);
+          tma_load_2d(b_hi, &w_map, kb * kBlockK, vg * P.n_pad, b_full + 8u * sb);
+          tma_load_2d(b_lo, &w_map, kb * kBlockK, P.lo_row_offset + vg * P.n_pad, b_full + 8u * sb);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    int tile_iter = 0;
+    for (int t = blockIdx.x; t < P.total_tiles; t += gridDim.x, ++tile_iter) {
+      const int vg = t / P.n_pix_tiles, ptile = t - vg * P.n_pix_tiles;
+      const int grp = vg / P.tiles_per_group, ntile = vg % P.tiles_per_group;
+      const int buf = tile_iter % P.acc_bufs, ause = tile_iter / P.acc_bufs;
+      const int pix = ptile * kTileM + row;
+      int b = 0, qy = 0, qx = 0;
+      if (pix < P.n_pix) {
+        const int per_img = P.q_h * P.q_w;
+        b = pix / per_img;
+        const int r = pix - b * per_img;
+        qy = r / P.q_w;
+        qx = r - qy * P.q_w;
+      }
+      const int oy0 = qy * P.oy_mul + P.oy_add, ox0 = qx * P.ox_mul + P.ox_add;
+      const int ch0 = grp * P.out_group_channels + ntile * P.out_tile_channels;
+      float* op = P.out + (long long)b * P.out_batch_stride + (long long)ch0 * P.out_plane +
+                  (long long)oy0 * P.out_pitch + ox0;
+      const float* bias = P.bias ? P.bias + ch0 : nullptr;
+      mbar_wait(acc_full + 8u * buf, (uint32_t)ause & 1u, failed, P.status, 0x200);
+      tc_fence_after();
+      const bool live = pix < P.n_pix && !failed;
+      const uint32_t acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P.n_pad);
+      const int chunks = P.n_pad / 16;
+      for (int c = 0; c < chunks; ++c) {
+        float v[16];
+        tmem_ld16(acc + (uint32_t)(c * 16), v);
+        if (live) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int col = c * 16 + j;
+            if (col < P.n) {
+              const ColEnt ce = s_cols[col];
+              const bool ok = !P.check_out || ((unsigned)(oy0 + ce.cy) < (unsigned)P.out_lim &&
+                                               (unsigned)(ox0 + ce.cx) < (unsigned)P.out_lim);
+              if (ok) {
+                float y = v[j];
+                if (bias) y += __ldg(bias + col);
+                if (P.relu) y = fmaxf(y, 0.f);
+                op[ce.off] = y;
+              }
+            }
           }
         }
       }
+      tc_fence_before();
+      mbar_arrive(acc_empty + 8u * buf);
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem_d, ncols);
+  if (warp == 0) tmem_dealloc(tmem_base, 512);
 }
 
 // ---------------------------------------------------------------------------------- weight-gradient kernel
@@ -510,7 +648,7 @@ __global__ void wgrad_reduce_kernel(const float* __restrict__ partial, float* __
 }
 
 // ------------------------------------------------------------------------------------------ weight packing
-// Forward B operand: [vg][n_pad][k_pad] <- W[o][Dg*k*k], zero padded, split hi/lo.
+// Forward B operand: [2 (hi, lo)][vg][n_pad][k_pad] <- W[o][Dg*k*k], zero padded.
 __global__ void pack_fwd_kernel(const float* __restrict__ W, float* __restrict__ hi, float* __restrict__ lo, int vgroups,
                                 int tiles_per_group, int og, int n_real, int n_pad, int k_real, int k_pad) {
   const size_t total = (size_t)vgroups * n_pad * k_pad;
@@ -530,11 +668,12 @@ __global__ void pack_fwd_kernel(const float* __restrict__ W, float* __restrict__
   }
 }
 
-// Data-gradient B operand of one phase: [vg][n_pad][k_pad], row = input channel d (tile nt of group g),
-// column kk = (oc, jy, jx) <- W[g*og + oc][d][py + jy*s][px + jx*s].
+// Data-gradient B operand: [2][vg][n_pad][k_pad]; row j = (d, py, px) of channel tile nt of group g (py, px: position
+// inside an s x s block of input pixels), column kk = (oc, jy, jx) <- W[g*og + oc][d][py + jy*s][px + jx*s], zero where
+// the tap index exceeds the kernel.
 __global__ void pack_dgrad_kernel(const float* __restrict__ W, float* __restrict__ hi, float* __restrict__ lo,
-                                  int vgroups, int tiles_per_group, int og, int Dg, int k, int s, int py, int px,
-                                  int jh, int jw, int n_real, int n_pad, int k_real, int k_pad) {
+                                  int vgroups, int tiles_per_group, int og, int Dg, int k, int s, int taps, int d_tile,
+                                  int n_real, int n_pad, int k_real, int k_pad) {
   const size_t total = (size_t)vgroups * n_pad * k_pad;
   for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
     const int kk = (int)(t % k_pad);
@@ -543,9 +682,11 @@ __global__ void pack_dgrad_kernel(const float* __restrict__ W, float* __restrict
     float v = 0.f;
     if (j < n_real && kk < k_real) {
       const int grp = vg / tiles_per_group;
-      const int d = (vg % tiles_per_group) * n_real + j;
-      const int jx = kk % jw, jy = (kk / jw) % jh, oc = kk / (jw * jh);
-      v = W[(((size_t)(grp * og + oc)) * Dg + d) * k * k + (py + jy * s) * k + (px + jx * s)];
+      const int d = (vg % tiles_per_group) * d_tile + j / (s * s);
+      const int py = (j / s) % s, px = j % s;
+      const int jx = kk % taps, jy = (kk / taps) % taps, oc = kk / (taps * taps);
+      const int kr = py + jy * s, kc = px + jx * s;
+      if (kr < k && kc < k) v = W[(((size_t)(grp * og + oc)) * Dg + d) * k * k + kr * k + kc];
     }
     float h, l;
     split_tf32(v, h, l);
@@ -566,49 +707,65 @@ int dbg_knobs() {
 
 int round_up(int v, int a) { return (v + a - 1) / a * a; }
 
-// Smallest number of equal channel tiles such that a tile has at most 256 channels.
-int channel_tiles(int channels) {
+// Smallest number of equal channel tiles such that a tile spans at most `limit` accumulator columns.
+int channel_tiles(int channels, int cols_per_channel) {
   for (int t = 1; t <= channels; ++t)
-    if (channels % t == 0 && channels / t <= 256) return t;
-  return channels;
+    if (channels % t == 0 && (channels / t) * cols_per_channel <= 256) return t;
+  return 0;
 }
 
 }  // namespace
 
-// One stride phase of the data gradient (stride 1 has a single phase).
-struct DgradPhase {
-  int py, px, jh, jw;      // phase and number of taps per axis
-  int y0, x0, qh, qw;      // first input row/column of the phase and how many
-  int ry0, rx0;            // dY coordinate of tap (0,0) for qy = 0 / qx = 0
-  int k_real, k_pad;
-  Tap* taps = nullptr;     // device
-  float *w_hi = nullptr, *w_lo = nullptr;
+// One gather problem (forward, or the data gradient): tables, packed weights and their tensor map.
+struct GatherProblem {
+  int tiles = 1, ch_tile = 0;  // channel tiles per group, channels per tile
+  int n = 0, n_pad = 0, k_real = 0, k_pad = 0;
+  Tap* taps = nullptr;
+  ColEnt* cols = nullptr;
+  float* w = nullptr;  // [2][vgroups][n_pad][k_pad]
+  size_t w_half = 0;   // elements in one half
+  CUtensorMap map;
+  int a_stages = 4, b_stages = 4, acc_bufs = 1;
+  size_t smem = 0;
 };
 
 struct UmmaPlan {
   ConvGeom G;
-  // forward / weight gradient share the lowering table
-  int f_tiles, f_n, f_npad, f_kreal, f_kpad;
-  Tap* f_taps = nullptr;
-  float *f_whi = nullptr, *f_wlo = nullptr;
+  GatherProblem fwd, dgr;
+  int dgr_taps = 0, dgr_q = 0, dgr_q0 = 0;  // taps per axis; super-pixels per axis and the first one that holds a pixel
   // weight gradient
-  int w_mtiles, w_splits, w_kblocks_total, w_kblocks_per_split;
+  int w_mtiles, w_splits, w_kblocks_total, w_kblocks_per_split, w_npad;
   Tap* w_taps = nullptr;
   float* w_partial = nullptr;
-  // data gradient
-  int d_tiles, d_n, d_npad;
-  std::vector<DgradPhase> phases;
   size_t bytes = 0;
 };
 
 bool umma_supported(const ConvGeom& G) {
-  const int fn = G.og / channel_tiles(G.og), dn = G.Dg / channel_tiles(G.Dg);
-  if (fn > 256 || dn > 256) return false;
+  if (channel_tiles(G.og, 1) == 0 || channel_tiles(G.Dg, G.s * G.s) == 0) return false;
   if (G.k > 255 || G.n > 8000) return false;  // tap coordinates are 16-bit
+  const int taps = (G.k + G.s - 1) / G.s;
+  const long long kf = (long long)G.Dg * G.k * G.k, kd = (long long)G.og * taps * taps;
+  if (kf > 16384 || kd > 16384) return false;  // the tap table lives in shared memory next to the weight stages
   return true;
 }
 
 namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
 
 template <class T>
 int dev_alloc(cct_ctx* ctx, UmmaPlan* p, T** ptr, size_t count) {
@@ -617,10 +774,11 @@ int dev_alloc(cct_ctx* ctx, UmmaPlan* p, T** ptr, size_t count) {
   return CCT_OK;
 }
 
-int upload_taps(cct_ctx* ctx, UmmaPlan* p, Tap** dst, const std::vector<Tap>& host) {
+template <class T>
+int upload(cct_ctx* ctx, UmmaPlan* p, T** dst, const std::vector<T>& host) {
   int rc = dev_alloc(ctx, p, dst, host.size());
   if (rc != CCT_OK) return rc;
-  CCT_CUDA(ctx, cudaMemcpy(*dst, host.data(), host.size() * sizeof(Tap), cudaMemcpyHostToDevice));
+  CCT_CUDA(ctx, cudaMemcpy(*dst, host.data(), host.size() * sizeof(T), cudaMemcpyHostToDevice));
   return CCT_OK;
 }
 
@@ -635,6 +793,36 @@ int pack_grid(cct_ctx* ctx, size_t total) {
   return (int)std::min<size_t>(std::max<size_t>(b, 1), (size_t)ctx->sm_count * 8);
 }
 
+// Tensor-memory and shared-memory budget of a gather problem, packed-weight buffer and its tensor map.
+int finish_problem(cct_ctx* ctx, UmmaPlan* p, GatherProblem& gp, int vgroups) {
+  if (gp.n_pad <= 128) { gp.acc_bufs = 2; gp.a_stages = 4; }
+  else { gp.acc_bufs = 1; gp.a_stages = 4; }
+  const int fixed = gp.k_pad * 8 + gp.n_pad * 8 + 512 + 1024;
+  int bs = (kSmemLimit - fixed) / (2 * gp.n_pad * 128);
+  gp.b_stages = std::max(1, std::min(kMaxBStages, bs));
+  gp.smem = std::max<size_t>(gather_smem(gp.n_pad, gp.k_pad, gp.b_stages).total + 1024, 120 * 1024);  // > half an SM: one CTA per SM
+  gp.w_half = (size_t)vgroups * gp.n_pad * gp.k_pad;
+  int rc = dev_alloc(ctx, p, &gp.w, 2 * gp.w_half);
+  if (rc != CCT_OK) return rc;
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) {
+    ctx->last_error = "cuTensorMapEncodeTiled is not available from this driver";
+    return CCT_ERR_CUDA;
+  }
+  const cuuint64_t gdim[2] = {(cuuint64_t)gp.k_pad, (cuuint64_t)(2 * vgroups * gp.n_pad)};
+  const cuuint64_t gstride[1] = {(cuuint64_t)gp.k_pad * sizeof(float)};
+  const cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)gp.n_pad};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(&gp.map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, gp.w, gdim, gstride, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    ctx->last_error = "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r);
+    return CCT_ERR_CUDA;
+  }
+  return CCT_OK;
+}
+
 }  // namespace
 
 int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out) {
@@ -642,88 +830,88 @@ int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out) {
   p->G = G;
   int rc = CCT_OK;
   const int kk = G.k * G.k;
-  // ---- forward: rows = output channels of a tile, reduction = (d, kr, kc)
-  p->f_tiles = channel_tiles(G.og);
-  p->f_n = G.og / p->f_tiles;
-  p->f_npad = round_up(p->f_n, 16);
-  p->f_kreal = G.Dg * kk;
-  p->f_kpad = round_up(p->f_kreal, kBlockK);
+  // ---- forward: accumulator columns = output channels of a tile, reduction = (d, kr, kc)
   {
-    std::vector<Tap> t(p->f_kpad);
-    for (int i = 0; i < p->f_kpad; ++i) {
-      if (i < p->f_kreal) {
+    GatherProblem& f = p->fwd;
+    f.tiles = channel_tiles(G.og, 1);
+    f.ch_tile = f.n = G.og / f.tiles;
+    f.n_pad = round_up(f.n, 16);
+    f.k_real = G.Dg * kk;
+    f.k_pad = round_up(f.k_real, kBlockK);
+    std::vector<Tap> t(f.k_pad);
+    for (int i = 0; i < f.k_pad; ++i) {
+      if (i < f.k_real) {
         const int d = i / kk, kr = (i / G.k) % G.k, kc = i % G.k;
         t[i] = Tap{d * G.n * G.n + kr * G.n + kc, (short)kr, (short)kc};
       } else {
         t[i] = Tap{0, (short)kPadTap, (short)kPadTap};
       }
     }
-    rc = upload_taps(ctx, p, &p->f_taps, t);
+    std::vector<ColEnt> c(f.n_pad);
+    for (int j = 0; j < f.n_pad; ++j) c[j] = ColEnt{j * G.m * G.m, 0, 0};
+    rc = upload(ctx, p, &f.taps, t);
+    if (rc == CCT_OK) rc = upload(ctx, p, &f.cols, c);
+    if (rc == CCT_OK) rc = finish_problem(ctx, p, f, G.g * f.tiles);
   }
-  const size_t fw = (size_t)G.g * p->f_tiles * p->f_npad * p->f_kpad;
-  if (rc == CCT_OK) rc = dev_alloc(ctx, p, &p->f_whi, fw);
-  if (rc == CCT_OK) rc = dev_alloc(ctx, p, &p->f_wlo, fw);
+  // ---- data gradient as a stride-1 gather over dY: one "super pixel" = an s x s block of input pixels; accumulator
+  //      columns = (d, py, px), reduction = (oc, jy, jx) with jy, jx < ceil(k/s); depth-to-space in the epilogue.
+  if (rc == CCT_OK) {
+    GatherProblem& d = p->dgr;
+    const int ss = G.s * G.s;
+    p->dgr_taps = (G.k + G.s - 1) / G.s;
+    p->dgr_q0 = G.p / G.s;
+    p->dgr_q = (G.n - 1 + G.p) / G.s + 1 - p->dgr_q0;
+    d.tiles = channel_tiles(G.Dg, ss);
+    d.ch_tile = G.Dg / d.tiles;
+    d.n = d.ch_tile * ss;
+    d.n_pad = round_up(d.n, 16);
+    const int J = p->dgr_taps;
+    d.k_real = G.og * J * J;
+    d.k_pad = round_up(d.k_real, kBlockK);
+    std::vector<Tap> t(d.k_pad);
+    for (int i = 0; i < d.k_pad; ++i) {
+      if (i < d.k_real) {
+        const int jx = i % J, jy = (i / J) % J, oc = i / (J * J);
+        t[i] = Tap{oc * G.m * G.m - jy * G.m - jx, (short)-jy, (short)-jx};
+      } else {
+        t[i] = Tap{0, (short)kPadTap, (short)kPadTap};
+      }
+    }
+    std::vector<ColEnt> c(d.n_pad);
+    for (int j = 0; j < d.n_pad; ++j) {
+      const int dl = j / ss, py = (j / G.s) % G.s, px = j % G.s;
+      c[j] = ColEnt{dl * G.n * G.n + py * G.n + px, (short)py, (short)px};
+    }
+    rc = upload(ctx, p, &d.taps, t);
+    if (rc == CCT_OK) rc = upload(ctx, p, &d.cols, c);
+    if (rc == CCT_OK) rc = finish_problem(ctx, p, d, G.g * d.tiles);
+  }
   // ---- weight gradient: rows = (d, kr, kc) plus the all-ones row, columns = output channels of a tile
   if (rc == CCT_OK) {
-    p->w_mtiles = (p->f_kreal + 1 + kTileM - 1) / kTileM;
+    const GatherProblem& f = p->fwd;
+    p->w_npad = f.n_pad;
+    p->w_mtiles = (f.k_real + 1 + kTileM - 1) / kTileM;
     std::vector<Tap> t((size_t)p->w_mtiles * kTileM);
     for (size_t i = 0; i < t.size(); ++i) {
-      if ((int)i < p->f_kreal) {
+      if ((int)i < f.k_real) {
         const int d = (int)i / kk, kr = ((int)i / G.k) % G.k, kc = (int)i % G.k;
         t[i] = Tap{d * G.n * G.n + kr * G.n + kc, (short)kr, (short)kc};
-      } else if ((int)i == p->f_kreal) {
+      } else if ((int)i == f.k_real) {
         t[i] = Tap{0, (short)kOnesTap, 0};
       } else {
         t[i] = Tap{0, (short)kPadTap, (short)kPadTap};
       }
     }
-    rc = upload_taps(ctx, p, &p->w_taps, t);
+    rc = upload(ctx, p, &p->w_taps, t);
     const int n_pix = G.B * G.m * G.m;
     p->w_kblocks_total = (n_pix + kBlockK - 1) / kBlockK;
-    const int out_tiles = p->w_mtiles * G.g * p->f_tiles;
+    const int out_tiles = p->w_mtiles * G.g * f.tiles;
     int splits = std::max(1, ctx->sm_count / out_tiles);
     splits = std::min(splits, std::max(1, p->w_kblocks_total / 8));  // at least 8 k-blocks per CTA
     p->w_kblocks_per_split = (p->w_kblocks_total + splits - 1) / splits;
     p->w_splits = (p->w_kblocks_total + p->w_kblocks_per_split - 1) / p->w_kblocks_per_split;
     if (rc == CCT_OK)
-      rc = dev_alloc(ctx, p, &p->w_partial,
-                     (size_t)p->w_splits * G.g * p->f_tiles * p->w_mtiles * kTileM * p->f_npad);
-  }
-  // ---- data gradient: one gather problem per stride phase
-  if (rc == CCT_OK) {
-    p->d_tiles = channel_tiles(G.Dg);
-    p->d_n = G.Dg / p->d_tiles;
-    p->d_npad = round_up(p->d_n, 16);
-    for (int py = 0; py < G.s && rc == CCT_OK; ++py)
-      for (int px = 0; px < G.s && rc == CCT_OK; ++px) {
-        DgradPhase ph;
-        ph.py = py; ph.px = px;
-        ph.jh = py < G.k ? (G.k - py + G.s - 1) / G.s : 0;
-        ph.jw = px < G.k ? (G.k - px + G.s - 1) / G.s : 0;
-        ph.y0 = ((py - G.p) % G.s + G.s) % G.s;
-        ph.x0 = ((px - G.p) % G.s + G.s) % G.s;
-        ph.qh = ph.y0 < G.n ? (G.n - ph.y0 + G.s - 1) / G.s : 0;
-        ph.qw = ph.x0 < G.n ? (G.n - ph.x0 + G.s - 1) / G.s : 0;
-        if (ph.qh == 0 || ph.qw == 0) continue;
-        ph.ry0 = (ph.y0 + G.p - py) / G.s;
-        ph.rx0 = (ph.x0 + G.p - px) / G.s;
-        ph.k_real = G.og * ph.jh * ph.jw;
-        ph.k_pad = std::max(kBlockK, round_up(ph.k_real, kBlockK));
-        std::vector<Tap> t(ph.k_pad);
-        for (int i = 0; i < ph.k_pad; ++i) {
-          if (i < ph.k_real) {
-            const int jx = i % ph.jw, jy = (i / ph.jw) % ph.jh, oc = i / (ph.jw * ph.jh);
-            t[i] = Tap{oc * G.m * G.m - jy * G.m - jx, (short)-jy, (short)-jx};
-          } else {
-            t[i] = Tap{0, (short)kPadTap, (short)kPadTap};
-          }
-        }
-        rc = upload_taps(ctx, p, &ph.taps, t);
-        const size_t dw = (size_t)G.g * p->d_tiles * p->d_npad * ph.k_pad;
-        if (rc == CCT_OK) rc = dev_alloc(ctx, p, &ph.w_hi, dw);
-        if (rc == CCT_OK) rc = dev_alloc(ctx, p, &ph.w_lo, dw);
-        p->phases.push_back(ph);
-      }
+      rc = dev_alloc(ctx, p, &p->w_partial, (size_t)p->w_splits * G.g * f.tiles * p->w_mtiles * kTileM * f.n_pad);
   }
   if (rc == CCT_OK) rc = set_smem(ctx, gather_conv_kernel, kSmemLimit);
   if (rc == CCT_OK) rc = set_smem(ctx, wgrad_kernel, kSmemLimit);
@@ -737,45 +925,59 @@ int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out) {
 
 void umma_plan_destroy(cct_ctx* ctx, UmmaPlan* p) {
   if (!p) return;
-  cudaFree(p->f_taps); cudaFree(p->f_whi); cudaFree(p->f_wlo);
+  for (GatherProblem* gp : {&p->fwd, &p->dgr}) { cudaFree(gp->taps); cudaFree(gp->cols); cudaFree(gp->w); }
   cudaFree(p->w_taps); cudaFree(p->w_partial);
-  for (DgradPhase& ph : p->phases) { cudaFree(ph.taps); cudaFree(ph.w_hi); cudaFree(ph.w_lo); }
   delete p;
 }
 
 size_t umma_plan_workspace_bytes(const UmmaPlan* p) { return p->bytes; }
 
+namespace {
+
+void fill_common(GatherParams& P, const GatherProblem& gp, cct_ctx* ctx, int vgroups) {
+  P.taps = gp.taps; P.cols = gp.cols;
+  P.tiles_per_group = gp.tiles;
+  P.out_tile_channels = gp.ch_tile;
+  P.n = gp.n; P.n_pad = gp.n_pad; P.k_pad = gp.k_pad;
+  P.n_pix_tiles = (P.n_pix + kTileM - 1) / kTileM;
+  P.total_tiles = P.n_pix_tiles * vgroups;
+  P.a_stages = gp.a_stages; P.b_stages = gp.b_stages; P.acc_bufs = gp.acc_bufs;
+  P.lo_row_offset = vgroups * gp.n_pad;
+  P.status = ctx->status_dev;
+  P.dbg = dbg_knobs();
+}
+
+}  // namespace
+
 int umma_conv_forward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W, const float* bias, float* Y,
                       int relu, PhaseTimer* t) {
   if (*ctx->status_host != 0) return CCT_ERR_TIMEOUT;  // an earlier bounded wait gave up: do not pile up behind it
   const ConvGeom& G = p->G;
-  const int vgroups = G.g * p->f_tiles;
+  GatherProblem& f = p->fwd;
+  const int vgroups = G.g * f.tiles;
   t->begin(4, ctx->stream);
-  const size_t fw = (size_t)vgroups * p->f_npad * p->f_kpad;
-  pack_fwd_kernel<<<pack_grid(ctx, fw), 256, 0, ctx->stream>>>(W, p->f_whi, p->f_wlo, vgroups, p->f_tiles, G.og, p->f_n,
-                                                              p->f_npad, p->f_kreal, p->f_kpad);
+  pack_fwd_kernel<<<pack_grid(ctx, f.w_half), 256, 0, ctx->stream>>>(W, f.w, f.w + f.w_half, vgroups, f.tiles, G.og, f.n,
+                                                                   f.n_pad, f.k_real, f.k_pad);
   t->end(4, ctx->stream);
   CCT_CHECK_LAUNCH(ctx);
   GatherParams P{};
-  P.in = X; P.out = Y; P.w_hi = p->f_whi; P.w_lo = p->f_wlo; P.taps = p->f_taps;
+  P.in = X; P.out = Y;
   P.bias = G.bias ? bias : nullptr;
   P.n_pix = G.B * G.m * G.m; P.q_h = G.m; P.q_w = G.m;
   P.iy_mul = G.s; P.iy_add = -G.p; P.ix_mul = G.s; P.ix_add = -G.p;
   P.in_lim = G.n;
   P.in_batch_stride = (long long)G.D * G.n * G.n;
   P.in_group_stride = G.Dg * G.n * G.n;
-  P.tiles_per_group = p->f_tiles;
   P.oy_mul = 1; P.oy_add = 0; P.ox_mul = 1; P.ox_add = 0;
+  P.out_lim = G.m; P.check_out = 0;
   P.out_pitch = G.m; P.out_plane = G.m * G.m;
   P.out_batch_stride = (long long)G.o * G.m * G.m;
   P.out_group_channels = G.og;
-  P.n = p->f_n; P.n_pad = p->f_npad; P.k_pad = p->f_kpad;
   P.relu = relu;
-  P.status = ctx->status_dev;
-  P.dbg = dbg_knobs();
-  dim3 grid((P.n_pix + kTileM - 1) / kTileM, vgroups);
+  fill_common(P, f, ctx, vgroups);
+  const int grid = std::min(P.total_tiles, ctx->sm_count);
   t->begin(0, ctx->stream);
-  gather_conv_kernel<<<grid, kThreads, smem_bytes(P.n_pad), ctx->stream>>>(P);
+  gather_conv_kernel<<<grid, kGatherThreads, f.smem, ctx->stream>>>(P, f.map);
   t->end(0, ctx->stream);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
@@ -787,6 +989,7 @@ int umma_conv_backward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W
   const ConvGeom& G = p->G;
   // ---- weight + bias gradient
   {
+    const GatherProblem& f = p->fwd;
     WgradParams P{};
     P.x = X; P.dy = dY; P.partial = p->w_partial; P.taps = p->w_taps;
     P.n_pix = G.B * G.m * G.m; P.m = G.m; P.mm = G.m * G.m; P.n = G.n; P.s = G.s; P.p = G.p;
@@ -794,61 +997,52 @@ int umma_conv_backward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W
     P.x_group_stride = G.Dg * G.n * G.n;
     P.dy_batch_stride = (long long)G.o * G.m * G.m;
     P.dy_group_channels = G.og;
-    P.tiles_per_group = p->f_tiles;
-    P.n_real = p->f_n; P.n_pad = p->f_npad;
+    P.tiles_per_group = f.tiles;
+    P.n_real = f.n; P.n_pad = f.n_pad;
     P.kblocks_total = p->w_kblocks_total; P.kblocks_per_split = p->w_kblocks_per_split;
     P.status = ctx->status_dev;
     P.dbg = dbg_knobs();
-    const int vgroups = G.g * p->f_tiles;
+    const int vgroups = G.g * f.tiles;
     dim3 grid(p->w_mtiles, p->w_splits, vgroups);
     t->begin(1, ctx->stream);
     wgrad_kernel<<<grid, kThreads, smem_bytes(P.n_pad), ctx->stream>>>(P);
     t->end(1, ctx->stream);
     CCT_CHECK_LAUNCH(ctx);
     t->begin(2, ctx->stream);
-    const size_t total = (size_t)vgroups * (p->f_kreal + 1) * p->f_n;
+    const size_t total = (size_t)vgroups * (f.k_real + 1) * f.n;
     wgrad_reduce_kernel<<<pack_grid(ctx, total), 256, 0, ctx->stream>>>(p->w_partial, dW, G.bias ? db : nullptr,
-                                                                      p->w_splits, vgroups, p->f_tiles,
-                                                                      p->w_mtiles * kTileM, p->f_n, p->f_npad,
-                                                                      p->f_kreal, G.og);
+                                                                      p->w_splits, vgroups, f.tiles,
+                                                                      p->w_mtiles * kTileM, f.n, f.n_pad, f.k_real, G.og);
     t->end(2, ctx->stream);
     CCT_CHECK_LAUNCH(ctx);
   }
   // ---- data gradient
   if (dX) {
-    const int vgroups = G.g * p->d_tiles;
+    GatherProblem& d = p->dgr;
+    const int vgroups = G.g * d.tiles;
     t->begin(3, ctx->stream);
-    if ((int)p->phases.size() < G.s * G.s) {
-      // some phase has no input pixels or was skipped: nothing writes those pixels otherwise
-      CCT_CUDA(ctx, cudaMemsetAsync(dX, 0, (size_t)G.B * G.D * G.n * G.n * sizeof(float), ctx->stream));
-    }
-    for (DgradPhase& ph : p->phases) {
-      const size_t dw = (size_t)vgroups * p->d_npad * ph.k_pad;
-      pack_dgrad_kernel<<<pack_grid(ctx, dw), 256, 0, ctx->stream>>>(W, ph.w_hi, ph.w_lo, vgroups, p->d_tiles, G.og,
-                                                                    G.Dg, G.k, G.s, ph.py, ph.px, ph.jh, ph.jw, p->d_n,
-                                                                    p->d_npad, ph.k_real, ph.k_pad);
-      CCT_CHECK_LAUNCH(ctx);
-      GatherParams P{};
-      P.in = dY; P.out = dX; P.w_hi = ph.w_hi; P.w_lo = ph.w_lo; P.taps = ph.taps; P.bias = nullptr;
-      P.n_pix = G.B * ph.qh * ph.qw; P.q_h = ph.qh; P.q_w = ph.qw;
-      P.iy_mul = 1; P.iy_add = ph.ry0; P.ix_mul = 1; P.ix_add = ph.rx0;
-      P.in_lim = G.m;
-      P.in_batch_stride = (long long)G.o * G.m * G.m;
-      P.in_group_stride = G.og * G.m * G.m;
-      P.tiles_per_group = p->d_tiles;
-      P.oy_mul = G.s; P.oy_add = ph.y0; P.ox_mul = G.s; P.ox_add = ph.x0;
-      P.out_pitch = G.n; P.out_plane = G.n * G.n;
-      P.out_batch_stride = (long long)G.D * G.n * G.n;
-      P.out_group_channels = G.Dg;
-      P.n = p->d_n; P.n_pad = p->d_npad; P.k_pad = ph.k_pad;
-      P.relu = 0;
-      P.status = ctx->status_dev;
-      P.dbg = dbg_knobs();
-      dim3 grid((P.n_pix + kTileM - 1) / kTileM, vgroups);
-      gather_conv_kernel<<<grid, kThreads, smem_bytes(P.n_pad), ctx->stream>>>(P);
-      CCT_CHECK_LAUNCH(ctx);
-    }
+    pack_dgrad_kernel<<<pack_grid(ctx, d.w_half), 256, 0, ctx->stream>>>(W, d.w, d.w + d.w_half, vgroups, d.tiles, G.og,
+                                                                       G.Dg, G.k, G.s, p->dgr_taps, d.ch_tile, d.n,
+                                                                       d.n_pad, d.k_real, d.k_pad);
+    CCT_CHECK_LAUNCH(ctx);
+    GatherParams P{};
+    P.in = dY; P.out = dX; P.bias = nullptr;
+    P.n_pix = G.B * p->dgr_q * p->dgr_q; P.q_h = p->dgr_q; P.q_w = p->dgr_q;
+    P.iy_mul = 1; P.iy_add = p->dgr_q0; P.ix_mul = 1; P.ix_add = p->dgr_q0;
+    P.in_lim = G.m;
+    P.in_batch_stride = (long long)G.o * G.m * G.m;
+    P.in_group_stride = G.og * G.m * G.m;
+    P.oy_mul = G.s; P.oy_add = p->dgr_q0 * G.s - G.p; P.ox_mul = G.s; P.ox_add = p->dgr_q0 * G.s - G.p;
+    P.out_lim = G.n; P.check_out = 1;
+    P.out_pitch = G.n; P.out_plane = G.n * G.n;
+    P.out_batch_stride = (long long)G.D * G.n * G.n;
+    P.out_group_channels = G.Dg;
+    P.relu = 0;
+    fill_common(P, d, ctx, vgroups);
+    const int grid = std::min(P.total_tiles, ctx->sm_count);
+    gather_conv_kernel<<<grid, kGatherThreads, d.smem, ctx->stream>>>(P, d.map);
     t->end(3, ctx->stream);
+    CCT_CHECK_LAUNCH(ctx);
   }
   return CCT_OK;
 }
