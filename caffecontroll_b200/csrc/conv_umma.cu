@@ -42,14 +42,30 @@ constexpr int kSmemLimit = 227 * 1024;
 #else
 #define DBG(P, bit) 0
 #endif
-constexpr int kPadTap = 0x4000;  // tap coordinate that fails every bounds test (marks padding rows of a table)
+constexpr int kPadTap = 0x4000;  // tap coordinate that fails every bounds test (weight-gradient table)
+constexpr int kMaxTapsPerAxis = 15;
+constexpr uint32_t kPadBit = 0x80000000u;  // never set in a pixel's validity mask: marks padding entries
 
-// One entry per reduction index of a gathered operand: element offset from the pixel's tap origin and the tap's
-// (dy, dx) for the bounds test.
+// One entry per reduction index of a gathered operand (weight-gradient kernel): element offset from the pixel's tap
+// origin and the tap's (dy, dx) for the bounds test.
 struct Tap {
   int off;
   short dy, dx;
 };
+
+// Gather-kernel form: the tap is in bounds for a pixel iff (pixel_mask & bits) == bits, where bit i (rows) and bit
+// 16+j (columns) of the pixel's mask say whether tap row i / tap column j falls inside the gathered plane.
+struct MaskTap {
+  int off;
+  uint32_t bits;
+};
+
+// Bits [lo, hi) set; 0 <= lo, hi <= 15.
+__device__ __forceinline__ uint32_t bit_range(int lo, int hi) {
+  lo = max(lo, 0);
+  hi = min(hi, kMaxTapsPerAxis);
+  return hi > lo ? ((1u << hi) - 1u) & ~((1u << lo) - 1u) : 0u;
+}
 
 // ---------------------------------------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -149,6 +165,12 @@ __device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
   hi = __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
   lo = x - hi;
 }
+// Cheaper split for the gather producers: hi = x truncated to tf32; |lo| < 2^-10 |x| still, and the MMA unit's
+// own truncation of lo costs < 2^-20 |x|.
+__device__ __forceinline__ void split_tf32_trunc(float x, uint32_t& hi, uint32_t& lo) {
+  hi = __float_as_uint(x) & 0xFFFFE000u;
+  lo = __float_as_uint(x - __uint_as_float(hi));
+}
 
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, float a, float b, float c, float d) {
   asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
@@ -203,17 +225,18 @@ __host__ __device__ inline uint32_t tmem_cols(int n_pad) {
 // ------------------------------------------------------------------------------ gather kernel (forward, dgrad)
 //
 // Persistent, warp-specialised: one CTA per SM walks over (channel tile, 128-pixel tile) pairs.
-//   warps 0-7   producers: thread = one pixel of the tile = one TMEM lane.  Per k-block a thread gathers its 32
+//   warps 0-15  producers: thread = one pixel of the tile = one TMEM lane.  Per k-block a thread gathers its 32
 //               lowered values, splits them hi/lo and writes them with tcgen05.st into the A stage in tensor memory
-//               (warps 0-3 take even k-blocks, warps 4-7 odd ones; both sets cover all 128 lanes).
-//   warp 8      one thread issues the MMAs: A from tensor memory, B from shared memory.
-//   warp 9      one thread streams the pre-split weight tiles (B) into shared memory with TMA (128-byte swizzle).
-//   warps 10-13 epilogue: tcgen05.ld the finished accumulator, add bias / clamp, store NCHW (or depth-to-space for
+//               (four sets of four warps; set g takes the k-blocks with running index == g mod 4, each set covers
+//               all 128 lanes).
+//   warp 16     one thread issues the MMAs: A from tensor memory, B from shared memory.
+//   warp 17     one thread streams the pre-split weight tiles (B) into shared memory with TMA (128-byte swizzle).
+//   warps 18-21 epilogue: tcgen05.ld the finished accumulator, add bias / clamp, store NCHW (or depth-to-space for
 //               the strided data gradient); overlaps the next tile's MMAs when two accumulators fit.
 // Tensor memory (512 columns): [accumulator(s) | A stages of 64 columns: 32 hi + 32 lo].
-constexpr int kProducerWarps = 8;
-constexpr int kMmaWarp = 8, kTmaWarp = 9, kEpiWarp0 = 10, kEpiWarps = 4;
-constexpr int kGatherThreads = (kEpiWarp0 + kEpiWarps) * 32;  // 448
+constexpr int kProducerWarps = 16;  // four sets of four; set g fills the A stages with index == g (mod 4)
+constexpr int kMmaWarp = 16, kTmaWarp = 17, kEpiWarp0 = 18, kEpiWarps = 4;
+constexpr int kGatherThreads = (kEpiWarp0 + kEpiWarps) * 32;  // 704
 constexpr int kMaxAStages = 4, kMaxBStages = 8, kMaxAccBufs = 2;
 
 struct ColEnt {  // one accumulator column -> where it lands in the output
@@ -224,12 +247,13 @@ struct ColEnt {  // one accumulator column -> where it lands in the output
 struct GatherParams {
   const float* in;    // gathered tensor: X (forward) or dY (data gradient)
   float* out;         // Y or dX
-  const Tap* taps;    // [k_pad]
-  const ColEnt* cols; // [n_pad]
+  const MaskTap* taps; // [k_pad]
+  const ColEnt* cols;  // [n_pad]
   const float* bias;  // indexed by output channel, or null
   int n_pix, q_h, q_w;                 // pixels = batch * q_h * q_w
   int iy_mul, iy_add, ix_mul, ix_add;  // tap origin in the gathered tensor: iy0 = qy*iy_mul + iy_add
   int in_lim;                          // gathered tensor is in_lim x in_lim per channel
+  int tap_sign, taps_per_axis;         // tap i of an axis sits at coordinate origin + tap_sign * i
   long long in_batch_stride;
   int in_group_stride;   // elements between the channel blocks of consecutive groups
   int tiles_per_group;   // virtual groups per real group (channel tiles)
@@ -270,12 +294,10 @@ __device__ __forceinline__ void umma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, u
       : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-      : "memory");
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]), "r"(r[1]),
+               "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -302,7 +324,7 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
   const uint32_t a_full = bars, a_empty = a_full + 8u * kMaxAStages, b_full = a_empty + 8u * kMaxAStages,
                  b_empty = b_full + 8u * kMaxBStages, acc_full = b_empty + 8u * kMaxBStages,
                  acc_empty = acc_full + 8u * kMaxAccBufs, tmem_slot = acc_empty + 8u * kMaxAccBufs;
-  Tap* s_taps = reinterpret_cast<Tap*>(base_ptr + L.taps_off);
+  MaskTap* s_taps = reinterpret_cast<MaskTap*>(base_ptr + L.taps_off);
   ColEnt* s_cols = reinterpret_cast<ColEnt*>(base_ptr + L.cols_off);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -326,60 +348,79 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
 
   if (warp < kProducerWarps) {
     // ------------------------------------------------------------------ producers
+    // Set `group` owns A stage `group` and fills it for the k-blocks with running index == group (mod 4).  The raw
+    // values of the set's next k-block are already in flight (in registers) while the current one is split and
+    // stored, so the global-load latency is paid once per k-block per set, off the critical path.
     const int group = warp >> 2, quarter = warp & 3;
     const int row = quarter * 32 + lane;
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + a_col0;
-    int it = 0;
-    for (int t = blockIdx.x; t < P.total_tiles; t += gridDim.x) {
+    const uint32_t st_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + a_col0 + (uint32_t)(group * 64);
+    const uint32_t full_bar = a_full + 8u * group, empty_bar = a_empty + 8u * group;
+    const int my_tiles = (P.total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int my_stages = my_tiles * kblocks;
+    const float* in_px = P.in;
+    uint32_t mask = 0;
+    auto setup_tile = [&](int tile_local) {
+      const int t = blockIdx.x + tile_local * gridDim.x;
       const int vg = t / P.n_pix_tiles, ptile = t - vg * P.n_pix_tiles;
       const int grp = vg / P.tiles_per_group;
       const int pix = ptile * kTileM + row;
-      const bool pix_ok = pix < P.n_pix;
-      int b = 0, qy = 0, qx = 0;
-      if (pix_ok) {
+      in_px = P.in;
+      mask = 0;  // which tap rows (bits 0-14) and tap columns (bits 16-30) fall inside the plane
+      if (pix < P.n_pix) {
         const int per_img = P.q_h * P.q_w;
-        b = pix / per_img;
+        const int b = pix / per_img;
         const int r = pix - b * per_img;
-        qy = r / P.q_w;
-        qx = r - qy * P.q_w;
+        const int qy = r / P.q_w;
+        const int qx = r - qy * P.q_w;
+        const int iy0 = qy * P.iy_mul + P.iy_add, ix0 = qx * P.ix_mul + P.ix_add;
+        in_px = P.in + (long long)b * P.in_batch_stride + (long long)grp * P.in_group_stride +
+                (long long)iy0 * P.in_lim + ix0;
+        if (P.tap_sign > 0)  // coordinate origin + i in [0, lim)
+          mask = bit_range(-iy0, min(P.taps_per_axis, P.in_lim - iy0)) |
+                 (bit_range(-ix0, min(P.taps_per_axis, P.in_lim - ix0)) << 16);
+        else  // coordinate origin - i in [0, lim)
+          mask = bit_range(iy0 - P.in_lim + 1, min(P.taps_per_axis, iy0 + 1)) |
+                 (bit_range(ix0 - P.in_lim + 1, min(P.taps_per_axis, ix0 + 1)) << 16);
       }
-      const int iy0 = pix_ok ? qy * P.iy_mul + P.iy_add : -2 * kPadTap;
-      const int ix0 = qx * P.ix_mul + P.ix_add;
-      const float* in_px = pix_ok ? P.in + (long long)b * P.in_batch_stride + (long long)grp * P.in_group_stride +
-                                        (long long)iy0 * P.in_lim + ix0
-                                  : P.in;
-      for (int kb = 0; kb < kblocks; ++kb, ++it) {
-        if ((it & 1) != group) continue;
-        const int sa = it % P.a_stages, use = it / P.a_stages;
-        if (use > 0) mbar_wait(a_empty + 8u * sa, (uint32_t)(use - 1) & 1u, failed, P.status, 0x10);
-        tc_fence_after();
-        const Tap* tp = s_taps + kb * kBlockK;
-        const uint32_t st_addr = lane_addr + (uint32_t)(sa * 64);
+    };
+    float v[kBlockK];
+    auto gather = [&](int kb) {
+      const MaskTap* tp = s_taps + kb * kBlockK;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          float v[16];
-#pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const Tap tap = tp[h * 16 + e];
-            const bool ok =
-                (unsigned)(iy0 + tap.dy) < (unsigned)P.in_lim && (unsigned)(ix0 + tap.dx) < (unsigned)P.in_lim;
-            v[e] = (ok && !DBG(P, 1)) ? __ldg(in_px + tap.off) : 0.f;
-          }
-          uint32_t hi[16], lo[16];
-#pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            float fh, fl;
-            split_tf32(v[e], fh, fl);
-            hi[e] = __float_as_uint(fh);
-            lo[e] = __float_as_uint(fl);
-          }
-          tmem_st16(st_addr + (uint32_t)(h * 16), hi);
-          tmem_st16(st_addr + 32u + (uint32_t)(h * 16), lo);
-        }
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(a_full + 8u * sa);
+      for (int e = 0; e < kBlockK; ++e) {
+        const MaskTap tap = tp[e];
+        v[e] = 0.f;
+        if ((mask & tap.bits) == tap.bits && !DBG(P, 1)) v[e] = __ldg(in_px + tap.off);
       }
+    };
+    int tile_local = 0, kb = group;
+    while (kb >= kblocks && tile_local < my_tiles) { kb -= kblocks; ++tile_local; }
+    if (group < my_stages) {
+      setup_tile(tile_local);
+      gather(kb);
+    }
+    for (int it = group; it < my_stages; it += 4) {
+      const int use = it >> 2;
+      if (use > 0) mbar_wait(empty_bar, (uint32_t)(use - 1) & 1u, failed, P.status, 0x10);
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < kBlockK / 8; ++c) {
+        uint32_t hi[8], lo[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) split_tf32_trunc(v[c * 8 + e], hi[e], lo[e]);
+        tmem_st8(st_addr + (uint32_t)(c * 8), hi);
+        tmem_st8(st_addr + 32u + (uint32_t)(c * 8), lo);
+      }
+      if (it + 4 < my_stages) {  // put the next k-block's loads in flight before waiting for the stores
+        const int before = tile_local;
+        kb += 4;
+        while (kb >= kblocks) { kb -= kblocks; ++tile_local; }
+        if (tile_local != before) setup_tile(tile_local);
+        gather(kb);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(full_bar);
     }
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issue
@@ -392,8 +433,8 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * P.n_pad);
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const int sa = it % P.a_stages, sb = it % P.b_stages;
-          mbar_wait(a_full + 8u * sa, (uint32_t)(it / P.a_stages) & 1u, failed, P.status, 0x40);
+          const int sa = it & 3, sb = it % P.b_stages;
+          mbar_wait(a_full + 8u * sa, (uint32_t)(it >> 2) & 1u, failed, P.status, 0x40);
           mbar_wait(b_full + 8u * sb, (uint32_t)(it / P.b_stages) & 1u, failed, P.status, 0x80);
           tc_fence_after();
           const uint32_t b_hi = base + (uint32_t)sb * L.b_stage_bytes, b_lo = b_hi + (uint32_t)P.n_pad * 128u;
@@ -720,7 +761,7 @@ int channel_tiles(int channels, int cols_per_channel) {
 struct GatherProblem {
   int tiles = 1, ch_tile = 0;  // channel tiles per group, channels per tile
   int n = 0, n_pad = 0, k_real = 0, k_pad = 0;
-  Tap* taps = nullptr;
+  MaskTap* taps = nullptr;
   ColEnt* cols = nullptr;
   float* w = nullptr;  // [2][vgroups][n_pad][k_pad]
   size_t w_half = 0;   // elements in one half
@@ -742,7 +783,7 @@ struct UmmaPlan {
 
 bool umma_supported(const ConvGeom& G) {
   if (channel_tiles(G.og, 1) == 0 || channel_tiles(G.Dg, G.s * G.s) == 0) return false;
-  if (G.k > 255 || G.n > 8000) return false;  // tap coordinates are 16-bit
+  if (G.k > kMaxTapsPerAxis || G.n > 8000) return false;  // tap rows / columns are bits of a 32-bit validity mask
   const int taps = (G.k + G.s - 1) / G.s;
   const long long kf = (long long)G.Dg * G.k * G.k, kd = (long long)G.og * taps * taps;
   if (kf > 16384 || kd > 16384) return false;  // the tap table lives in shared memory next to the weight stages
@@ -795,12 +836,12 @@ int pack_grid(cct_ctx* ctx, size_t total) {
 
 // Tensor-memory and shared-memory budget of a gather problem, packed-weight buffer and its tensor map.
 int finish_problem(cct_ctx* ctx, UmmaPlan* p, GatherProblem& gp, int vgroups) {
-  if (gp.n_pad <= 128) { gp.acc_bufs = 2; gp.a_stages = 4; }
-  else { gp.acc_bufs = 1; gp.a_stages = 4; }
-  const int fixed = gp.k_pad * 8 + gp.n_pad * 8 + 512 + 1024;
-  int bs = (kSmemLimit - fixed) / (2 * gp.n_pad * 128);
-  gp.b_stages = std::max(1, std::min(kMaxBStages, bs));
-  gp.smem = std::max<size_t>(gather_smem(gp.n_pad, gp.k_pad, gp.b_stages).total + 1024, 120 * 1024);  // > half an SM: one CTA per SM
+  gp.a_stages = 4;
+  gp.acc_bufs = gp.n_pad <= 128 ? 2 : 1;
+  // Weight stages: enough to cover the TMA latency, small enough to leave most of the SM's memory to the L1 cache
+  // that serves the gathers (704 threads x 80 registers already limit an SM to one CTA).
+  gp.b_stages = std::max(2, std::min(6, (96 * 1024) / (2 * gp.n_pad * 128)));
+  gp.smem = gather_smem(gp.n_pad, gp.k_pad, gp.b_stages).total + 1024;
   gp.w_half = (size_t)vgroups * gp.n_pad * gp.k_pad;
   int rc = dev_alloc(ctx, p, &gp.w, 2 * gp.w_half);
   if (rc != CCT_OK) return rc;
@@ -838,13 +879,13 @@ int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out) {
     f.n_pad = round_up(f.n, 16);
     f.k_real = G.Dg * kk;
     f.k_pad = round_up(f.k_real, kBlockK);
-    std::vector<Tap> t(f.k_pad);
+    std::vector<MaskTap> t(f.k_pad);
     for (int i = 0; i < f.k_pad; ++i) {
       if (i < f.k_real) {
         const int d = i / kk, kr = (i / G.k) % G.k, kc = i % G.k;
-        t[i] = Tap{d * G.n * G.n + kr * G.n + kc, (short)kr, (short)kc};
+        t[i] = MaskTap{d * G.n * G.n + kr * G.n + kc, (1u << kr) | (1u << (16 + kc))};
       } else {
-        t[i] = Tap{0, (short)kPadTap, (short)kPadTap};
+        t[i] = MaskTap{0, kPadBit};
       }
     }
     std::vector<ColEnt> c(f.n_pad);
@@ -868,13 +909,13 @@ int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out) {
     const int J = p->dgr_taps;
     d.k_real = G.og * J * J;
     d.k_pad = round_up(d.k_real, kBlockK);
-    std::vector<Tap> t(d.k_pad);
+    std::vector<MaskTap> t(d.k_pad);
     for (int i = 0; i < d.k_pad; ++i) {
       if (i < d.k_real) {
         const int jx = i % J, jy = (i / J) % J, oc = i / (J * J);
-        t[i] = Tap{oc * G.m * G.m - jy * G.m - jx, (short)-jy, (short)-jx};
+        t[i] = MaskTap{oc * G.m * G.m - jy * G.m - jx, (1u << jy) | (1u << (16 + jx))};
       } else {
-        t[i] = Tap{0, (short)kPadTap, (short)kPadTap};
+        t[i] = MaskTap{0, kPadBit};
       }
     }
     std::vector<ColEnt> c(d.n_pad);
@@ -966,6 +1007,7 @@ int umma_conv_forward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W,
   P.n_pix = G.B * G.m * G.m; P.q_h = G.m; P.q_w = G.m;
   P.iy_mul = G.s; P.iy_add = -G.p; P.ix_mul = G.s; P.ix_add = -G.p;
   P.in_lim = G.n;
+  P.tap_sign = 1; P.taps_per_axis = G.k;
   P.in_batch_stride = (long long)G.D * G.n * G.n;
   P.in_group_stride = G.Dg * G.n * G.n;
   P.oy_mul = 1; P.oy_add = 0; P.ox_mul = 1; P.ox_add = 0;
@@ -1030,6 +1072,7 @@ int umma_conv_backward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W
     P.n_pix = G.B * p->dgr_q * p->dgr_q; P.q_h = p->dgr_q; P.q_w = p->dgr_q;
     P.iy_mul = 1; P.iy_add = p->dgr_q0; P.ix_mul = 1; P.ix_add = p->dgr_q0;
     P.in_lim = G.m;
+    P.tap_sign = -1; P.taps_per_axis = p->dgr_taps;
     P.in_batch_stride = (long long)G.o * G.m * G.m;
     P.in_group_stride = G.og * G.m * G.m;
     P.oy_mul = G.s; P.oy_add = p->dgr_q0 * G.s - G.p; P.ox_mul = G.s; P.ox_add = p->dgr_q0 * G.s - G.p;
