@@ -31,30 +31,20 @@
 
 namespace {
 
-constexpr int kThreads = 256;
 constexpr int kTileM = 128;
 constexpr int kBlockK = 32;  // fp32 per k-block: one 128-byte swizzled row
-constexpr int kMaxStages = 4;
-constexpr int kATileBytes = kTileM * 128;
 constexpr int kSmemLimit = 227 * 1024;
 #ifdef CCT_DBG
 #define DBG(P, bit) ((P).dbg & (bit))
 #else
 #define DBG(P, bit) 0
 #endif
-constexpr int kPadTap = 0x4000;  // tap coordinate that fails every bounds test (weight-gradient table)
 constexpr int kMaxTapsPerAxis = 15;
 constexpr uint32_t kPadBit = 0x80000000u;  // never set in a pixel's validity mask: marks padding entries
 
-// One entry per reduction index of a gathered operand (weight-gradient kernel): element offset from the pixel's tap
-// origin and the tap's (dy, dx) for the bounds test.
-struct Tap {
-  int off;
-  short dy, dx;
-};
-
-// Gather-kernel form: the tap is in bounds for a pixel iff (pixel_mask & bits) == bits, where bit i (rows) and bit
-// 16+j (columns) of the pixel's mask say whether tap row i / tap column j falls inside the gathered plane.
+// One entry per reduction index of a gathered operand: element offset from the pixel's tap origin, and the tap's
+// row / column as mask bits.  The tap is in bounds for a pixel iff (pixel_mask & bits) == bits, where bit i (rows) and
+// bit 16+j (columns) of the pixel's mask say whether tap row i / tap column j falls inside the gathered plane.
 struct MaskTap {
   int off;
   uint32_t bits;
@@ -116,18 +106,6 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
 
-// D[tmem] (+)= A[smem] * B[smem]^T, both operands K-major, tf32 inputs, fp32 accumulate.
-__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-      :
-      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
 // The mbarrier receives one arrival when every MMA issued so far by this thread has finished.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -170,56 +148,6 @@ __device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
 __device__ __forceinline__ void split_tf32_trunc(float x, uint32_t& hi, uint32_t& lo) {
   hi = __float_as_uint(x) & 0xFFFFE000u;
   lo = __float_as_uint(x - __uint_as_float(hi));
-}
-
-__device__ __forceinline__ void st_shared_v4(uint32_t addr, float a, float b, float c, float d) {
-  asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
-
-__device__ __forceinline__ void store_split4(uint32_t hi_addr, uint32_t lo_addr, const float* v) {
-  float h[4], l[4];
-#pragma unroll
-  for (int e = 0; e < 4; ++e) split_tf32(v[e], h[e], l[e]);
-  st_shared_v4(hi_addr, h[0], h[1], h[2], h[3]);
-  st_shared_v4(lo_addr, l[0], l[1], l[2], l[3]);
-}
-
-// The 12 MMAs of one stage: for each of the 4 k-steps (8 tf32 = 32 bytes), lo*hi, hi*lo, hi*hi.
-__device__ __forceinline__ void issue_stage(uint32_t tmem_d, uint32_t a_hi, uint32_t a_lo, uint32_t b_hi, uint32_t b_lo,
-                                            uint32_t idesc, bool first_stage) {
-  const uint64_t dah = make_desc(a_hi), dal = make_desc(a_lo), dbh = make_desc(b_hi), dbl = make_desc(b_lo);
-#pragma unroll
-  for (int j = 0; j < kBlockK / 8; ++j) {
-    const uint64_t adv = (uint64_t)(j * 2);  // 32 bytes >> 4
-    umma_tf32(tmem_d, dal + adv, dbh + adv, idesc, (first_stage && j == 0) ? 0u : 1u);
-    umma_tf32(tmem_d, dah + adv, dbl + adv, idesc, 1u);
-    umma_tf32(tmem_d, dah + adv, dbh + adv, idesc, 1u);
-  }
-}
-
-struct SmemLayout {
-  uint32_t stage_bytes, b_tile_bytes;
-  int stages;
-};
-
-__host__ __device__ inline SmemLayout smem_layout(int n_pad) {
-  SmemLayout L;
-  L.b_tile_bytes = (uint32_t)n_pad * 128u;
-  L.stage_bytes = 2u * kATileBytes + 2u * L.b_tile_bytes;
-  int s = (kSmemLimit - 2048) / (int)L.stage_bytes;
-  L.stages = s > kMaxStages ? kMaxStages : s;
-  return L;
-}
-
-inline size_t smem_bytes(int n_pad) {
-  const SmemLayout L = smem_layout(n_pad);
-  return (size_t)L.stages * L.stage_bytes + 1024 /*alignment slack*/ + 256 /*barriers, tmem slot*/;
-}
-
-__host__ __device__ inline uint32_t tmem_cols(int n_pad) {
-  uint32_t c = 32;
-  while ((int)c < n_pad) c <<= 1;
-  return c;
 }
 
 // ------------------------------------------------------------------------------ gather kernel (forward, dgrad)
@@ -530,143 +458,246 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
 }
 
 // ---------------------------------------------------------------------------------- weight-gradient kernel
+//
+// dW[kk][o] (+ the bias row) = sum over pixels of Lowered(X)[pix][kk] * dY[pix][o], split over pixel ranges.
+// One CTA owns up to `subs` M-tiles of 128 lowered-matrix columns kk (accumulators side by side in tensor memory) and
+// a range of 32-pixel k-blocks.
+//   warps 0-15  A producers, four sets of four: thread = one row kk of an M-tile = one TMEM lane.  Per (k-block,
+//               M-tile) a thread gathers the 32 pixels of its tap from X, splits hi/lo, tcgen05.st into an A slot.
+//               The per-pixel address and validity mask come from a small table the B producers publish.
+//   warps 16-19 B producers: lane = one pixel of the k-block.  They decompose the pixel index once, publish the
+//               table, and copy the dY tile (rows = output channels, 32 pixels = one 128-byte swizzled row) into
+//               shared memory as hi/lo.  The same dY tile serves all `subs` M-tiles.
+//   warp 20     one thread issues the MMAs (A from tensor memory, B from shared memory).
+// The finished accumulators are written to the split's slice of the scratch buffer by warps 0-15.
+constexpr int kWgAWarps = 16, kWgBWarp0 = 16, kWgBWarps = 4, kWgMmaWarp = 20;
+constexpr int kWgThreads = (kWgMmaWarp + 1) * 32;  // 672
+constexpr int kWgMaxSlots = 4, kWgMaxBStages = 4, kWgMaxSubs = 4;
+constexpr uint32_t kWgValidBit = 0x80000000u;  // set in a pixel's mask when the pixel exists
+constexpr uint32_t kWgPadBit = 0x00008000u;    // never set in a pixel's mask: rows beyond the lowered matrix
+constexpr uint32_t kWgOnesBits = kWgValidBit;  // the all-ones row: in bounds wherever the pixel exists
+
+struct PixInfo {
+  int xbase;      // offset of the pixel's tap origin inside the group's slice of X
+  uint32_t mask;  // valid bit | tap-column bits << 16 | tap-row bits
+};
+
 struct WgradParams {
   const float* x;
   const float* dy;
-  float* partial;   // [splits][vgroups][m_tiles*128][n_pad]
-  const Tap* taps;  // [m_tiles*128]; row k_real is the all-ones row (dy == kOnesTap)
-  int n_pix, m, mm, n, s, p;
+  float* partial;       // [splits][vgroups][m_tiles*128][n_pad]
+  const MaskTap* taps;  // [m_tiles*128]; row k_real is the all-ones row, rows beyond it are padding
+  int n_pix, m, mm, n, s, p, k;
   long long x_batch_stride;
   int x_group_stride;
   long long dy_batch_stride;
   int dy_group_channels;  // output channels per real group
   int tiles_per_group;
   int n_real, n_pad;
+  int m_tiles, subs, slots, b_stages;
   int kblocks_total, kblocks_per_split;
   int* status;
   int dbg;
 };
-constexpr int kOnesTap = 0x2000;
 
-__global__ void __launch_bounds__(kThreads, 1) wgrad_kernel(const __grid_constant__ WgradParams P) {
+struct WgSmem {
+  uint32_t b_stage_bytes, pix_off, bars_off, total;
+};
+__host__ __device__ inline WgSmem wg_smem(int n_pad, int b_stages) {
+  WgSmem L;
+  L.b_stage_bytes = 2u * (uint32_t)n_pad * 128u;
+  L.pix_off = (uint32_t)b_stages * L.b_stage_bytes;
+  L.bars_off = L.pix_off + (uint32_t)b_stages * 32u * 8u;
+  L.total = L.bars_off + 8u * (2 * kWgMaxSlots + 3 * kWgMaxBStages + 1) + 16u;
+  return L;
+}
+
+__global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_constant__ WgradParams P) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const SmemLayout L = smem_layout(P.n_pad);
-  const uint32_t bar0 = base + (uint32_t)L.stages * L.stage_bytes;
-  const uint32_t tmem_slot = bar0 + 8u * kMaxStages;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const WgSmem L = wg_smem(P.n_pad, P.b_stages);
+  const uint32_t bars = base + L.bars_off;
+  const uint32_t a_full = bars, a_empty = a_full + 8u * kWgMaxSlots, b_full = a_empty + 8u * kWgMaxSlots,
+                 b_empty = b_full + 8u * kWgMaxBStages, pix_full = b_empty + 8u * kWgMaxBStages,
+                 acc_full = pix_full + 8u * kWgMaxBStages, tmem_slot = acc_full + 8u;
+  PixInfo* s_pix = reinterpret_cast<PixInfo*>(base_ptr + L.pix_off);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int mtile = blockIdx.x, split = blockIdx.y, vg = blockIdx.z;
+  const int mgroup = blockIdx.x, split = blockIdx.y, vg = blockIdx.z;
   const int grp = vg / P.tiles_per_group, ntile = vg % P.tiles_per_group;
-  const uint32_t ncols = tmem_cols(P.n_pad);
+  const int subs = min(P.subs, P.m_tiles - mgroup * P.subs);  // M-tiles this CTA really has
 
   if (tid == 0) {
-    for (int s = 0; s < L.stages; ++s) mbar_init(bar0 + 8u * s, 1);
+    for (int s = 0; s < kWgMaxSlots; ++s) { mbar_init(a_full + 8u * s, 128); mbar_init(a_empty + 8u * s, 1); }
+    for (int s = 0; s < kWgMaxBStages; ++s) {
+      mbar_init(b_full + 8u * s, kWgBWarps * 32);
+      mbar_init(b_empty + 8u * s, 1);
+      mbar_init(pix_full + 8u * s, 32);
+    }
+    mbar_init(acc_full, 1);
     fence_mbar_init();
   }
-  if (warp == 0) tmem_alloc(tmem_slot, ncols);
+  if (warp == 0) tmem_alloc(tmem_slot, 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  uint32_t tmem_d;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_d) : "r"(tmem_slot));
-
-  // Thread (q, r0): 4 consecutive pixels (chunk q of the 32-pixel block) for rows r0, r0+32, r0+64, r0+96.
-  const int q = tid & 7, r0 = tid >> 3;
-  Tap tap[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) tap[i] = P.taps[mtile * kTileM + r0 + 32 * i];
-  const float* xg = P.x + (long long)grp * P.x_group_stride;
-  const float* dyg = P.dy + (long long)(grp * P.dy_group_channels + ntile * P.n_real) * P.mm;
-  const uint32_t idesc = make_idesc(P.n_pad);
+  uint32_t tmem_base;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+  const uint32_t a_col0 = (uint32_t)(P.subs * P.n_pad);
   const int kb_begin = split * P.kblocks_per_split;
   const int kb_end = min(P.kblocks_total, kb_begin + P.kblocks_per_split);
   const int kblocks = kb_end - kb_begin;  // >= 1 by construction of the grid
+  const int total_it = kblocks * subs;    // (k-block, M-tile) pairs, M-tile fastest
   bool failed = false;
 
-  for (int it = 0; it < kblocks; ++it) {
-    const int s = it % L.stages, use = it / L.stages;
-    const uint32_t st = base + (uint32_t)s * L.stage_bytes;
-    const uint32_t a_hi = st, a_lo = st + kATileBytes, b_hi = st + 2 * kATileBytes, b_lo = b_hi + L.b_tile_bytes;
-    if (use > 0) mbar_wait(bar0 + 8u * s, (uint32_t)(use - 1) & 1u, failed, P.status, 0x4);
-
-    // Decompose this thread's 4 pixels.
-    long long xoff[4], dyoff[4];
-    int iy0[4], ix0[4];
-    bool ok[4];
-    {
-      int pix = (kb_begin + it) * kBlockK + q * 4;
-      int b = pix / P.mm;
-      int pin = pix - b * P.mm;
-      int r = pin / P.m;
-      int c = pin - r * P.m;
+  if (warp < kWgAWarps) {
+    // ------------------------------------------------------------------ A producers
+    const int group = warp >> 2, quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + a_col0;
+    MaskTap tap[kWgMaxSubs];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        ok[e] = pix + e < P.n_pix;
-        iy0[e] = r * P.s - P.p;
-        ix0[e] = c * P.s - P.p;
-        xoff[e] = (long long)b * P.x_batch_stride + (long long)iy0[e] * P.n + ix0[e];
-        dyoff[e] = (long long)b * P.dy_batch_stride + r * P.m + c;
-        if (++c == P.m) {
-          c = 0;
-          if (++r == P.m) { r = 0; ++b; }
-        }
+    for (int u = 0; u < kWgMaxSubs; ++u)
+      tap[u] = u < subs ? P.taps[(mgroup * P.subs + u) * kTileM + row] : MaskTap{0, kWgPadBit};
+    const float* xg = P.x + (long long)grp * P.x_group_stride;
+    float v[kBlockK];
+    auto gather = [&](int it) {
+      const int kbl = it / subs, u = it - kbl * subs;
+      const int sb = kbl % P.b_stages;
+      mbar_wait(pix_full + 8u * sb, (uint32_t)(kbl / P.b_stages) & 1u, failed, P.status, 0x1000);
+      MaskTap mine = tap[0];
+#pragma unroll
+      for (int q = 1; q < kWgMaxSubs; ++q)
+        if (u == q) mine = tap[q];
+      const PixInfo* pi = s_pix + sb * 32;
+      const bool ones = mine.bits == kWgOnesBits;
+#pragma unroll
+      for (int j = 0; j < kBlockK; ++j) {
+        const PixInfo px = pi[j];
+        const bool ok = (px.mask & mine.bits) == mine.bits;
+        v[j] = (ok && ones) ? 1.f : 0.f;
+        if (ok && !ones && !DBG(P, 1)) v[j] = __ldg(xg + px.xbase + mine.off);
       }
-    }
-    // A: rows = reduction indices of the lowered input (kk), columns = pixels.
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float v[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        if (tap[i].dy == kOnesTap) {
-          v[e] = ok[e] ? 1.f : 0.f;
-        } else {
-          const bool in = ok[e] && (unsigned)(iy0[e] + tap[i].dy) < (unsigned)P.n &&
-                          (unsigned)(ix0[e] + tap[i].dx) < (unsigned)P.n;
-          v[e] = (in && !DBG(P, 1)) ? __ldg(xg + xoff[e] + tap[i].off) : 0.f;
-        }
-      }
-      const uint32_t o = swz(r0 + 32 * i, q);
-      if (!DBG(P, 8)) store_split4(a_hi + o, a_lo + o, v);
-    }
-    // B: rows = output channels, columns = the same pixels.
-    for (int j = r0; j < P.n_pad && !DBG(P, 2); j += 32) {
-      float v[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) v[e] = (ok[e] && j < P.n_real) ? __ldg(dyg + dyoff[e] + (long long)j * P.mm) : 0.f;
-      const uint32_t o = swz(j, q);
-      store_split4(b_hi + o, b_lo + o, v);
-    }
-    if (!DBG(P, 16)) fence_proxy_async_smem();
-    __syncthreads();
-    if (tid == 0) {
+    };
+    if (group < total_it) gather(group);
+    for (int it = group; it < total_it; it += 4) {
+      const int slot = it % P.slots, use = it / P.slots;
+      if (use > 0) mbar_wait(a_empty + 8u * slot, (uint32_t)(use - 1) & 1u, failed, P.status, 0x10);
       tc_fence_after();
-      if (!DBG(P, 4)) issue_stage(tmem_d, a_hi, a_lo, b_hi, b_lo, idesc, it == 0);
-      umma_commit(bar0 + 8u * s);
-    }
-  }
-  {
-    const int last = kblocks - 1;
-    mbar_wait(bar0 + 8u * (last % L.stages), (uint32_t)(last / L.stages) & 1u, failed, P.status, 0x8);
-  }
-  tc_fence_after();
-
-  {
-    const int erow = (warp & 3) * 32 + lane;
-    float* op = P.partial +
-                (((size_t)split * gridDim.z + vg) * gridDim.x * kTileM + (size_t)mtile * kTileM + erow) * P.n_pad;
-    const int chunks = P.n_pad / 16;
-    for (int c = warp >> 2; c < chunks; c += 2) {
-      float v[16];
-      tmem_ld16(tmem_d + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(c * 16), v);
-      float4* o4 = reinterpret_cast<float4*>(op + c * 16);
+      const uint32_t st_addr = lane_addr + (uint32_t)(slot * 64);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) o4[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+      for (int c = 0; c < kBlockK / 8; ++c) {
+        uint32_t hi[8], lo[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) split_tf32_trunc(v[c * 8 + e], hi[e], lo[e]);
+        tmem_st8(st_addr + (uint32_t)(c * 8), hi);
+        tmem_st8(st_addr + 32u + (uint32_t)(c * 8), lo);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(a_full + 8u * slot);
+      // Only now: the pixel table of a later k-block is published after earlier MMAs retire, and those wait for the
+      // arrival above.
+      if (it + 4 < total_it) gather(it + 4);
+    }
+    // ---- epilogue: accumulator u, columns in chunks of 16; set g takes the (u, chunk) pairs with index == g mod 4
+    mbar_wait(acc_full, 0u, failed, P.status, 0x2000);
+    tc_fence_after();
+    const int chunks = P.n_pad / 16;
+    for (int w = group; w < subs * chunks; w += 4) {
+      const int u = w / chunks, c = w - u * chunks;
+      float acc[16];
+      tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(u * P.n_pad + c * 16), acc);
+      float* op = P.partial + (((size_t)split * gridDim.z + vg) * P.m_tiles * kTileM +
+                               (size_t)(mgroup * P.subs + u) * kTileM + row) * P.n_pad + c * 16;
+      if (!failed) {
+        float4* o4 = reinterpret_cast<float4*>(op);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o4[j] = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+      }
+    }
+  } else if (warp < kWgMmaWarp) {
+    // ------------------------------------------------------------------ B producers (lane = pixel of the k-block)
+    const int bw = warp - kWgBWarp0;
+    const float* dyg = P.dy + (long long)(grp * P.dy_group_channels + ntile * P.n_real) * P.mm;
+    for (int kbl = 0; kbl < kblocks; ++kbl) {
+      const int sb = kbl % P.b_stages, use = kbl / P.b_stages;
+      const int pix = (kb_begin + kbl) * kBlockK + lane;
+      const bool ok = pix < P.n_pix;
+      const int b = pix / P.mm;
+      const int pin = pix - b * P.mm;
+      const int r = pin / P.m;
+      const int c = pin - r * P.m;
+      if (use > 0) mbar_wait(b_empty + 8u * sb, (uint32_t)(use - 1) & 1u, failed, P.status, 0x100);
+      if (bw == 0) {
+        PixInfo pi;
+        const int iy0 = r * P.s - P.p, ix0 = c * P.s - P.p;
+        pi.xbase = ok ? (int)((long long)b * P.x_batch_stride + (long long)iy0 * P.n + ix0) : 0;
+        pi.mask = ok ? (kWgValidBit | bit_range(-iy0, min(P.k, P.n - iy0)) |
+                        (bit_range(-ix0, min(P.k, P.n - ix0)) << 16))
+                     : 0u;
+        s_pix[sb * 32 + lane] = pi;
+        mbar_arrive(pix_full + 8u * sb);
+      }
+      const float* src = dyg + (long long)b * P.dy_batch_stride + pin;
+      const uint32_t b_hi = base + (uint32_t)sb * L.b_stage_bytes, b_lo = b_hi + (uint32_t)P.n_pad * 128u;
+      for (int o0 = bw; o0 < P.n_pad; o0 += kWgBWarps * 4) {
+        float val[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int o = o0 + i * kWgBWarps;
+          val[i] = (ok && o < P.n_real && !DBG(P, 2)) ? __ldg(src + (long long)o * P.mm) : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int o = o0 + i * kWgBWarps;
+          if (o < P.n_pad) {
+            uint32_t h, l;
+            split_tf32_trunc(val[i], h, l);
+            const uint32_t off = swz(o, lane >> 2) + (uint32_t)((lane & 3) * 4);
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(b_hi + off), "r"(h) : "memory");
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(b_lo + off), "r"(l) : "memory");
+          }
+        }
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(b_full + 8u * sb);
+    }
+  } else {
+    // ------------------------------------------------------------------ MMA issue
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(P.n_pad);
+      int it = 0;
+      for (int kbl = 0; kbl < kblocks; ++kbl) {
+        const int sb = kbl % P.b_stages;
+        mbar_wait(b_full + 8u * sb, (uint32_t)(kbl / P.b_stages) & 1u, failed, P.status, 0x80);
+        const uint32_t b_hi = base + (uint32_t)sb * L.b_stage_bytes, b_lo = b_hi + (uint32_t)P.n_pad * 128u;
+        const uint64_t dbh = make_desc(b_hi), dbl = make_desc(b_lo);
+        for (int u = 0; u < subs; ++u, ++it) {
+          const int slot = it % P.slots;
+          mbar_wait(a_full + 8u * slot, (uint32_t)(it / P.slots) & 1u, failed, P.status, 0x40);
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + (uint32_t)(u * P.n_pad);
+          const uint32_t a_hi = tmem_base + a_col0 + (uint32_t)(slot * 64), a_lo = a_hi + 32u;
+          if (!DBG(P, 4)) {
+#pragma unroll
+            for (int j = 0; j < kBlockK / 8; ++j) {
+              const uint64_t adv = (uint64_t)(j * 2);
+              umma_tf32_ts(d_tmem, a_lo + (uint32_t)(j * 8), dbh + adv, idesc, (kbl == 0 && j == 0) ? 0u : 1u);
+              umma_tf32_ts(d_tmem, a_hi + (uint32_t)(j * 8), dbl + adv, idesc, 1u);
+              umma_tf32_ts(d_tmem, a_hi + (uint32_t)(j * 8), dbh + adv, idesc, 1u);
+            }
+          }
+          umma_commit(a_empty + 8u * slot);
+        }
+        umma_commit(b_empty + 8u * sb);
+      }
+      umma_commit(acc_full);
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem_d, ncols);
+  if (warp == 0) tmem_dealloc(tmem_base, 512);
 }
 
 // dW[o][kk] and db[o] from the split partial sums, added in split order (deterministic).
@@ -775,8 +806,9 @@ struct UmmaPlan {
   GatherProblem fwd, dgr;
   int dgr_taps = 0, dgr_q = 0, dgr_q0 = 0;  // taps per axis; super-pixels per axis and the first one that holds a pixel
   // weight gradient
-  int w_mtiles, w_splits, w_kblocks_total, w_kblocks_per_split, w_npad;
-  Tap* w_taps = nullptr;
+  int w_mtiles, w_subs, w_slots, w_bstages, w_mgroups, w_splits, w_kblocks_total, w_kblocks_per_split, w_npad;
+  size_t w_smem = 0;
+  MaskTap* w_taps = nullptr;
   float* w_partial = nullptr;
   size_t bytes = 0;
 };
@@ -932,21 +964,30 @@ int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out) {
     const GatherProblem& f = p->fwd;
     p->w_npad = f.n_pad;
     p->w_mtiles = (f.k_real + 1 + kTileM - 1) / kTileM;
-    std::vector<Tap> t((size_t)p->w_mtiles * kTileM);
+    std::vector<MaskTap> t((size_t)p->w_mtiles * kTileM);
     for (size_t i = 0; i < t.size(); ++i) {
       if ((int)i < f.k_real) {
         const int d = (int)i / kk, kr = ((int)i / G.k) % G.k, kc = (int)i % G.k;
-        t[i] = Tap{d * G.n * G.n + kr * G.n + kc, (short)kr, (short)kc};
+        t[i] = MaskTap{d * G.n * G.n + kr * G.n + kc, kWgValidBit | (1u << kr) | (1u << (16 + kc))};
       } else if ((int)i == f.k_real) {
-        t[i] = Tap{0, (short)kOnesTap, 0};
+        t[i] = MaskTap{0, kWgOnesBits};
       } else {
-        t[i] = Tap{0, (short)kPadTap, (short)kPadTap};
+        t[i] = MaskTap{0, kWgPadBit};
       }
     }
     rc = upload(ctx, p, &p->w_taps, t);
+    // M-tiles per CTA: as many accumulators as tensor memory holds next to at least 3 A slots of 64 columns
+    int subs = 1;
+    for (int u = 2; u <= kWgMaxSubs; ++u)
+      if (u <= p->w_mtiles && u * f.n_pad + 3 * 64 <= 512) subs = u;
+    p->w_subs = subs;
+    p->w_slots = std::min(kWgMaxSlots, (512 - subs * f.n_pad) / 64);
+    p->w_mgroups = (p->w_mtiles + subs - 1) / subs;
+    p->w_bstages = std::max(2, std::min(kWgMaxBStages, (128 * 1024) / (2 * f.n_pad * 128)));
+    p->w_smem = wg_smem(f.n_pad, p->w_bstages).total + 1024;
     const int n_pix = G.B * G.m * G.m;
     p->w_kblocks_total = (n_pix + kBlockK - 1) / kBlockK;
-    const int out_tiles = p->w_mtiles * G.g * f.tiles;
+    const int out_tiles = p->w_mgroups * G.g * f.tiles;
     int splits = std::max(1, ctx->sm_count / out_tiles);
     splits = std::min(splits, std::max(1, p->w_kblocks_total / 8));  // at least 8 k-blocks per CTA
     p->w_kblocks_per_split = (p->w_kblocks_total + splits - 1) / splits;
@@ -1034,20 +1075,21 @@ int umma_conv_backward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W
     const GatherProblem& f = p->fwd;
     WgradParams P{};
     P.x = X; P.dy = dY; P.partial = p->w_partial; P.taps = p->w_taps;
-    P.n_pix = G.B * G.m * G.m; P.m = G.m; P.mm = G.m * G.m; P.n = G.n; P.s = G.s; P.p = G.p;
+    P.n_pix = G.B * G.m * G.m; P.m = G.m; P.mm = G.m * G.m; P.n = G.n; P.s = G.s; P.p = G.p; P.k = G.k;
     P.x_batch_stride = (long long)G.D * G.n * G.n;
     P.x_group_stride = G.Dg * G.n * G.n;
     P.dy_batch_stride = (long long)G.o * G.m * G.m;
     P.dy_group_channels = G.og;
     P.tiles_per_group = f.tiles;
     P.n_real = f.n; P.n_pad = f.n_pad;
+    P.m_tiles = p->w_mtiles; P.subs = p->w_subs; P.slots = p->w_slots; P.b_stages = p->w_bstages;
     P.kblocks_total = p->w_kblocks_total; P.kblocks_per_split = p->w_kblocks_per_split;
     P.status = ctx->status_dev;
     P.dbg = dbg_knobs();
     const int vgroups = G.g * f.tiles;
-    dim3 grid(p->w_mtiles, p->w_splits, vgroups);
+    dim3 grid(p->w_mgroups, p->w_splits, vgroups);
     t->begin(1, ctx->stream);
-    wgrad_kernel<<<grid, kThreads, smem_bytes(P.n_pad), ctx->stream>>>(P);
+    wgrad_kernel<<<grid, kWgThreads, p->w_smem, ctx->stream>>>(P);
     t->end(1, ctx->stream);
     CCT_CHECK_LAUNCH(ctx);
     t->begin(2, ctx->stream);
