@@ -135,8 +135,6 @@ __host__ __device__ constexpr uint32_t make_idesc(int n) {
   return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
 }
 
-// Byte offset of 16-byte chunk q (0..7) of row r inside a swizzled tile.
-__device__ __forceinline__ uint32_t swz(int r, int q) { return (uint32_t)(r * 128 + ((q ^ (r & 7)) << 4)); }
 
 // hi = x rounded to tf32 (10 explicit mantissa bits), lo = x - hi (exact in fp32).
 __device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
@@ -460,27 +458,23 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
 // ---------------------------------------------------------------------------------- weight-gradient kernel
 //
 // dW[kk][o] (+ the bias row) = sum over pixels of Lowered(X)[pix][kk] * dY[pix][o], split over pixel ranges.
-// One CTA owns up to `subs` M-tiles of 128 lowered-matrix columns kk (accumulators side by side in tensor memory) and
-// a range of 32-pixel k-blocks.
-//   warps 0-15  A producers, four sets of four: thread = one row kk of an M-tile = one TMEM lane.  Per (k-block,
-//               M-tile) a thread gathers the 32 pixels of its tap from X, splits hi/lo, tcgen05.st into an A slot.
-//               The per-pixel address and validity mask come from a small table the B producers publish.
-//   warps 16-19 B producers: lane = one pixel of the k-block.  They decompose the pixel index once, publish the
-//               table, and copy the dY tile (rows = output channels, 32 pixels = one 128-byte swizzled row) into
-//               shared memory as hi/lo.  The same dY tile serves all `subs` M-tiles.
-//   warp 20     one thread issues the MMAs (A from tensor memory, B from shared memory).
+// Both operands are K-major shared-memory tiles whose rows are 32 consecutive pixels (one 128-byte swizzled row):
+// a row of the lowered operand is one tap (d, kr, kc) seen by 32 consecutive output pixels, a row of the other
+// operand is one output channel of dY for the same pixels.  With lane = pixel every global load is a coalesced run
+// and every shared-memory store fills one row, conflict free.
+// One CTA owns up to `subs` M-tiles of 128 taps (accumulators side by side in tensor memory), one channel tile of dY
+// and a range of 32-pixel k-blocks; the dY tile of a k-block is staged once for all its M-tiles.
+//   warps 0-15  producers: warp w stages rows w, w+16, ... of the stage (tap rows first, then channel rows): load,
+//               split hi/lo, two st.shared per row; the loads of the next k-block are issued before the warp waits
+//               for the stage buffer to drain.
+//   warp 16     one thread issues the MMAs (both operands from shared memory).
 // The finished accumulators are written to the split's slice of the scratch buffer by warps 0-15.
-constexpr int kWgAWarps = 16, kWgBWarp0 = 16, kWgBWarps = 4, kWgMmaWarp = 20;
-constexpr int kWgThreads = (kWgMmaWarp + 1) * 32;  // 672
-constexpr int kWgMaxSlots = 4, kWgMaxBStages = 4, kWgMaxSubs = 4;
-constexpr uint32_t kWgValidBit = 0x80000000u;  // set in a pixel's mask when the pixel exists
-constexpr uint32_t kWgPadBit = 0x00008000u;    // never set in a pixel's mask: rows beyond the lowered matrix
-constexpr uint32_t kWgOnesBits = kWgValidBit;  // the all-ones row: in bounds wherever the pixel exists
-
-struct PixInfo {
-  int xbase;      // offset of the pixel's tap origin inside the group's slice of X
-  uint32_t mask;  // valid bit | tap-column bits << 16 | tap-row bits
-};
+constexpr int kWgProdWarps = 16, kWgMmaWarp = 16;
+constexpr int kWgThreads = (kWgMmaWarp + 1) * 32;  // 544
+constexpr int kWgMaxStages = 4, kWgMaxSubs = 2;
+constexpr uint32_t kWgValidBit = 0x80000000u;      // set in a pixel's mask when the pixel exists
+constexpr uint32_t kWgPadBit = 0x00008000u;        // never set in a pixel's mask: rows beyond the lowered matrix
+constexpr uint32_t kWgOnesBits = kWgValidBit;      // the all-ones row: in bounds wherever the pixel exists
 
 struct WgradParams {
   const float* x;
@@ -494,46 +488,65 @@ struct WgradParams {
   int dy_group_channels;  // output channels per real group
   int tiles_per_group;
   int n_real, n_pad;
-  int m_tiles, subs, slots, b_stages;
+  int m_tiles, subs, stages;
+  int ones_row;           // index of the all-ones row among the lowered-matrix rows
   int kblocks_total, kblocks_per_split;
   int* status;
   int dbg;
 };
 
 struct WgSmem {
-  uint32_t b_stage_bytes, pix_off, bars_off, total;
+  uint32_t a_tile_bytes, b_tile_bytes, stage_bytes, taps_off, bars_off, total;
 };
-__host__ __device__ inline WgSmem wg_smem(int n_pad, int b_stages) {
+__host__ __device__ inline WgSmem wg_smem(int n_pad, int subs, int stages) {
   WgSmem L;
-  L.b_stage_bytes = 2u * (uint32_t)n_pad * 128u;
-  L.pix_off = (uint32_t)b_stages * L.b_stage_bytes;
-  L.bars_off = L.pix_off + (uint32_t)b_stages * 32u * 8u;
-  L.total = L.bars_off + 8u * (2 * kWgMaxSlots + 3 * kWgMaxBStages + 1) + 16u;
+  L.a_tile_bytes = kTileM * 128u;           // one of hi / lo of one M-tile
+  L.b_tile_bytes = (uint32_t)n_pad * 128u;  // one of hi / lo of the dY tile
+  L.stage_bytes = 2u * (uint32_t)subs * L.a_tile_bytes + 2u * L.b_tile_bytes;
+  L.taps_off = (uint32_t)stages * L.stage_bytes;
+  L.bars_off = L.taps_off + (uint32_t)subs * kTileM * 8u;
+  L.total = L.bars_off + 8u * (2 * kWgMaxStages + 1) + 16u;
   return L;
 }
 
+// D[tmem] (+)= A[smem] * B[smem]^T, both operands K-major, tf32 inputs, fp32 accumulate.
+__device__ __forceinline__ void umma_tf32_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// SUBS: M-tiles per CTA (accumulators), NB: dY-tile rows per producer warp (= n_pad / 16).  With both fixed at
+// compile time every warp stages exactly 8*SUBS tap rows and NB channel rows per k-block, all loads of a k-block are
+// in flight together, and the shared-memory addresses are one per-warp base plus immediates: row warp+16*i of a
+// 128-byte-swizzled tile has the same swizzle phase ((warp+16*i) & 7 == warp & 7) for every i.
+template <int SUBS, int NB>
 __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_constant__ WgradParams P) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  const WgSmem L = wg_smem(P.n_pad, P.b_stages);
+  const WgSmem L = wg_smem(NB * 16, SUBS, P.stages);
   const uint32_t bars = base + L.bars_off;
-  const uint32_t a_full = bars, a_empty = a_full + 8u * kWgMaxSlots, b_full = a_empty + 8u * kWgMaxSlots,
-                 b_empty = b_full + 8u * kWgMaxBStages, pix_full = b_empty + 8u * kWgMaxBStages,
-                 acc_full = pix_full + 8u * kWgMaxBStages, tmem_slot = acc_full + 8u;
-  PixInfo* s_pix = reinterpret_cast<PixInfo*>(base_ptr + L.pix_off);
+  const uint32_t full = bars, empty = full + 8u * kWgMaxStages, acc_full = empty + 8u * kWgMaxStages,
+                 tmem_slot = acc_full + 8u;
+  MaskTap* s_taps = reinterpret_cast<MaskTap*>(base_ptr + L.taps_off);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int mgroup = blockIdx.x, split = blockIdx.y, vg = blockIdx.z;
   const int grp = vg / P.tiles_per_group, ntile = vg % P.tiles_per_group;
-  const int subs = min(P.subs, P.m_tiles - mgroup * P.subs);  // M-tiles this CTA really has
+  const int subs = min(SUBS, P.m_tiles - mgroup * SUBS);  // M-tiles this CTA really has
+  constexpr int kARows = 8 * SUBS;                        // tap rows per producer warp and k-block
+  constexpr uint32_t kATile = kTileM * 128u, kBTile = NB * 16u * 128u;
+  constexpr int kNPad = NB * 16;
 
+  for (int i = tid; i < SUBS * kTileM; i += kWgThreads)
+    s_taps[i] = i < subs * kTileM ? P.taps[mgroup * SUBS * kTileM + i] : MaskTap{0, kWgPadBit};
   if (tid == 0) {
-    for (int s = 0; s < kWgMaxSlots; ++s) { mbar_init(a_full + 8u * s, 128); mbar_init(a_empty + 8u * s, 1); }
-    for (int s = 0; s < kWgMaxBStages; ++s) {
-      mbar_init(b_full + 8u * s, kWgBWarps * 32);
-      mbar_init(b_empty + 8u * s, 1);
-      mbar_init(pix_full + 8u * s, 32);
-    }
+    for (int s = 0; s < kWgMaxStages; ++s) { mbar_init(full + 8u * s, kWgProdWarps * 32); mbar_init(empty + 8u * s, 1); }
     mbar_init(acc_full, 1);
     fence_mbar_init();
   }
@@ -543,154 +556,135 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
   tc_fence_after();
   uint32_t tmem_base;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
-  const uint32_t a_col0 = (uint32_t)(P.subs * P.n_pad);
   const int kb_begin = split * P.kblocks_per_split;
   const int kb_end = min(P.kblocks_total, kb_begin + P.kblocks_per_split);
   const int kblocks = kb_end - kb_begin;  // >= 1 by construction of the grid
-  const int total_it = kblocks * subs;    // (k-block, M-tile) pairs, M-tile fastest
   bool failed = false;
 
-  if (warp < kWgAWarps) {
-    // ------------------------------------------------------------------ A producers
-    const int group = warp >> 2, quarter = warp & 3;
-    const int row = quarter * 32 + lane;
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + a_col0;
-    MaskTap tap[kWgMaxSubs];
-#pragma unroll
-    for (int u = 0; u < kWgMaxSubs; ++u)
-      tap[u] = u < subs ? P.taps[(mgroup * P.subs + u) * kTileM + row] : MaskTap{0, kWgPadBit};
+  if (warp < kWgProdWarps) {
+    // ------------------------------------------------------------------ producers (lane = pixel of the k-block)
     const float* xg = P.x + (long long)grp * P.x_group_stride;
-    float v[kBlockK];
-    auto gather = [&](int it) {
-      const int kbl = it / subs, u = it - kbl * subs;
-      const int sb = kbl % P.b_stages;
-      mbar_wait(pix_full + 8u * sb, (uint32_t)(kbl / P.b_stages) & 1u, failed, P.status, 0x1000);
-      MaskTap mine = tap[0];
+    const float* dyg = P.dy + (long long)(grp * P.dy_group_channels + ntile * P.n_real + warp) * P.mm;
+    const int dy_step = kWgProdWarps * P.mm;  // elements between consecutive channel rows of this warp
+    const int b_live = P.n_real > warp ? (P.n_real - warp + kWgProdWarps - 1) / kWgProdWarps : 0;  // real rows
+    // Does this CTA hold the all-ones row (bias gradient)?  Only then the tap loads need the extra select.
+    const int ones_row = P.ones_row - mgroup * SUBS * kTileM;
+    const bool has_ones = ones_row >= 0 && ones_row < subs * kTileM;
+    // this lane's pixel, advanced by 32 per k-block
+    int pix = kb_begin * kBlockK + lane;
+    int pb = pix / P.mm, pr, pc;
+    {
+      const int pin = pix - pb * P.mm;
+      pr = pin / P.m;
+      pc = pin - pr * P.m;
+    }
+    // This lane's word in row `warp` of a tile; the warp's further rows are 2048 bytes apart.
+    uint8_t* lane_ptr = base_ptr + warp * 128 + ((((lane >> 2) ^ (warp & 7)) << 4) + (lane & 3) * 4);
+    const MaskTap* my_taps = s_taps + warp;
+    float va[kARows], vb[NB];
+    auto load_rows = [&]() {
+      const bool ok = pix < P.n_pix;
+      const int iy0 = pr * P.s - P.p, ix0 = pc * P.s - P.p;
+      const float* xsrc = xg + (long long)pb * P.x_batch_stride + (long long)iy0 * P.n + ix0;
+      const float* dsrc = dyg + (long long)pb * P.dy_batch_stride + pr * P.m + pc;
+      const uint32_t mask =
+          ok ? (kWgValidBit | bit_range(-iy0, min(P.k, P.n - iy0)) | (bit_range(-ix0, min(P.k, P.n - ix0)) << 16))
+             : 0u;
+      if (!has_ones) {
 #pragma unroll
-      for (int q = 1; q < kWgMaxSubs; ++q)
-        if (u == q) mine = tap[q];
-      const PixInfo* pi = s_pix + sb * 32;
-      const bool ones = mine.bits == kWgOnesBits;
+        for (int i = 0; i < kARows; ++i) {
+          const MaskTap tap = my_taps[kWgProdWarps * i];
+          va[i] = 0.f;
+          if ((mask & tap.bits) == tap.bits && !DBG(P, 1)) va[i] = __ldg(xsrc + tap.off);
+        }
+      } else {
 #pragma unroll
-      for (int j = 0; j < kBlockK; ++j) {
-        const PixInfo px = pi[j];
-        const bool ok = (px.mask & mine.bits) == mine.bits;
-        v[j] = (ok && ones) ? 1.f : 0.f;
-        if (ok && !ones && !DBG(P, 1)) v[j] = __ldg(xg + px.xbase + mine.off);
+        for (int i = 0; i < kARows; ++i) {
+          const MaskTap tap = my_taps[kWgProdWarps * i];
+          va[i] = 0.f;
+          if ((mask & tap.bits) == tap.bits) va[i] = tap.bits == kWgOnesBits ? 1.f : __ldg(xsrc + tap.off);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < NB; ++i) {
+        vb[i] = 0.f;
+        if (ok && i < b_live && !DBG(P, 2)) vb[i] = __ldg(dsrc + i * dy_step);
       }
     };
-    if (group < total_it) gather(group);
-    for (int it = group; it < total_it; it += 4) {
-      const int slot = it % P.slots, use = it / P.slots;
-      if (use > 0) mbar_wait(a_empty + 8u * slot, (uint32_t)(use - 1) & 1u, failed, P.status, 0x10);
-      tc_fence_after();
-      const uint32_t st_addr = lane_addr + (uint32_t)(slot * 64);
+    load_rows();
+    for (int kbl = 0; kbl < kblocks; ++kbl) {
+      const int s = kbl % P.stages, use = kbl / P.stages;
+      uint8_t* st = lane_ptr + (size_t)s * L.stage_bytes;
+      if (use > 0) mbar_wait(empty + 8u * s, (uint32_t)(use - 1) & 1u, failed, P.status, 0x10);
 #pragma unroll
-      for (int c = 0; c < kBlockK / 8; ++c) {
-        uint32_t hi[8], lo[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) split_tf32_trunc(v[c * 8 + e], hi[e], lo[e]);
-        tmem_st8(st_addr + (uint32_t)(c * 8), hi);
-        tmem_st8(st_addr + 32u + (uint32_t)(c * 8), lo);
+      for (int i = 0; i < kARows; ++i) {  // tile i/8 (hi then lo), row warp + 16*(i%8)
+        uint32_t h, l;
+        split_tf32_trunc(va[i], h, l);
+        uint8_t* dst = st + (i / 8) * 2 * kATile + (i % 8) * 2048;
+        *reinterpret_cast<uint32_t*>(dst) = h;
+        *reinterpret_cast<uint32_t*>(dst + kATile) = l;
       }
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(a_full + 8u * slot);
-      // Only now: the pixel table of a later k-block is published after earlier MMAs retire, and those wait for the
-      // arrival above.
-      if (it + 4 < total_it) gather(it + 4);
+#pragma unroll
+      for (int i = 0; i < NB; ++i) {  // dY tile (hi then lo) behind the SUBS tap tiles, row warp + 16*i
+        uint32_t h, l;
+        split_tf32_trunc(vb[i], h, l);
+        uint8_t* dst = st + SUBS * 2 * kATile + i * 2048;
+        *reinterpret_cast<uint32_t*>(dst) = h;
+        *reinterpret_cast<uint32_t*>(dst + kBTile) = l;
+      }
+      if (kbl + 1 < kblocks) {  // the next k-block's loads go in flight before the barrier work
+        pix += kBlockK;
+        pc += kBlockK;
+        while (pc >= P.m) { pc -= P.m; ++pr; }
+        while (pr >= P.m) { pr -= P.m; ++pb; }
+        load_rows();
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(full + 8u * s);
     }
-    // ---- epilogue: accumulator u, columns in chunks of 16; set g takes the (u, chunk) pairs with index == g mod 4
+    // ---- epilogue: accumulator u, columns in chunks of 16; warp w takes lanes 32*(w%4).. and the (u, chunk) pairs
+    //      with index == w/4 (mod 4)
     mbar_wait(acc_full, 0u, failed, P.status, 0x2000);
     tc_fence_after();
-    const int chunks = P.n_pad / 16;
-    for (int w = group; w < subs * chunks; w += 4) {
-      const int u = w / chunks, c = w - u * chunks;
+    const int quarter = warp & 3, row = quarter * 32 + lane;
+    for (int w = warp >> 2; w < subs * NB; w += 4) {
+      const int u = w / NB, c = w - u * NB;
       float acc[16];
-      tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(u * P.n_pad + c * 16), acc);
+      tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(u * kNPad + c * 16), acc);
       float* op = P.partial + (((size_t)split * gridDim.z + vg) * P.m_tiles * kTileM +
-                               (size_t)(mgroup * P.subs + u) * kTileM + row) * P.n_pad + c * 16;
+                               (size_t)(mgroup * SUBS + u) * kTileM + row) * kNPad + c * 16;
       if (!failed) {
         float4* o4 = reinterpret_cast<float4*>(op);
 #pragma unroll
         for (int j = 0; j < 4; ++j) o4[j] = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
       }
     }
-  } else if (warp < kWgMmaWarp) {
-    // ------------------------------------------------------------------ B producers (lane = pixel of the k-block)
-    const int bw = warp - kWgBWarp0;
-    const float* dyg = P.dy + (long long)(grp * P.dy_group_channels + ntile * P.n_real) * P.mm;
-    for (int kbl = 0; kbl < kblocks; ++kbl) {
-      const int sb = kbl % P.b_stages, use = kbl / P.b_stages;
-      const int pix = (kb_begin + kbl) * kBlockK + lane;
-      const bool ok = pix < P.n_pix;
-      const int b = pix / P.mm;
-      const int pin = pix - b * P.mm;
-      const int r = pin / P.m;
-      const int c = pin - r * P.m;
-      if (use > 0) mbar_wait(b_empty + 8u * sb, (uint32_t)(use - 1) & 1u, failed, P.status, 0x100);
-      if (bw == 0) {
-        PixInfo pi;
-        const int iy0 = r * P.s - P.p, ix0 = c * P.s - P.p;
-        pi.xbase = ok ? (int)((long long)b * P.x_batch_stride + (long long)iy0 * P.n + ix0) : 0;
-        pi.mask = ok ? (kWgValidBit | bit_range(-iy0, min(P.k, P.n - iy0)) |
-                        (bit_range(-ix0, min(P.k, P.n - ix0)) << 16))
-                     : 0u;
-        s_pix[sb * 32 + lane] = pi;
-        mbar_arrive(pix_full + 8u * sb);
-      }
-      const float* src = dyg + (long long)b * P.dy_batch_stride + pin;
-      const uint32_t b_hi = base + (uint32_t)sb * L.b_stage_bytes, b_lo = b_hi + (uint32_t)P.n_pad * 128u;
-      for (int o0 = bw; o0 < P.n_pad; o0 += kWgBWarps * 4) {
-        float val[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int o = o0 + i * kWgBWarps;
-          val[i] = (ok && o < P.n_real && !DBG(P, 2)) ? __ldg(src + (long long)o * P.mm) : 0.f;
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int o = o0 + i * kWgBWarps;
-          if (o < P.n_pad) {
-            uint32_t h, l;
-            split_tf32_trunc(val[i], h, l);
-            const uint32_t off = swz(o, lane >> 2) + (uint32_t)((lane & 3) * 4);
-            asm volatile("st.shared.b32 [%0], %1;" ::"r"(b_hi + off), "r"(h) : "memory");
-            asm volatile("st.shared.b32 [%0], %1;" ::"r"(b_lo + off), "r"(l) : "memory");
-          }
-        }
-      }
-      fence_proxy_async_smem();
-      mbar_arrive(b_full + 8u * sb);
-    }
   } else {
     // ------------------------------------------------------------------ MMA issue
     if (lane == 0) {
-      const uint32_t idesc = make_idesc(P.n_pad);
-      int it = 0;
+      const uint32_t idesc = make_idesc(kNPad);
       for (int kbl = 0; kbl < kblocks; ++kbl) {
-        const int sb = kbl % P.b_stages;
-        mbar_wait(b_full + 8u * sb, (uint32_t)(kbl / P.b_stages) & 1u, failed, P.status, 0x80);
-        const uint32_t b_hi = base + (uint32_t)sb * L.b_stage_bytes, b_lo = b_hi + (uint32_t)P.n_pad * 128u;
+        const int s = kbl % P.stages;
+        mbar_wait(full + 8u * s, (uint32_t)(kbl / P.stages) & 1u, failed, P.status, 0x40);
+        tc_fence_after();
+        const uint32_t st = base + (uint32_t)s * L.stage_bytes;
+        const uint32_t b_hi = st + SUBS * 2u * kATile, b_lo = b_hi + kBTile;
         const uint64_t dbh = make_desc(b_hi), dbl = make_desc(b_lo);
-        for (int u = 0; u < subs; ++u, ++it) {
-          const int slot = it % P.slots;
-          mbar_wait(a_full + 8u * slot, (uint32_t)(it / P.slots) & 1u, failed, P.status, 0x40);
-          tc_fence_after();
-          const uint32_t d_tmem = tmem_base + (uint32_t)(u * P.n_pad);
-          const uint32_t a_hi = tmem_base + a_col0 + (uint32_t)(slot * 64), a_lo = a_hi + 32u;
-          if (!DBG(P, 4)) {
+        if (!DBG(P, 4)) {
+          for (int u = 0; u < subs; ++u) {
+            const uint32_t d_tmem = tmem_base + (uint32_t)(u * kNPad);
+            const uint32_t a_hi = st + (uint32_t)u * 2u * kATile;
+            const uint64_t dah = make_desc(a_hi), dal = make_desc(a_hi + kATile);
 #pragma unroll
             for (int j = 0; j < kBlockK / 8; ++j) {
               const uint64_t adv = (uint64_t)(j * 2);
-              umma_tf32_ts(d_tmem, a_lo + (uint32_t)(j * 8), dbh + adv, idesc, (kbl == 0 && j == 0) ? 0u : 1u);
-              umma_tf32_ts(d_tmem, a_hi + (uint32_t)(j * 8), dbl + adv, idesc, 1u);
-              umma_tf32_ts(d_tmem, a_hi + (uint32_t)(j * 8), dbh + adv, idesc, 1u);
+              umma_tf32_ss(d_tmem, dal + adv, dbh + adv, idesc, (kbl == 0 && j == 0) ? 0u : 1u);
+              umma_tf32_ss(d_tmem, dah + adv, dbl + adv, idesc, 1u);
+              umma_tf32_ss(d_tmem, dah + adv, dbh + adv, idesc, 1u);
             }
           }
-          umma_commit(a_empty + 8u * slot);
         }
-        umma_commit(b_empty + 8u * sb);
+        umma_commit(empty + 8u * s);
       }
       umma_commit(acc_full);
     }
@@ -698,6 +692,25 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem_base, 512);
+}
+
+typedef void (*WgradKernel)(const WgradParams);
+template <int SUBS>
+WgradKernel wgrad_pick_nb(int nb) {
+  switch (nb) {
+    case 1: return wgrad_kernel<SUBS, 1>;   case 2: return wgrad_kernel<SUBS, 2>;
+    case 3: return wgrad_kernel<SUBS, 3>;   case 4: return wgrad_kernel<SUBS, 4>;
+    case 5: return wgrad_kernel<SUBS, 5>;   case 6: return wgrad_kernel<SUBS, 6>;
+    case 7: return wgrad_kernel<SUBS, 7>;   case 8: return wgrad_kernel<SUBS, 8>;
+    case 9: return wgrad_kernel<SUBS, 9>;   case 10: return wgrad_kernel<SUBS, 10>;
+    case 11: return wgrad_kernel<SUBS, 11>; case 12: return wgrad_kernel<SUBS, 12>;
+    case 13: return wgrad_kernel<SUBS, 13>; case 14: return wgrad_kernel<SUBS, 14>;
+    case 15: return wgrad_kernel<SUBS, 15>; case 16: return wgrad_kernel<SUBS, 16>;
+  }
+  return nullptr;
+}
+WgradKernel wgrad_pick(int subs, int n_pad) {
+  return subs == 2 ? wgrad_pick_nb<2>(n_pad / 16) : wgrad_pick_nb<1>(n_pad / 16);
 }
 
 // dW[o][kk] and db[o] from the split partial sums, added in split order (deterministic).
@@ -806,7 +819,7 @@ struct UmmaPlan {
   GatherProblem fwd, dgr;
   int dgr_taps = 0, dgr_q = 0, dgr_q0 = 0;  // taps per axis; super-pixels per axis and the first one that holds a pixel
   // weight gradient
-  int w_mtiles, w_subs, w_slots, w_bstages, w_mgroups, w_splits, w_kblocks_total, w_kblocks_per_split, w_npad;
+  int w_mtiles, w_subs, w_stages, w_mgroups, w_splits, w_kblocks_total, w_kblocks_per_split, w_npad;
   size_t w_smem = 0;
   MaskTap* w_taps = nullptr;
   float* w_partial = nullptr;
@@ -976,15 +989,17 @@ int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out) {
       }
     }
     rc = upload(ctx, p, &p->w_taps, t);
-    // M-tiles per CTA: as many accumulators as tensor memory holds next to at least 3 A slots of 64 columns
+    // M-tiles per CTA: as many as leave room for two stages in shared memory (and whose accumulators fit in tensor
+    // memory); the dY tile of a k-block is staged once for all of them.
     int subs = 1;
     for (int u = 2; u <= kWgMaxSubs; ++u)
-      if (u <= p->w_mtiles && u * f.n_pad + 3 * 64 <= 512) subs = u;
+      if (u <= p->w_mtiles && u * f.n_pad <= 512 && 2 * wg_smem(f.n_pad, u, 2).stage_bytes + 8192 <= (uint32_t)kSmemLimit)
+        subs = u;
     p->w_subs = subs;
-    p->w_slots = std::min(kWgMaxSlots, (512 - subs * f.n_pad) / 64);
     p->w_mgroups = (p->w_mtiles + subs - 1) / subs;
-    p->w_bstages = std::max(2, std::min(kWgMaxBStages, (128 * 1024) / (2 * f.n_pad * 128)));
-    p->w_smem = wg_smem(f.n_pad, p->w_bstages).total + 1024;
+    const uint32_t stage_bytes = wg_smem(f.n_pad, subs, 2).stage_bytes;
+    p->w_stages = std::max(2, std::min(kWgMaxStages, (int)((kSmemLimit - 8192) / stage_bytes)));
+    p->w_smem = wg_smem(f.n_pad, subs, p->w_stages).total + 1024;
     const int n_pix = G.B * G.m * G.m;
     p->w_kblocks_total = (n_pix + kBlockK - 1) / kBlockK;
     const int out_tiles = p->w_mgroups * G.g * f.tiles;
@@ -996,7 +1011,7 @@ int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out) {
       rc = dev_alloc(ctx, p, &p->w_partial, (size_t)p->w_splits * G.g * f.tiles * p->w_mtiles * kTileM * f.n_pad);
   }
   if (rc == CCT_OK) rc = set_smem(ctx, gather_conv_kernel, kSmemLimit);
-  if (rc == CCT_OK) rc = set_smem(ctx, wgrad_kernel, kSmemLimit);
+  if (rc == CCT_OK) rc = set_smem(ctx, wgrad_pick(p->w_subs, p->fwd.n_pad), kSmemLimit);
   if (rc != CCT_OK) {
     umma_plan_destroy(ctx, p);
     return rc;
@@ -1082,14 +1097,15 @@ int umma_conv_backward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W
     P.dy_group_channels = G.og;
     P.tiles_per_group = f.tiles;
     P.n_real = f.n; P.n_pad = f.n_pad;
-    P.m_tiles = p->w_mtiles; P.subs = p->w_subs; P.slots = p->w_slots; P.b_stages = p->w_bstages;
+    P.m_tiles = p->w_mtiles; P.subs = p->w_subs; P.stages = p->w_stages;
+    P.ones_row = f.k_real;
     P.kblocks_total = p->w_kblocks_total; P.kblocks_per_split = p->w_kblocks_per_split;
     P.status = ctx->status_dev;
     P.dbg = dbg_knobs();
     const int vgroups = G.g * f.tiles;
     dim3 grid(p->w_mgroups, p->w_splits, vgroups);
     t->begin(1, ctx->stream);
-    wgrad_kernel<<<grid, kWgThreads, p->w_smem, ctx->stream>>>(P);
+    wgrad_pick(p->w_subs, f.n_pad)<<<grid, kWgThreads, p->w_smem, ctx->stream>>>(P);
     t->end(1, ctx->stream);
     CCT_CHECK_LAUNCH(ctx);
     t->begin(2, ctx->stream);
