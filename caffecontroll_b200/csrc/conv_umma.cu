@@ -36,8 +36,16 @@ constexpr int kBlockK = 32;  // fp32 per k-block: one 128-byte swizzled row
 constexpr int kSmemLimit = 227 * 1024;
 #ifdef CCT_DBG
 #define DBG(P, bit) ((P).dbg & (bit))
+// Cycle accounting of debug builds: per role, cycles spent in each wait and in the work between waits.
+__device__ unsigned long long g_prof[64];
+#define PROF_DECL long long prof_t = clock64(); long long prof_acc[6] = {0, 0, 0, 0, 0, 0}
+#define PROF_LAP(i) do { const long long prof_n = clock64(); prof_acc[i] += prof_n - prof_t; prof_t = prof_n; } while (0)
+#define PROF_FLUSH(role, cond) do { if (cond) for (int prof_i = 0; prof_i < 6; ++prof_i) atomicAdd(&g_prof[(role) * 8 + prof_i], (unsigned long long)prof_acc[prof_i]); } while (0)
 #else
 #define DBG(P, bit) 0
+#define PROF_DECL
+#define PROF_LAP(i)
+#define PROF_FLUSH(role, cond)
 #endif
 constexpr int kMaxTapsPerAxis = 15;
 constexpr uint32_t kPadBit = 0x80000000u;  // never set in a pixel's validity mask: marks padding entries
@@ -257,9 +265,9 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
   for (int i = tid; i < P.k_pad; i += kGatherThreads) s_taps[i] = P.taps[i];
   for (int i = tid; i < P.n_pad; i += kGatherThreads) s_cols[i] = P.cols[i];
   if (tid == 0) {
-    for (int s = 0; s < kMaxAStages; ++s) { mbar_init(a_full + 8u * s, 128); mbar_init(a_empty + 8u * s, 1); }
+    for (int s = 0; s < kMaxAStages; ++s) { mbar_init(a_full + 8u * s, 4); mbar_init(a_empty + 8u * s, 1); }
     for (int s = 0; s < kMaxBStages; ++s) { mbar_init(b_full + 8u * s, 1); mbar_init(b_empty + 8u * s, 1); }
-    for (int s = 0; s < kMaxAccBufs; ++s) { mbar_init(acc_full + 8u * s, 1); mbar_init(acc_empty + 8u * s, 128); }
+    for (int s = 0; s < kMaxAccBufs; ++s) { mbar_init(acc_full + 8u * s, 1); mbar_init(acc_empty + 8u * s, kEpiWarps); }
     fence_mbar_init();
   }
   if (warp == 0) tmem_alloc(tmem_slot, 512);
@@ -325,10 +333,13 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
       setup_tile(tile_local);
       gather(kb);
     }
+    PROF_DECL;
     for (int it = group; it < my_stages; it += 4) {
       const int use = it >> 2;
+      PROF_LAP(0);
       if (use > 0) mbar_wait(empty_bar, (uint32_t)(use - 1) & 1u, failed, P.status, 0x10);
       tc_fence_after();
+      PROF_LAP(1);
 #pragma unroll
       for (int c = 0; c < kBlockK / 8; ++c) {
         uint32_t hi[8], lo[8];
@@ -337,6 +348,7 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
         tmem_st8(st_addr + (uint32_t)(c * 8), hi);
         tmem_st8(st_addr + 32u + (uint32_t)(c * 8), lo);
       }
+      PROF_LAP(2);
       if (it + 4 < my_stages) {  // put the next k-block's loads in flight before waiting for the stores
         const int before = tile_local;
         kb += 4;
@@ -344,25 +356,35 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
         if (tile_local != before) setup_tile(tile_local);
         gather(kb);
       }
+      PROF_LAP(3);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(full_bar);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(full_bar);  // one arrival per warp: same-address arrivals serialise
+      PROF_LAP(4);
     }
+    PROF_FLUSH(0, warp == 0 && lane == 0 && blockIdx.x == 0);
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issue
     if (lane == 0) {
       const uint32_t idesc = make_idesc(P.n_pad);
       int it = 0, tile_iter = 0;
+      PROF_DECL;
       for (int t = blockIdx.x; t < P.total_tiles; t += gridDim.x, ++tile_iter) {
         const int buf = tile_iter % P.acc_bufs, ause = tile_iter / P.acc_bufs;
+        PROF_LAP(0);
         if (ause > 0) mbar_wait(acc_empty + 8u * buf, (uint32_t)(ause - 1) & 1u, failed, P.status, 0x20);
         tc_fence_after();
+        PROF_LAP(1);
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * P.n_pad);
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int sa = it & 3, sb = it % P.b_stages;
+          PROF_LAP(0);
           mbar_wait(a_full + 8u * sa, (uint32_t)(it >> 2) & 1u, failed, P.status, 0x40);
+          PROF_LAP(2);
           mbar_wait(b_full + 8u * sb, (uint32_t)(it / P.b_stages) & 1u, failed, P.status, 0x80);
           tc_fence_after();
+          PROF_LAP(3);
           const uint32_t b_hi = base + (uint32_t)sb * L.b_stage_bytes, b_lo = b_hi + (uint32_t)P.n_pad * 128u;
           const uint64_t dbh = make_desc(b_hi), dbl = make_desc(b_lo);
           const uint32_t a_hi = tmem_base + a_col0 + (uint32_t)(sa * 64), a_lo = a_hi + 32u;
@@ -380,6 +402,8 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
         }
         umma_commit(acc_full + 8u * buf);
       }
+      PROF_LAP(0);
+      PROF_FLUSH(1, blockIdx.x == 0);
     }
   } else if (warp == kTmaWarp) {
     // ------------------------------------------------------------------ weight tiles by TMA
@@ -402,6 +426,7 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     int tile_iter = 0;
+    PROF_DECL;
     for (int t = blockIdx.x; t < P.total_tiles; t += gridDim.x, ++tile_iter) {
       const int vg = t / P.n_pix_tiles, ptile = t - vg * P.n_pix_tiles;
       const int grp = vg / P.tiles_per_group, ntile = vg % P.tiles_per_group;
@@ -420,8 +445,10 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
       float* op = P.out + (long long)b * P.out_batch_stride + (long long)ch0 * P.out_plane +
                   (long long)oy0 * P.out_pitch + ox0;
       const float* bias = P.bias ? P.bias + ch0 : nullptr;
+      PROF_LAP(0);
       mbar_wait(acc_full + 8u * buf, (uint32_t)ause & 1u, failed, P.status, 0x200);
       tc_fence_after();
+      PROF_LAP(1);
       const bool live = pix < P.n_pix && !failed;
       const uint32_t acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P.n_pad);
       const int chunks = P.n_pad / 16;
@@ -447,8 +474,11 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
         }
       }
       tc_fence_before();
-      mbar_arrive(acc_empty + 8u * buf);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty + 8u * buf);
+      PROF_LAP(2);
     }
+    PROF_FLUSH(2, warp == kEpiWarp0 && lane == 0 && blockIdx.x == 0);
   }
   tc_fence_before();
   __syncthreads();
@@ -546,7 +576,7 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
   for (int i = tid; i < SUBS * kTileM; i += kWgThreads)
     s_taps[i] = i < subs * kTileM ? P.taps[mgroup * SUBS * kTileM + i] : MaskTap{0, kWgPadBit};
   if (tid == 0) {
-    for (int s = 0; s < kWgMaxStages; ++s) { mbar_init(full + 8u * s, kWgProdWarps * 32); mbar_init(empty + 8u * s, 1); }
+    for (int s = 0; s < kWgMaxStages; ++s) { mbar_init(full + 8u * s, kWgProdWarps); mbar_init(empty + 8u * s, 1); }
     mbar_init(acc_full, 1);
     fence_mbar_init();
   }
@@ -612,10 +642,13 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
       }
     };
     load_rows();
+    PROF_DECL;
     for (int kbl = 0; kbl < kblocks; ++kbl) {
       const int s = kbl % P.stages, use = kbl / P.stages;
       uint8_t* st = lane_ptr + (size_t)s * L.stage_bytes;
+      PROF_LAP(0);
       if (use > 0) mbar_wait(empty + 8u * s, (uint32_t)(use - 1) & 1u, failed, P.status, 0x10);
+      PROF_LAP(1);
 #pragma unroll
       for (int i = 0; i < kARows; ++i) {  // tile i/8 (hi then lo), row warp + 16*(i%8)
         uint32_t h, l;
@@ -632,6 +665,7 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
         *reinterpret_cast<uint32_t*>(dst) = h;
         *reinterpret_cast<uint32_t*>(dst + kBTile) = l;
       }
+      PROF_LAP(2);
       if (kbl + 1 < kblocks) {  // the next k-block's loads go in flight before the barrier work
         pix += kBlockK;
         pc += kBlockK;
@@ -639,9 +673,13 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
         while (pr >= P.m) { pr -= P.m; ++pb; }
         load_rows();
       }
+      PROF_LAP(3);
       fence_proxy_async_smem();
-      mbar_arrive(full + 8u * s);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(full + 8u * s);  // one arrival per warp: same-address arrivals serialise
+      PROF_LAP(4);
     }
+    PROF_FLUSH(4, warp == 0 && lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
     // ---- epilogue: accumulator u, columns in chunks of 16; warp w takes lanes 32*(w%4).. and the (u, chunk) pairs
     //      with index == w/4 (mod 4)
     mbar_wait(acc_full, 0u, failed, P.status, 0x2000);
@@ -663,10 +701,13 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
     // ------------------------------------------------------------------ MMA issue
     if (lane == 0) {
       const uint32_t idesc = make_idesc(kNPad);
+      PROF_DECL;
       for (int kbl = 0; kbl < kblocks; ++kbl) {
         const int s = kbl % P.stages;
+        PROF_LAP(0);
         mbar_wait(full + 8u * s, (uint32_t)(kbl / P.stages) & 1u, failed, P.status, 0x40);
         tc_fence_after();
+        PROF_LAP(1);
         const uint32_t st = base + (uint32_t)s * L.stage_bytes;
         const uint32_t b_hi = st + SUBS * 2u * kATile, b_lo = b_hi + kBTile;
         const uint64_t dbh = make_desc(b_hi), dbl = make_desc(b_lo);
@@ -687,6 +728,8 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
         umma_commit(empty + 8u * s);
       }
       umma_commit(acc_full);
+      PROF_LAP(0);
+      PROF_FLUSH(5, blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
     }
   }
   tc_fence_before();
@@ -1147,3 +1190,15 @@ int umma_conv_backward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W
   }
   return CCT_OK;
 }
+
+#ifdef CCT_DBG
+extern "C" int cct_dbg_read_prof(unsigned long long* out, int reset) {
+  cudaDeviceSynchronize();
+  if (cudaMemcpyFromSymbol(out, g_prof, sizeof(unsigned long long) * 64) != cudaSuccess) return 1;
+  if (reset) {
+    static unsigned long long zeros[64];
+    cudaMemcpyToSymbol(g_prof, zeros, sizeof zeros);
+  }
+  return 0;
+}
+#endif
