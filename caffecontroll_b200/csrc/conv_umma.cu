@@ -53,7 +53,7 @@ constexpr uint32_t kPadBit = 0x80000000u;  // never set in a pixel's validity ma
 // One entry per reduction index of a gathered operand: element offset from the pixel's tap origin, and the tap's
 // row / column as mask bits.  The tap is in bounds for a pixel iff (pixel_mask & bits) == bits, where bit i (rows) and
 // bit 16+j (columns) of the pixel's mask say whether tap row i / tap column j falls inside the gathered plane.
-struct MaskTap {
+struct alignas(8) MaskTap {
   int off;
   uint32_t bits;
 };
@@ -173,7 +173,7 @@ constexpr int kMmaWarp = 16, kTmaWarp = 17, kEpiWarp0 = 18, kEpiWarps = 4;
 constexpr int kGatherThreads = (kEpiWarp0 + kEpiWarps) * 32;  // 704
 constexpr int kMaxAStages = 4, kMaxBStages = 8, kMaxAccBufs = 2;
 
-struct ColEnt {  // one accumulator column -> where it lands in the output
+struct alignas(8) ColEnt {  // one accumulator column -> where it lands in the output
   int off;       // element offset from the pixel's output origin
   short cy, cx;  // displacement of the output pixel (depth-to-space), for the bounds test
 };
@@ -199,6 +199,9 @@ struct GatherParams {
   int n, n_pad, k_pad;     // real / padded accumulator columns per virtual group, padded reduction length
   int n_pix_tiles, total_tiles;
   int a_stages, b_stages, acc_bufs;
+  int dual;                // 1: one MMA covers [B_hi; B_lo] (N = 2*n_pad) and the epilogue adds the two halves
+  int acc_cols;            // accumulator width in tensor-memory columns: n_pad, or 2*n_pad when dual
+  int n_bias;              // entries of `bias` (all output channels), staged in shared memory
   int lo_row_offset;       // first row of the "lo" half inside the packed-weight tensor map
   int relu;
   int* status;
@@ -236,14 +239,15 @@ __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 struct GatherSmem {
-  uint32_t b_stage_bytes, taps_off, cols_off, bars_off, total;
+  uint32_t b_stage_bytes, taps_off, cols_off, bias_off, bars_off, total;
 };
-__host__ __device__ inline GatherSmem gather_smem(int n_pad, int k_pad, int b_stages) {
+__host__ __device__ inline GatherSmem gather_smem(int n_pad, int k_pad, int b_stages, int n_bias) {
   GatherSmem L;
   L.b_stage_bytes = 2u * (uint32_t)n_pad * 128u;
   L.taps_off = (uint32_t)b_stages * L.b_stage_bytes;
   L.cols_off = L.taps_off + (uint32_t)k_pad * 8u;
-  L.bars_off = (L.cols_off + (uint32_t)n_pad * 8u + 15u) & ~15u;
+  L.bias_off = L.cols_off + (uint32_t)n_pad * 8u;
+  L.bars_off = (L.bias_off + (uint32_t)n_bias * 4u + 15u) & ~15u;
   L.total = L.bars_off + 8u * (2 * kMaxAStages + 2 * kMaxBStages + 2 * kMaxAccBufs) + 16u;
   return L;
 }
@@ -253,19 +257,21 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  const GatherSmem L = gather_smem(P.n_pad, P.k_pad, P.b_stages);
+  const GatherSmem L = gather_smem(P.n_pad, P.k_pad, P.b_stages, P.n_bias);
   const uint32_t bars = base + L.bars_off;
   const uint32_t a_full = bars, a_empty = a_full + 8u * kMaxAStages, b_full = a_empty + 8u * kMaxAStages,
                  b_empty = b_full + 8u * kMaxBStages, acc_full = b_empty + 8u * kMaxBStages,
                  acc_empty = acc_full + 8u * kMaxAccBufs, tmem_slot = acc_empty + 8u * kMaxAccBufs;
   MaskTap* s_taps = reinterpret_cast<MaskTap*>(base_ptr + L.taps_off);
   ColEnt* s_cols = reinterpret_cast<ColEnt*>(base_ptr + L.cols_off);
+  float* s_bias = reinterpret_cast<float*>(base_ptr + L.bias_off);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   for (int i = tid; i < P.k_pad; i += kGatherThreads) s_taps[i] = P.taps[i];
   for (int i = tid; i < P.n_pad; i += kGatherThreads) s_cols[i] = P.cols[i];
+  for (int i = tid; i < P.n_bias; i += kGatherThreads) s_bias[i] = P.bias[i];
   if (tid == 0) {
-    for (int s = 0; s < kMaxAStages; ++s) { mbar_init(a_full + 8u * s, 4); mbar_init(a_empty + 8u * s, 1); }
+    for (int s = 0; s < kMaxAStages; ++s) { mbar_init(a_full + 8u * s, 4); mbar_init(a_empty + 8u * s, 1); }  // 4 warps fill a stage
     for (int s = 0; s < kMaxBStages; ++s) { mbar_init(b_full + 8u * s, 1); mbar_init(b_empty + 8u * s, 1); }
     for (int s = 0; s < kMaxAccBufs; ++s) { mbar_init(acc_full + 8u * s, 1); mbar_init(acc_empty + 8u * s, kEpiWarps); }
     fence_mbar_init();
@@ -276,7 +282,7 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
   tc_fence_after();
   uint32_t tmem_base;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
-  const uint32_t a_col0 = (uint32_t)(P.acc_bufs * P.n_pad);
+  const uint32_t a_col0 = (uint32_t)(P.acc_bufs * P.acc_cols);
   const int kblocks = P.k_pad / kBlockK;
   bool failed = false;
 
@@ -287,8 +293,7 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
     // stored, so the global-load latency is paid once per k-block per set, off the critical path.
     const int group = warp >> 2, quarter = warp & 3;
     const int row = quarter * 32 + lane;
-    const uint32_t st_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + a_col0 + (uint32_t)(group * 64);
-    const uint32_t full_bar = a_full + 8u * group, empty_bar = a_empty + 8u * group;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + a_col0;
     const int my_tiles = (P.total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
     const int my_stages = my_tiles * kblocks;
     const float* in_px = P.in;
@@ -335,9 +340,15 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
     }
     PROF_DECL;
     for (int it = group; it < my_stages; it += 4) {
-      const int use = it >> 2;
+      const int sa = it % P.a_stages, use = it / P.a_stages;
+      const uint32_t st_addr = lane_addr + (uint32_t)(sa * 64);
+      const uint32_t full_bar = a_full + 8u * sa, empty_bar = a_empty + 8u * sa;
       PROF_LAP(0);
-      if (use > 0) mbar_wait(empty_bar, (uint32_t)(use - 1) & 1u, failed, P.status, 0x10);
+      // The stage was last drained `use - 1` phases into its barrier's life.  A parity wait is only meaningful for
+      // the phase that follows one already seen complete, and with two stages this set revisits a stage only every
+      // other use, so it walks through the phases it skipped.
+      for (int ph = use - 4 / P.a_stages; ph < use; ++ph)
+        if (ph >= 0) mbar_wait(empty_bar, (uint32_t)ph & 1u, failed, P.status, 0x10);
       tc_fence_after();
       PROF_LAP(1);
 #pragma unroll
@@ -367,7 +378,7 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issue
     if (lane == 0) {
-      const uint32_t idesc = make_idesc(P.n_pad);
+      const uint32_t idesc = make_idesc(P.acc_cols);
       int it = 0, tile_iter = 0;
       PROF_DECL;
       for (int t = blockIdx.x; t < P.total_tiles; t += gridDim.x, ++tile_iter) {
@@ -376,11 +387,11 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
         if (ause > 0) mbar_wait(acc_empty + 8u * buf, (uint32_t)(ause - 1) & 1u, failed, P.status, 0x20);
         tc_fence_after();
         PROF_LAP(1);
-        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * P.n_pad);
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * P.acc_cols);
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const int sa = it & 3, sb = it % P.b_stages;
+          const int sa = it % P.a_stages, sb = it % P.b_stages;
           PROF_LAP(0);
-          mbar_wait(a_full + 8u * sa, (uint32_t)(it >> 2) & 1u, failed, P.status, 0x40);
+          mbar_wait(a_full + 8u * sa, (uint32_t)(it / P.a_stages) & 1u, failed, P.status, 0x40);
           PROF_LAP(2);
           mbar_wait(b_full + 8u * sb, (uint32_t)(it / P.b_stages) & 1u, failed, P.status, 0x80);
           tc_fence_after();
@@ -389,12 +400,24 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
           const uint64_t dbh = make_desc(b_hi), dbl = make_desc(b_lo);
           const uint32_t a_hi = tmem_base + a_col0 + (uint32_t)(sa * 64), a_lo = a_hi + 32u;
           if (!DBG(P, 4)) {
+            if (P.dual) {
+              // The lo tile sits right behind the hi tile: one descriptor spans both, so a single MMA of width
+              // 2*n_pad produces A*B_hi in the first n_pad columns and A*B_lo in the next (an MMA costs about 90
+              // cycles however narrow it is, so two wide ones beat three narrow ones).
 #pragma unroll
-            for (int j = 0; j < kBlockK / 8; ++j) {
-              const uint64_t adv = (uint64_t)(j * 2);
-              umma_tf32_ts(d_tmem, a_lo + (uint32_t)(j * 8), dbh + adv, idesc, (kb == 0 && j == 0) ? 0u : 1u);
-              umma_tf32_ts(d_tmem, a_hi + (uint32_t)(j * 8), dbl + adv, idesc, 1u);
-              umma_tf32_ts(d_tmem, a_hi + (uint32_t)(j * 8), dbh + adv, idesc, 1u);
+              for (int j = 0; j < kBlockK / 8; ++j) {
+                const uint64_t adv = (uint64_t)(j * 2);
+                umma_tf32_ts(d_tmem, a_lo + (uint32_t)(j * 8), dbh + adv, idesc, (kb == 0 && j == 0) ? 0u : 1u);
+                umma_tf32_ts(d_tmem, a_hi + (uint32_t)(j * 8), dbh + adv, idesc, 1u);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < kBlockK / 8; ++j) {
+                const uint64_t adv = (uint64_t)(j * 2);
+                umma_tf32_ts(d_tmem, a_lo + (uint32_t)(j * 8), dbh + adv, idesc, (kb == 0 && j == 0) ? 0u : 1u);
+                umma_tf32_ts(d_tmem, a_hi + (uint32_t)(j * 8), dbl + adv, idesc, 1u);
+                umma_tf32_ts(d_tmem, a_hi + (uint32_t)(j * 8), dbh + adv, idesc, 1u);
+              }
             }
           }
           umma_commit(a_empty + 8u * sa);
@@ -444,34 +467,49 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
       const int ch0 = grp * P.out_group_channels + ntile * P.out_tile_channels;
       float* op = P.out + (long long)b * P.out_batch_stride + (long long)ch0 * P.out_plane +
                   (long long)oy0 * P.out_pitch + ox0;
-      const float* bias = P.bias ? P.bias + ch0 : nullptr;
+      const float* bias = P.n_bias ? s_bias + ch0 : nullptr;
       PROF_LAP(0);
       mbar_wait(acc_full + 8u * buf, (uint32_t)ause & 1u, failed, P.status, 0x200);
       tc_fence_after();
       PROF_LAP(1);
       const bool live = pix < P.n_pix && !failed;
-      const uint32_t acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P.n_pad);
+      const uint32_t acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P.acc_cols);
       const int chunks = P.n_pad / 16;
       for (int c = 0; c < chunks; ++c) {
         float v[16];
         tmem_ld16(acc + (uint32_t)(c * 16), v);
-        if (live) {
+        if (P.dual) {
+          float w[16];
+          tmem_ld16(acc + (uint32_t)(P.n_pad + c * 16), w);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int col = c * 16 + j;
-            if (col < P.n) {
-              const ColEnt ce = s_cols[col];
-              const bool ok = !P.check_out || ((unsigned)(oy0 + ce.cy) < (unsigned)P.out_lim &&
-                                               (unsigned)(ox0 + ce.cx) < (unsigned)P.out_lim);
-              if (ok) {
-                float y = v[j];
-                if (bias) y += __ldg(bias + col);
-                if (P.relu) y = fmaxf(y, 0.f);
-                op[ce.off] = y;
-              }
+          for (int j = 0; j < 16; ++j) v[j] += w[j];
+        }
+        PROF_LAP(3);
+        if (live) {
+          // Table and bias reads first, then the stores as explicit st.global: a generic store could alias shared
+          // memory and would pin every following table read behind it.
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            ColEnt ce[8];
+            float bv[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int col = c * 16 + h * 8 + j;
+              ce[j] = s_cols[col];
+              bv[j] = (bias && col < P.n) ? bias[col] : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int col = c * 16 + h * 8 + j;
+              const bool ok = col < P.n && (!P.check_out || ((unsigned)(oy0 + ce[j].cy) < (unsigned)P.out_lim &&
+                                                             (unsigned)(ox0 + ce[j].cx) < (unsigned)P.out_lim));
+              float y = v[h * 8 + j] + bv[j];
+              if (P.relu) y = fmaxf(y, 0.f);
+              if (ok) asm volatile("st.global.f32 [%0], %1;" ::"l"(op + ce[j].off), "f"(y));
             }
           }
         }
+        PROF_LAP(4);
       }
       tc_fence_before();
       __syncwarp();
@@ -572,6 +610,10 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
   constexpr int kARows = 8 * SUBS;                        // tap rows per producer warp and k-block
   constexpr uint32_t kATile = kTileM * 128u, kBTile = NB * 16u * 128u;
   constexpr int kNPad = NB * 16;
+  // Narrow dY tiles run "dual": the lo tile sits right behind the hi tile, one MMA of width 2*kNPad covers both (an
+  // MMA costs about 90 cycles however narrow it is), and the epilogue adds the two halves of the accumulator.
+  constexpr bool kDual = kNPad <= 64;  // operands from shared memory: an MMA wider than 128 is slower than two narrow ones
+  constexpr int kAccCols = kDual ? 2 * kNPad : kNPad;
 
   for (int i = tid; i < SUBS * kTileM; i += kWgThreads)
     s_taps[i] = i < subs * kTileM ? P.taps[mgroup * SUBS * kTileM + i] : MaskTap{0, kWgPadBit};
@@ -688,7 +730,14 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
     for (int w = warp >> 2; w < subs * NB; w += 4) {
       const int u = w / NB, c = w - u * NB;
       float acc[16];
-      tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(u * kNPad + c * 16), acc);
+      const uint32_t col = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(u * kAccCols + c * 16);
+      tmem_ld16(col, acc);
+      if (kDual) {
+        float lo_part[16];
+        tmem_ld16(col + kNPad, lo_part);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[j] += lo_part[j];
+      }
       float* op = P.partial + (((size_t)split * gridDim.z + vg) * P.m_tiles * kTileM +
                                (size_t)(mgroup * SUBS + u) * kTileM + row) * kNPad + c * 16;
       if (!failed) {
@@ -700,7 +749,7 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
   } else {
     // ------------------------------------------------------------------ MMA issue
     if (lane == 0) {
-      const uint32_t idesc = make_idesc(kNPad);
+      const uint32_t idesc = make_idesc(kAccCols);
       PROF_DECL;
       for (int kbl = 0; kbl < kblocks; ++kbl) {
         const int s = kbl % P.stages;
@@ -713,15 +762,20 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
         const uint64_t dbh = make_desc(b_hi), dbl = make_desc(b_lo);
         if (!DBG(P, 4)) {
           for (int u = 0; u < subs; ++u) {
-            const uint32_t d_tmem = tmem_base + (uint32_t)(u * kNPad);
+            const uint32_t d_tmem = tmem_base + (uint32_t)(u * kAccCols);
             const uint32_t a_hi = st + (uint32_t)u * 2u * kATile;
             const uint64_t dah = make_desc(a_hi), dal = make_desc(a_hi + kATile);
 #pragma unroll
             for (int j = 0; j < kBlockK / 8; ++j) {
               const uint64_t adv = (uint64_t)(j * 2);
-              umma_tf32_ss(d_tmem, dal + adv, dbh + adv, idesc, (kbl == 0 && j == 0) ? 0u : 1u);
-              umma_tf32_ss(d_tmem, dah + adv, dbl + adv, idesc, 1u);
-              umma_tf32_ss(d_tmem, dah + adv, dbh + adv, idesc, 1u);
+              if (kDual) {
+                umma_tf32_ss(d_tmem, dal + adv, dbh + adv, idesc, (kbl == 0 && j == 0) ? 0u : 1u);
+                umma_tf32_ss(d_tmem, dah + adv, dbh + adv, idesc, 1u);
+              } else {
+                umma_tf32_ss(d_tmem, dal + adv, dbh + adv, idesc, (kbl == 0 && j == 0) ? 0u : 1u);
+                umma_tf32_ss(d_tmem, dah + adv, dbl + adv, idesc, 1u);
+                umma_tf32_ss(d_tmem, dah + adv, dbh + adv, idesc, 1u);
+              }
             }
           }
         }
@@ -853,7 +907,7 @@ struct GatherProblem {
   float* w = nullptr;  // [2][vgroups][n_pad][k_pad]
   size_t w_half = 0;   // elements in one half
   CUtensorMap map;
-  int a_stages = 4, b_stages = 4, acc_bufs = 1;
+  int a_stages = 4, b_stages = 4, acc_bufs = 1, dual = 0, acc_cols = 0;
   size_t smem = 0;
 };
 
@@ -923,13 +977,18 @@ int pack_grid(cct_ctx* ctx, size_t total) {
 }
 
 // Tensor-memory and shared-memory budget of a gather problem, packed-weight buffer and its tensor map.
-int finish_problem(cct_ctx* ctx, UmmaPlan* p, GatherProblem& gp, int vgroups) {
-  gp.a_stages = 4;
-  gp.acc_bufs = gp.n_pad <= 128 ? 2 : 1;
+int finish_problem(cct_ctx* ctx, UmmaPlan* p, GatherProblem& gp, int vgroups, int n_bias) {
+  // Tensor memory (512 columns) = accumulator buffers + A stages of 64 columns.  Narrow problems run "dual" (see the
+  // MMA loop): their accumulator is 2*n_pad wide.  Two accumulator buffers let the epilogue overlap the next tile.
+  gp.dual = gp.n_pad <= 64;  // 2 MMAs of width <= 128 (93 cycles each) instead of 3; wider ones gain nothing
+  gp.acc_cols = gp.dual ? 2 * gp.n_pad : gp.n_pad;
+  if (2 * gp.acc_cols + 4 * 64 <= 512) { gp.acc_bufs = 2; gp.a_stages = 4; }
+  else if (2 * gp.acc_cols + 2 * 64 <= 512 && gp.k_pad / kBlockK <= 16) { gp.acc_bufs = 2; gp.a_stages = 2; }  // short K: the epilogue matters more
+  else { gp.acc_bufs = 1; gp.a_stages = std::min(4, (512 - gp.acc_cols) / 64); }
   // Weight stages: enough to cover the TMA latency, small enough to leave most of the SM's memory to the L1 cache
   // that serves the gathers (704 threads x 80 registers already limit an SM to one CTA).
   gp.b_stages = std::max(2, std::min(6, (96 * 1024) / (2 * gp.n_pad * 128)));
-  gp.smem = gather_smem(gp.n_pad, gp.k_pad, gp.b_stages).total + 1024;
+  gp.smem = gather_smem(gp.n_pad, gp.k_pad, gp.b_stages, n_bias).total + 1024;
   gp.w_half = (size_t)vgroups * gp.n_pad * gp.k_pad;
   int rc = dev_alloc(ctx, p, &gp.w, 2 * gp.w_half);
   if (rc != CCT_OK) return rc;
@@ -980,7 +1039,7 @@ int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out) {
     for (int j = 0; j < f.n_pad; ++j) c[j] = ColEnt{j * G.m * G.m, 0, 0};
     rc = upload(ctx, p, &f.taps, t);
     if (rc == CCT_OK) rc = upload(ctx, p, &f.cols, c);
-    if (rc == CCT_OK) rc = finish_problem(ctx, p, f, G.g * f.tiles);
+    if (rc == CCT_OK) rc = finish_problem(ctx, p, f, G.g * f.tiles, G.bias ? G.o : 0);
   }
   // ---- data gradient as a stride-1 gather over dY: one "super pixel" = an s x s block of input pixels; accumulator
   //      columns = (d, py, px), reduction = (oc, jy, jx) with jy, jx < ceil(k/s); depth-to-space in the epilogue.
@@ -1013,7 +1072,7 @@ int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out) {
     }
     rc = upload(ctx, p, &d.taps, t);
     if (rc == CCT_OK) rc = upload(ctx, p, &d.cols, c);
-    if (rc == CCT_OK) rc = finish_problem(ctx, p, d, G.g * d.tiles);
+    if (rc == CCT_OK) rc = finish_problem(ctx, p, d, G.g * d.tiles, 0);
   }
   // ---- weight gradient: rows = (d, kr, kc) plus the all-ones row, columns = output channels of a tile
   if (rc == CCT_OK) {
@@ -1036,7 +1095,7 @@ int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out) {
     // memory); the dY tile of a k-block is staged once for all of them.
     int subs = 1;
     for (int u = 2; u <= kWgMaxSubs; ++u)
-      if (u <= p->w_mtiles && u * f.n_pad <= 512 && 2 * wg_smem(f.n_pad, u, 2).stage_bytes + 8192 <= (uint32_t)kSmemLimit)
+      if (u <= p->w_mtiles && u * (f.n_pad <= 64 ? 2 : 1) * f.n_pad <= 512 && 2 * wg_smem(f.n_pad, u, 2).stage_bytes + 8192 <= (uint32_t)kSmemLimit)
         subs = u;
     p->w_subs = subs;
     p->w_mgroups = (p->w_mtiles + subs - 1) / subs;
@@ -1074,7 +1133,7 @@ size_t umma_plan_workspace_bytes(const UmmaPlan* p) { return p->bytes; }
 
 namespace {
 
-void fill_common(GatherParams& P, const GatherProblem& gp, cct_ctx* ctx, int vgroups) {
+void fill_common(GatherParams& P, const GatherProblem& gp, cct_ctx* ctx, int vgroups, int n_bias) {
   P.taps = gp.taps; P.cols = gp.cols;
   P.tiles_per_group = gp.tiles;
   P.out_tile_channels = gp.ch_tile;
@@ -1082,6 +1141,8 @@ void fill_common(GatherParams& P, const GatherProblem& gp, cct_ctx* ctx, int vgr
   P.n_pix_tiles = (P.n_pix + kTileM - 1) / kTileM;
   P.total_tiles = P.n_pix_tiles * vgroups;
   P.a_stages = gp.a_stages; P.b_stages = gp.b_stages; P.acc_bufs = gp.acc_bufs;
+  P.dual = gp.dual; P.acc_cols = gp.acc_cols;
+  P.n_bias = P.bias ? n_bias : 0;
   P.lo_row_offset = vgroups * gp.n_pad;
   P.status = ctx->status_dev;
   P.dbg = dbg_knobs();
@@ -1115,7 +1176,7 @@ int umma_conv_forward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W,
   P.out_batch_stride = (long long)G.o * G.m * G.m;
   P.out_group_channels = G.og;
   P.relu = relu;
-  fill_common(P, f, ctx, vgroups);
+  fill_common(P, f, ctx, vgroups, G.o);
   const int grid = std::min(P.total_tiles, ctx->sm_count);
   t->begin(0, ctx->stream);
   gather_conv_kernel<<<grid, kGatherThreads, f.smem, ctx->stream>>>(P, f.map);
@@ -1182,7 +1243,7 @@ int umma_conv_backward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W
     P.out_batch_stride = (long long)G.D * G.n * G.n;
     P.out_group_channels = G.Dg;
     P.relu = 0;
-    fill_common(P, d, ctx, vgroups);
+    fill_common(P, d, ctx, vgroups, 0);
     const int grid = std::min(P.total_tiles, ctx->sm_count);
     gather_conv_kernel<<<grid, kGatherThreads, d.smem, ctx->stream>>>(P, d.map);
     t->end(3, ctx->stream);
