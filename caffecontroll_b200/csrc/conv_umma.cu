@@ -22,6 +22,7 @@
 // the fill of the next stage overlaps the MMAs.  Every mbarrier wait is bounded: when it runs out the thread sets
 // the context's status word, stops waiting on anything else, and the kernel still frees its tensor memory.
 #include <algorithm>
+#include <cstdio>
 #include <cstdlib>
 #include <vector>
 
@@ -1249,6 +1250,127 @@ int umma_conv_backward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W
     t->end(3, ctx->stream);
     CCT_CHECK_LAUNCH(ctx);
   }
+  return CCT_OK;
+}
+
+// ------------------------------------------------------------------ weight gradient without any allocation
+// Scratch for cct_conv_weight_grad_noalloc: the lowered-matrix row table followed by the split partial sums.  It is a
+// fixed part of the library image: every device that loads the library holds these 16 MiB until the process exits.
+constexpr size_t kNoAllocScratchBytes = 16u << 20;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+// Device address of the array above, per device ordinal, looked up once.  In host code the array's name is only a
+// handle for the runtime, never an address a kernel may be given.
+static void* g_noalloc_dev_ptr[64] = {};
+
+namespace {
+
+// Fills the weight-gradient row table on the device (the plan-based path builds it on the host and uploads it).
+__global__ void noalloc_taps_kernel(MaskTap* taps, int rows, int k_real, int k, int n) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < rows; i += gridDim.x * blockDim.x) {
+    MaskTap t;
+    if (i < k_real) {
+      const int d = i / (k * k), kr = (i / k) % k, kc = i % k;
+      t.off = d * n * n + kr * n + kc;
+      t.bits = kWgValidBit | (1u << kr) | (1u << (16 + kc));
+    } else {
+      t.off = 0;
+      t.bits = i == k_real ? kWgOnesBits : kWgPadBit;
+    }
+    taps[i] = t;
+  }
+}
+
+}  // namespace
+
+extern "C" int cct_conv_weight_grad_noalloc(cct_ctx* ctx, const cct_conv_desc* desc, const float* X, const float* dY,
+                                            float* dW, float* db) {
+  if (!ctx || !desc || !X || !dY || !dW) return CCT_ERR_INVALID;
+  if (desc->batch <= 0 || desc->in_depth <= 0 || desc->in_size <= 0 || desc->out_depth <= 0 || desc->kernel <= 0 ||
+      desc->stride <= 0 || desc->pad < 0 || desc->groups <= 0 || desc->in_depth % desc->groups ||
+      desc->out_depth % desc->groups || desc->in_size + 2 * desc->pad < desc->kernel)
+    return CCT_ERR_INVALID;
+  if (desc->bias_term && !db) return CCT_ERR_INVALID;
+  ConvGeom G;
+  G.B = desc->batch; G.D = desc->in_depth; G.n = desc->in_size; G.o = desc->out_depth;
+  G.k = desc->kernel; G.s = desc->stride; G.p = desc->pad; G.g = desc->groups;
+  G.m = (G.n + 2 * G.p - G.k) / G.s + 1;
+  G.Dg = G.D / G.g; G.og = G.o / G.g; G.bias = desc->bias_term != 0;
+  if ((double)G.B * G.D * G.n * G.n > 2147483647.0 || (double)G.B * G.o * G.m * G.m > 2147483647.0 ||
+      !umma_supported(G)) {
+    ctx->last_error = "cct_conv_weight_grad_noalloc: shape outside what the tensor-core path supports";
+    return CCT_ERR_UNSUPPORTED;
+  }
+  if (ctx->device < 0 || ctx->device >= 64) return CCT_ERR_UNSUPPORTED;
+  if (*ctx->status_host != 0) return CCT_ERR_TIMEOUT;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  // Set-up, once per device and with that device current: ask the runtime where the array lives on this device.
+  if (!g_noalloc_dev_ptr[ctx->device]) {
+    void* ptr = nullptr;
+    CCT_CUDA(ctx, cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+    g_noalloc_dev_ptr[ctx->device] = ptr;
+  }
+  unsigned char* scratch = static_cast<unsigned char*>(g_noalloc_dev_ptr[ctx->device]);
+
+  // Same tiling rules as the plan-based path, with the split count additionally capped by the scratch size.
+  const int tiles = channel_tiles(G.og, 1);
+  const int n_real = G.og / tiles, n_pad = round_up(n_real, 16);
+  const int k_real = G.Dg * G.k * G.k;
+  const int m_tiles = (k_real + 1 + kTileM - 1) / kTileM;
+  int subs = 1;
+  for (int u = 2; u <= kWgMaxSubs; ++u)
+    if (u <= m_tiles && u * (n_pad <= 64 ? 2 : 1) * n_pad <= 512 &&
+        2 * wg_smem(n_pad, u, 2).stage_bytes + 8192 <= (uint32_t)kSmemLimit)
+      subs = u;
+  const int mgroups = (m_tiles + subs - 1) / subs;
+  const int stages = std::max(2, std::min(kWgMaxStages, (int)((kSmemLimit - 8192) / wg_smem(n_pad, subs, 2).stage_bytes)));
+  const size_t smem = wg_smem(n_pad, subs, stages).total + 1024;
+  const int vgroups = G.g * tiles;
+  const size_t taps_bytes = ((size_t)m_tiles * kTileM * sizeof(MaskTap) + 255) & ~(size_t)255;
+  const size_t split_bytes = (size_t)vgroups * m_tiles * kTileM * n_pad * sizeof(float);
+  if (taps_bytes + split_bytes > kNoAllocScratchBytes) {
+    char msg[200];
+    snprintf(msg, sizeof msg,
+             "cct_conv_weight_grad_noalloc: this layer needs %zu bytes of scratch for one split, the built-in buffer "
+             "holds %zu",
+             taps_bytes + split_bytes, kNoAllocScratchBytes);
+    ctx->last_error = msg;
+    return CCT_ERR_UNSUPPORTED;
+  }
+  const int n_pix = G.B * G.m * G.m;
+  const int kblocks_total = (n_pix + kBlockK - 1) / kBlockK;
+  int splits = std::max(1, ctx->sm_count / (mgroups * vgroups));
+  splits = std::min(splits, std::max(1, kblocks_total / 8));
+  splits = std::min<size_t>(splits, (kNoAllocScratchBytes - taps_bytes) / split_bytes);
+  const int kblocks_per_split = (kblocks_total + splits - 1) / splits;
+  splits = (kblocks_total + kblocks_per_split - 1) / kblocks_per_split;
+
+  MaskTap* taps = reinterpret_cast<MaskTap*>(scratch);
+  float* partial = reinterpret_cast<float*>(scratch + taps_bytes);
+  WgradKernel kernel = wgrad_pick(subs, n_pad);
+  CCT_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+  noalloc_taps_kernel<<<8, 256, 0, ctx->stream>>>(taps, m_tiles * kTileM, k_real, G.k, G.n);
+  CCT_CHECK_LAUNCH(ctx);
+  WgradParams P{};
+  P.x = X; P.dy = dY; P.partial = partial; P.taps = taps;
+  P.n_pix = n_pix; P.m = G.m; P.mm = G.m * G.m; P.n = G.n; P.s = G.s; P.p = G.p; P.k = G.k;
+  P.x_batch_stride = (long long)G.D * G.n * G.n;
+  P.x_group_stride = G.Dg * G.n * G.n;
+  P.dy_batch_stride = (long long)G.o * G.m * G.m;
+  P.dy_group_channels = G.og;
+  P.tiles_per_group = tiles;
+  P.n_real = n_real; P.n_pad = n_pad;
+  P.m_tiles = m_tiles; P.subs = subs; P.stages = stages;
+  P.ones_row = k_real;
+  P.kblocks_total = kblocks_total; P.kblocks_per_split = kblocks_per_split;
+  P.status = ctx->status_dev;
+  P.dbg = 0;
+  kernel<<<dim3(mgroups, splits, vgroups), kWgThreads, smem, ctx->stream>>>(P);
+  CCT_CHECK_LAUNCH(ctx);
+  const size_t total = (size_t)vgroups * (k_real + 1) * n_real;
+  const int rgrid = (int)std::min<size_t>(std::max<size_t>((total + 255) / 256, 1), (size_t)ctx->sm_count * 8);
+  wgrad_reduce_kernel<<<rgrid, 256, 0, ctx->stream>>>(partial, dW, G.bias ? db : nullptr, splits, vgroups, tiles,
+                                                     m_tiles * kTileM, n_real, n_pad, k_real, G.og);
+  CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }
 

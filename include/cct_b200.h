@@ -113,6 +113,25 @@ int cct_conv_forward_host(cct_conv_plan* plan, const float* hX, const float* hW,
 int cct_conv_backward_host(cct_conv_plan* plan, const float* hX, const float* hW, const float* hdY, float* hdX,
                            float* hdW, float* hdb);
 
+/* The weight and bias gradient of cct_conv_backward for callers that must not allocate device memory at the point
+ * of the call.  No counterpart in the reference.  Who needs it: code running where a cudaMalloc would fail or stall —
+ * under a memory pool that already owns the whole device, inside a latency-critical section, or in a process whose
+ * allocator hooks forbid late allocations.  Such a caller cannot create a cct_conv_plan (a plan allocates its tables
+ * and split-K scratch), so this call takes the layer description directly and keeps its scratch (the lowered-matrix
+ * row table and the split partial sums) in a 16 MiB array that is part of the library image on every device that
+ * loads it.  It calls no cudaMalloc / cudaFree and no allocating library routine; X, dY, dW, db are the caller's
+ * device buffers as in cct_conv_backward (dW, db overwritten; db ignored without bias_term).
+ *   - Limit: table + one split of partial sums must fit in 16 MiB, else CCT_ERR_UNSUPPORTED with the needed size in
+ *     cct_last_error_string; larger layers simply run with fewer splits than the plan-based path would use.
+ *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress); make that first call
+ *     before starting any stream capture.
+ *   - All calls on a device share the one array and it keeps the previous call's contents (nothing in it needs to
+ *     start at zero: every slot that is read is written first by the same call).  Two calls that overlap on the GPU —
+ *     different streams or contexts of the same device — race on it; serialise them.
+ * Results equal cct_conv_backward's dW, db up to the rounding of a different split count. */
+int cct_conv_weight_grad_noalloc(cct_ctx* ctx, const cct_conv_desc* desc, const float* X, const float* dY, float* dW,
+                                 float* db);
+
 /* Per-kernel device times of the plan's most recent forward and backward call, for measurement: when enabled,
  * CUDA events are recorded around each kernel group on the context's stream.  ms[0] forward contraction,
  * ms[1] weight(+bias)-gradient contraction, ms[2] its split reduction, ms[3] data-gradient contraction(s),
