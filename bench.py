@@ -261,34 +261,23 @@ def main():
     m = out_size(w)
     X, W, bias, dY = synth(w, 1000 * (rank + 1))
     nw = W.size
-    tX, tdY = torch.from_numpy(X).to(dev), torch.from_numpy(dY).to(dev)
-    tY = torch.empty((B, o, m, m), device=dev)
-    tdX = torch.empty_like(tX)
-    params = torch.cat([torch.from_numpy(W).reshape(-1), torch.from_numpy(bias)]).to(dev)   # W | bias
-    grads = torch.zeros_like(params)                                                          # dW | db
-    hist = torch.zeros_like(params)
-    pW, pb = params.data_ptr(), params.data_ptr() + 4 * nw
-    pdW, pdb = grads.data_ptr(), grads.data_ptr() + 4 * nw
-    phW, phb = hist.data_ptr(), hist.data_ptr() + 4 * nw
-
-    desc = capi.ConvDesc(B, D, n, o, k, w["s"], w["p"], g, 1, args.algo)
-    plan = C.c_void_p()
-    capi.check(lib.cct_conv_plan_create(ctx.h, C.byref(desc), C.byref(plan)), "cct_conv_plan_create", ctx.h)
-    algo = C.c_int()
-    lib.cct_conv_plan_algo(plan, C.byref(algo))
+    # This rank's partition of the mini-batch, resident in HBM before the timed region starts.
+    from caffecontroll_b200.bridge import ConvolutionBridge, Layer, LogicalCube
+    from caffecontroll_b200.parallel import DeviceOps, ParallelizedBridge, SolverParameter
+    xin = Layer(LogicalCube.from_numpy(ctx, X), LogicalCube(ctx, n, n, D, B))
+    out = Layer(LogicalCube(ctx, m, m, o, B), LogicalCube.from_numpy(ctx, dY))
+    conv = ConvolutionBridge(xin, out, k, w["s"], w["p"], g, True, algo=args.algo)
+    pbridge = ParallelizedBridge(conv, SolverParameter(SOLVER["base_lr"], "step", 0.1, 100000, momentum=SOLVER["momentum"],
+                                                       weight_decay=SOLVER["weight_decay"]), DeviceOps(ctx))
+    conv.p_model_cube.upload(W)
+    conv.p_bias_cube.upload(bias)
+    plan = conv.plan
+    algo = C.c_int(conv.algo)
     vp = C.c_void_p
-    lr = SOLVER["base_lr"]
 
     def step():
-        capi.check(lib.cct_conv_forward(plan, vp(tX.data_ptr()), vp(pW), vp(pb), vp(tY.data_ptr()), 0), "forward", ctx.h)
-        capi.check(lib.cct_conv_backward(plan, vp(tX.data_ptr()), vp(pW), vp(tdY.data_ptr()), vp(tdX.data_ptr()),
-                                         vp(pdW), vp(pdb)), "backward", ctx.h)
-        if world > 1:
-            dist.all_reduce(grads)  # SUM over partitions, as ParallelizedBridge does on the host
-        # weights: lr_mult 1, decay_mult 1; bias: lr_mult 2, decay_mult 0 (CaffeNet's blobs_lr / weight_decay)
-        capi.check(lib.cct_sgd_step(ctx.h, nw, vp(pW), vp(pdW), vp(phW), lr, SOLVER["momentum"],
-                                    SOLVER["weight_decay"]), "sgd W", ctx.h)
-        capi.check(lib.cct_sgd_step(ctx.h, o, vp(pb), vp(pdb), vp(phb), 2 * lr, SOLVER["momentum"], 0.0), "sgd b", ctx.h)
+        pbridge.forward()   # cct_conv_forward
+        pbridge.backward()  # cct_conv_backward (dX, dW, db) -> all-reduce(SUM) of dW|db over ranks -> cct_sgd_step x2
 
     def barrier():
         if world > 1:
@@ -375,7 +364,7 @@ def main():
     h2d = 4 * (X.size + W.size + bias.size + dY.size)
     d2h = 4 * (hY.numel() + X.size + W.size + bias.size)
 
-    lib.cct_conv_plan_destroy(plan)
+    conv.close()
     if rank == 0:
         cpu = None
         if world == 1 and not args.no_cpu_baseline:

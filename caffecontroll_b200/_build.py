@@ -38,5 +38,22 @@ def build(force=False, verbose_ptxas=False):
     return LIB
 
 
+HOST_TEST = os.path.join(HERE, "host", "host_selftest")
+
+
+def build_host_selftest(force=False):
+    """The C++ bridge mirror's self-test program (g++ only: it sees nothing but the C ABI)."""
+    src = os.path.join(HERE, "host", "host_selftest.cpp")
+    hdr = os.path.join(HERE, "host", "cct_host.h")
+    if not force and os.path.exists(HOST_TEST) and all(
+            os.path.getmtime(f) <= os.path.getmtime(HOST_TEST) for f in (src, hdr, LIB)):
+        return HOST_TEST
+    cmd = ["g++", "-std=c++14", "-O2", "-Wall", "-o", HOST_TEST, src, "-L" + HERE, "-lcct_b200", "-Wl,-rpath,$ORIGIN/.."]
+    print(" ".join(cmd), flush=True)
+    subprocess.check_call(cmd)
+    return HOST_TEST
+
+
 if __name__ == "__main__":
     build(force="--force" in sys.argv, verbose_ptxas="-v" in sys.argv)
+    build_host_selftest(force="--force" in sys.argv)

@@ -1,0 +1,273 @@
+// C++ host-side mirror of the reference types the convolution hot path touches, on top of the C ABI alone
+// (include/cct_b200.h).  Member names and call order follow the reference so code written against it reads the same:
+//   LogicalCube<T>            src/LogicalCube.h (R x C x D x B, "c" fastest = NCHW; owns memory iff built from sizes)
+//   Layer                     src/Layer.h:36-37 (a data cube and a gradient cube)
+//   PhysicalOperator          src/bridges/PhysicalOperator.h:15-30 (forward()/backward())
+//   B200Driver                the slice of src/sched/DeviceDriver.h:56-274 the path needs
+//   ConvolutionBridge         src/bridges/ConvolutionBridge.h + AbstractBridge.h members (iR..oB, p_*_layer,
+//                             needs_to_calc_backward_grad, bias_term, model / bias / gradient cube accessors)
+//   SGDGradientUpdater        src/algorithms/GradientUpdater.h:154-193
+//   ParallelizedBridge        one partition per process: owns model, gradient and history, sums gradients through a
+//                             caller-supplied all-reduce (src/bridges/ParallelizedBridge_impl.hxx:876-971), then updates
+// Errors: the reference's convention is print + assert(false) (src/sched/DeviceDriver.h:48-51); here the failing call
+// prints the library's message and aborts, unless a handler was installed with B200Driver::set_error_handler.
+#pragma once
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <functional>
+#include <string>
+#include <vector>
+
+#include "../../include/cct_b200.h"
+
+namespace cct {
+
+class B200Driver {
+ public:
+  typedef void (*ErrorHandler)(int code, const char* what, const char* detail);
+  explicit B200Driver(int device = 0, void* cuda_stream = nullptr, bool own_stream = true) {
+    const int rc = own_stream ? cct_ctx_create(device, &ctx_) : cct_ctx_create_on_stream(device, cuda_stream, &ctx_);
+    if (rc != CCT_OK) fail(rc, "cct_ctx_create");
+  }
+  ~B200Driver() {
+    if (ctx_) cct_ctx_destroy(ctx_);
+  }
+  B200Driver(const B200Driver&) = delete;
+  B200Driver& operator=(const B200Driver&) = delete;
+
+  void* malloc(size_t bytes) { void* p = nullptr; check(cct_malloc(ctx_, bytes, &p), "cct_malloc"); return p; }
+  void free(void* p) { check(cct_free(ctx_, p), "cct_free"); }
+  void memcpy_h2d(void* dst, const void* src, size_t bytes) { check(cct_memcpy_h2d(ctx_, dst, src, bytes), "cct_memcpy_h2d"); }
+  void memcpy_d2h(void* dst, const void* src, size_t bytes) { check(cct_memcpy_d2h(ctx_, dst, src, bytes), "cct_memcpy_d2h"); }
+  void memset(void* p, int v, size_t bytes) { check(cct_memset(ctx_, p, v, bytes), "cct_memset"); }
+  void sconstant_initialize(float* p, size_t count, float v) { check(cct_fill_f32(ctx_, p, count, v), "cct_fill_f32"); }
+  void device_sync() { check(cct_sync(ctx_), "cct_sync"); }
+  cct_ctx* ctx() const { return ctx_; }
+
+  void check(int rc, const char* what) {
+    if (rc != CCT_OK) fail(rc, what);
+  }
+  static void set_error_handler(ErrorHandler h) { handler() = h; }
+
+ private:
+  static ErrorHandler& handler() { static ErrorHandler h = nullptr; return h; }
+  void fail(int rc, const char* what) {
+    const char* detail = ctx_ ? cct_last_error_string(ctx_) : "";
+    if (handler()) { handler()(rc, what, detail); return; }
+    std::fprintf(stderr, "cct_b200: %s failed with code %d: %s\n", what, rc, detail);
+    std::abort();
+  }
+  cct_ctx* ctx_ = nullptr;
+};
+
+template <typename T>
+class LogicalCube {
+ public:
+  const size_t R, C, D, B, n_elements;
+  LogicalCube(size_t r, size_t c, size_t d, size_t b, B200Driver* driver)
+      : R(r), C(c), D(d), B(b), n_elements(r * c * d * b), p_driver_(driver), own_data_(true) {
+    p_data_ = static_cast<T*>(driver->malloc(n_elements * sizeof(T)));
+  }
+  LogicalCube(T* data, size_t r, size_t c, size_t d, size_t b, B200Driver* driver)
+      : R(r), C(c), D(d), B(b), n_elements(r * c * d * b), p_driver_(driver), own_data_(false), p_data_(data) {}
+  ~LogicalCube() {
+    if (own_data_ && p_data_) p_driver_->free(p_data_);
+  }
+  LogicalCube(const LogicalCube&) = delete;
+  T* get_p_data() const { return p_data_; }
+  void set_p_data(T* data) {  // an owning cube releases its memory first (src/LogicalCube_impl.hxx:20-34)
+    if (own_data_ && p_data_) p_driver_->free(p_data_);
+    own_data_ = false;
+    p_data_ = data;
+  }
+  void reset_cube(T v = T(0)) { p_driver_->sconstant_initialize(reinterpret_cast<float*>(p_data_), n_elements, (float)v); }
+  void copy_from_host(const T* src) { p_driver_->memcpy_h2d(p_data_, src, n_elements * sizeof(T)); p_driver_->device_sync(); }
+  void copy_to_host(T* dst) const { p_driver_->memcpy_d2h(dst, p_data_, n_elements * sizeof(T)); p_driver_->device_sync(); }
+
+ private:
+  B200Driver* p_driver_;
+  bool own_data_;
+  T* p_data_ = nullptr;
+};
+
+struct Layer {
+  LogicalCube<float>* const p_data_cube;
+  LogicalCube<float>* const p_gradient_cube;
+  Layer(LogicalCube<float>* data, LogicalCube<float>* grad) : p_data_cube(data), p_gradient_cube(grad) {}
+};
+
+class PhysicalOperator {
+ public:
+  int run_with_n_threads = 1;
+  virtual void forward() = 0;
+  virtual void backward() = 0;
+  virtual ~PhysicalOperator() {}
+};
+
+// The convolution_param fields the bridge reads (src/bridges/ConvolutionBridge_impl.hxx:33-60).
+struct ConvolutionParameter {
+  int num_output = 0, kernel_size = 0, stride = 1, pad = 0, group = 1;
+  bool bias_term = true;
+};
+
+class ConvolutionBridge : public PhysicalOperator {
+ public:
+  const size_t iR, iC, iD, iB, oR, oC, oD, oB;
+  Layer* const p_input_layer;
+  Layer* const p_output_layer;
+  B200Driver* const p_driver;
+  bool needs_to_calc_backward_grad = true;
+  const bool bias_term;
+  bool fuse_relu = false;  // fold the ReLU bridge that follows into the epilogue
+  const size_t K, stride, padding, group;
+
+  ConvolutionBridge(Layer* in, Layer* out, const ConvolutionParameter& cp, B200Driver* driver, int algo = CCT_ALGO_AUTO)
+      : iR(in->p_data_cube->R), iC(in->p_data_cube->C), iD(in->p_data_cube->D), iB(in->p_data_cube->B),
+        oR(out->p_data_cube->R), oC(out->p_data_cube->C), oD(out->p_data_cube->D), oB(out->p_data_cube->B),
+        p_input_layer(in), p_output_layer(out), p_driver(driver), bias_term(cp.bias_term), K(cp.kernel_size),
+        stride(cp.stride), padding(cp.pad), group(cp.group) {
+    cct_conv_desc d = {(int)iB, (int)iD, (int)iR, (int)oD, cp.kernel_size, cp.stride, cp.pad, cp.group, cp.bias_term ? 1 : 0,
+                       algo};
+    int m = 0;
+    driver->check(cct_conv_out_size(&d, &m), "cct_conv_out_size");
+    if (iR != iC || (size_t)m != oR || oR != oC || iB != oB || (int)oD != cp.num_output)
+      driver->check(CCT_ERR_INVALID, "ConvolutionBridge: layer shapes do not match the convolution");
+    driver->check(cct_conv_plan_create(driver->ctx(), &d, &plan_), "cct_conv_plan_create");
+    const size_t dg = iD / cp.group;
+    p_model_cube_ = new LogicalCube<float>(K, K, dg, oD, driver);
+    p_model_gradient_cube_ = new LogicalCube<float>(K, K, dg, oD, driver);
+    if (bias_term) {
+      p_bias_cube_ = new LogicalCube<float>(1, 1, oD, 1, driver);
+      p_bias_gradient_cube_ = new LogicalCube<float>(1, 1, oD, 1, driver);
+      p_bias_cube_->reset_cube(0.f);
+    }
+  }
+  ~ConvolutionBridge() {
+    if (plan_) cct_conv_plan_destroy(plan_);
+    delete p_model_cube_; delete p_model_gradient_cube_; delete p_bias_cube_; delete p_bias_gradient_cube_;
+  }
+
+  LogicalCube<float>* get_model_cube() { return p_model_cube_; }
+  LogicalCube<float>* get_bias_cube() { return p_bias_cube_; }
+  LogicalCube<float>* get_model_grad_cube() { return p_model_gradient_cube_; }
+  LogicalCube<float>* get_bias_grad_cube() { return p_bias_gradient_cube_; }
+  // The scheduler may hand the bridge its own model / bias / gradient storage (ParallelizedBridge_impl.hxx:519-532).
+  void set_model_cube(float* p) { p_model_cube_->set_p_data(p); }
+  void set_bias_cube(float* p) { if (p_bias_cube_) p_bias_cube_->set_p_data(p); }
+  void set_model_grad_cube(float* p) { p_model_gradient_cube_->set_p_data(p); }
+  void set_bias_grad_cube(float* p) { if (p_bias_gradient_cube_) p_bias_gradient_cube_->set_p_data(p); }
+
+  void forward() override {
+    p_driver->check(cct_conv_forward(plan_, p_input_layer->p_data_cube->get_p_data(), p_model_cube_->get_p_data(),
+                                     bias_term ? p_bias_cube_->get_p_data() : nullptr,
+                                     p_output_layer->p_data_cube->get_p_data(), fuse_relu ? 1 : 0),
+                    "cct_conv_forward");
+  }
+  void backward() override {
+    p_driver->check(cct_conv_backward(plan_, p_input_layer->p_data_cube->get_p_data(), p_model_cube_->get_p_data(),
+                                      p_output_layer->p_gradient_cube->get_p_data(),
+                                      needs_to_calc_backward_grad ? p_input_layer->p_gradient_cube->get_p_data() : nullptr,
+                                      p_model_gradient_cube_->get_p_data(),
+                                      bias_term ? p_bias_gradient_cube_->get_p_data() : nullptr),
+                    "cct_conv_backward");
+  }
+
+ private:
+  cct_conv_plan* plan_ = nullptr;
+  LogicalCube<float>* p_model_cube_ = nullptr;
+  LogicalCube<float>* p_model_gradient_cube_ = nullptr;
+  LogicalCube<float>* p_bias_cube_ = nullptr;
+  LogicalCube<float>* p_bias_gradient_cube_ = nullptr;
+};
+
+// The solver fields the updater reads, with the reference's learning-rate policies (src/util.h:76-100).
+struct SolverParameter {
+  float base_lr = 0.01f, gamma = 0.1f, power = 0.f, momentum = 0.9f, weight_decay = 0.0005f;
+  int stepsize = 100000, max_iter = 1;
+  std::string lr_policy = "step";
+  float learning_rate(float iter) const {
+    if (lr_policy == "fixed") return base_lr;
+    if (lr_policy == "step") return (float)(base_lr * std::pow((double)gamma, (double)(int)(iter / stepsize)));
+    if (lr_policy == "exp") return (float)(base_lr * std::pow((double)gamma, (double)iter));
+    if (lr_policy == "inv") return (float)(base_lr * std::pow(1.0 + gamma * iter, -(double)power));
+    if (lr_policy == "poly") return (float)(base_lr * std::pow(1.0 - (iter / max_iter), (double)power));
+    if (lr_policy == "sigmoid") return (float)(base_lr * (1.0 / (1.0 + std::exp(-gamma * (iter - stepsize)))));
+    std::fprintf(stderr, "Unknown learning rate policy: %s\n", lr_policy.c_str());
+    std::abort();
+  }
+};
+
+class SGDGradientUpdater {
+ public:
+  int current_iter = 0;
+  SGDGradientUpdater(size_t n_elements, float* p_model, const SolverParameter* solver, float base_learning_rate,
+                     float base_regularization, B200Driver* driver)
+      : n_elements_(n_elements), p_model_(p_model), p_solver_(solver), blr_(base_learning_rate),
+        br_(base_regularization), p_driver_(driver), history_(n_elements, 1, 1, 1, driver) {
+    history_.reset_cube(0.f);
+  }
+  void set_current_iter(int it) { current_iter = it; }
+  float get_stepsize() const { return blr_ * p_solver_->learning_rate((float)current_iter); }
+  float get_weight_decay() const { return p_solver_->weight_decay * br_; }
+  void update(float* p_gradient) {  // ++iter; g += lambda w; h = lr g + mu h; w -= h
+    ++current_iter;
+    p_driver_->check(cct_sgd_step(p_driver_->ctx(), n_elements_, p_model_, p_gradient, history_.get_p_data(), get_stepsize(),
+                                  p_solver_->momentum, get_weight_decay()),
+                     "cct_sgd_step");
+  }
+
+ private:
+  size_t n_elements_;
+  float* p_model_;
+  const SolverParameter* p_solver_;
+  float blr_, br_;
+  B200Driver* p_driver_;
+  LogicalCube<float> history_;
+};
+
+// One process = one batch partition.  forward()/backward() run the sub-bridge; backward() then sums the model and bias
+// gradients over all partitions through `allreduce_sum` (NULL: single partition) and applies the SGD update, identical
+// on every partition.  Model and bias (and their gradients) are contiguous (W | bias) so one all-reduce covers both.
+class ParallelizedBridge : public PhysicalOperator {
+ public:
+  typedef std::function<void(float* device_buffer, size_t count)> AllReduceSum;
+  ParallelizedBridge(ConvolutionBridge* sub, const SolverParameter* solver, B200Driver* driver,
+                     AllReduceSum allreduce_sum = nullptr, float model_lr_mult = 1.f, float model_decay_mult = 1.f,
+                     float bias_lr_mult = 2.f, float bias_decay_mult = 0.f)
+      : sub_(sub), p_driver_(driver), allreduce_(allreduce_sum), n_w_(sub->get_model_cube()->n_elements),
+        n_b_(sub->bias_term ? sub->get_bias_cube()->n_elements : 0), params_(n_w_ + n_b_, 1, 1, 1, driver),
+        grads_(n_w_ + n_b_, 1, 1, 1, driver),
+        p_grad_updater(n_w_, params_.get_p_data(), solver, model_lr_mult, model_decay_mult, driver),
+        p_grad_updater_bias(n_b_ ? n_b_ : 1, params_.get_p_data() + n_w_, solver, bias_lr_mult, bias_decay_mult, driver) {
+    sub->set_model_cube(params_.get_p_data());
+    sub->set_model_grad_cube(grads_.get_p_data());
+    sub->set_bias_cube(params_.get_p_data() + n_w_);
+    sub->set_bias_grad_cube(grads_.get_p_data() + n_w_);
+  }
+  bool update_model_gradients = true;
+  void set_update_model_gradients(bool v) { update_model_gradients = v; }
+  LogicalCube<float>* get_model_cube() { return sub_->get_model_cube(); }
+  LogicalCube<float>* get_bias_cube() { return sub_->get_bias_cube(); }
+  float* get_model_gradient_device() { return grads_.get_p_data(); }
+  void forward() override { sub_->forward(); }
+  void backward() override {
+    sub_->backward();
+    if (allreduce_) allreduce_(grads_.get_p_data(), n_w_ + n_b_);
+    if (!update_model_gradients) return;
+    p_grad_updater.update(grads_.get_p_data());
+    if (n_b_) p_grad_updater_bias.update(grads_.get_p_data() + n_w_);
+  }
+
+ private:
+  ConvolutionBridge* sub_;
+  B200Driver* p_driver_;
+  AllReduceSum allreduce_;
+  size_t n_w_, n_b_;
+  LogicalCube<float> params_, grads_;
+
+ public:
+  SGDGradientUpdater p_grad_updater, p_grad_updater_bias;
+};
+
+}  // namespace cct

@@ -1,0 +1,58 @@
+"""The C++ mirror of the reference's bridge interface (caffecontroll_b200/host/cct_host.h): it must compile and link
+against the C ABI alone (CPU check), and on a GPU produce what the CPU oracle produces for the same files."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from tests.parity import TOL, assert_close, make_inputs, maxnorm_rel  # noqa: E402
+
+
+def _build():
+    from caffecontroll_b200 import _build
+    _build.build()
+    return _build.build_host_selftest()
+
+
+def test_host_mirror_compiles_and_links_against_the_c_abi_only():
+    exe = _build()
+    assert os.path.exists(exe)
+    with open(os.path.join(ROOT, "caffecontroll_b200", "host", "cct_host.h")) as f:
+        text = f.read()
+    assert "cuda" not in text.lower().replace("cuda_stream", "")  # no CUDA headers or types: plain C ABI
+    out = subprocess.run([exe], capture_output=True, text=True)
+    assert out.returncode == 2 and "usage" in out.stderr
+
+
+@pytest.mark.gpu
+def test_host_mirror_matches_oracle(port, tmp_path):
+    exe = _build()
+    B, D, n, o, k, s, p, g = 4, 6, 13, 10, 3, 1, 1, 2
+    X, W, b, dY = make_inputs(55, B, D, n, o, k, s, p, g)
+    for name, arr in (("X", X), ("W", W), ("b", b), ("dY", dY)):
+        arr.tofile(os.path.join(str(tmp_path), name + ".bin"))
+    steps = 2
+    subprocess.run([exe, str(tmp_path)] + [str(v) for v in (B, D, n, o, k, s, p, g, steps)], check=True)
+    rd = lambda name, shape: np.fromfile(os.path.join(str(tmp_path), name + ".bin"), np.float32).reshape(shape)
+    m = (n + 2 * p - k) // s + 1
+    Yr = port.conv_forward(X, W, b, k, s, p, g)
+    dXr, dWr, dbr = port.conv_backward(X, W, dY, k, s, p, g)
+    assert_close(rd("Y", (B, o, m, m)), Yr, "Y")
+    assert_close(rd("dX", X.shape), dXr, "dX")
+    assert_close(rd("dW", W.shape), dWr, "dW")
+    assert_close(rd("db", (o,)), dbr, "db")
+    Wc, bc = W.copy(), b.copy()
+    hw, hb = np.zeros_like(W), np.zeros_like(b)
+    for it in range(1, steps + 1):
+        _, dW, db = port.conv_backward(X, Wc, dY, k, s, p, g, needs_dx=False)
+        lr = port.learning_rate("step", 0.01, 0.1, float(it), 100000.0)
+        port.sgd_update(Wc, dW, hw, lr, 0.9, 0.0005)
+        port.sgd_update(bc, db, hb, float(np.float32(lr * 2.0)), 0.9, 0.0)
+    assert maxnorm_rel(rd("Wnew", W.shape), Wc) <= TOL
+    assert maxnorm_rel(rd("bnew", (o,)), bc) <= TOL
