@@ -86,7 +86,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
-                                          "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
         except OSError:
@@ -223,8 +223,8 @@ def config_of(args, w, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="alexnet_conv1", choices=sorted(WORKLOADS))
     ap.add_argument("--algo", type=int, default=0, help="0 auto, 1 SIMT fp32, 2 tcgen05 3xTF32")
@@ -322,9 +322,8 @@ def main():
     tensor_peak = peaks["bf16_tflops"] / 2.0 / 3.0  # TF32 = 1/2 bf16 rate; 3 MMAs per product
     dom = max(passes, key=lambda x: passes[x])
     ach = F / (passes[dom] * 1e-3) / 1e12 if passes[dom] > 0 else 0.0
-    n_phase = w["s"] ** 2
     roofline = {
-        "bound": "tensor", "kernel": {"forward": "gather_conv_kernel", "dgrad": "gather_conv_kernel (x%d stride phases)" % n_phase,
+        "bound": "tensor", "kernel": {"forward": "gather_conv_kernel (forward)", "dgrad": "gather_conv_kernel (data gradient)",
                                       "wgrad": "wgrad_kernel"}[dom] if algo.value == 2 else "simt_%s" % dom,
         "pass": dom, "achieved": ach, "peak": tensor_peak, "unit": "TFLOP/s", "frac": ach / tensor_peak,
         "traffic": None,
@@ -370,7 +369,8 @@ def main():
         if world == 1 and not args.no_cpu_baseline:
             cpu = cpu_reference_time(w, 3, 1, False)
             cpu.pop("seconds_per_step", None)
-        launches_per_step = (2 + 2 + 2 * n_phase + 2) if algo.value == 2 else (1 + 3 + 2)
+        # tcgen05 path: pack + gather (forward); wgrad + reduce + pack + gather (backward); two SGD kernels
+        launches_per_step = (2 + 4 + 2) if algo.value == 2 else (1 + 3 + 2)
         line = {
             "metric": METRIC, "value": world * B / (ms_step * 1e-3), "unit": "images/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
