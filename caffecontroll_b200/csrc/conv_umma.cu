@@ -85,7 +85,33 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return done;
 }
 
+// Position in a ring of `n` stages: stage index and how many times the ring has wrapped.  Kept incrementally: the
+// GPU has no integer divider, and a runtime "% n" in a one-thread issue loop costs more than the MMAs it feeds.
+struct Ring {
+  int idx = 0, use = 0;
+  __device__ __forceinline__ void advance(int n) {
+    if (++idx == n) { idx = 0; ++use; }
+  }
+};
+
+// try_wait that lets the hardware park the thread for up to `ns` nanoseconds while the phase is incomplete (it is
+// woken when the phase completes).  A parked warp takes no issue slots from the warps that do the work.
+__device__ __forceinline__ uint32_t mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return done;
+}
+
 // Bounded wait.  Returns false (and records `code` in the status word) after about 0.2 s without completion.
+// PARK = true: the many warps that mostly wait (producers, epilogue) park in hardware between polls; the MMA and TMA
+// threads, whose wake-up latency is on the critical path, poll.
+template <bool PARK = true>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, bool& failed, int* status, int code) {
   if (failed) return false;
   if (mbar_try_wait(bar, parity)) return true;
@@ -93,7 +119,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, bool& f
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 256; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
+      if (PARK ? mbar_try_wait_parked(bar, parity, 20000u) : mbar_try_wait(bar, parity)) return true;
     if (clock64() - t0 > 400000000LL) break;
   }
   failed = true;
@@ -341,14 +367,14 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
     }
     PROF_DECL;
     for (int it = group; it < my_stages; it += 4) {
-      const int sa = it % P.a_stages, use = it / P.a_stages;
+      const int sa = it & (P.a_stages - 1), use = it >> (P.a_stages == 4 ? 2 : 1);  // a_stages is 2 or 4
       const uint32_t st_addr = lane_addr + (uint32_t)(sa * 64);
       const uint32_t full_bar = a_full + 8u * sa, empty_bar = a_empty + 8u * sa;
       PROF_LAP(0);
       // The stage was last drained `use - 1` phases into its barrier's life.  A parity wait is only meaningful for
       // the phase that follows one already seen complete, and with two stages this set revisits a stage only every
       // other use, so it walks through the phases it skipped.
-      for (int ph = use - 4 / P.a_stages; ph < use; ++ph)
+      for (int ph = use - (P.a_stages == 4 ? 1 : 2); ph < use; ++ph)
         if (ph >= 0) mbar_wait(empty_bar, (uint32_t)ph & 1u, failed, P.status, 0x10);
       tc_fence_after();
       PROF_LAP(1);
@@ -381,20 +407,21 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
     if (lane == 0) {
       const uint32_t idesc = make_idesc(P.acc_cols);
       int it = 0, tile_iter = 0;
+      Ring ra, rb;
       PROF_DECL;
       for (int t = blockIdx.x; t < P.total_tiles; t += gridDim.x, ++tile_iter) {
-        const int buf = tile_iter % P.acc_bufs, ause = tile_iter / P.acc_bufs;
+        const int buf = tile_iter & (P.acc_bufs - 1), ause = tile_iter >> (P.acc_bufs - 1);  // acc_bufs is 1 or 2
         PROF_LAP(0);
-        if (ause > 0) mbar_wait(acc_empty + 8u * buf, (uint32_t)(ause - 1) & 1u, failed, P.status, 0x20);
+        if (ause > 0) mbar_wait<false>(acc_empty + 8u * buf, (uint32_t)(ause - 1) & 1u, failed, P.status, 0x20);
         tc_fence_after();
         PROF_LAP(1);
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * P.acc_cols);
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const int sa = it % P.a_stages, sb = it % P.b_stages;
+          const int sa = ra.idx, sb = rb.idx;
           PROF_LAP(0);
-          mbar_wait(a_full + 8u * sa, (uint32_t)(it / P.a_stages) & 1u, failed, P.status, 0x40);
+          mbar_wait<false>(a_full + 8u * sa, (uint32_t)ra.use & 1u, failed, P.status, 0x40);
           PROF_LAP(2);
-          mbar_wait(b_full + 8u * sb, (uint32_t)(it / P.b_stages) & 1u, failed, P.status, 0x80);
+          mbar_wait<false>(b_full + 8u * sb, (uint32_t)rb.use & 1u, failed, P.status, 0x80);
           tc_fence_after();
           PROF_LAP(3);
           const uint32_t b_hi = base + (uint32_t)sb * L.b_stage_bytes, b_lo = b_hi + (uint32_t)P.n_pad * 128u;
@@ -421,8 +448,12 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
               }
             }
           }
+          PROF_LAP(4);
           umma_commit(a_empty + 8u * sa);
           umma_commit(b_empty + 8u * sb);
+          ra.advance(P.a_stages);
+          rb.advance(P.b_stages);
+          PROF_LAP(5);
         }
         umma_commit(acc_full + 8u * buf);
       }
@@ -432,16 +463,17 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
   } else if (warp == kTmaWarp) {
     // ------------------------------------------------------------------ weight tiles by TMA
     if (lane == 0) {
-      int it = 0;
+      Ring rb;
       for (int t = blockIdx.x; t < P.total_tiles; t += gridDim.x) {
         const int vg = t / P.n_pix_tiles;
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const int sb = it % P.b_stages, use = it / P.b_stages;
-          if (use > 0) mbar_wait(b_empty + 8u * sb, (uint32_t)(use - 1) & 1u, failed, P.status, 0x100);
+        for (int kb = 0; kb < kblocks; ++kb) {
+          const int sb = rb.idx;
+          if (rb.use > 0) mbar_wait<false>(b_empty + 8u * sb, (uint32_t)(rb.use - 1) & 1u, failed, P.status, 0x100);
           const uint32_t b_hi = base + (uint32_t)sb * L.b_stage_bytes, b_lo = b_hi + (uint32_t)P.n_pad * 128u;
           mbar_expect_tx(b_full + 8u * sb, L.b_stage_bytes);
           tma_load_2d(b_hi, &w_map, kb * kBlockK, vg * P.n_pad, b_full + 8u * sb);
           tma_load_2d(b_lo, &w_map, kb * kBlockK, P.lo_row_offset + vg * P.n_pad, b_full + 8u * sb);
+          rb.advance(P.b_stages);
         }
       }
     }
@@ -454,7 +486,7 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
     for (int t = blockIdx.x; t < P.total_tiles; t += gridDim.x, ++tile_iter) {
       const int vg = t / P.n_pix_tiles, ptile = t - vg * P.n_pix_tiles;
       const int grp = vg / P.tiles_per_group, ntile = vg % P.tiles_per_group;
-      const int buf = tile_iter % P.acc_bufs, ause = tile_iter / P.acc_bufs;
+      const int buf = tile_iter & (P.acc_bufs - 1), ause = tile_iter >> (P.acc_bufs - 1);
       const int pix = ptile * kTileM + row;
       int b = 0, qy = 0, qx = 0;
       if (pix < P.n_pix) {
@@ -686,8 +718,9 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
     };
     load_rows();
     PROF_DECL;
-    for (int kbl = 0; kbl < kblocks; ++kbl) {
-      const int s = kbl % P.stages, use = kbl / P.stages;
+    Ring ring;
+    for (int kbl = 0; kbl < kblocks; ++kbl, ring.advance(P.stages)) {
+      const int s = ring.idx, use = ring.use;
       uint8_t* st = lane_ptr + (size_t)s * L.stage_bytes;
       PROF_LAP(0);
       if (use > 0) mbar_wait(empty + 8u * s, (uint32_t)(use - 1) & 1u, failed, P.status, 0x10);
@@ -752,10 +785,11 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
     if (lane == 0) {
       const uint32_t idesc = make_idesc(kAccCols);
       PROF_DECL;
-      for (int kbl = 0; kbl < kblocks; ++kbl) {
-        const int s = kbl % P.stages;
+      Ring ring;
+      for (int kbl = 0; kbl < kblocks; ++kbl, ring.advance(P.stages)) {
+        const int s = ring.idx;
         PROF_LAP(0);
-        mbar_wait(full + 8u * s, (uint32_t)(kbl / P.stages) & 1u, failed, P.status, 0x40);
+        mbar_wait<false>(full + 8u * s, (uint32_t)ring.use & 1u, failed, P.status, 0x40);
         tc_fence_after();
         PROF_LAP(1);
         const uint32_t st = base + (uint32_t)s * L.stage_bytes;
