@@ -85,6 +85,33 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return done;
 }
 
+// v = ((mask & bits) == bits) ? *p : 0 as straight-line predicated code: written through the compiler, each guarded
+// load becomes a branch around the load, and the branch bookkeeping costs more issue slots than the load itself.
+__device__ __forceinline__ float ldg_if_bits(const float* p, uint32_t mask, uint32_t bits) {
+  float v;
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t.reg .b32 t;\n\t"
+      "and.b32 t, %2, %3;\n\t"
+      "setp.eq.u32 q, t, %3;\n\t"
+      "mov.f32 %0, 0f00000000;\n\t"
+      "@q ld.global.nc.f32 %0, [%1];\n\t}"
+      : "=f"(v)
+      : "l"(p), "r"(mask), "r"(bits));
+  return v;
+}
+// v = flag ? *p : 0, same form.
+__device__ __forceinline__ float ldg_if(const float* p, uint32_t flag) {
+  float v;
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t"
+      "setp.ne.u32 q, %2, 0;\n\t"
+      "mov.f32 %0, 0f00000000;\n\t"
+      "@q ld.global.nc.f32 %0, [%1];\n\t}"
+      : "=f"(v)
+      : "l"(p), "r"(flag));
+  return v;
+}
+
 // Position in a ring of `n` stages: stage index and how many times the ring has wrapped.  Kept incrementally: the
 // GPU has no integer divider, and a runtime "% n" in a one-thread issue loop costs more than the MMAs it feeds.
 struct Ring {
@@ -355,8 +382,7 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
 #pragma unroll
       for (int e = 0; e < kBlockK; ++e) {
         const MaskTap tap = tp[e];
-        v[e] = 0.f;
-        if ((mask & tap.bits) == tap.bits && !DBG(P, 1)) v[e] = __ldg(in_px + tap.off);
+        v[e] = ldg_if_bits(in_px + tap.off, DBG(P, 1) ? 0u : mask, tap.bits);
       }
     };
     int tile_local = 0, kb = group;
@@ -699,8 +725,7 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
 #pragma unroll
         for (int i = 0; i < kARows; ++i) {
           const MaskTap tap = my_taps[kWgProdWarps * i];
-          va[i] = 0.f;
-          if ((mask & tap.bits) == tap.bits && !DBG(P, 1)) va[i] = __ldg(xsrc + tap.off);
+          va[i] = ldg_if_bits(xsrc + tap.off, DBG(P, 1) ? 0u : mask, tap.bits);
         }
       } else {
 #pragma unroll
@@ -712,8 +737,7 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
       }
 #pragma unroll
       for (int i = 0; i < NB; ++i) {
-        vb[i] = 0.f;
-        if (ok && i < b_live && !DBG(P, 2)) vb[i] = __ldg(dsrc + i * dy_step);
+        vb[i] = ldg_if(dsrc + i * dy_step, (ok && i < b_live && !DBG(P, 2)) ? 1u : 0u);
       }
     };
     load_rows();
