@@ -225,7 +225,7 @@ __device__ __forceinline__ void split_tf32_trunc(float x, uint32_t& hi, uint32_t
 constexpr int kProducerWarps = 16;  // four sets of four; set g fills the A stages with index == g (mod 4)
 constexpr int kMmaWarp = 16, kTmaWarp = 17, kEpiWarp0 = 18, kEpiWarps = 4;
 constexpr int kGatherThreads = (kEpiWarp0 + kEpiWarps) * 32;  // 704
-constexpr int kMaxAStages = 4, kMaxBStages = 8, kMaxAccBufs = 2;
+constexpr int kMaxAStages = 4, kMaxAccBufs = 2;
 
 struct alignas(8) ColEnt {  // one accumulator column -> where it lands in the output
   int off;       // element offset from the pixel's output origin
@@ -302,7 +302,7 @@ __host__ __device__ inline GatherSmem gather_smem(int n_pad, int k_pad, int b_st
   L.cols_off = L.taps_off + (uint32_t)k_pad * 8u;
   L.bias_off = L.cols_off + (uint32_t)n_pad * 8u;
   L.bars_off = (L.bias_off + (uint32_t)n_bias * 4u + 15u) & ~15u;
-  L.total = L.bars_off + 8u * (2 * kMaxAStages + 2 * kMaxBStages + 2 * kMaxAccBufs) + 16u;
+  L.total = L.bars_off + 8u * (2 * kMaxAStages + 2 * kMaxAccBufs) + 16u;
   return L;
 }
 
@@ -313,8 +313,7 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
   const GatherSmem L = gather_smem(P.n_pad, P.k_pad, P.b_stages, P.n_bias);
   const uint32_t bars = base + L.bars_off;
-  const uint32_t a_full = bars, a_empty = a_full + 8u * kMaxAStages, b_full = a_empty + 8u * kMaxAStages,
-                 b_empty = b_full + 8u * kMaxBStages, acc_full = b_empty + 8u * kMaxBStages,
+  const uint32_t a_full = bars, a_empty = a_full + 8u * kMaxAStages, acc_full = a_empty + 8u * kMaxAStages,
                  acc_empty = acc_full + 8u * kMaxAccBufs, tmem_slot = acc_empty + 8u * kMaxAccBufs;
   MaskTap* s_taps = reinterpret_cast<MaskTap*>(base_ptr + L.taps_off);
   ColEnt* s_cols = reinterpret_cast<ColEnt*>(base_ptr + L.cols_off);
@@ -325,8 +324,7 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
   for (int i = tid; i < P.n_pad; i += kGatherThreads) s_cols[i] = P.cols[i];
   for (int i = tid; i < P.n_bias; i += kGatherThreads) s_bias[i] = P.bias[i];
   if (tid == 0) {
-    for (int s = 0; s < kMaxAStages; ++s) { mbar_init(a_full + 8u * s, 4); mbar_init(a_empty + 8u * s, 1); }  // 4 warps fill a stage
-    for (int s = 0; s < kMaxBStages; ++s) { mbar_init(b_full + 8u * s, 1); mbar_init(b_empty + 8u * s, 1); }
+    for (int s = 0; s < kMaxAStages; ++s) { mbar_init(a_full + 8u * s, 5); mbar_init(a_empty + 8u * s, 1); }  // 4 producer warps + the TMA thread
     for (int s = 0; s < kMaxAccBufs; ++s) { mbar_init(acc_full + 8u * s, 1); mbar_init(acc_empty + 8u * s, kEpiWarps); }
     fence_mbar_init();
   }
@@ -433,7 +431,7 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
     if (lane == 0) {
       const uint32_t idesc = make_idesc(P.acc_cols);
       int it = 0, tile_iter = 0;
-      Ring ra, rb;
+      Ring ra;
       PROF_DECL;
       for (int t = blockIdx.x; t < P.total_tiles; t += gridDim.x, ++tile_iter) {
         const int buf = tile_iter & (P.acc_bufs - 1), ause = tile_iter >> (P.acc_bufs - 1);  // acc_bufs is 1 or 2
@@ -443,13 +441,12 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
         PROF_LAP(1);
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * P.acc_cols);
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const int sa = ra.idx, sb = rb.idx;
+          // Stage = A slot `sa` in tensor memory + weight slot `sa` in shared memory, one "full" barrier for both.
+          const int sa = ra.idx, sb = ra.idx;
           PROF_LAP(0);
           mbar_wait<false>(a_full + 8u * sa, (uint32_t)ra.use & 1u, failed, P.status, 0x40);
-          PROF_LAP(2);
-          mbar_wait<false>(b_full + 8u * sb, (uint32_t)rb.use & 1u, failed, P.status, 0x80);
           tc_fence_after();
-          PROF_LAP(3);
+          PROF_LAP(2);
           const uint32_t b_hi = base + (uint32_t)sb * L.b_stage_bytes, b_lo = b_hi + (uint32_t)P.n_pad * 128u;
           const uint64_t dbh = make_desc(b_hi), dbl = make_desc(b_lo);
           const uint32_t a_hi = tmem_base + a_col0 + (uint32_t)(sa * 64), a_lo = a_hi + 32u;
@@ -475,10 +472,8 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
             }
           }
           PROF_LAP(4);
-          umma_commit(a_empty + 8u * sa);
-          umma_commit(b_empty + 8u * sb);
+          umma_commit(a_empty + 8u * sa);  // frees the A slot for the producers and the weight slot for the TMA thread
           ra.advance(P.a_stages);
-          rb.advance(P.b_stages);
           PROF_LAP(5);
         }
         umma_commit(acc_full + 8u * buf);
@@ -494,12 +489,12 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
         const int vg = t / P.n_pix_tiles;
         for (int kb = 0; kb < kblocks; ++kb) {
           const int sb = rb.idx;
-          if (rb.use > 0) mbar_wait<false>(b_empty + 8u * sb, (uint32_t)(rb.use - 1) & 1u, failed, P.status, 0x100);
+          if (rb.use > 0) mbar_wait<false>(a_empty + 8u * sb, (uint32_t)(rb.use - 1) & 1u, failed, P.status, 0x100);
           const uint32_t b_hi = base + (uint32_t)sb * L.b_stage_bytes, b_lo = b_hi + (uint32_t)P.n_pad * 128u;
-          mbar_expect_tx(b_full + 8u * sb, L.b_stage_bytes);
-          tma_load_2d(b_hi, &w_map, kb * kBlockK, vg * P.n_pad, b_full + 8u * sb);
-          tma_load_2d(b_lo, &w_map, kb * kBlockK, P.lo_row_offset + vg * P.n_pad, b_full + 8u * sb);
-          rb.advance(P.b_stages);
+          mbar_expect_tx(a_full + 8u * sb, L.b_stage_bytes);
+          tma_load_2d(b_hi, &w_map, kb * kBlockK, vg * P.n_pad, a_full + 8u * sb);
+          tma_load_2d(b_lo, &w_map, kb * kBlockK, P.lo_row_offset + vg * P.n_pad, a_full + 8u * sb);
+          rb.advance(P.a_stages);
         }
       }
     }
@@ -1044,9 +1039,9 @@ int finish_problem(cct_ctx* ctx, UmmaPlan* p, GatherProblem& gp, int vgroups, in
   if (2 * gp.acc_cols + 4 * 64 <= 512) { gp.acc_bufs = 2; gp.a_stages = 4; }
   else if (2 * gp.acc_cols + 2 * 64 <= 512 && gp.k_pad / kBlockK <= 16) { gp.acc_bufs = 2; gp.a_stages = 2; }  // short K: the epilogue matters more
   else { gp.acc_bufs = 1; gp.a_stages = std::min(4, (512 - gp.acc_cols) / 64); }
-  // Weight stages: enough to cover the TMA latency, small enough to leave most of the SM's memory to the L1 cache
-  // that serves the gathers (704 threads x 80 registers already limit an SM to one CTA).
-  gp.b_stages = std::max(2, std::min(6, (96 * 1024) / (2 * gp.n_pad * 128)));
+  // One ring: stage s = A slot s in tensor memory + weight slot s (hi and lo tile) in shared memory.
+  if (gp.a_stages == 4 && 4 * 2 * gp.n_pad * 128 > 200 * 1024) gp.a_stages = 2;
+  gp.b_stages = gp.a_stages;
   gp.smem = gather_smem(gp.n_pad, gp.k_pad, gp.b_stages, n_bias).total + 1024;
   gp.w_half = (size_t)vgroups * gp.n_pad * gp.k_pad;
   int rc = dev_alloc(ctx, p, &gp.w, 2 * gp.w_half);
