@@ -62,6 +62,22 @@ def synth(w, seed):
     return X, W, bias, dY
 
 
+# dram__bytes_read.sum per launch of each contraction kernel in the ncu capture of the batch-64 AlexNet conv1 case
+# (profiles/alexnet_conv1_b64_ncu_full.md).  Reads equal the pass's input bytes and grow with the batch.
+NCU_DRAM_READ_B64 = {"alexnet_conv1": {"forward": 39.9e6, "wgrad": 116.4e6, "dgrad": 74.7e6}}
+
+
+def dram_traffic(workload, w, pass_name, batch):
+    """DRAM bytes per launch of one pass: measured reads scaled to this batch plus the pass's output bytes."""
+    table = NCU_DRAM_READ_B64.get(workload)
+    if table is None:
+        return None
+    m = (w["n"] + 2 * w["p"] - w["k"]) // w["s"] + 1
+    out_elems = {"forward": batch * w["o"] * m * m, "dgrad": batch * w["D"] * w["n"] * w["n"],
+                 "wgrad": w["o"] * (w["D"] // w["g"]) * w["k"] * w["k"] + w["o"]}[pass_name]
+    return table[pass_name] * batch / 64.0 + 4.0 * out_elems
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -326,7 +342,9 @@ def main():
         "bound": "tensor", "kernel": {"forward": "gather_conv_kernel (forward)", "dgrad": "gather_conv_kernel (data gradient)",
                                       "wgrad": "wgrad_kernel"}[dom] if algo.value == 2 else "simt_%s" % dom,
         "pass": dom, "achieved": ach, "peak": tensor_peak, "unit": "TFLOP/s", "frac": ach / tensor_peak,
-        "traffic": None,
+        "traffic": dram_traffic(args.workload, w, dom, B) if algo.value == 2 else None,
+        "traffic_source": "ncu dram__bytes_read.sum of the batch-64 capture scaled by batch/64, plus the pass's "
+                          "output bytes (the batch-64 outputs stayed in L2, so its write counter undercounts)",
         "peak_source": "%s: bf16 burst %.1f TFLOP/s / 2 (TF32 rate) / 3 (3xTF32) — of measured" %
                        (peaks["source"], peaks["bf16_tflops"]),
         "flops_per_launch": F, "ms_per_launch": passes[dom],
