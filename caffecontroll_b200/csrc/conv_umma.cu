@@ -213,18 +213,22 @@ __device__ __forceinline__ void split_tf32_trunc(float x, uint32_t& hi, uint32_t
 // ------------------------------------------------------------------------------ gather kernel (forward, dgrad)
 //
 // Persistent, warp-specialised: one CTA per SM walks over (channel tile, 128-pixel tile) pairs.
-//   warps 0-15  producers: thread = one pixel of the tile = one TMEM lane.  Per k-block a thread gathers its 32
-//               lowered values, splits them hi/lo and writes them with tcgen05.st into the A stage in tensor memory
-//               (four sets of four warps; set g takes the k-blocks with running index == g mod 4, each set covers
+//   producers   (4 * SETS warps) thread = one pixel of the tile = one TMEM lane.  Per k-block a thread gathers its
+//               32 lowered values, splits them hi/lo and writes them with tcgen05.st into an A slot in tensor memory
+//               (sets of four warps; set g takes the k-blocks with running index == g mod SETS, each set covers
 //               all 128 lanes).
-//   warp 16     one thread issues the MMAs: A from tensor memory, B from shared memory.
-//   warp 17     one thread streams the pre-split weight tiles (B) into shared memory with TMA (128-byte swizzle).
-//   warps 18-21 epilogue: tcgen05.ld the finished accumulator, add bias / clamp, store NCHW (or depth-to-space for
+//   MMA warp    one thread issues the MMAs: A from tensor memory, B from shared memory.
+//   TMA warp    one thread streams the pre-split weight tiles (B) into shared memory with TMA (128-byte swizzle).
+//   epilogue    (4 warps) tcgen05.ld the finished accumulator, add bias / clamp, store NCHW (or depth-to-space for
 //               the strided data gradient); overlaps the next tile's MMAs when two accumulators fit.
-// Tensor memory (512 columns): [accumulator(s) | A stages of 64 columns: 32 hi + 32 lo].
-constexpr int kProducerWarps = 16;  // four sets of four; set g fills the A stages with index == g (mod 4)
-constexpr int kMmaWarp = 16, kTmaWarp = 17, kEpiWarp0 = 18, kEpiWarps = 4;
-constexpr int kGatherThreads = (kEpiWarp0 + kEpiWarps) * 32;  // 704
+// Tensor memory: [accumulator(s) | A slots of 64 columns: 32 hi + 32 lo].
+// The kernel comes in two shapes.  SETS = 4: sixteen producer warps (four sets of four; set g fills the k-blocks with
+// running index == g mod 4), 704 threads, one CTA per SM with all 512 tensor-memory columns.  SETS = 2: eight producer
+// warps, 448 threads, 256 columns, two stages, one accumulator - two such CTAs share an SM, so two threads issue MMAs
+// into the SM's tensor pipe (one thread cannot issue them faster than one per ~75 cycles, however narrow they are)
+// and one CTA's epilogue overlaps the other's main loop.
+constexpr int kEpiWarps = 4;
+__host__ __device__ constexpr int gather_threads(int sets) { return (4 * sets + 2 + kEpiWarps) * 32; }  // 704 or 448
 constexpr int kMaxAStages = 4, kMaxAccBufs = 2;
 
 struct alignas(8) ColEnt {  // one accumulator column -> where it lands in the output
@@ -253,6 +257,7 @@ struct GatherParams {
   int n, n_pad, k_pad;     // real / padded accumulator columns per virtual group, padded reduction length
   int n_pix_tiles, total_tiles;
   int a_stages, b_stages, acc_bufs;
+  int tmem_cols;           // tensor-memory columns this CTA allocates: 512, or 256 when two CTAs share an SM
   int dual;                // 1: one MMA covers [B_hi; B_lo] (N = 2*n_pad) and the epilogue adds the two halves
   int acc_cols;            // accumulator width in tensor-memory columns: n_pad, or 2*n_pad when dual
   int n_bias;              // entries of `bias` (all output channels), staged in shared memory
@@ -306,14 +311,22 @@ __host__ __device__ inline GatherSmem gather_smem(int n_pad, int k_pad, int b_st
   return L;
 }
 
-__global__ void __launch_bounds__(kGatherThreads, 1)
+template <int SETS>
+__global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
     gather_conv_kernel(const __grid_constant__ GatherParams P, const __grid_constant__ CUtensorMap w_map) {
+  constexpr int kProducerWarps = 4 * SETS, kMmaWarp = kProducerWarps, kTmaWarp = kMmaWarp + 1, kEpiWarp0 = kTmaWarp + 1;
+  constexpr int kGatherThreads = gather_threads(SETS);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
   const GatherSmem L = gather_smem(P.n_pad, P.k_pad, P.b_stages, P.n_bias);
   const uint32_t bars = base + L.bars_off;
-  const uint32_t a_full = bars, a_empty = a_full + 8u * kMaxAStages, acc_full = a_empty + 8u * kMaxAStages,
+  // K-block i (running index over this CTA's tiles) uses A slot i % a_stages, weight slot i % b_stages and the
+  // barrier pair i % 4: "ready" completes when the four producer warps of the block's set and the weight tile's TMA
+  // bytes have arrived, "done" when the block's MMAs have finished (one tcgen05.commit), which frees both slots.
+  // Rings of different depth share the barriers because no waiter can fall a whole barrier phase (4 blocks) behind:
+  // block i + 4 cannot finish before the slots of block i + 3 were refilled, which waits for block i.
+  const uint32_t ready_bar = bars, done_bar = ready_bar + 8u * kMaxAStages, acc_full = done_bar + 8u * kMaxAStages,
                  acc_empty = acc_full + 8u * kMaxAccBufs, tmem_slot = acc_empty + 8u * kMaxAccBufs;
   MaskTap* s_taps = reinterpret_cast<MaskTap*>(base_ptr + L.taps_off);
   ColEnt* s_cols = reinterpret_cast<ColEnt*>(base_ptr + L.cols_off);
@@ -324,11 +337,11 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
   for (int i = tid; i < P.n_pad; i += kGatherThreads) s_cols[i] = P.cols[i];
   for (int i = tid; i < P.n_bias; i += kGatherThreads) s_bias[i] = P.bias[i];
   if (tid == 0) {
-    for (int s = 0; s < kMaxAStages; ++s) { mbar_init(a_full + 8u * s, 5); mbar_init(a_empty + 8u * s, 1); }  // 4 producer warps + the TMA thread
+    for (int s = 0; s < kMaxAStages; ++s) { mbar_init(ready_bar + 8u * s, 5); mbar_init(done_bar + 8u * s, 1); }  // 4 producer warps + the TMA thread
     for (int s = 0; s < kMaxAccBufs; ++s) { mbar_init(acc_full + 8u * s, 1); mbar_init(acc_empty + 8u * s, kEpiWarps); }
     fence_mbar_init();
   }
-  if (warp == 0) tmem_alloc(tmem_slot, 512);
+  if (warp == 0) tmem_alloc(tmem_slot, (uint32_t)P.tmem_cols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -340,7 +353,7 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
 
   if (warp < kProducerWarps) {
     // ------------------------------------------------------------------ producers
-    // Set `group` owns A stage `group` and fills it for the k-blocks with running index == group (mod 4).  The raw
+    // Set `group` fills the A stages of the k-blocks with running index == group (mod SETS).  The raw
     // values of the set's next k-block are already in flight (in registers) while the current one is split and
     // stored, so the global-load latency is paid once per k-block per set, off the critical path.
     const int group = warp >> 2, quarter = warp & 3;
@@ -390,16 +403,13 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
       gather(kb);
     }
     PROF_DECL;
-    for (int it = group; it < my_stages; it += 4) {
-      const int sa = it & (P.a_stages - 1), use = it >> (P.a_stages == 4 ? 2 : 1);  // a_stages is 2 or 4
+    for (int it = group; it < my_stages; it += SETS) {
+      const int sa = it & (P.a_stages - 1);  // a_stages is 2 or 4
       const uint32_t st_addr = lane_addr + (uint32_t)(sa * 64);
-      const uint32_t full_bar = a_full + 8u * sa, empty_bar = a_empty + 8u * sa;
       PROF_LAP(0);
-      // The stage was last drained `use - 1` phases into its barrier's life.  A parity wait is only meaningful for
-      // the phase that follows one already seen complete, and with two stages this set revisits a stage only every
-      // other use, so it walks through the phases it skipped.
-      for (int ph = use - (P.a_stages == 4 ? 1 : 2); ph < use; ++ph)
-        if (ph >= 0) mbar_wait(empty_bar, (uint32_t)ph & 1u, failed, P.status, 0x10);
+      // The A slot was last read by the MMAs of k-block it - a_stages.
+      const int prev = it - P.a_stages;
+      if (prev >= 0) mbar_wait(done_bar + 8u * (prev & 3), (uint32_t)(prev >> 2) & 1u, failed, P.status, 0x10);
       tc_fence_after();
       PROF_LAP(1);
 #pragma unroll
@@ -411,18 +421,28 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
         tmem_st8(st_addr + 32u + (uint32_t)(c * 8), lo);
       }
       PROF_LAP(2);
-      if (it + 4 < my_stages) {  // put the next k-block's loads in flight before waiting for the stores
+      // With two stages the hand-over of a filled stage is on the critical path: arrive first, then fetch.
+      if (P.a_stages == 2) {
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ready_bar + 8u * (it & 3));
+      }
+      PROF_LAP(4);
+      if (it + SETS < my_stages) {  // the set's next k-block: loads in flight across the next wait
         const int before = tile_local;
-        kb += 4;
+        kb += SETS;
         while (kb >= kblocks) { kb -= kblocks; ++tile_local; }
         if (tile_local != before) setup_tile(tile_local);
         gather(kb);
       }
       PROF_LAP(3);
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(full_bar);  // one arrival per warp: same-address arrivals serialise
+      if (P.a_stages != 2) {
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ready_bar + 8u * (it & 3));  // one arrival per warp: same-address arrivals serialise
+      }
       PROF_LAP(4);
     }
     PROF_FLUSH(0, warp == 0 && lane == 0 && blockIdx.x == 0);
@@ -430,8 +450,8 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
     // ------------------------------------------------------------------ MMA issue
     if (lane == 0) {
       const uint32_t idesc = make_idesc(P.acc_cols);
-      int it = 0, tile_iter = 0;
-      Ring ra;
+      int tile_iter = 0;
+      Ring ra, rb, rbar;  // A slot, weight slot, barrier pair of the current k-block
       PROF_DECL;
       for (int t = blockIdx.x; t < P.total_tiles; t += gridDim.x, ++tile_iter) {
         const int buf = tile_iter & (P.acc_bufs - 1), ause = tile_iter >> (P.acc_bufs - 1);  // acc_bufs is 1 or 2
@@ -440,21 +460,19 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
         tc_fence_after();
         PROF_LAP(1);
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * P.acc_cols);
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          // Stage = A slot `sa` in tensor memory + weight slot `sa` in shared memory, one "full" barrier for both.
-          const int sa = ra.idx, sb = ra.idx;
+        for (int kb = 0; kb < kblocks; ++kb) {
           PROF_LAP(0);
-          mbar_wait<false>(a_full + 8u * sa, (uint32_t)ra.use & 1u, failed, P.status, 0x40);
+          mbar_wait<false>(ready_bar + 8u * rbar.idx, (uint32_t)rbar.use & 1u, failed, P.status, 0x40);
           tc_fence_after();
           PROF_LAP(2);
-          const uint32_t b_hi = base + (uint32_t)sb * L.b_stage_bytes, b_lo = b_hi + (uint32_t)P.n_pad * 128u;
+          const uint32_t b_hi = base + (uint32_t)rb.idx * L.b_stage_bytes, b_lo = b_hi + (uint32_t)P.n_pad * 128u;
           const uint64_t dbh = make_desc(b_hi), dbl = make_desc(b_lo);
-          const uint32_t a_hi = tmem_base + a_col0 + (uint32_t)(sa * 64), a_lo = a_hi + 32u;
+          const uint32_t a_hi = tmem_base + a_col0 + (uint32_t)(ra.idx * 64), a_lo = a_hi + 32u;
           if (!DBG(P, 4)) {
             if (P.dual) {
               // The lo tile sits right behind the hi tile: one descriptor spans both, so a single MMA of width
-              // 2*n_pad produces A*B_hi in the first n_pad columns and A*B_lo in the next (an MMA costs about 90
-              // cycles however narrow it is, so two wide ones beat three narrow ones).
+              // 2*n_pad produces A*B_hi in the first n_pad columns and A*B_lo in the next (issuing an MMA costs
+              // this thread ~75 cycles however narrow it is, so two wide ones beat three narrow ones).
 #pragma unroll
               for (int j = 0; j < kBlockK / 8; ++j) {
                 const uint64_t adv = (uint64_t)(j * 2);
@@ -472,8 +490,10 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
             }
           }
           PROF_LAP(4);
-          umma_commit(a_empty + 8u * sa);  // frees the A slot for the producers and the weight slot for the TMA thread
+          umma_commit(done_bar + 8u * rbar.idx);  // frees the A slot for the producers and the weight slot for the TMA thread
           ra.advance(P.a_stages);
+          rb.advance(P.b_stages);
+          rbar.advance(4);
           PROF_LAP(5);
         }
         umma_commit(acc_full + 8u * buf);
@@ -485,16 +505,19 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
     // ------------------------------------------------------------------ weight tiles by TMA
     if (lane == 0) {
       Ring rb;
+      int i = 0;  // running k-block index
       for (int t = blockIdx.x; t < P.total_tiles; t += gridDim.x) {
         const int vg = t / P.n_pix_tiles;
-        for (int kb = 0; kb < kblocks; ++kb) {
+        for (int kb = 0; kb < kblocks; ++kb, ++i) {
           const int sb = rb.idx;
-          if (rb.use > 0) mbar_wait<false>(a_empty + 8u * sb, (uint32_t)(rb.use - 1) & 1u, failed, P.status, 0x100);
+          const int prev = i - P.b_stages;  // the k-block whose MMAs read this weight slot last
+          if (prev >= 0) mbar_wait<false>(done_bar + 8u * (prev & 3), (uint32_t)(prev >> 2) & 1u, failed, P.status, 0x100);
           const uint32_t b_hi = base + (uint32_t)sb * L.b_stage_bytes, b_lo = b_hi + (uint32_t)P.n_pad * 128u;
-          mbar_expect_tx(a_full + 8u * sb, L.b_stage_bytes);
-          tma_load_2d(b_hi, &w_map, kb * kBlockK, vg * P.n_pad, a_full + 8u * sb);
-          tma_load_2d(b_lo, &w_map, kb * kBlockK, P.lo_row_offset + vg * P.n_pad, a_full + 8u * sb);
-          rb.advance(P.a_stages);
+          const uint32_t bar = ready_bar + 8u * (i & 3);
+          mbar_expect_tx(bar, L.b_stage_bytes);
+          tma_load_2d(b_hi, &w_map, kb * kBlockK, vg * P.n_pad, bar);
+          tma_load_2d(b_lo, &w_map, kb * kBlockK, P.lo_row_offset + vg * P.n_pad, bar);
+          rb.advance(P.b_stages);
         }
       }
     }
@@ -559,7 +582,7 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
                                                              (unsigned)(ox0 + ce[j].cx) < (unsigned)P.out_lim));
               float y = v[h * 8 + j] + bv[j];
               if (P.relu) y = fmaxf(y, 0.f);
-              if (ok) asm volatile("st.global.f32 [%0], %1;" ::"l"(op + ce[j].off), "f"(y));
+              if (ok && !DBG(P, 32)) asm volatile("st.global.f32 [%0], %1;" ::"l"(op + ce[j].off), "f"(y));
             }
           }
         }
@@ -574,7 +597,7 @@ __global__ void __launch_bounds__(kGatherThreads, 1)
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem_base, 512);
+  if (warp == 0) tmem_dealloc(tmem_base, (uint32_t)P.tmem_cols);
 }
 
 // ---------------------------------------------------------------------------------- weight-gradient kernel
@@ -962,6 +985,7 @@ struct GatherProblem {
   size_t w_half = 0;   // elements in one half
   CUtensorMap map;
   int a_stages = 4, b_stages = 4, acc_bufs = 1, dual = 0, acc_cols = 0;
+  int sets = 4, tmem_cols = 512;  // kernel shape: 4 producer sets and one CTA per SM, or 2 sets and two CTAs per SM
   size_t smem = 0;
 };
 
@@ -1030,6 +1054,14 @@ int pack_grid(cct_ctx* ctx, size_t total) {
   return (int)std::min<size_t>(std::max<size_t>(b, 1), (size_t)ctx->sm_count * 8);
 }
 
+bool two_ctas_allowed() {
+#ifdef CCT_DBG
+  const char* e = getenv("CCT_DBG_ONE_CTA");
+  if (e && atoi(e)) return false;
+#endif
+  return true;
+}
+
 // Tensor-memory and shared-memory budget of a gather problem, packed-weight buffer and its tensor map.
 int finish_problem(cct_ctx* ctx, UmmaPlan* p, GatherProblem& gp, int vgroups, int n_bias) {
   // Tensor memory (512 columns) = accumulator buffers + A stages of 64 columns.  Narrow problems run "dual" (see the
@@ -1039,9 +1071,19 @@ int finish_problem(cct_ctx* ctx, UmmaPlan* p, GatherProblem& gp, int vgroups, in
   if (2 * gp.acc_cols + 4 * 64 <= 512) { gp.acc_bufs = 2; gp.a_stages = 4; }
   else if (2 * gp.acc_cols + 2 * 64 <= 512 && gp.k_pad / kBlockK <= 16) { gp.acc_bufs = 2; gp.a_stages = 2; }  // short K: the epilogue matters more
   else { gp.acc_bufs = 1; gp.a_stages = std::min(4, (512 - gp.acc_cols) / 64); }
-  // One ring: stage s = A slot s in tensor memory + weight slot s (hi and lo tile) in shared memory.
-  if (gp.a_stages == 4 && 4 * 2 * gp.n_pad * 128 > 200 * 1024) gp.a_stages = 2;
-  gp.b_stages = gp.a_stages;
+  // Weight slots (hi and lo tile each) in shared memory: up to four, independent of the number of A slots.
+  auto slots_that_fit = [&](size_t limit) {
+    int b = 4;
+    while (b > 1 && gather_smem(gp.n_pad, gp.k_pad, b, n_bias).total + 1024 > limit) --b;
+    return b;
+  };
+  gp.b_stages = slots_that_fit(kSmemLimit);
+  // Accumulators of at most 128 columns leave room for two CTAs per SM: 256 columns each (accumulator + two A
+  // slots) and half the shared memory (the SM holds 228 KB, 1 KB of it reserved per resident CTA).
+  const int b_two = slots_that_fit(113 * 1024);
+  if (gp.acc_cols <= 128 && b_two >= 3 && two_ctas_allowed()) {
+    gp.sets = 2; gp.tmem_cols = 256; gp.acc_bufs = 1; gp.a_stages = 2; gp.b_stages = b_two;
+  }
   gp.smem = gather_smem(gp.n_pad, gp.k_pad, gp.b_stages, n_bias).total + 1024;
   gp.w_half = (size_t)vgroups * gp.n_pad * gp.k_pad;
   int rc = dev_alloc(ctx, p, &gp.w, 2 * gp.w_half);
@@ -1166,7 +1208,8 @@ int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out) {
     if (rc == CCT_OK)
       rc = dev_alloc(ctx, p, &p->w_partial, (size_t)p->w_splits * G.g * f.tiles * p->w_mtiles * kTileM * f.n_pad);
   }
-  if (rc == CCT_OK) rc = set_smem(ctx, gather_conv_kernel, kSmemLimit);
+  if (rc == CCT_OK) rc = set_smem(ctx, gather_conv_kernel<4>, kSmemLimit);
+  if (rc == CCT_OK) rc = set_smem(ctx, gather_conv_kernel<2>, 113 * 1024);
   if (rc == CCT_OK) rc = set_smem(ctx, wgrad_pick(p->w_subs, p->fwd.n_pad), kSmemLimit);
   if (rc != CCT_OK) {
     umma_plan_destroy(ctx, p);
@@ -1195,11 +1238,22 @@ void fill_common(GatherParams& P, const GatherProblem& gp, cct_ctx* ctx, int vgr
   P.n_pix_tiles = (P.n_pix + kTileM - 1) / kTileM;
   P.total_tiles = P.n_pix_tiles * vgroups;
   P.a_stages = gp.a_stages; P.b_stages = gp.b_stages; P.acc_bufs = gp.acc_bufs;
-  P.dual = gp.dual; P.acc_cols = gp.acc_cols;
+  P.dual = gp.dual; P.acc_cols = gp.acc_cols; P.tmem_cols = gp.tmem_cols;
   P.n_bias = P.bias ? n_bias : 0;
   P.lo_row_offset = vgroups * gp.n_pad;
   P.status = ctx->status_dev;
   P.dbg = dbg_knobs();
+}
+
+// Persistent grid: one CTA per SM (4 producer sets) or two (2 sets).
+void launch_gather(cct_ctx* ctx, const GatherParams& P, const GatherProblem& gp) {
+  if (gp.sets == 2) {
+    const int grid = std::min(P.total_tiles, 2 * ctx->sm_count);
+    gather_conv_kernel<2><<<grid, gather_threads(2), gp.smem, ctx->stream>>>(P, gp.map);
+  } else {
+    const int grid = std::min(P.total_tiles, ctx->sm_count);
+    gather_conv_kernel<4><<<grid, gather_threads(4), gp.smem, ctx->stream>>>(P, gp.map);
+  }
 }
 
 }  // namespace
@@ -1231,9 +1285,8 @@ int umma_conv_forward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W,
   P.out_group_channels = G.og;
   P.relu = relu;
   fill_common(P, f, ctx, vgroups, G.o);
-  const int grid = std::min(P.total_tiles, ctx->sm_count);
   t->begin(0, ctx->stream);
-  gather_conv_kernel<<<grid, kGatherThreads, f.smem, ctx->stream>>>(P, f.map);
+  launch_gather(ctx, P, f);
   t->end(0, ctx->stream);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
@@ -1298,8 +1351,7 @@ int umma_conv_backward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W
     P.out_group_channels = G.Dg;
     P.relu = 0;
     fill_common(P, d, ctx, vgroups, 0);
-    const int grid = std::min(P.total_tiles, ctx->sm_count);
-    gather_conv_kernel<<<grid, kGatherThreads, d.smem, ctx->stream>>>(P, d.map);
+    launch_gather(ctx, P, d);
     t->end(3, ctx->stream);
     CCT_CHECK_LAUNCH(ctx);
   }
