@@ -112,6 +112,15 @@ __device__ __forceinline__ float ldg_if(const float* p, uint32_t flag) {
   return v;
 }
 
+// if (flag) *p = v, as one predicated st.global.
+__device__ __forceinline__ void stg_if(float* p, float v, uint32_t flag) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t"
+      "setp.ne.u32 q, %2, 0;\n\t"
+      "@q st.global.f32 [%0], %1;\n\t}" ::"l"(p), "f"(v), "r"(flag)
+      : "memory");
+}
+
 // Position in a ring of `n` stages: stage index and how many times the ring has wrapped.  Kept incrementally: the
 // GPU has no integer divider, and a runtime "% n" in a one-thread issue loop costs more than the MMAs it feeds.
 struct Ring {
@@ -297,6 +306,7 @@ __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+constexpr int kBiasPad = 256;  // zeros behind the staged bias: every accumulator column of a tile reads an entry
 struct GatherSmem {
   uint32_t b_stage_bytes, taps_off, cols_off, bias_off, bars_off, total;
 };
@@ -306,7 +316,7 @@ __host__ __device__ inline GatherSmem gather_smem(int n_pad, int k_pad, int b_st
   L.taps_off = (uint32_t)b_stages * L.b_stage_bytes;
   L.cols_off = L.taps_off + (uint32_t)k_pad * 8u;
   L.bias_off = L.cols_off + (uint32_t)n_pad * 8u;
-  L.bars_off = (L.bias_off + (uint32_t)n_bias * 4u + 15u) & ~15u;
+  L.bars_off = (L.bias_off + (uint32_t)(n_bias + kBiasPad) * 4u + 15u) & ~15u;
   L.total = L.bars_off + 8u * (2 * kMaxAStages + 2 * kMaxAccBufs) + 16u;
   return L;
 }
@@ -335,7 +345,7 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
 
   for (int i = tid; i < P.k_pad; i += kGatherThreads) s_taps[i] = P.taps[i];
   for (int i = tid; i < P.n_pad; i += kGatherThreads) s_cols[i] = P.cols[i];
-  for (int i = tid; i < P.n_bias; i += kGatherThreads) s_bias[i] = P.bias[i];
+  for (int i = tid; i < P.n_bias + kBiasPad; i += kGatherThreads) s_bias[i] = i < P.n_bias ? P.bias[i] : 0.f;
   if (tid == 0) {
     for (int s = 0; s < kMaxAStages; ++s) { mbar_init(ready_bar + 8u * s, 5); mbar_init(done_bar + 8u * s, 1); }  // 4 producer warps + the TMA thread
     for (int s = 0; s < kMaxAccBufs; ++s) { mbar_init(acc_full + 8u * s, 1); mbar_init(acc_empty + 8u * s, kEpiWarps); }
@@ -544,12 +554,13 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
       const int ch0 = grp * P.out_group_channels + ntile * P.out_tile_channels;
       float* op = P.out + (long long)b * P.out_batch_stride + (long long)ch0 * P.out_plane +
                   (long long)oy0 * P.out_pitch + ox0;
-      const float* bias = P.n_bias ? s_bias + ch0 : nullptr;
+      const float* bias = s_bias + (P.n_bias ? ch0 : 0);  // zero padded: readable for every column of the tile
       PROF_LAP(0);
       mbar_wait(acc_full + 8u * buf, (uint32_t)ause & 1u, failed, P.status, 0x200);
       tc_fence_after();
       PROF_LAP(1);
-      const bool live = pix < P.n_pix && !failed;
+      const uint32_t live = (pix < P.n_pix && !failed) ? 1u : 0u;
+      const uint32_t unchecked = P.check_out ? 0u : 1u;
       const uint32_t acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P.acc_cols);
       const int chunks = P.n_pad / 16;
       for (int c = 0; c < chunks; ++c) {
@@ -562,9 +573,10 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
           for (int j = 0; j < 16; ++j) v[j] += w[j];
         }
         PROF_LAP(3);
-        if (live) {
-          // Table and bias reads first, then the stores as explicit st.global: a generic store could alias shared
-          // memory and would pin every following table read behind it.
+        if (!DBG(P, 128)) {
+          // Straight-line code: table and bias reads first, then predicated st.global (a generic store could alias
+          // shared memory and would pin every following table read behind it; a branch per column costs more than
+          // the store it guards).
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             ColEnt ce[8];
@@ -573,16 +585,17 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
             for (int j = 0; j < 8; ++j) {
               const int col = c * 16 + h * 8 + j;
               ce[j] = s_cols[col];
-              bv[j] = (bias && col < P.n) ? bias[col] : 0.f;
+              bv[j] = bias[col];
             }
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               const int col = c * 16 + h * 8 + j;
-              const bool ok = col < P.n && (!P.check_out || ((unsigned)(oy0 + ce[j].cy) < (unsigned)P.out_lim &&
-                                                             (unsigned)(ox0 + ce[j].cx) < (unsigned)P.out_lim));
+              const uint32_t in_y = (unsigned)(oy0 + ce[j].cy) < (unsigned)P.out_lim ? 1u : 0u;
+              const uint32_t in_x = (unsigned)(ox0 + ce[j].cx) < (unsigned)P.out_lim ? 1u : 0u;
+              const uint32_t ok = live & (col < P.n ? 1u : 0u) & (unchecked | (in_y & in_x)) & (DBG(P, 32) ? 0u : 1u);
               float y = v[h * 8 + j] + bv[j];
-              if (P.relu) y = fmaxf(y, 0.f);
-              if (ok && !DBG(P, 32)) asm volatile("st.global.f32 [%0], %1;" ::"l"(op + ce[j].off), "f"(y));
+              y = P.relu ? fmaxf(y, 0.f) : y;
+              stg_if(op + ce[j].off, y, ok);
             }
           }
         }
@@ -609,13 +622,16 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
 // and every shared-memory store fills one row, conflict free.
 // One CTA owns up to `subs` M-tiles of 128 taps (accumulators side by side in tensor memory), one channel tile of dY
 // and a range of 32-pixel k-blocks; the dY tile of a k-block is staged once for all its M-tiles.
-//   warps 0-15  producers: warp w stages rows w, w+16, ... of the stage (tap rows first, then channel rows): load,
-//               split hi/lo, two st.shared per row; the loads of the next k-block are issued before the warp waits
-//               for the stage buffer to drain.
-//   warp 16     one thread issues the MMAs (both operands from shared memory).
-// The finished accumulators are written to the split's slice of the scratch buffer by warps 0-15.
-constexpr int kWgProdWarps = 16, kWgMmaWarp = 16;
-constexpr int kWgThreads = (kWgMmaWarp + 1) * 32;  // 544
+//   warps 0-15  tap producers: warp w stages rows w, w+16, ... of every M-tile of the stage: load, split hi/lo, two
+//               st.shared per row; the loads of the next k-block are issued before the warp waits for the stage
+//               buffer to drain.
+//   warps 16-23 dY producers: warp 16+w stages channel rows w, w+8, ... of the dY tile the same way.
+//   warp 24     one thread issues the MMAs (both operands from shared memory).
+// The producers run at about one instruction per eight cycles each (latency bound), so their number, not their
+// instruction count alone, sets the staging rate.  The finished accumulators are written to the split's slice of the
+// scratch buffer by warps 0-15.
+constexpr int kWgTapWarps = 16, kWgDyWarps = 8, kWgProdWarps = kWgTapWarps + kWgDyWarps, kWgMmaWarp = kWgProdWarps;
+constexpr int kWgThreads = (kWgMmaWarp + 1) * 32;  // 800
 constexpr int kWgMaxStages = 4, kWgMaxSubs = 2;
 constexpr uint32_t kWgValidBit = 0x80000000u;      // set in a pixel's mask when the pixel exists
 constexpr uint32_t kWgPadBit = 0x00008000u;        // never set in a pixel's mask: rows beyond the lowered matrix
@@ -712,13 +728,6 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
 
   if (warp < kWgProdWarps) {
     // ------------------------------------------------------------------ producers (lane = pixel of the k-block)
-    const float* xg = P.x + (long long)grp * P.x_group_stride;
-    const float* dyg = P.dy + (long long)(grp * P.dy_group_channels + ntile * P.n_real + warp) * P.mm;
-    const int dy_step = kWgProdWarps * P.mm;  // elements between consecutive channel rows of this warp
-    const int b_live = P.n_real > warp ? (P.n_real - warp + kWgProdWarps - 1) / kWgProdWarps : 0;  // real rows
-    // Does this CTA hold the all-ones row (bias gradient)?  Only then the tap loads need the extra select.
-    const int ones_row = P.ones_row - mgroup * SUBS * kTileM;
-    const bool has_ones = ones_row >= 0 && ones_row < subs * kTileM;
     // this lane's pixel, advanced by 32 per k-block
     int pix = kb_begin * kBlockK + lane;
     int pb = pix / P.mm, pr, pc;
@@ -727,77 +736,112 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
       pr = pin / P.m;
       pc = pin - pr * P.m;
     }
-    // This lane's word in row `warp` of a tile; the warp's further rows are 2048 bytes apart.
-    uint8_t* lane_ptr = base_ptr + warp * 128 + ((((lane >> 2) ^ (warp & 7)) << 4) + (lane & 3) * 4);
-    const MaskTap* my_taps = s_taps + warp;
-    float va[kARows], vb[NB];
-    auto load_rows = [&]() {
-      const bool ok = pix < P.n_pix;
-      const int iy0 = pr * P.s - P.p, ix0 = pc * P.s - P.p;
-      const float* xsrc = xg + (long long)pb * P.x_batch_stride + (long long)iy0 * P.n + ix0;
-      const float* dsrc = dyg + (long long)pb * P.dy_batch_stride + pr * P.m + pc;
-      const uint32_t mask =
-          ok ? (kWgValidBit | bit_range(-iy0, min(P.k, P.n - iy0)) | (bit_range(-ix0, min(P.k, P.n - ix0)) << 16))
-             : 0u;
-      if (!has_ones) {
-#pragma unroll
-        for (int i = 0; i < kARows; ++i) {
-          const MaskTap tap = my_taps[kWgProdWarps * i];
-          va[i] = ldg_if_bits(xsrc + tap.off, DBG(P, 1) ? 0u : mask, tap.bits);
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < kARows; ++i) {
-          const MaskTap tap = my_taps[kWgProdWarps * i];
-          va[i] = 0.f;
-          if ((mask & tap.bits) == tap.bits) va[i] = tap.bits == kWgOnesBits ? 1.f : __ldg(xsrc + tap.off);
-        }
-      }
-#pragma unroll
-      for (int i = 0; i < NB; ++i) {
-        vb[i] = ldg_if(dsrc + i * dy_step, (ok && i < b_live && !DBG(P, 2)) ? 1u : 0u);
-      }
+    auto next_pixel = [&]() {
+      pix += kBlockK;
+      pc += kBlockK;
+      while (pc >= P.m) { pc -= P.m; ++pr; }
+      while (pr >= P.m) { pr -= P.m; ++pb; }
     };
-    load_rows();
-    PROF_DECL;
-    Ring ring;
-    for (int kbl = 0; kbl < kblocks; ++kbl, ring.advance(P.stages)) {
-      const int s = ring.idx, use = ring.use;
-      uint8_t* st = lane_ptr + (size_t)s * L.stage_bytes;
-      PROF_LAP(0);
-      if (use > 0) mbar_wait(empty + 8u * s, (uint32_t)(use - 1) & 1u, failed, P.status, 0x10);
-      PROF_LAP(1);
+    if (warp < kWgTapWarps) {
+      // ---- tap rows: row warp + 16*i of every M-tile
+      const float* xg = P.x + (long long)grp * P.x_group_stride;
+      // Does this CTA hold the all-ones row (bias gradient)?  Only then the tap loads need the extra select.
+      const int ones_row = P.ones_row - mgroup * SUBS * kTileM;
+      const bool has_ones = ones_row >= 0 && ones_row < subs * kTileM;
+      // This lane's word in row `warp` of a tile; the warp's further rows are 2048 bytes apart.
+      uint8_t* lane_ptr = base_ptr + warp * 128 + ((((lane >> 2) ^ (warp & 7)) << 4) + (lane & 3) * 4);
+      const MaskTap* my_taps = s_taps + warp;
+      float va[kARows];
+      auto load_rows = [&]() {
+        const bool ok = pix < P.n_pix;
+        const int iy0 = pr * P.s - P.p, ix0 = pc * P.s - P.p;
+        const float* xsrc = xg + (long long)pb * P.x_batch_stride + (long long)iy0 * P.n + ix0;
+        const uint32_t mask =
+            ok ? (kWgValidBit | bit_range(-iy0, min(P.k, P.n - iy0)) | (bit_range(-ix0, min(P.k, P.n - ix0)) << 16))
+               : 0u;
+        if (!has_ones) {
 #pragma unroll
-      for (int i = 0; i < kARows; ++i) {  // tile i/8 (hi then lo), row warp + 16*(i%8)
-        uint32_t h, l;
-        split_tf32_trunc(va[i], h, l);
-        uint8_t* dst = st + (i / 8) * 2 * kATile + (i % 8) * 2048;
-        *reinterpret_cast<uint32_t*>(dst) = h;
-        *reinterpret_cast<uint32_t*>(dst + kATile) = l;
-      }
+          for (int i = 0; i < kARows; ++i) {
+            const MaskTap tap = my_taps[kWgTapWarps * i];
+            va[i] = ldg_if_bits(xsrc + tap.off, DBG(P, 1) ? 0u : mask, tap.bits);
+          }
+        } else {
 #pragma unroll
-      for (int i = 0; i < NB; ++i) {  // dY tile (hi then lo) behind the SUBS tap tiles, row warp + 16*i
-        uint32_t h, l;
-        split_tf32_trunc(vb[i], h, l);
-        uint8_t* dst = st + SUBS * 2 * kATile + i * 2048;
-        *reinterpret_cast<uint32_t*>(dst) = h;
-        *reinterpret_cast<uint32_t*>(dst + kBTile) = l;
+          for (int i = 0; i < kARows; ++i) {
+            const MaskTap tap = my_taps[kWgTapWarps * i];
+            va[i] = 0.f;
+            if ((mask & tap.bits) == tap.bits) va[i] = tap.bits == kWgOnesBits ? 1.f : __ldg(xsrc + tap.off);
+          }
+        }
+      };
+      load_rows();
+      PROF_DECL;
+      Ring ring;
+      for (int kbl = 0; kbl < kblocks; ++kbl, ring.advance(P.stages)) {
+        const int s = ring.idx, use = ring.use;
+        uint8_t* st = lane_ptr + (size_t)s * L.stage_bytes;
+        PROF_LAP(0);
+        if (use > 0) mbar_wait(empty + 8u * s, (uint32_t)(use - 1) & 1u, failed, P.status, 0x10);
+        PROF_LAP(1);
+#pragma unroll
+        for (int i = 0; i < kARows; ++i) {  // tile i/8 (hi then lo), row warp + 16*(i%8)
+          uint32_t h, l;
+          split_tf32_trunc(va[i], h, l);
+          uint8_t* dst = st + (i / 8) * 2 * kATile + (i % 8) * 2048;
+          *reinterpret_cast<uint32_t*>(dst) = h;
+          *reinterpret_cast<uint32_t*>(dst + kATile) = l;
+        }
+        PROF_LAP(2);
+        if (kbl + 1 < kblocks) {  // the next k-block's loads go in flight before the barrier work
+          next_pixel();
+          load_rows();
+        }
+        PROF_LAP(3);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full + 8u * s);  // one arrival per warp: same-address arrivals serialise
+        PROF_LAP(4);
       }
-      PROF_LAP(2);
-      if (kbl + 1 < kblocks) {  // the next k-block's loads go in flight before the barrier work
-        pix += kBlockK;
-        pc += kBlockK;
-        while (pc >= P.m) { pc -= P.m; ++pr; }
-        while (pr >= P.m) { pr -= P.m; ++pb; }
-        load_rows();
+      PROF_FLUSH(4, warp == 0 && lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
+    } else {
+      // ---- dY rows: channel w8 + 8*i of the tile (hi then lo), behind the SUBS tap tiles of the stage
+      const int w8 = warp - kWgTapWarps;
+      constexpr int kDyRows = kNPad / kWgDyWarps;
+      const float* dyg = P.dy + (long long)(grp * P.dy_group_channels + ntile * P.n_real + w8) * P.mm;
+      const int dy_step = kWgDyWarps * P.mm;  // elements between consecutive channel rows of this warp
+      const int b_live = P.n_real > w8 ? (P.n_real - w8 + kWgDyWarps - 1) / kWgDyWarps : 0;  // real rows
+      uint8_t* lane_ptr = base_ptr + SUBS * 2 * kATile + w8 * 128 + ((((lane >> 2) ^ (w8 & 7)) << 4) + (lane & 3) * 4);
+      float vb[kDyRows];
+      auto load_rows = [&]() {
+        const bool ok = pix < P.n_pix;
+        const float* dsrc = dyg + (long long)pb * P.dy_batch_stride + pr * P.m + pc;
+#pragma unroll
+        for (int i = 0; i < kDyRows; ++i) vb[i] = ldg_if(dsrc + i * dy_step, (ok && i < b_live && !DBG(P, 2)) ? 1u : 0u);
+      };
+      load_rows();
+      Ring ring;
+      for (int kbl = 0; kbl < kblocks; ++kbl, ring.advance(P.stages)) {
+        const int s = ring.idx, use = ring.use;
+        uint8_t* st = lane_ptr + (size_t)s * L.stage_bytes;
+        if (use > 0) mbar_wait(empty + 8u * s, (uint32_t)(use - 1) & 1u, failed, P.status, 0x11);
+#pragma unroll
+        for (int i = 0; i < kDyRows; ++i) {
+          uint32_t h, l;
+          split_tf32_trunc(vb[i], h, l);
+          uint8_t* dst = st + i * (kWgDyWarps * 128);
+          *reinterpret_cast<uint32_t*>(dst) = h;
+          *reinterpret_cast<uint32_t*>(dst + kBTile) = l;
+        }
+        if (kbl + 1 < kblocks) {
+          next_pixel();
+          load_rows();
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full + 8u * s);
       }
-      PROF_LAP(3);
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(full + 8u * s);  // one arrival per warp: same-address arrivals serialise
-      PROF_LAP(4);
     }
-    PROF_FLUSH(4, warp == 0 && lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
+    if (warp < kWgTapWarps) {
     // ---- epilogue: accumulator u, columns in chunks of 16; warp w takes lanes 32*(w%4).. and the (u, chunk) pairs
     //      with index == w/4 (mod 4)
     mbar_wait(acc_full, 0u, failed, P.status, 0x2000);
@@ -821,6 +865,7 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
 #pragma unroll
         for (int j = 0; j < 4; ++j) o4[j] = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
       }
+    }
     }
   } else {
     // ------------------------------------------------------------------ MMA issue
