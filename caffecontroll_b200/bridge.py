@@ -122,7 +122,9 @@ class ConvolutionBridge:
         self.K, self.stride, self.padding, self.group = kernel_size, stride, pad, group
         self.bias_term = bias_term
         self.needs_to_calc_backward_grad = True
-        self.fuse_relu = False
+        self.fuse_relu = False           # forward(): clamp the output at 0 (the ReLU bridge behind this layer)
+        self.fuse_relu_backward = False  # backward(): input gradient times [input > 0] (the ReLU bridge in front)
+        self.pool_fusion = None          # see fuse_pool_relu_backward()
         if self.iR != self.iC:
             raise ValueError("square inputs only, as in the reference")
         self.desc = capi.ConvDesc(self.iB, self.iD, self.iR, self.oD, kernel_size, stride, pad, group,
@@ -179,13 +181,28 @@ class ConvolutionBridge:
                                              self.p_output_layer.p_data_cube.ptr, int(self.fuse_relu)),
                    "cct_conv_forward", self.ctx.h)
 
+    def fuse_pool_relu_backward(self, pooled_gradient_cube, max_index_cube, kernel_size, stride):
+        """Fold the ReLU and max-pooling bridges that follow this layer into backward(): the output gradient is
+        rebuilt from the pooled tensor's gradient and the pooling indices (MaxPoolingBridge::backward then
+        ReLUBridge::backward in the reference) instead of being read from p_output_layer.p_gradient_cube."""
+        self.pool_fusion = (pooled_gradient_cube, max_index_cube, kernel_size, stride)
+
     def backward(self):
         dx = self.p_input_layer.p_gradient_cube.ptr if self.needs_to_calc_backward_grad else None
         db = self.p_bias_gradient_cube.ptr if self.bias_term else None
-        capi.check(self.lib.cct_conv_backward(self.plan, self.p_input_layer.p_data_cube.ptr, self.p_model_cube.ptr,
-                                              self.p_output_layer.p_gradient_cube.ptr, dx,
-                                              self.p_model_gradient_cube.ptr, db),
-                   "cct_conv_backward", self.ctx.h)
+        x, w, dw = self.p_input_layer.p_data_cube.ptr, self.p_model_cube.ptr, self.p_model_gradient_cube.ptr
+        if self.pool_fusion is None and not self.fuse_relu_backward:
+            capi.check(self.lib.cct_conv_backward(self.plan, x, w, self.p_output_layer.p_gradient_cube.ptr, dx, dw, db),
+                       "cct_conv_backward", self.ctx.h)
+            return
+        f = capi.BwdFusion(None, None, None, 0, 0, int(self.fuse_relu_backward))
+        dy = self.p_output_layer.p_gradient_cube.ptr
+        if self.pool_fusion is not None:
+            dp, idx, k, s = self.pool_fusion
+            f.A, f.idx, f.dP, f.pool_k, f.pool_s = self.p_output_layer.p_data_cube.ptr, idx.ptr, dp.ptr, k, s
+            dy = None
+        capi.check(self.lib.cct_conv_backward_fused(self.plan, x, w, dy, C.byref(f), dx, dw, db),
+                   "cct_conv_backward_fused", self.ctx.h)
 
     def close(self):
         if self.plan:

@@ -20,7 +20,7 @@ EXPORTS = [
     "cct_device_count", "cct_malloc", "cct_free", "cct_malloc_host", "cct_free_host", "cct_memcpy_h2d",
     "cct_memcpy_d2h", "cct_memcpy_d2d", "cct_memset", "cct_fill_f32", "cct_conv_plan_create",
     "cct_conv_plan_destroy", "cct_conv_out_size", "cct_conv_plan_algo", "cct_conv_plan_workspace_bytes",
-    "cct_conv_plan_enable_timing", "cct_conv_plan_last_timings", "cct_conv_forward", "cct_conv_backward", "cct_conv_forward_host", "cct_conv_backward_host", "cct_conv_weight_grad_noalloc",
+    "cct_conv_plan_enable_timing", "cct_conv_plan_last_timings", "cct_conv_forward", "cct_conv_backward", "cct_conv_backward_fused", "cct_conv_forward_host", "cct_conv_backward_host", "cct_conv_weight_grad_noalloc",
     "cct_maxpool_forward", "cct_maxpool_backward", "cct_relu_forward", "cct_relu_backward",
     "cct_pool_relu_backward", "cct_sgd_step",
 ]
@@ -30,6 +30,12 @@ class CctError(RuntimeError):
     def __init__(self, code, where, detail=""):
         self.code = code
         super().__init__("%s failed: %s%s" % (where, _ERR_NAMES.get(code, code), (" — " + detail) if detail else ""))
+
+
+class BwdFusion(C.Structure):
+    """cct_bwd_fusion: what cct_conv_backward_fused folds into the backward pass."""
+    _fields_ = [("A", C.c_void_p), ("idx", C.c_void_p), ("dP", C.c_void_p), ("pool_k", C.c_int), ("pool_s", C.c_int),
+                ("relu_mask_dx", C.c_int)]
 
 
 class ConvDesc(C.Structure):
@@ -75,6 +81,7 @@ def load():
         "cct_conv_plan_last_timings": [_vp, C.POINTER(C.c_float)],
         "cct_conv_forward": [_vp, _vp, _vp, _vp, _vp, i],
         "cct_conv_backward": [_vp, _vp, _vp, _vp, _vp, _vp, _vp],
+        "cct_conv_backward_fused": [_vp, _vp, _vp, _vp, C.POINTER(BwdFusion), _vp, _vp, _vp],
         "cct_conv_forward_host": [_vp, _vp, _vp, _vp, _vp, i],
         "cct_conv_backward_host": [_vp, _vp, _vp, _vp, _vp, _vp, _vp],
         "cct_conv_weight_grad_noalloc": [_vp, C.POINTER(ConvDesc), _vp, _vp, _vp, _vp],

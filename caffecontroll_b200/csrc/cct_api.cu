@@ -15,6 +15,7 @@ struct cct_conv_plan {
         *sdb = nullptr;
   size_t staging_bytes = 0;
   bool staged_forward = false;  // sX / sW hold what the last cct_conv_forward_host uploaded
+  float* mask_dY = nullptr;     // output gradient rebuilt from the pooled gradient (cct_conv_backward_fused), on first use
   PhaseTimer timer;
 };
 
@@ -242,7 +243,7 @@ int cct_conv_plan_destroy(cct_conv_plan* plan) {
   if (plan->umma) umma_plan_destroy(ctx, plan->umma);
   for (cudaEvent_t e : plan->timer.ev)
     if (e) cudaEventDestroy(e);
-  float* slots[] = {plan->sX, plan->sW, plan->sb, plan->sY, plan->sdY, plan->sdX, plan->sdW, plan->sdb};
+  float* slots[] = {plan->sX, plan->sW, plan->sb, plan->sY, plan->sdY, plan->sdX, plan->sdW, plan->sdb, plan->mask_dY};
   for (float* s : slots)
     if (s) cudaFree(s);
   delete plan;
@@ -300,8 +301,34 @@ int cct_conv_backward(cct_conv_plan* plan, const float* X, const float* W, const
   cct_ctx* ctx = plan->ctx;
   if (plan->G.bias && !db) return CCT_ERR_INVALID;
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
-  if (plan->algo == CCT_ALGO_UMMA_3XTF32) return umma_conv_backward(ctx, plan->umma, X, W, dY, dX, dW, db, &plan->timer);
+  if (plan->algo == CCT_ALGO_UMMA_3XTF32)
+    return umma_conv_backward(ctx, plan->umma, X, W, dY, dX, dW, db, 0, &plan->timer);
   return simt_conv_backward(ctx, plan->G, X, W, dY, dX, dW, db, &plan->timer);
+}
+
+int cct_conv_backward_fused(cct_conv_plan* plan, const float* X, const float* W, const float* dY,
+                            const cct_bwd_fusion* f, float* dX, float* dW, float* db) {
+  if (!f) return cct_conv_backward(plan, X, W, dY, dX, dW, db);
+  if (!plan || !X || !W || !dW) return CCT_ERR_INVALID;
+  cct_ctx* ctx = plan->ctx;
+  const ConvGeom& G = plan->G;
+  if (G.bias && !db) return CCT_ERR_INVALID;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (f->dP) {
+    // conv -> ReLU -> max-pool behind this layer: one pass builds the output gradient both kernels read.
+    if (!f->A || !f->idx || f->pool_k <= 0 || f->pool_s <= 0 || f->pool_k > G.m) return CCT_ERR_INVALID;
+    if (!plan->mask_dY) CCT_CUDA(ctx, cudaMalloc((void**)&plan->mask_dY, (size_t)G.B * G.o * G.m * G.m * sizeof(float)));
+    const int rc = cct_pool_relu_backward(ctx, f->A, f->idx, f->dP, plan->mask_dY, G.B * G.o, G.m, f->pool_k, f->pool_s);
+    if (rc != CCT_OK) return rc;
+    dY = plan->mask_dY;
+  }
+  if (!dY) return CCT_ERR_INVALID;
+  const int mask_dx = f->relu_mask_dx && dX;
+  if (plan->algo == CCT_ALGO_UMMA_3XTF32)
+    return umma_conv_backward(ctx, plan->umma, X, W, dY, dX, dW, db, mask_dx, &plan->timer);
+  int rc = simt_conv_backward(ctx, G, X, W, dY, dX, dW, db, &plan->timer);
+  if (rc == CCT_OK && mask_dx) rc = cct_relu_backward(ctx, X, dX, dX, (size_t)G.B * G.D * G.n * G.n);
+  return rc;
 }
 
 int cct_conv_forward_host(cct_conv_plan* plan, const float* hX, const float* hW, const float* hbias, float* hY,

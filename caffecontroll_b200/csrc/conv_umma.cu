@@ -24,6 +24,7 @@
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
+#include <type_traits>
 #include <vector>
 
 #include <cuda.h>
@@ -251,6 +252,7 @@ struct GatherParams {
   const MaskTap* taps; // [k_pad]
   const ColEnt* cols;  // [n_pad]
   const float* bias;  // indexed by output channel, or null
+  const float* sign_src;  // same shape as `out`, or null: outputs are zeroed where sign_src <= 0 (ReLU backward)
   int n_pix, q_h, q_w;                 // pixels = batch * q_h * q_w
   int iy_mul, iy_add, ix_mul, ix_add;  // tap origin in the gathered tensor: iy0 = qy*iy_mul + iy_add
   int in_lim;                          // gathered tensor is in_lim x in_lim per channel
@@ -555,6 +557,7 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
       float* op = P.out + (long long)b * P.out_batch_stride + (long long)ch0 * P.out_plane +
                   (long long)oy0 * P.out_pitch + ox0;
       const float* bias = s_bias + (P.n_bias ? ch0 : 0);  // zero padded: readable for every column of the tile
+      const float* sp = P.sign_src + (op - P.out);
       PROF_LAP(0);
       mbar_wait(acc_full + 8u * buf, (uint32_t)ause & 1u, failed, P.status, 0x200);
       tc_fence_after();
@@ -573,10 +576,11 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
           for (int j = 0; j < 16; ++j) v[j] += w[j];
         }
         PROF_LAP(3);
-        if (!DBG(P, 128)) {
-          // Straight-line code: table and bias reads first, then predicated st.global (a generic store could alias
-          // shared memory and would pin every following table read behind it; a branch per column costs more than
-          // the store it guards).
+        // Straight-line code: table and bias reads first, then predicated st.global (a generic store could alias
+        // shared memory and would pin every following table read behind it; a branch per column costs more than
+        // the store it guards).  MASKED: the output is zeroed where the tensor `sign_src` is not positive.
+        auto store_chunk = [&](auto masked_tag) {
+          constexpr bool MASKED = decltype(masked_tag)::value;
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             ColEnt ce[8];
@@ -587,17 +591,28 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
               ce[j] = s_cols[col];
               bv[j] = bias[col];
             }
+            uint32_t ok[8];
+            float sg[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               const int col = c * 16 + h * 8 + j;
               const uint32_t in_y = (unsigned)(oy0 + ce[j].cy) < (unsigned)P.out_lim ? 1u : 0u;
               const uint32_t in_x = (unsigned)(ox0 + ce[j].cx) < (unsigned)P.out_lim ? 1u : 0u;
-              const uint32_t ok = live & (col < P.n ? 1u : 0u) & (unchecked | (in_y & in_x)) & (DBG(P, 32) ? 0u : 1u);
+              ok[j] = live & (col < P.n ? 1u : 0u) & (unchecked | (in_y & in_x)) & (DBG(P, 32) ? 0u : 1u);
+              if (MASKED) sg[j] = ldg_if(sp + ce[j].off, ok[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
               float y = v[h * 8 + j] + bv[j];
               y = P.relu ? fmaxf(y, 0.f) : y;
-              stg_if(op + ce[j].off, y, ok);
+              if (MASKED) y = sg[j] > 0.f ? y : 0.f;
+              stg_if(op + ce[j].off, y, ok[j]);
             }
           }
+        };
+        if (!DBG(P, 128)) {
+          if (P.sign_src) store_chunk(std::true_type{});
+          else store_chunk(std::false_type{});
         }
         PROF_LAP(4);
       }
@@ -635,7 +650,7 @@ constexpr int kWgThreads = (kWgMmaWarp + 1) * 32;  // 800
 constexpr int kWgMaxStages = 4, kWgMaxSubs = 2;
 constexpr uint32_t kWgValidBit = 0x80000000u;      // set in a pixel's mask when the pixel exists
 constexpr uint32_t kWgPadBit = 0x00008000u;        // never set in a pixel's mask: rows beyond the lowered matrix
-constexpr uint32_t kWgOnesBits = kWgValidBit;      // the all-ones row: in bounds wherever the pixel exists
+constexpr uint32_t kWgOnesBits = kWgValidBit | kWgPadBit;  // the all-ones row: never loaded, patched in by its warp
 
 struct WgradParams {
   const float* x;
@@ -745,9 +760,11 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
     if (warp < kWgTapWarps) {
       // ---- tap rows: row warp + 16*i of every M-tile
       const float* xg = P.x + (long long)grp * P.x_group_stride;
-      // Does this CTA hold the all-ones row (bias gradient)?  Only then the tap loads need the extra select.
-      const int ones_row = P.ones_row - mgroup * SUBS * kTileM;
-      const bool has_ones = ones_row >= 0 && ones_row < subs * kTileM;
+      // The all-ones row (bias gradient) is one fixed row of one CTA column: its table entry never passes the
+      // bounds test (so nothing is loaded for it) and the warp that owns it patches the value in.
+      const int ones_local = P.ones_row - mgroup * SUBS * kTileM;
+      const bool mine = ones_local >= 0 && ones_local < subs * kTileM && ((ones_local & (kTileM - 1)) % kWgTapWarps) == warp;
+      const int ones_i = mine ? (ones_local / kTileM) * 8 + (ones_local & (kTileM - 1)) / kWgTapWarps : -1;
       // This lane's word in row `warp` of a tile; the warp's further rows are 2048 bytes apart.
       uint8_t* lane_ptr = base_ptr + warp * 128 + ((((lane >> 2) ^ (warp & 7)) << 4) + (lane & 3) * 4);
       const MaskTap* my_taps = s_taps + warp;
@@ -759,19 +776,14 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
         const uint32_t mask =
             ok ? (kWgValidBit | bit_range(-iy0, min(P.k, P.n - iy0)) | (bit_range(-ix0, min(P.k, P.n - ix0)) << 16))
                : 0u;
-        if (!has_ones) {
 #pragma unroll
-          for (int i = 0; i < kARows; ++i) {
-            const MaskTap tap = my_taps[kWgTapWarps * i];
-            va[i] = ldg_if_bits(xsrc + tap.off, DBG(P, 1) ? 0u : mask, tap.bits);
-          }
-        } else {
+        for (int i = 0; i < kARows; ++i) {
+          const MaskTap tap = my_taps[kWgTapWarps * i];
+          va[i] = ldg_if_bits(xsrc + tap.off, DBG(P, 1) ? 0u : mask, tap.bits);
+        }
+        if (ones_i >= 0) {
 #pragma unroll
-          for (int i = 0; i < kARows; ++i) {
-            const MaskTap tap = my_taps[kWgTapWarps * i];
-            va[i] = 0.f;
-            if ((mask & tap.bits) == tap.bits) va[i] = tap.bits == kWgOnesBits ? 1.f : __ldg(xsrc + tap.off);
-          }
+          for (int i = 0; i < kARows; ++i) va[i] = i == ones_i ? (ok ? 1.f : 0.f) : va[i];
         }
       };
       load_rows();
@@ -1338,7 +1350,7 @@ int umma_conv_forward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W,
 }
 
 int umma_conv_backward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W, const float* dY, float* dX,
-                       float* dW, float* db, PhaseTimer* t) {
+                       float* dW, float* db, int relu_mask_dx, PhaseTimer* t) {
   if (*ctx->status_host != 0) return CCT_ERR_TIMEOUT;
   const ConvGeom& G = p->G;
   // ---- weight + bias gradient
@@ -1383,6 +1395,7 @@ int umma_conv_backward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W
     CCT_CHECK_LAUNCH(ctx);
     GatherParams P{};
     P.in = dY; P.out = dX; P.bias = nullptr;
+    P.sign_src = relu_mask_dx ? X : nullptr;  // X has dX's shape: the ReLU in front of this layer, folded in
     P.n_pix = G.B * p->dgr_q * p->dgr_q; P.q_h = p->dgr_q; P.q_w = p->dgr_q;
     P.iy_mul = 1; P.iy_add = p->dgr_q0; P.ix_mul = 1; P.ix_add = p->dgr_q0;
     P.in_lim = G.m;

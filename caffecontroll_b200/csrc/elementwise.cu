@@ -43,8 +43,8 @@ __global__ void relu_fwd_kernel(const float* __restrict__ x, float* __restrict__
     y[i] = fmaxf(x[i], 0.f);
 }
 
-__global__ void relu_bwd_kernel(const float* __restrict__ x, const float* __restrict__ dy, float* __restrict__ dx,
-                                size_t count) {
+// dy and dx may be the same buffer (in-place use by the fused backward of the SIMT path).
+__global__ void relu_bwd_kernel(const float* __restrict__ x, const float* dy, float* dx, size_t count) {
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x)
     dx[i] = dy[i] * (x[i] > 0.f ? 1.f : 0.f);
 }

@@ -102,6 +102,28 @@ int cct_conv_forward(cct_conv_plan* plan, const float* X, const float* W, const 
 int cct_conv_backward(cct_conv_plan* plan, const float* X, const float* W, const float* dY, float* dX, float* dW,
                       float* db);
 
+/* cct_conv_backward with the backward passes of the neighbouring bridges folded in (the reference runs them as
+ * separate bridges: MaxPoolingBridge::backward src/bridges/MaxPoolingBridge_impl.hxx:106-151, ReLUBridge::backward
+ * src/bridges/ReLUBridge_impl.hxx:65-99).
+ *   - Output side.  With f->dP != NULL the gradient of this layer's output is not taken from dY (pass NULL) but built
+ *     from what sits behind the convolution, conv -> ReLU -> max-pool(pool_k, pool_s):
+ *         dY = (A > 0) * maxpool_backward(dP, idx)
+ *     A = this layer's forward output [batch][out_depth][m][m] (pre- or post-ReLU: only its sign is used), idx = the
+ *     int32 indices cct_maxpool_forward wrote, dP = gradient of the pooled tensor.  One HBM-bound pass into
+ *     plan-owned scratch feeds both gradient kernels.
+ *   - Input side.  relu_mask_dx != 0 writes dX * [X > 0] instead of dX: the ReLU bridge in front of this layer (whose
+ *     output X is) folded into the data-gradient epilogue.
+ * f == NULL behaves like cct_conv_backward. */
+typedef struct cct_bwd_fusion {
+  const float* A;
+  const int32_t* idx;
+  const float* dP;
+  int pool_k, pool_s;
+  int relu_mask_dx;
+} cct_bwd_fusion;
+int cct_conv_backward_fused(cct_conv_plan* plan, const float* X, const float* W, const float* dY,
+                            const cct_bwd_fusion* f, float* dX, float* dW, float* db);
+
 /* Host-buffer forms of the two calls above, for callers that keep cubes in host memory as the reference's
  * ParallelizedBridge does (src/bridges/ParallelizedBridge_impl.hxx:538-671, 686-738, 779-830, 895-910,
  * 1071-1122): inputs are copied to plan-owned device buffers, the kernels run, results are copied back, and the
