@@ -29,7 +29,9 @@ WORKLOADS = {
     # BASELINE config 2: AlexNet conv1, batch 256 per GPU, X ~ N(0,1), W ~ N(0,0.01), bias 0, dY ~ N(0,1)
     "alexnet_conv1": dict(B=256, D=3, n=227, o=96, k=11, s=4, p=0, g=1, x="normal", bias="zero"),
     # BASELINE config 3 geometry: CaffeNet conv2 (grouped), post-ReLU inputs
-    "caffenet_conv2": dict(B=256, D=96, n=27, o=256, k=5, s=1, p=2, g=2, x="relu", bias="one"),
+    # (its backward runs fused: output gradient rebuilt from the 3x3/2 max-pool indices and the ReLU sign, input
+    # gradient masked by the ReLU in front of the layer)
+    "caffenet_conv2": dict(B=256, D=96, n=27, o=256, k=5, s=1, p=2, g=2, x="relu", bias="one", pool=(3, 2)),
     # BASELINE config 1: LeNet conv1
     "lenet_conv1": dict(B=64, D=1, n=28, o=20, k=5, s=1, p=0, g=1, x="uniform", bias="normal"),
 }
@@ -230,7 +232,9 @@ def config_of(args, w, world):
     return {"workload": args.workload, "batch_per_gpu": w["B"], "global_batch": w["B"] * world,
             "in": "%dx%dx%d" % (w["D"], w["n"], w["n"]), "filters": "%d x %dx%d stride %d pad %d groups %d" %
             (w["o"], w["k"], w["k"], w["s"], w["p"], w["g"]),
-            "step": "forward + backward (dX, dW, db) + gradient all-reduce (N>1) + SGD momentum step",
+            "step": ("forward (+ReLU) + fused backward (dY from max-pool indices and ReLU sign; dX masked by the input's "
+                     "sign; dW, db) + gradient all-reduce (N>1) + SGD momentum step") if w.get("pool") else
+            "forward + backward (dX, dW, db) + gradient all-reduce (N>1) + SGD momentum step",
             "l2": "inputs larger than L2 (X + dY per step exceed 126 MB)" if
             4 * w["B"] * (w["D"] * w["n"] ** 2 + w["o"] * out_size(w) ** 2) > 126e6 else "L2 flushed between steps",
             "parallelism": "dp%d" % world}
@@ -290,6 +294,36 @@ def main():
     plan = conv.plan
     algo = C.c_int(conv.algo)
     vp = C.c_void_p
+
+    remnants = {}
+    if w.get("pool"):
+        # conv -> ReLU -> max-pool behind the layer: the pooled gradient dP ~ N(0,1) is what arrives from above.
+        pk, ps = w["pool"]
+        mp = (m - pk) // ps + 1
+        conv.fuse_relu, conv.fuse_relu_backward = True, True
+        pooled, idx = LogicalCube(ctx, mp, mp, o, B), LogicalCube(ctx, mp, mp, o, B, np.int32)
+        dP = LogicalCube.from_numpy(ctx, np.random.default_rng(1000 * (rank + 1) + 7).standard_normal(
+            (B, o, mp, mp), dtype=np.float32))
+        conv.forward()
+        capi.check(lib.cct_maxpool_forward(ctx.h, vp(out.p_data_cube.ptr), vp(pooled.ptr), vp(idx.ptr), B * o, m, pk, ps),
+                   "cct_maxpool_forward", ctx.h)
+        conv.fuse_pool_relu_backward(dP, idx, pk, ps)
+        # The mask pass alone (HBM-bound): reads A, idx, dP once, writes dY once.
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        scratch = LogicalCube(ctx, m, m, o, B)
+        for it in range(13):
+            if it == 3:
+                ev[0].record(stream)
+            capi.check(lib.cct_pool_relu_backward(ctx.h, vp(out.p_data_cube.ptr), vp(idx.ptr), vp(dP.ptr), vp(scratch.ptr),
+                                                  B * o, m, pk, ps), "cct_pool_relu_backward", ctx.h)
+        ev[1].record(stream)
+        torch.cuda.synchronize()
+        ms = ev[0].elapsed_time(ev[1]) / 10
+        nbytes = 4.0 * B * o * (2 * m * m + 2 * mp * mp)
+        hbm = load_peaks().get("hbm_gbs")
+        remnants["pool_relu_mask_pass"] = {"ms": ms, "bytes": nbytes, "achieved_gbs": nbytes / ms / 1e6,
+                                           "peak_gbs": hbm, "frac": nbytes / ms / 1e6 / hbm if hbm else None}
+        scratch.free()
 
     def step():
         pbridge.forward()   # cct_conv_forward
@@ -398,8 +432,10 @@ def main():
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": {"value": world * B / e2e_s, "unit": "images/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3, "steps": args.e2e_steps},
-            "clocks": clocks, "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks, "gpu_launches": (launches_per_step + (1 if w.get("pool") else 0)) * args.steps,
         }
+        if remnants:
+            line["hbm_bound_passes"] = remnants
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

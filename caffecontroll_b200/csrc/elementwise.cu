@@ -3,6 +3,8 @@
 // bounded by HBM bandwidth (bytes per element noted at each kernel).
 #include <float.h>
 
+#include <algorithm>
+
 #include "cct_internal.h"
 
 namespace {
@@ -14,6 +16,14 @@ inline int grid_for(cct_ctx* ctx, size_t work, int threads) {
   if (blocks < 1) blocks = 1;
   return (int)blocks;
 }
+
+// Magic for fast_div: valid when max_x * d < 2^32 and d > 1, else 0 (plain division).
+inline uint32_t fast_div_magic(uint64_t max_x, uint32_t d) {
+  return (d > 1 && max_x * d < (1ull << 32)) ? (uint32_t)((1ull << 32) / d) + 1u : 0u;
+}
+
+// Blocks for the per-plane kernels: a multiple of the SM count, at most one block per plane.
+inline int plane_grid(cct_ctx* ctx, int planes) { return std::max(1, std::min(planes, ctx->sm_count * 8)); }
 
 // 4 B written per element.
 __global__ void fill_kernel(float* __restrict__ p, size_t count, float v) {
@@ -49,52 +59,154 @@ __global__ void relu_bwd_kernel(const float* __restrict__ x, const float* dy, fl
     dx[i] = dy[i] * (x[i] > 0.f ? 1.f : 0.f);
 }
 
-// One thread per pooled element; rows then columns, strict '>' so the first maximum wins.
+// One block per plane at a time (planes are small: 13x13 ... 55x55), so all index arithmetic is 32-bit and the
+// plane offset is the only 64-bit product.  Rows then columns, strict '>' so the first maximum wins.
 __global__ void maxpool_fwd_kernel(const float* __restrict__ X, float* __restrict__ Y, int32_t* __restrict__ idx,
                                    int planes, int n, int m, int k, int s) {
-  const size_t total = (size_t)planes * m * m;
-  for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
-    const int pw = (int)(t % m), ph = (int)((t / m) % m);
-    const size_t plane = t / ((size_t)m * m);
-    const float* in = X + plane * n * n;
-    const int he = min(ph * s + k, n), we = min(pw * s + k, n);
-    float best = -FLT_MAX;
-    int where = 0;
-    for (int h = ph * s; h < he; ++h)
-      for (int w = pw * s; w < we; ++w) {
-        const float v = in[h * n + w];
-        if (v > best) { best = v; where = h * n + w; }
-      }
-    Y[t] = best;
-    idx[t] = where;
+  const int mm = m * m;
+  for (int plane = blockIdx.x; plane < planes; plane += gridDim.x) {
+    const float* in = X + (size_t)plane * n * n;
+    for (int t = threadIdx.x; t < mm; t += blockDim.x) {
+      const int ph = t / m, pw = t - ph * m;
+      const int he = min(ph * s + k, n), we = min(pw * s + k, n);
+      float best = -FLT_MAX;
+      int where = 0;
+      for (int h = ph * s; h < he; ++h)
+        for (int w = pw * s; w < we; ++w) {
+          const float v = in[h * n + w];
+          if (v > best) { best = v; where = h * n + w; }
+        }
+      Y[(size_t)plane * mm + t] = best;
+      idx[(size_t)plane * mm + t] = where;
+    }
   }
+}
+
+// x / d for x * d < 2^32 as one multiply-high: inv = floor(2^32 / d) + 1 (host side, fast_div_magic); inv == 0 means
+// "divide".  The GPU has no integer divider, and these kernels would otherwise spend more on index arithmetic than on
+// memory.
+__device__ __forceinline__ uint32_t fast_div(uint32_t x, uint32_t d, uint32_t inv) {
+  return inv ? __umulhi(x, inv) : x / d;
 }
 
 // Gather form of "zero-fill, then dX[idx] += dY in (ph, pw) order": each input element visits the windows that
 // cover it in the same order, so the fp32 sum is the same.  RELU additionally multiplies by (A > 0).
-template <bool RELU>
-__global__ void maxpool_bwd_kernel(const float* __restrict__ A, const int32_t* __restrict__ idx,
-                                   const float* __restrict__ dP, float* __restrict__ dA, int planes, int n, int m,
-                                   int k, int s) {
-  const size_t total = (size_t)planes * n * n;
-  for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
-    const int w = (int)(t % n), h = (int)((t / n) % n);
-    const size_t plane = t / ((size_t)n * n);
-    float acc = 0.f;
-    bool live = true;
-    if (RELU) live = A[t] > 0.f;
-    if (live) {
-      const int here = h * n + w;
-      const int ph0 = h < k ? 0 : (h - k) / s + 1, pw0 = w < k ? 0 : (w - k) / s + 1;
-      const int ph1 = min(h / s, m - 1), pw1 = min(w / s, m - 1);
-      const int32_t* ip = idx + plane * m * m;
-      const float* gp = dP + plane * m * m;
-      for (int ph = ph0; ph <= ph1; ++ph)
-        for (int pw = pw0; pw <= pw1; ++pw)
-          if (ip[ph * m + pw] == here) acc += gp[ph * m + pw];
-    }
-    dA[t] = acc;
+// One warp per plane at a time, eight elements per lane with their loads issued together; the pooled indices and
+// gradients (each read by up to ceil(k/s)^2 elements) come through L1.  HBM-bound: reads A, idx, dP once and writes
+// dA once.
+// T = ceil(k / s) = the most windows that cover an element per axis, as a compile-time bound (1..3) so the window
+// loop is straight-line code; T = 0 keeps runtime loops for larger ratios.  Adding 0.f for a window that does not
+// point here leaves the sum bit-identical.
+// One warp per plane at a time.  The warp first puts everything it will read in flight together - the plane's pooled
+// indices and gradients (into its slice of shared memory) and the first sixteen rows-worth of A (into registers) -
+// so a plane costs about two memory round trips; the window tests then run out of shared memory.
+constexpr int kPoolWarps = 8;  // warps (= planes in flight) per block
+template <int T, bool RELU>
+__global__ void __launch_bounds__(kPoolWarps * 32) maxpool_bwd_kernel(const float* __restrict__ A,
+                                                                      const int32_t* __restrict__ idx,
+                                                                      const float* __restrict__ dP,
+                                                                      float* __restrict__ dA, int planes, int n, int m,
+                                                                      int k, int s, uint32_t inv_s, int mm_pad) {
+  extern __shared__ uint32_t pool_smem[];
+  const int mm = m * m, nn = n * n;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // [n] coordinate -> first | last << 16 pooled coordinate whose window covers it, then one slice per warp
+  uint32_t* s_rng = pool_smem;
+  int32_t* s_idx = reinterpret_cast<int32_t*>(pool_smem) + ((n + 31) & ~31) + warp * 2 * mm_pad;
+  float* s_dp = reinterpret_cast<float*>(s_idx + mm_pad);
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    const int p0 = c < k ? 0 : (int)fast_div((uint32_t)(c - k), (uint32_t)s, inv_s) + 1;
+    const int p1 = min((int)fast_div((uint32_t)c, (uint32_t)s, inv_s), m - 1);
+    s_rng[c] = (uint32_t)p0 | ((uint32_t)p1 << 16);
   }
+  __syncthreads();
+  const int warp0 = blockIdx.x * kPoolWarps + warp, nwarps = gridDim.x * kPoolWarps;
+  for (int plane = warp0; plane < planes; plane += nwarps) {
+    const int32_t* ip = idx + (size_t)plane * mm;
+    const float* gp = dP + (size_t)plane * mm;
+    const float* a = RELU ? A + (size_t)plane * nn : nullptr;
+    float* out = dA + (size_t)plane * nn;
+    __syncwarp();  // the previous plane's window tests are done with the shared slice
+    for (int i = lane; i < mm; i += 32) {
+      s_idx[i] = __ldg(ip + i);
+      s_dp[i] = __ldg(gp + i);
+    }
+    // lane = column (in chunks of 32), sixteen rows per step with their A values loaded together: no division and no
+    // global load inside the window tests.
+    for (int w0 = 0; w0 < n; w0 += 32) {
+      const int w = w0 + lane;
+      const bool wok = w < n;
+      const uint32_t rw = s_rng[wok ? w : 0];
+      int pwc[T > 0 ? T : 1];
+      bool pwv[T > 0 ? T : 1];
+#pragma unroll
+      for (int jj = 0; jj < T; ++jj) {
+        const int pw = (int)(rw >> 16) - (T - 1) + jj;
+        pwv[jj] = wok && pw >= (int)(rw & 0xffffu);
+        pwc[jj] = max(pw, 0);
+      }
+      float av[16];
+      auto fetch = [&](int h0) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) av[j] = (RELU && wok && h0 + j < n) ? __ldg(a + (h0 + j) * n + w) : 1.f;
+      };
+      fetch(0);
+      __syncwarp();  // staged values visible (first column chunk) / harmless afterwards
+      for (int h0 = 0; h0 < n; h0 += 16) {
+        float res[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int h = min(h0 + j, n - 1);
+          const int here = h * n + w;
+          const bool live = av[j] > 0.f;
+          const uint32_t rh = s_rng[h];
+          const int ph1 = (int)(rh >> 16), ph0 = (int)(rh & 0xffffu);
+          float acc = 0.f;
+          if (T > 0) {
+#pragma unroll
+            for (int i = 0; i < T; ++i) {
+              const int ph = ph1 - (T - 1) + i;
+              const bool phv = live && ph >= ph0;
+              const int base = max(ph, 0) * m;
+#pragma unroll
+              for (int jj = 0; jj < T; ++jj) {
+                const int at = base + pwc[jj];
+                acc += (phv && pwv[jj] && s_idx[at] == here) ? s_dp[at] : 0.f;
+              }
+            }
+          } else if (live && wok) {
+            for (int ph = ph0; ph <= ph1; ++ph)
+              for (int pw = (int)(rw & 0xffffu); pw <= (int)(rw >> 16); ++pw)
+                if (s_idx[ph * m + pw] == here) acc += s_dp[ph * m + pw];
+          }
+          res[j] = acc;
+        }
+        if (h0 + 16 < n) fetch(h0 + 16);  // next rows' A in flight while these results are stored
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (wok && h0 + j < n) out[(h0 + j) * n + w] = res[j];
+      }
+    }
+  }
+}
+
+template <bool RELU>
+int launch_maxpool_bwd(cct_ctx* ctx, const float* A, const int32_t* idx, const float* dP, float* dA, int planes, int n,
+                       int m, int k, int s) {
+  const int grid = plane_grid(ctx, (planes + kPoolWarps - 1) / kPoolWarps);
+  const uint32_t inv_s = fast_div_magic((uint64_t)n, (uint32_t)s);
+  const int taps = (k + s - 1) / s;
+  const int mm_pad = (m * m + 31) & ~31;
+  const size_t smem = ((size_t)((n + 31) & ~31) + (size_t)kPoolWarps * 2 * mm_pad) * 4;
+  if (smem > 200 * 1024) {
+    ctx->last_error = "pooled plane too large for the shared-memory staging of maxpool backward";
+    return CCT_ERR_UNSUPPORTED;
+  }
+  auto kernel = taps == 1 ? maxpool_bwd_kernel<1, RELU> : taps == 2 ? maxpool_bwd_kernel<2, RELU>
+              : taps == 3 ? maxpool_bwd_kernel<3, RELU> : maxpool_bwd_kernel<0, RELU>;
+  if (smem > 48 * 1024) CCT_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kernel<<<grid, kPoolWarps * 32, smem, ctx->stream>>>(A, idx, dP, dA, planes, n, m, k, s, inv_s, mm_pad);
+  return CCT_OK;
 }
 
 }  // namespace
@@ -141,7 +253,7 @@ int cct_maxpool_forward(cct_ctx* ctx, const float* X, float* Y, int32_t* idx, in
   if (!ctx || !X || !Y || !idx || !pool_args_ok(planes, n, k, s)) return CCT_ERR_INVALID;
   const int m = (n - k) / s + 1;
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
-  maxpool_fwd_kernel<<<grid_for(ctx, (size_t)planes * m * m, 256), 256, 0, ctx->stream>>>(X, Y, idx, planes, n, m, k,
+  maxpool_fwd_kernel<<<plane_grid(ctx, planes), 256, 0, ctx->stream>>>(X, Y, idx, planes, n, m, k,
                                                                                         s);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
@@ -152,8 +264,8 @@ int cct_maxpool_backward(cct_ctx* ctx, const float* dY, const int32_t* idx, floa
   if (!ctx || !dY || !idx || !dX || !pool_args_ok(planes, n, k, s)) return CCT_ERR_INVALID;
   const int m = (n - k) / s + 1;
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
-  maxpool_bwd_kernel<false><<<grid_for(ctx, (size_t)planes * n * n, 256), 256, 0, ctx->stream>>>(nullptr, idx, dY, dX,
-                                                                                                planes, n, m, k, s);
+  const int rc = launch_maxpool_bwd<false>(ctx, nullptr, idx, dY, dX, planes, n, m, k, s);
+  if (rc != CCT_OK) return rc;
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }
@@ -163,8 +275,8 @@ int cct_pool_relu_backward(cct_ctx* ctx, const float* A, const int32_t* idx, con
   if (!ctx || !A || !idx || !dP || !dA || !pool_args_ok(planes, n, k, s)) return CCT_ERR_INVALID;
   const int m = (n - k) / s + 1;
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
-  maxpool_bwd_kernel<true><<<grid_for(ctx, (size_t)planes * n * n, 256), 256, 0, ctx->stream>>>(A, idx, dP, dA, planes,
-                                                                                               n, m, k, s);
+  const int rc = launch_maxpool_bwd<true>(ctx, A, idx, dP, dA, planes, n, m, k, s);
+  if (rc != CCT_OK) return rc;
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }

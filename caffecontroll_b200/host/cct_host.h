@@ -164,13 +164,38 @@ class ConvolutionBridge : public PhysicalOperator {
                                      p_output_layer->p_data_cube->get_p_data(), fuse_relu ? 1 : 0),
                     "cct_conv_forward");
   }
+  // Fold the bridges around this layer into backward(): the ReLU in front of it (input gradient times
+  // [input > 0]) and, with pooled_gradient / max_index set, the ReLU + max-pooling bridges behind it (the output
+  // gradient is rebuilt from the pooled tensor's gradient instead of being read from p_output_layer).
+  bool fuse_relu_backward = false;
+  const float* pooled_gradient = nullptr;
+  const int32_t* max_index = nullptr;
+  int pool_kernel_size = 0, pool_stride = 0;
+
   void backward() override {
-    p_driver->check(cct_conv_backward(plan_, p_input_layer->p_data_cube->get_p_data(), p_model_cube_->get_p_data(),
-                                      p_output_layer->p_gradient_cube->get_p_data(),
-                                      needs_to_calc_backward_grad ? p_input_layer->p_gradient_cube->get_p_data() : nullptr,
-                                      p_model_gradient_cube_->get_p_data(),
-                                      bias_term ? p_bias_gradient_cube_->get_p_data() : nullptr),
-                    "cct_conv_backward");
+    float* dx = needs_to_calc_backward_grad ? p_input_layer->p_gradient_cube->get_p_data() : nullptr;
+    float* db = bias_term ? p_bias_gradient_cube_->get_p_data() : nullptr;
+    const float* x = p_input_layer->p_data_cube->get_p_data();
+    if (!fuse_relu_backward && !pooled_gradient) {
+      p_driver->check(cct_conv_backward(plan_, x, p_model_cube_->get_p_data(),
+                                        p_output_layer->p_gradient_cube->get_p_data(), dx,
+                                        p_model_gradient_cube_->get_p_data(), db),
+                      "cct_conv_backward");
+      return;
+    }
+    cct_bwd_fusion f = {nullptr, nullptr, nullptr, 0, 0, fuse_relu_backward ? 1 : 0};
+    const float* dy = p_output_layer->p_gradient_cube->get_p_data();
+    if (pooled_gradient) {
+      f.A = p_output_layer->p_data_cube->get_p_data();
+      f.idx = max_index;
+      f.dP = pooled_gradient;
+      f.pool_k = pool_kernel_size;
+      f.pool_s = pool_stride;
+      dy = nullptr;
+    }
+    p_driver->check(cct_conv_backward_fused(plan_, x, p_model_cube_->get_p_data(), dy, &f, dx,
+                                            p_model_gradient_cube_->get_p_data(), db),
+                    "cct_conv_backward_fused");
   }
 
  private:
