@@ -374,7 +374,7 @@ def main():
     ach = F / (passes[dom] * 1e-3) / 1e12 if passes[dom] > 0 else 0.0
     roofline = {
         "bound": "tensor", "kernel": {"forward": "gather_conv_kernel (forward)", "dgrad": "gather_conv_kernel (data gradient)",
-                                      "wgrad": "wgrad_kernel"}[dom] if algo.value == 2 else "simt_%s" % dom,
+                                      "wgrad": "split_dy_kernel + gather_conv_kernel (weight gradient)"}[dom] if algo.value == 2 else "simt_%s" % dom,
         "pass": dom, "achieved": ach, "peak": tensor_peak, "unit": "TFLOP/s", "frac": ach / tensor_peak,
         "traffic": dram_traffic(args.workload, w, dom, B) if algo.value == 2 else None,
         "traffic_source": "ncu dram__bytes_read.sum of the batch-64 capture scaled by batch/64, plus the pass's "
@@ -421,8 +421,9 @@ def main():
         if world == 1 and not args.no_cpu_baseline:
             cpu = cpu_reference_time(w, 3, 1, False)
             cpu.pop("seconds_per_step", None)
-        # tcgen05 path: pack + gather (forward); wgrad + reduce + pack + gather (backward); two SGD kernels
-        launches_per_step = (2 + 4 + 2) if algo.value == 2 else (1 + 3 + 2)
+        # tcgen05 path: pack + gather (forward); dY split + gather + reduce + bias sums, pack + gather (backward);
+        # two SGD kernels
+        launches_per_step = (2 + 6 + 2) if algo.value == 2 else (1 + 3 + 2)
         line = {
             "metric": METRIC, "value": world * B / (ms_step * 1e-3), "unit": "images/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,

@@ -100,6 +100,19 @@ __device__ __forceinline__ float ldg_if_bits(const float* p, uint32_t mask, uint
       : "l"(p), "r"(mask), "r"(bits));
   return v;
 }
+// v = ((a & b) == 0) ? *p : 0, same form (a, b: "what is out of bounds here" against "what this entry needs").
+__device__ __forceinline__ float ldg_if_clear(const float* p, uint32_t a, uint32_t b) {
+  float v;
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t.reg .b32 t;\n\t"
+      "and.b32 t, %2, %3;\n\t"
+      "setp.eq.u32 q, t, 0;\n\t"
+      "mov.f32 %0, 0f00000000;\n\t"
+      "@q ld.global.nc.f32 %0, [%1];\n\t}"
+      : "=f"(v)
+      : "l"(p), "r"(a), "r"(b));
+  return v;
+}
 // v = flag ? *p : 0, same form.
 __device__ __forceinline__ float ldg_if(const float* p, uint32_t flag) {
   float v;
@@ -274,9 +287,38 @@ struct GatherParams {
   int n_bias;              // entries of `bias` (all output channels), staged in shared memory
   int lo_row_offset;       // first row of the "lo" half inside the packed-weight tensor map
   int relu;
+  // Weight-gradient mode: the TMEM lanes are rows of the lowered matrix (taps), the reduction runs over pixels.
+  // `taps` then points to a table in global memory with one entry per pixel (offset of the pixel's tap origin and
+  // the set of tap rows / columns that fall outside the plane there), `out` to the split partial sums.
+  int wg;
+  int wg_mtiles, wg_vgroups;  // tiles = splits x channel tiles x M-tiles (M-tile fastest)
+  int wg_rows_pad;            // rows of one split's partial-sum slice (M-tiles * 128)
+  int wg_k, wg_kreal;         // kernel size, real rows of the lowered matrix
+  int taps_smem;              // entries of `taps` staged in shared memory (0 in weight-gradient mode)
   int* status;
   int dbg;
 };
+
+// Which tile a persistent CTA works on: channel tile, pixel tile (or M-tile), first k-block, split.
+struct TileId {
+  int vg, ptile, kb0, split;
+};
+__device__ __forceinline__ TileId decode_tile(const GatherParams& P, int t, int kblocks) {
+  TileId id;
+  if (!P.wg) {
+    id.vg = t / P.n_pix_tiles;
+    id.ptile = t - id.vg * P.n_pix_tiles;
+    id.kb0 = 0;
+    id.split = 0;
+  } else {
+    const int r = t / P.wg_mtiles;
+    id.ptile = t - r * P.wg_mtiles;
+    id.split = r / P.wg_vgroups;
+    id.vg = r - id.split * P.wg_vgroups;
+    id.kb0 = id.split * kblocks;
+  }
+  return id;
+}
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -331,7 +373,7 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  const GatherSmem L = gather_smem(P.n_pad, P.k_pad, P.b_stages, P.n_bias);
+  const GatherSmem L = gather_smem(P.n_pad, P.taps_smem, P.b_stages, P.n_bias);
   const uint32_t bars = base + L.bars_off;
   // K-block i (running index over this CTA's tiles) uses A slot i % a_stages, weight slot i % b_stages and the
   // barrier pair i % 4: "ready" completes when the four producer warps of the block's set and the weight tile's TMA
@@ -345,8 +387,9 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
   float* s_bias = reinterpret_cast<float*>(base_ptr + L.bias_off);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-  for (int i = tid; i < P.k_pad; i += kGatherThreads) s_taps[i] = P.taps[i];
-  for (int i = tid; i < P.n_pad; i += kGatherThreads) s_cols[i] = P.cols[i];
+  for (int i = tid; i < P.taps_smem; i += kGatherThreads) s_taps[i] = P.taps[i];
+  if (P.cols)
+    for (int i = tid; i < P.n_pad; i += kGatherThreads) s_cols[i] = P.cols[i];
   for (int i = tid; i < P.n_bias + kBiasPad; i += kGatherThreads) s_bias[i] = i < P.n_bias ? P.bias[i] : 0.f;
   if (tid == 0) {
     for (int s = 0; s < kMaxAStages; ++s) { mbar_init(ready_bar + 8u * s, 5); mbar_init(done_bar + 8u * s, 1); }  // 4 producer warps + the TMA thread
@@ -374,13 +417,28 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
     const int my_tiles = (P.total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
     const int my_stages = my_tiles * kblocks;
     const float* in_px = P.in;
-    uint32_t mask = 0;
+    uint32_t mask = 0;                   // forward / data gradient: which taps are in bounds for this lane's pixel
+    const MaskTap* pix_tab = P.taps;     // weight gradient: this tile's slice of the per-pixel table
     auto setup_tile = [&](int tile_local) {
       const int t = blockIdx.x + tile_local * gridDim.x;
-      const int vg = t / P.n_pix_tiles, ptile = t - vg * P.n_pix_tiles;
-      const int grp = vg / P.tiles_per_group;
-      const int pix = ptile * kTileM + row;
+      const TileId id = decode_tile(P, t, kblocks);
+      const int grp = id.vg / P.tiles_per_group;
       in_px = P.in;
+      if (P.wg) {
+        // lane = row of the lowered matrix: (d, kr, kc); `mask` holds the tap's row and column bit
+        const int r = id.ptile * kTileM + row;
+        mask = kPadBit;
+        if (r < P.wg_kreal) {
+          const int kk = P.wg_k * P.wg_k;
+          const int d = r / kk, rem = r - d * kk;
+          const int kr = rem / P.wg_k, kc = rem - kr * P.wg_k;
+          in_px = P.in + (long long)grp * P.in_group_stride + (long long)d * P.in_lim * P.in_lim + kr * P.in_lim + kc;
+          mask = (1u << kr) | (1u << (16 + kc));
+        }
+        pix_tab = P.taps + (size_t)id.kb0 * kBlockK;
+        return;
+      }
+      const int pix = id.ptile * kTileM + row;
       mask = 0;  // which tap rows (bits 0-14) and tap columns (bits 16-30) fall inside the plane
       if (pix < P.n_pix) {
         const int per_img = P.q_h * P.q_w;
@@ -401,6 +459,16 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
     };
     float v[kBlockK];
     auto gather = [&](int kb) {
+      if (P.wg) {
+        // entry = (offset of the pixel's tap origin, tap rows / columns out of bounds there); same for all lanes
+        const uint2* tp = reinterpret_cast<const uint2*>(pix_tab + kb * kBlockK);
+#pragma unroll
+        for (int e = 0; e < kBlockK; ++e) {
+          const uint2 ent = __ldg(tp + e);
+          v[e] = ldg_if_clear(in_px + (int)ent.x, DBG(P, 1) ? 0xffffffffu : ent.y, mask);
+        }
+        return;
+      }
       const MaskTap* tp = s_taps + kb * kBlockK;
 #pragma unroll
       for (int e = 0; e < kBlockK; ++e) {
@@ -519,7 +587,8 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
       Ring rb;
       int i = 0;  // running k-block index
       for (int t = blockIdx.x; t < P.total_tiles; t += gridDim.x) {
-        const int vg = t / P.n_pix_tiles;
+        const TileId id = decode_tile(P, t, kblocks);
+        const int vg = id.vg;
         for (int kb = 0; kb < kblocks; ++kb, ++i) {
           const int sb = rb.idx;
           const int prev = i - P.b_stages;  // the k-block whose MMAs read this weight slot last
@@ -527,8 +596,8 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
           const uint32_t b_hi = base + (uint32_t)sb * L.b_stage_bytes, b_lo = b_hi + (uint32_t)P.n_pad * 128u;
           const uint32_t bar = ready_bar + 8u * (i & 3);
           mbar_expect_tx(bar, L.b_stage_bytes);
-          tma_load_2d(b_hi, &w_map, kb * kBlockK, vg * P.n_pad, bar);
-          tma_load_2d(b_lo, &w_map, kb * kBlockK, P.lo_row_offset + vg * P.n_pad, bar);
+          tma_load_2d(b_hi, &w_map, (id.kb0 + kb) * kBlockK, vg * P.n_pad, bar);
+          tma_load_2d(b_lo, &w_map, (id.kb0 + kb) * kBlockK, P.lo_row_offset + vg * P.n_pad, bar);
           rb.advance(P.b_stages);
         }
       }
@@ -540,9 +609,40 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
     int tile_iter = 0;
     PROF_DECL;
     for (int t = blockIdx.x; t < P.total_tiles; t += gridDim.x, ++tile_iter) {
-      const int vg = t / P.n_pix_tiles, ptile = t - vg * P.n_pix_tiles;
+      const TileId id = decode_tile(P, t, kblocks);
+      const int vg = id.vg, ptile = id.ptile;
       const int grp = vg / P.tiles_per_group, ntile = vg % P.tiles_per_group;
       const int buf = tile_iter & (P.acc_bufs - 1), ause = tile_iter >> (P.acc_bufs - 1);
+      if (P.wg) {
+        // The accumulator is a 128-row slice of this split's partial sums: row-contiguous stores.
+        PROF_LAP(0);
+        mbar_wait(acc_full + 8u * buf, (uint32_t)ause & 1u, failed, P.status, 0x200);
+        tc_fence_after();
+        PROF_LAP(1);
+        const uint32_t acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P.acc_cols);
+        float* op = P.out + ((size_t)(id.split * P.wg_vgroups + vg) * P.wg_rows_pad + (size_t)ptile * kTileM + row) * P.n_pad;
+        for (int c = 0; c < P.n_pad / 16; ++c) {
+          float v[16];
+          tmem_ld16(acc + (uint32_t)(c * 16), v);
+          if (P.dual) {
+            float w[16];
+            tmem_ld16(acc + (uint32_t)(P.n_pad + c * 16), w);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] += w[j];
+          }
+          if (!failed) {
+            float4* o4 = reinterpret_cast<float4*>(op + c * 16);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) o4[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          }
+        }
+        PROF_LAP(4);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty + 8u * buf);
+        PROF_LAP(2);
+        continue;
+      }
       const int pix = ptile * kTileM + row;
       int b = 0, qy = 0, qx = 0;
       if (pix < P.n_pix) {
@@ -953,6 +1053,7 @@ __global__ void wgrad_reduce_kernel(const float* __restrict__ partial, float* __
     const int j = (int)(t % n_real);
     const int kk = (int)((t / n_real) % (k_real + 1));
     const int vg = (int)(t / ((size_t)n_real * (k_real + 1)));
+    if (kk == k_real && !db) continue;  // no bias row in the partial sums
     float acc = 0.f;
     for (int s = 0; s < splits; ++s) acc += partial[(((size_t)s * vgroups + vg) * rows_pad + kk) * n_pad + j];
     const int ch = (vg / tiles_per_group) * og + (vg % tiles_per_group) * n_real + j;
@@ -961,6 +1062,62 @@ __global__ void wgrad_reduce_kernel(const float* __restrict__ partial, float* __
     else if (db)
       db[ch] = acc;
   }
+}
+
+// ------------------------------------------------------------------- dY as a pre-split TMA operand, bias sums
+// dY[b][c][pix] -> hi / lo [row of channel c][b * mm + pix] with row = channel tile * n_pad + channel inside the
+// tile (K-major rows of `row_len` floats, so a TMA box is 32 consecutive pixels x one channel tile), and the plane
+// sum of dY[b][c] for the bias gradient.  One block per plane at a time; every access is a coalesced run.
+__global__ void __launch_bounds__(256) split_dy_kernel(const float* __restrict__ dY, float* __restrict__ hi,
+                                                       float* __restrict__ lo, float* __restrict__ plane_sums,
+                                                       int planes, int channels, int mm, int og, int ch_tile,
+                                                       int tiles_per_group, int n_pad, size_t row_len) {
+  // One warp per plane at a time, eight loads in flight per lane; no block-wide synchronisation.
+  const int lane = threadIdx.x & 31;
+  const int warp0 = (int)((blockIdx.x * blockDim.x + threadIdx.x) >> 5), nwarps = (int)((gridDim.x * blockDim.x) >> 5);
+  for (int plane = warp0; plane < planes; plane += nwarps) {
+    const int b = plane / channels, c = plane - b * channels;
+    const int grp = c / og, j = c - grp * og;
+    const int tile = j / ch_tile, within = j - tile * ch_tile;
+    const size_t row = (size_t)(grp * tiles_per_group + tile) * n_pad + within;
+    const float* src = dY + (size_t)plane * mm;
+    float* dh = hi + row * row_len + (size_t)b * mm;
+    float* dl = lo + row * row_len + (size_t)b * mm;
+    float sum = 0.f;
+    for (int i0 = 0; i0 < mm; i0 += 256) {
+      float x[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = i0 + u * 32 + lane;
+        x[u] = i < mm ? __ldg(src + i) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = i0 + u * 32 + lane;
+        uint32_t h, l;
+        split_tf32_trunc(x[u], h, l);
+        if (i < mm) {
+          dh[i] = __uint_as_float(h);
+          dl[i] = __uint_as_float(l);
+        }
+        sum += x[u];
+      }
+    }
+    if (plane_sums) {  // fixed-shape reduction: the result does not depend on the grid
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      if (lane == 0) plane_sums[plane] = sum;
+    }
+  }
+}
+
+// db[c] = sum over the batch of the plane sums, in batch order (ConvolutionBridge_impl.hxx:575-599 adds them so).
+__global__ void bias_grad_kernel(const float* __restrict__ plane_sums, float* __restrict__ db, int batch, int channels) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  float t = 0.f;
+  for (int b = 0; b < batch; ++b) t += plane_sums[(size_t)b * channels + c];
+  db[c] = t;
 }
 
 // ------------------------------------------------------------------------------------------ weight packing
@@ -1043,6 +1200,8 @@ struct GatherProblem {
   CUtensorMap map;
   int a_stages = 4, b_stages = 4, acc_bufs = 1, dual = 0, acc_cols = 0;
   int sets = 4, tmem_cols = 512;  // kernel shape: 4 producer sets and one CTA per SM, or 2 sets and two CTAs per SM
+  int taps_smem = -1;             // tap-table entries staged in shared memory (-1: k_pad)
+  size_t map_k = 0;               // extent of the packed operand along the reduction (0: k_pad)
   size_t smem = 0;
 };
 
@@ -1055,6 +1214,13 @@ struct UmmaPlan {
   size_t w_smem = 0;
   MaskTap* w_taps = nullptr;
   float* w_partial = nullptr;
+  // weight gradient through the gather kernel: lanes = rows of the lowered matrix, reduction over pixels, dY as the
+  // pre-split TMA operand [hi|lo][channel tile][channel][pixel]
+  bool wg_gather = false;
+  GatherProblem wgp;
+  MaskTap* wg_pix = nullptr;       // per pixel: offset of the tap origin, taps out of bounds (padded to splits * kps * 32)
+  float* wg_plane_sums = nullptr;  // [batch][channel] sums of dY for the bias gradient
+  int wg_splits = 1, wg_kps = 1, wg_mtiles = 1;
   size_t bytes = 0;
 };
 
@@ -1111,6 +1277,14 @@ int pack_grid(cct_ctx* ctx, size_t total) {
   return (int)std::min<size_t>(std::max<size_t>(b, 1), (size_t)ctx->sm_count * 8);
 }
 
+bool wgrad_gather_allowed() {
+#ifdef CCT_DBG
+  const char* e = getenv("CCT_DBG_OLD_WGRAD");
+  if (e && atoi(e)) return false;
+#endif
+  return true;
+}
+
 bool two_ctas_allowed() {
 #ifdef CCT_DBG
   const char* e = getenv("CCT_DBG_ONE_CTA");
@@ -1123,7 +1297,9 @@ bool two_ctas_allowed() {
 int finish_problem(cct_ctx* ctx, UmmaPlan* p, GatherProblem& gp, int vgroups, int n_bias) {
   // Tensor memory (512 columns) = accumulator buffers + A stages of 64 columns.  Narrow problems run "dual" (see the
   // MMA loop): their accumulator is 2*n_pad wide.  Two accumulator buffers let the epilogue overlap the next tile.
-  gp.dual = gp.n_pad <= 64;  // 2 MMAs of width <= 128 (93 cycles each) instead of 3; wider ones gain nothing
+  const int taps_smem = gp.taps_smem < 0 ? gp.k_pad : gp.taps_smem;
+  const size_t map_k = gp.map_k ? gp.map_k : (size_t)gp.k_pad;
+  gp.dual = gp.n_pad <= 64;  // 2 MMAs of width <= 128 instead of 3 narrow ones; wider ones gain nothing
   gp.acc_cols = gp.dual ? 2 * gp.n_pad : gp.n_pad;
   if (2 * gp.acc_cols + 4 * 64 <= 512) { gp.acc_bufs = 2; gp.a_stages = 4; }
   else if (2 * gp.acc_cols + 2 * 64 <= 512 && gp.k_pad / kBlockK <= 16) { gp.acc_bufs = 2; gp.a_stages = 2; }  // short K: the epilogue matters more
@@ -1131,7 +1307,7 @@ int finish_problem(cct_ctx* ctx, UmmaPlan* p, GatherProblem& gp, int vgroups, in
   // Weight slots (hi and lo tile each) in shared memory: up to four, independent of the number of A slots.
   auto slots_that_fit = [&](size_t limit) {
     int b = 4;
-    while (b > 1 && gather_smem(gp.n_pad, gp.k_pad, b, n_bias).total + 1024 > limit) --b;
+    while (b > 1 && gather_smem(gp.n_pad, taps_smem, b, n_bias).total + 1024 > limit) --b;
     return b;
   };
   gp.b_stages = slots_that_fit(kSmemLimit);
@@ -1141,8 +1317,8 @@ int finish_problem(cct_ctx* ctx, UmmaPlan* p, GatherProblem& gp, int vgroups, in
   if (gp.acc_cols <= 128 && b_two >= 3 && two_ctas_allowed()) {
     gp.sets = 2; gp.tmem_cols = 256; gp.acc_bufs = 1; gp.a_stages = 2; gp.b_stages = b_two;
   }
-  gp.smem = gather_smem(gp.n_pad, gp.k_pad, gp.b_stages, n_bias).total + 1024;
-  gp.w_half = (size_t)vgroups * gp.n_pad * gp.k_pad;
+  gp.smem = gather_smem(gp.n_pad, taps_smem, gp.b_stages, n_bias).total + 1024;
+  gp.w_half = (size_t)vgroups * gp.n_pad * map_k;
   int rc = dev_alloc(ctx, p, &gp.w, 2 * gp.w_half);
   if (rc != CCT_OK) return rc;
   EncodeTiledFn enc = encode_tiled_fn();
@@ -1150,8 +1326,8 @@ int finish_problem(cct_ctx* ctx, UmmaPlan* p, GatherProblem& gp, int vgroups, in
     ctx->last_error = "cuTensorMapEncodeTiled is not available from this driver";
     return CCT_ERR_CUDA;
   }
-  const cuuint64_t gdim[2] = {(cuuint64_t)gp.k_pad, (cuuint64_t)(2 * vgroups * gp.n_pad)};
-  const cuuint64_t gstride[1] = {(cuuint64_t)gp.k_pad * sizeof(float)};
+  const cuuint64_t gdim[2] = {(cuuint64_t)map_k, (cuuint64_t)(2 * vgroups * gp.n_pad)};
+  const cuuint64_t gstride[1] = {(cuuint64_t)map_k * sizeof(float)};
   const cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)gp.n_pad};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = enc(&gp.map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, gp.w, gdim, gstride, box, estr,
@@ -1265,6 +1441,52 @@ int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out) {
     if (rc == CCT_OK)
       rc = dev_alloc(ctx, p, &p->w_partial, (size_t)p->w_splits * G.g * f.tiles * p->w_mtiles * kTileM * f.n_pad);
   }
+  // ---- weight gradient through the gather kernel (the default): tiles = splits x channel tiles x M-tiles
+  if (rc == CCT_OK && wgrad_gather_allowed()) {
+    const GatherProblem& f = p->fwd;
+    GatherProblem& w = p->wgp;
+    const int n_pix = G.B * G.m * G.m;
+    const int kb_total = (n_pix + kBlockK - 1) / kBlockK;
+    const int vgroups = G.g * f.tiles;
+    w.tiles = f.tiles; w.ch_tile = f.ch_tile; w.n = f.n; w.n_pad = f.n_pad;
+    w.k_real = n_pix;
+    // about two tiles per persistent CTA, at least 16 k-blocks each
+    p->wg_mtiles = (f.k_real + kTileM - 1) / kTileM;  // no all-ones row here: the bias gradient comes from the dY pass
+    const int base_tiles = vgroups * p->wg_mtiles;
+    int splits = std::max(1, (4 * ctx->sm_count + base_tiles - 1) / base_tiles);
+    splits = std::min(splits, std::max(1, kb_total / 16));
+    p->wg_kps = (kb_total + splits - 1) / splits;
+    p->wg_splits = (kb_total + p->wg_kps - 1) / p->wg_kps;
+    w.k_pad = p->wg_kps * kBlockK;
+    w.taps_smem = 0;
+    w.map_k = (size_t)kb_total * kBlockK;
+    std::vector<MaskTap> t((size_t)p->wg_splits * p->wg_kps * kBlockK);
+    for (size_t i = 0; i < t.size(); ++i) {
+      if ((long long)i < n_pix) {
+        const int b = (int)(i / (G.m * G.m)), r = (int)(i % (G.m * G.m));
+        const int iy0 = (r / G.m) * G.s - G.p, ix0 = (r % G.m) * G.s - G.p;
+        uint32_t valid = 0;
+        for (int a = 0; a < G.k; ++a) {
+          if (iy0 + a >= 0 && iy0 + a < G.n) valid |= 1u << a;
+          if (ix0 + a >= 0 && ix0 + a < G.n) valid |= 1u << (16 + a);
+        }
+        const long long off = (long long)b * G.D * G.n * G.n + (long long)iy0 * G.n + ix0;
+        t[i] = MaskTap{(int)off, ~valid};
+      } else {
+        t[i] = MaskTap{0, 0xffffffffu};
+      }
+    }
+    rc = upload(ctx, p, &p->wg_pix, t);
+    if (rc == CCT_OK) rc = finish_problem(ctx, p, w, vgroups, 0);
+    if (rc == CCT_OK) CCT_CUDA(ctx, cudaMemsetAsync(w.w, 0, 2 * w.w_half * sizeof(float), ctx->stream));  // padded channel rows stay zero
+    if (rc == CCT_OK && G.bias) rc = dev_alloc(ctx, p, &p->wg_plane_sums, (size_t)G.B * G.o);
+    if (rc == CCT_OK) {
+      cudaFree(p->w_partial);  // sized for the other kernel's split count
+      p->w_partial = nullptr;
+      rc = dev_alloc(ctx, p, &p->w_partial, (size_t)p->wg_splits * vgroups * p->wg_mtiles * kTileM * f.n_pad);
+    }
+    p->wg_gather = rc == CCT_OK;
+  }
   if (rc == CCT_OK) rc = set_smem(ctx, gather_conv_kernel<4>, kSmemLimit);
   if (rc == CCT_OK) rc = set_smem(ctx, gather_conv_kernel<2>, 113 * 1024);
   if (rc == CCT_OK) rc = set_smem(ctx, wgrad_pick(p->w_subs, p->fwd.n_pad), kSmemLimit);
@@ -1278,7 +1500,8 @@ int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out) {
 
 void umma_plan_destroy(cct_ctx* ctx, UmmaPlan* p) {
   if (!p) return;
-  for (GatherProblem* gp : {&p->fwd, &p->dgr}) { cudaFree(gp->taps); cudaFree(gp->cols); cudaFree(gp->w); }
+  for (GatherProblem* gp : {&p->fwd, &p->dgr, &p->wgp}) { cudaFree(gp->taps); cudaFree(gp->cols); cudaFree(gp->w); }
+  cudaFree(p->wg_pix); cudaFree(p->wg_plane_sums);
   cudaFree(p->w_taps); cudaFree(p->w_partial);
   delete p;
 }
@@ -1292,6 +1515,7 @@ void fill_common(GatherParams& P, const GatherProblem& gp, cct_ctx* ctx, int vgr
   P.tiles_per_group = gp.tiles;
   P.out_tile_channels = gp.ch_tile;
   P.n = gp.n; P.n_pad = gp.n_pad; P.k_pad = gp.k_pad;
+  P.taps_smem = gp.taps_smem < 0 ? gp.k_pad : gp.taps_smem;
   P.n_pix_tiles = (P.n_pix + kTileM - 1) / kTileM;
   P.total_tiles = P.n_pix_tiles * vgroups;
   P.a_stages = gp.a_stages; P.b_stages = gp.b_stages; P.acc_bufs = gp.acc_bufs;
@@ -1354,7 +1578,37 @@ int umma_conv_backward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W
   if (*ctx->status_host != 0) return CCT_ERR_TIMEOUT;
   const ConvGeom& G = p->G;
   // ---- weight + bias gradient
-  {
+  if (p->wg_gather) {
+    const GatherProblem& f = p->fwd;
+    GatherProblem& w = p->wgp;
+    const int vgroups = G.g * f.tiles, mm = G.m * G.m;
+    t->begin(1, ctx->stream);
+    split_dy_kernel<<<std::min((G.B * G.o + 7) / 8, ctx->sm_count * 8), 256, 0, ctx->stream>>>(
+        dY, w.w, w.w + w.w_half, G.bias ? p->wg_plane_sums : nullptr, G.B * G.o, G.o, mm, G.og, f.ch_tile, f.tiles,
+        f.n_pad, w.map_k);
+    CCT_CHECK_LAUNCH(ctx);
+    GatherParams P{};
+    P.in = X; P.out = p->w_partial; P.bias = nullptr;
+    P.n_pix = p->wg_mtiles * kTileM;  // lanes = rows of the lowered matrix
+    P.in_lim = G.n;
+    P.in_group_stride = G.Dg * G.n * G.n;
+    P.wg = 1; P.wg_mtiles = p->wg_mtiles; P.wg_vgroups = vgroups; P.wg_rows_pad = p->wg_mtiles * kTileM;
+    P.wg_k = G.k; P.wg_kreal = f.k_real;
+    fill_common(P, w, ctx, vgroups, 0);
+    P.taps = p->wg_pix; P.cols = nullptr;
+    P.total_tiles = p->wg_splits * vgroups * p->wg_mtiles;
+    launch_gather(ctx, P, w);
+    t->end(1, ctx->stream);
+    CCT_CHECK_LAUNCH(ctx);
+    t->begin(2, ctx->stream);
+    const size_t total = (size_t)vgroups * (f.k_real + 1) * f.n;
+    wgrad_reduce_kernel<<<pack_grid(ctx, total), 256, 0, ctx->stream>>>(p->w_partial, dW, nullptr, p->wg_splits, vgroups,
+                                                                      f.tiles, p->wg_mtiles * kTileM, f.n, f.n_pad,
+                                                                      f.k_real, G.og);
+    if (G.bias) bias_grad_kernel<<<(G.o + 127) / 128, 128, 0, ctx->stream>>>(p->wg_plane_sums, db, G.B, G.o);
+    t->end(2, ctx->stream);
+    CCT_CHECK_LAUNCH(ctx);
+  } else {
     const GatherProblem& f = p->fwd;
     WgradParams P{};
     P.x = X; P.dy = dY; P.partial = p->w_partial; P.taps = p->w_taps;
