@@ -352,15 +352,17 @@ __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.
 
 constexpr int kBiasPad = 256;  // zeros behind the staged bias: every accumulator column of a tile reads an entry
 struct GatherSmem {
-  uint32_t b_stage_bytes, taps_off, cols_off, bias_off, bars_off, total;
+  uint32_t b_stage_bytes, taps_off, cols_off, bias_off, ptab_off, bars_off, total;
 };
-__host__ __device__ inline GatherSmem gather_smem(int n_pad, int k_pad, int b_stages, int n_bias) {
+// ptab_warps: producer warps that keep a double-buffered 32-entry slice of the per-pixel table (weight-gradient mode).
+__host__ __device__ inline GatherSmem gather_smem(int n_pad, int k_pad, int b_stages, int n_bias, int ptab_warps = 0) {
   GatherSmem L;
   L.b_stage_bytes = 2u * (uint32_t)n_pad * 128u;
   L.taps_off = (uint32_t)b_stages * L.b_stage_bytes;
   L.cols_off = L.taps_off + (uint32_t)k_pad * 8u;
   L.bias_off = L.cols_off + (uint32_t)n_pad * 8u;
-  L.bars_off = (L.bias_off + (uint32_t)(n_bias + kBiasPad) * 4u + 15u) & ~15u;
+  L.ptab_off = (L.bias_off + (uint32_t)(n_bias + kBiasPad) * 4u + 15u) & ~15u;
+  L.bars_off = L.ptab_off + (uint32_t)ptab_warps * 512u;
   L.total = L.bars_off + 8u * (2 * kMaxAStages + 2 * kMaxAccBufs) + 16u;
   return L;
 }
@@ -373,7 +375,7 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  const GatherSmem L = gather_smem(P.n_pad, P.taps_smem, P.b_stages, P.n_bias);
+  const GatherSmem L = gather_smem(P.n_pad, P.taps_smem, P.b_stages, P.n_bias, P.wg ? kProducerWarps : 0);
   const uint32_t bars = base + L.bars_off;
   // K-block i (running index over this CTA's tiles) uses A slot i % a_stages, weight slot i % b_stages and the
   // barrier pair i % 4: "ready" completes when the four producer warps of the block's set and the weight tile's TMA
@@ -458,13 +460,25 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
       }
     };
     float v[kBlockK];
+    // Weight gradient: the 32 table entries of a k-block are the same for every lane.  Lane e fetches entry e one
+    // step ahead (`ent_next`, in flight while the current block is split and stored), the warp passes them round
+    // through its own slice of shared memory.
+    uint2 ent_next = make_uint2(0u, 0xffffffffu);
+    uint2* my_ptab = reinterpret_cast<uint2*>(base_ptr + L.ptab_off) + warp * 64;
+    int pbuf = 0;
+    auto prefetch_entries = [&](int kb) {
+      if (P.wg) ent_next = __ldg(reinterpret_cast<const uint2*>(pix_tab + kb * kBlockK) + lane);
+    };
     auto gather = [&](int kb) {
       if (P.wg) {
-        // entry = (offset of the pixel's tap origin, tap rows / columns out of bounds there); same for all lanes
-        const uint2* tp = reinterpret_cast<const uint2*>(pix_tab + kb * kBlockK);
+        // entry = (offset of the pixel's tap origin, tap rows / columns out of bounds there)
+        uint2* slot = my_ptab + pbuf * 32;
+        pbuf ^= 1;
+        slot[lane] = ent_next;
+        __syncwarp();
 #pragma unroll
         for (int e = 0; e < kBlockK; ++e) {
-          const uint2 ent = __ldg(tp + e);
+          const uint2 ent = slot[e];
           v[e] = ldg_if_clear(in_px + (int)ent.x, DBG(P, 1) ? 0xffffffffu : ent.y, mask);
         }
         return;
@@ -480,12 +494,23 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
     while (kb >= kblocks && tile_local < my_tiles) { kb -= kblocks; ++tile_local; }
     if (group < my_stages) {
       setup_tile(tile_local);
+      prefetch_entries(kb);
       gather(kb);
     }
     PROF_DECL;
     for (int it = group; it < my_stages; it += SETS) {
       const int sa = it & (P.a_stages - 1);  // a_stages is 2 or 4
       const uint32_t st_addr = lane_addr + (uint32_t)(sa * 64);
+      // The set's next k-block: its tile state and (weight gradient) its table entries, requested now so that
+      // they have arrived when the gather is issued further down.  v[] still holds the current block.
+      const bool has_next = it + SETS < my_stages;
+      if (has_next) {
+        const int before = tile_local;
+        kb += SETS;
+        while (kb >= kblocks) { kb -= kblocks; ++tile_local; }
+        if (tile_local != before) setup_tile(tile_local);
+        prefetch_entries(kb);
+      }
       PROF_LAP(0);
       // The A slot was last read by the MMAs of k-block it - a_stages.
       const int prev = it - P.a_stages;
@@ -509,13 +534,7 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
         if (lane == 0) mbar_arrive(ready_bar + 8u * (it & 3));
       }
       PROF_LAP(4);
-      if (it + SETS < my_stages) {  // the set's next k-block: loads in flight across the next wait
-        const int before = tile_local;
-        kb += SETS;
-        while (kb >= kblocks) { kb -= kblocks; ++tile_local; }
-        if (tile_local != before) setup_tile(tile_local);
-        gather(kb);
-      }
+      if (has_next) gather(kb);  // loads in flight across the next wait
       PROF_LAP(3);
       if (P.a_stages != 2) {
         tmem_wait_st();
@@ -1111,13 +1130,20 @@ __global__ void __launch_bounds__(256) split_dy_kernel(const float* __restrict__
   }
 }
 
-// db[c] = sum over the batch of the plane sums, in batch order (ConvolutionBridge_impl.hxx:575-599 adds them so).
+// db[c] = sum over the batch of the plane sums (ConvolutionBridge_impl.hxx:575-599), in a fixed order.
 __global__ void bias_grad_kernel(const float* __restrict__ plane_sums, float* __restrict__ db, int batch, int channels) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= channels) return;
-  float t = 0.f;
-  for (int b = 0; b < batch; ++b) t += plane_sums[(size_t)b * channels + c];
-  db[c] = t;
+  float t0 = 0.f, t1 = 0.f, t2 = 0.f, t3 = 0.f;  // four interleaved chains: the loads of a group of four overlap
+  int b = 0;
+  for (; b + 3 < batch; b += 4) {
+    t0 += plane_sums[(size_t)b * channels + c];
+    t1 += plane_sums[(size_t)(b + 1) * channels + c];
+    t2 += plane_sums[(size_t)(b + 2) * channels + c];
+    t3 += plane_sums[(size_t)(b + 3) * channels + c];
+  }
+  for (; b < batch; ++b) t0 += plane_sums[(size_t)b * channels + c];
+  db[c] = (t0 + t1) + (t2 + t3);
 }
 
 // ------------------------------------------------------------------------------------------ weight packing
@@ -1305,9 +1331,10 @@ int finish_problem(cct_ctx* ctx, UmmaPlan* p, GatherProblem& gp, int vgroups, in
   else if (2 * gp.acc_cols + 2 * 64 <= 512 && gp.k_pad / kBlockK <= 16) { gp.acc_bufs = 2; gp.a_stages = 2; }  // short K: the epilogue matters more
   else { gp.acc_bufs = 1; gp.a_stages = std::min(4, (512 - gp.acc_cols) / 64); }
   // Weight slots (hi and lo tile each) in shared memory: up to four, independent of the number of A slots.
+  const int ptab = gp.taps_smem == 0 ? 16 : 0;  // weight-gradient mode: per-warp table slices (sized for 16 warps)
   auto slots_that_fit = [&](size_t limit) {
     int b = 4;
-    while (b > 1 && gather_smem(gp.n_pad, taps_smem, b, n_bias).total + 1024 > limit) --b;
+    while (b > 1 && gather_smem(gp.n_pad, taps_smem, b, n_bias, ptab).total + 1024 > limit) --b;
     return b;
   };
   gp.b_stages = slots_that_fit(kSmemLimit);
@@ -1317,7 +1344,7 @@ int finish_problem(cct_ctx* ctx, UmmaPlan* p, GatherProblem& gp, int vgroups, in
   if (gp.acc_cols <= 128 && b_two >= 3 && two_ctas_allowed()) {
     gp.sets = 2; gp.tmem_cols = 256; gp.acc_bufs = 1; gp.a_stages = 2; gp.b_stages = b_two;
   }
-  gp.smem = gather_smem(gp.n_pad, taps_smem, gp.b_stages, n_bias).total + 1024;
+  gp.smem = gather_smem(gp.n_pad, taps_smem, gp.b_stages, n_bias, gp.taps_smem == 0 ? 4 * gp.sets : 0).total + 1024;
   gp.w_half = (size_t)vgroups * gp.n_pad * map_k;
   int rc = dev_alloc(ctx, p, &gp.w, 2 * gp.w_half);
   if (rc != CCT_OK) return rc;
@@ -1442,7 +1469,10 @@ int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out) {
       rc = dev_alloc(ctx, p, &p->w_partial, (size_t)p->w_splits * G.g * f.tiles * p->w_mtiles * kTileM * f.n_pad);
   }
   // ---- weight gradient through the gather kernel (the default): tiles = splits x channel tiles x M-tiles
-  if (rc == CCT_OK && wgrad_gather_allowed()) {
+  // It needs one extra pass over dY (split into hi / lo, 12 bytes moved per element), which pays when every dY
+  // element takes part in many multiply-adds: measured faster from CaffeNet conv2 (1200 lowered rows) upwards,
+  // slower for AlexNet conv1 (363 rows), so short lowered matrices keep the shared-memory kernel above.
+  if (rc == CCT_OK && wgrad_gather_allowed() && p->fwd.k_real >= 512) {
     const GatherProblem& f = p->fwd;
     GatherProblem& w = p->wgp;
     const int n_pix = G.B * G.m * G.m;
