@@ -2,25 +2,23 @@
 //
 // All three contractions of the convolution bridge run on tcgen05.mma (kind::tf32, M = 128, fp32 accumulators in
 // tensor memory).  The lowered matrix of the reference (type-1 lowering, one row of k*k*D values per output pixel)
-// is never written to global memory: producer threads gather each 128 x 32 tile of it straight from the NCHW input
-// into shared memory, in the K-major 128-byte-swizzled layout the MMA unit reads, splitting every fp32 value into
-// hi = tf32(x) and lo = x - hi on the way.  Three MMAs per k-step (hi*hi + hi*lo + lo*hi) recover fp32-level
-// accuracy ("3xTF32"); flops are counted once.
+// is never written to global memory: producer threads gather each 128 x 32 tile of it straight from the NCHW
+// tensors, splitting every fp32 value into hi = its tf32 part and lo = x - hi on the way.  Three MMAs per k-step
+// (hi*hi + hi*lo + lo*hi) recover fp32-level accuracy ("3xTF32"); flops are counted once.
 //
 //   forward        Y[pix][o]   = sum_k  Lowered(X)[pix][k] * W[o][k]            (+ bias, optional ReLU)
-//   data gradient  dX[pix][d]  = sum_kk Gathered(dY)[pix][kk] * Wd[d][kk]       kk = (filter, tap)
-//                  — the inverse lowering (col2im) written as a gather: every input pixel sums the taps that
-//                  touch it inside the accumulator, so there is no scatter, no atomics, and the result is
-//                  deterministic.  For stride s > 1 the input pixels are processed in s*s phases; a phase only
-//                  sees the taps congruent to it, so no multiplication by structural zeros is issued.
+//   data gradient  dX[q][(d,py,px)] = sum_kk Gathered(dY)[q][kk] * Wd[(d,py,px)][kk]   kk = (filter, jy, jx)
+//                  - the inverse lowering (col2im) written as a gather over s x s blocks of input pixels q: every
+//                  block sums the taps that touch it inside the accumulator and the epilogue scatters the columns
+//                  (depth to space), so there is no atomics and the result is deterministic.
 //   weight gradient dW[kk][o]  = sum_pix Lowered(X)[pix][kk] * dY[pix][o]        split over pixel ranges across
-//                  CTAs, partial sums to scratch, fixed-order reduction; one extra all-ones row of the lowered
-//                  operand yields the bias gradient from the same MMAs.
+//                  CTAs, partial sums to scratch, fixed-order reduction.
 //
-// Pipeline inside a CTA (256 threads): a ring of S shared-memory stages; all threads fill stage s, fence to the
-// async proxy, barrier; one thread issues the 12 MMAs of the stage and a tcgen05.commit onto the stage's mbarrier;
-// the fill of the next stage overlaps the MMAs.  Every mbarrier wait is bounded: when it runs out the thread sets
-// the context's status word, stops waiting on anything else, and the kernel still frees its tensor memory.
+// gather_conv_kernel serves the forward pass, the data gradient and (lanes = rows of the lowered matrix, dY as the
+// pre-split TMA operand) the weight gradient of larger layers: gathered operand in tensor memory, the other operand
+// streamed by TMA into swizzled shared memory, warp-specialised roles.  wgrad_kernel is the weight gradient of small
+// layers with both operands staged in shared memory.  Every mbarrier wait is bounded: when it runs out the thread
+// sets the context's status word, stops waiting on anything else, and the kernel still frees its tensor memory.
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
@@ -372,6 +370,7 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
     gather_conv_kernel(const __grid_constant__ GatherParams P, const __grid_constant__ CUtensorMap w_map) {
   constexpr int kProducerWarps = 4 * SETS, kMmaWarp = kProducerWarps, kTmaWarp = kMmaWarp + 1, kEpiWarp0 = kTmaWarp + 1;
   constexpr int kGatherThreads = gather_threads(SETS);
+  (void)kEpiWarp0;  // named only by the cycle accounting of debug builds
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -1063,23 +1062,28 @@ WgradKernel wgrad_pick(int subs, int n_pad) {
   return subs == 2 ? wgrad_pick_nb<2>(n_pad / 16) : wgrad_pick_nb<1>(n_pad / 16);
 }
 
-// dW[o][kk] and db[o] from the split partial sums, added in split order (deterministic).
-__global__ void wgrad_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dW, float* __restrict__ db,
-                                    int splits, int vgroups, int tiles_per_group, int rows_pad, int n_real, int n_pad,
-                                    int k_real, int og) {
-  const size_t total = (size_t)vgroups * (k_real + 1) * n_real;
-  for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
-    const int j = (int)(t % n_real);
-    const int kk = (int)((t / n_real) % (k_real + 1));
-    const int vg = (int)(t / ((size_t)n_real * (k_real + 1)));
+// dW[o][kk] and db[o] from the split partial sums, added in split order (deterministic).  One block per row
+// (channel tile, kk) of the partial sums, threads over the row's channels: no division per element, coalesced reads.
+__global__ void __launch_bounds__(128) wgrad_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dW,
+                                                           float* __restrict__ db, int splits, int vgroups,
+                                                           int tiles_per_group, int rows_pad, int n_real, int n_pad,
+                                                           int k_real, int og) {
+  const int rows = vgroups * (k_real + 1);
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    const int vg = r / (k_real + 1), kk = r - vg * (k_real + 1);
     if (kk == k_real && !db) continue;  // no bias row in the partial sums
-    float acc = 0.f;
-    for (int s = 0; s < splits; ++s) acc += partial[(((size_t)s * vgroups + vg) * rows_pad + kk) * n_pad + j];
-    const int ch = (vg / tiles_per_group) * og + (vg % tiles_per_group) * n_real + j;
-    if (kk < k_real)
-      dW[(size_t)ch * k_real + kk] = acc;
-    else if (db)
-      db[ch] = acc;
+    const int ch0 = (vg / tiles_per_group) * og + (vg % tiles_per_group) * n_real;
+    const size_t split_stride = (size_t)vgroups * rows_pad * n_pad;
+    for (int j = threadIdx.x; j < n_real; j += blockDim.x) {
+      const float* src = partial + ((size_t)vg * rows_pad + kk) * n_pad + j;
+      float acc = 0.f;
+#pragma unroll 8
+      for (int s = 0; s < splits; ++s) acc += src[(size_t)s * split_stride];
+      if (kk < k_real)
+        dW[(size_t)(ch0 + j) * k_real + kk] = acc;
+      else
+        db[ch0 + j] = acc;
+    }
   }
 }
 
@@ -1297,6 +1301,8 @@ int set_smem(cct_ctx* ctx, K kernel, size_t bytes) {
   CCT_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
   return CCT_OK;
 }
+
+int reduce_grid(cct_ctx* ctx, int rows) { return std::max(1, std::min(rows, ctx->sm_count * 16)); }
 
 int pack_grid(cct_ctx* ctx, size_t total) {
   size_t b = (total + 255) / 256;
@@ -1631,10 +1637,8 @@ int umma_conv_backward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W
     t->end(1, ctx->stream);
     CCT_CHECK_LAUNCH(ctx);
     t->begin(2, ctx->stream);
-    const size_t total = (size_t)vgroups * (f.k_real + 1) * f.n;
-    wgrad_reduce_kernel<<<pack_grid(ctx, total), 256, 0, ctx->stream>>>(p->w_partial, dW, nullptr, p->wg_splits, vgroups,
-                                                                      f.tiles, p->wg_mtiles * kTileM, f.n, f.n_pad,
-                                                                      f.k_real, G.og);
+    wgrad_reduce_kernel<<<reduce_grid(ctx, vgroups * (f.k_real + 1)), 128, 0, ctx->stream>>>(
+        p->w_partial, dW, nullptr, p->wg_splits, vgroups, f.tiles, p->wg_mtiles * kTileM, f.n, f.n_pad, f.k_real, G.og);
     if (G.bias) bias_grad_kernel<<<(G.o + 127) / 128, 128, 0, ctx->stream>>>(p->wg_plane_sums, db, G.B, G.o);
     t->end(2, ctx->stream);
     CCT_CHECK_LAUNCH(ctx);
@@ -1661,10 +1665,9 @@ int umma_conv_backward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W
     t->end(1, ctx->stream);
     CCT_CHECK_LAUNCH(ctx);
     t->begin(2, ctx->stream);
-    const size_t total = (size_t)vgroups * (f.k_real + 1) * f.n;
-    wgrad_reduce_kernel<<<pack_grid(ctx, total), 256, 0, ctx->stream>>>(p->w_partial, dW, G.bias ? db : nullptr,
-                                                                      p->w_splits, vgroups, f.tiles,
-                                                                      p->w_mtiles * kTileM, f.n, f.n_pad, f.k_real, G.og);
+    wgrad_reduce_kernel<<<reduce_grid(ctx, vgroups * (f.k_real + 1)), 128, 0, ctx->stream>>>(
+        p->w_partial, dW, G.bias ? db : nullptr, p->w_splits, vgroups, f.tiles, p->w_mtiles * kTileM, f.n, f.n_pad,
+        f.k_real, G.og);
     t->end(2, ctx->stream);
     CCT_CHECK_LAUNCH(ctx);
   }
@@ -1813,10 +1816,8 @@ extern "C" int cct_conv_weight_grad_noalloc(cct_ctx* ctx, const cct_conv_desc* d
   P.dbg = 0;
   kernel<<<dim3(mgroups, splits, vgroups), kWgThreads, smem, ctx->stream>>>(P);
   CCT_CHECK_LAUNCH(ctx);
-  const size_t total = (size_t)vgroups * (k_real + 1) * n_real;
-  const int rgrid = (int)std::min<size_t>(std::max<size_t>((total + 255) / 256, 1), (size_t)ctx->sm_count * 8);
-  wgrad_reduce_kernel<<<rgrid, 256, 0, ctx->stream>>>(partial, dW, G.bias ? db : nullptr, splits, vgroups, tiles,
-                                                     m_tiles * kTileM, n_real, n_pad, k_real, G.og);
+  wgrad_reduce_kernel<<<reduce_grid(ctx, vgroups * (k_real + 1)), 128, 0, ctx->stream>>>(
+      partial, dW, G.bias ? db : nullptr, splits, vgroups, tiles, m_tiles * kTileM, n_real, n_pad, k_real, G.og);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }
