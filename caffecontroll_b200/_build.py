@@ -32,9 +32,11 @@ def build(force=False, verbose_ptxas=False):
     if not force and up_to_date():
         return LIB
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose_ptxas else []) + ["-o", LIB] + sources()
+    tmp = LIB + ".tmp"  # written beside the target, then renamed: a reader never sees a half-written library
+    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose_ptxas else []) + ["-o", tmp] + sources()
     print(" ".join(cmd), flush=True)
     subprocess.check_call(cmd)
+    os.replace(tmp, LIB)
     return LIB
 
 

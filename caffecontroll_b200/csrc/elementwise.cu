@@ -4,6 +4,7 @@
 #include <float.h>
 
 #include <algorithm>
+#include <initializer_list>
 
 #include "cct_internal.h"
 
@@ -31,32 +32,70 @@ __global__ void fill_kernel(float* __restrict__ p, size_t count, float v) {
     p[i] = v;
 }
 
+// The streaming kernels move four floats per thread and iteration (16-byte accesses) when every buffer is 16-byte
+// aligned, so that enough bytes are in flight per SM to approach the HBM rate; the last count % 4 elements, and all
+// of them for unaligned buffers, go through the scalar loop that follows.  Per-element arithmetic is identical.
+__device__ __forceinline__ float sgd_one(float& gi, float wi, float& hi_io, float lr, float momentum, float lambda) {
+  if (lambda != 0.f) gi = __fadd_rn(gi, __fmul_rn(lambda, wi));  // saxpy: separate multiply and add, as BLAS does without FMA contraction
+  hi_io = __fadd_rn(__fmul_rn(lr, gi), __fmul_rn(momentum, hi_io));
+  return __fadd_rn(wi, -hi_io);
+}
+
 // 12 B read + 12 B written per parameter (g is written back only when decay is on: the reference's updater adds
 // the decay term into the gradient buffer itself).
-__global__ void sgd_kernel(size_t count, float* __restrict__ w, float* __restrict__ g, float* __restrict__ h,
+__global__ void sgd_kernel(size_t count, size_t vec, float* __restrict__ w, float* __restrict__ g, float* __restrict__ h,
                            float lr, float momentum, float lambda) {
-  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x) {
-    float gi = g[i];
-    const float wi = w[i];
-    if (lambda != 0.f) {
-      gi = __fadd_rn(gi, __fmul_rn(lambda, wi));  // saxpy: separate multiply and add, as BLAS does without FMA contraction
-      g[i] = gi;
-    }
-    const float hi = __fadd_rn(__fmul_rn(lr, gi), __fmul_rn(momentum, h[i]));
+  const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, nthreads = (size_t)gridDim.x * blockDim.x;
+  float4* w4 = reinterpret_cast<float4*>(w);
+  float4* g4 = reinterpret_cast<float4*>(g);
+  float4* h4 = reinterpret_cast<float4*>(h);
+  for (size_t i = tid; i < vec; i += nthreads) {
+    float4 gi = g4[i], hi = h4[i];
+    const float4 wi = w4[i];
+    float4 wo;
+    wo.x = sgd_one(gi.x, wi.x, hi.x, lr, momentum, lambda);
+    wo.y = sgd_one(gi.y, wi.y, hi.y, lr, momentum, lambda);
+    wo.z = sgd_one(gi.z, wi.z, hi.z, lr, momentum, lambda);
+    wo.w = sgd_one(gi.w, wi.w, hi.w, lr, momentum, lambda);
+    if (lambda != 0.f) g4[i] = gi;
+    h4[i] = hi;
+    w4[i] = wo;
+  }
+  for (size_t i = 4 * vec + tid; i < count; i += nthreads) {
+    float gi = g[i], hi = h[i];
+    const float wo = sgd_one(gi, w[i], hi, lr, momentum, lambda);
+    if (lambda != 0.f) g[i] = gi;
     h[i] = hi;
-    w[i] = __fadd_rn(wi, -hi);
+    w[i] = wo;
   }
 }
 
-__global__ void relu_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, size_t count) {
-  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x)
-    y[i] = fmaxf(x[i], 0.f);
+__global__ void relu_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, size_t count, size_t vec) {
+  const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, nthreads = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = tid; i < vec; i += nthreads) {
+    const float4 v = reinterpret_cast<const float4*>(x)[i];
+    reinterpret_cast<float4*>(y)[i] = make_float4(fmaxf(v.x, 0.f), fmaxf(v.y, 0.f), fmaxf(v.z, 0.f), fmaxf(v.w, 0.f));
+  }
+  for (size_t i = 4 * vec + tid; i < count; i += nthreads) y[i] = fmaxf(x[i], 0.f);
 }
 
 // dy and dx may be the same buffer (in-place use by the fused backward of the SIMT path).
-__global__ void relu_bwd_kernel(const float* __restrict__ x, const float* dy, float* dx, size_t count) {
-  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x)
-    dx[i] = dy[i] * (x[i] > 0.f ? 1.f : 0.f);
+__global__ void relu_bwd_kernel(const float* __restrict__ x, const float* dy, float* dx, size_t count, size_t vec) {
+  const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, nthreads = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = tid; i < vec; i += nthreads) {
+    const float4 v = reinterpret_cast<const float4*>(x)[i];
+    const float4 d = reinterpret_cast<const float4*>(dy)[i];
+    reinterpret_cast<float4*>(dx)[i] = make_float4(d.x * (v.x > 0.f ? 1.f : 0.f), d.y * (v.y > 0.f ? 1.f : 0.f),
+                                                   d.z * (v.z > 0.f ? 1.f : 0.f), d.w * (v.w > 0.f ? 1.f : 0.f));
+  }
+  for (size_t i = 4 * vec + tid; i < count; i += nthreads) dx[i] = dy[i] * (x[i] > 0.f ? 1.f : 0.f);
+}
+
+// Number of float4 groups the streaming kernels may take: all of count / 4 when every pointer is 16-byte aligned.
+inline size_t vec_groups(size_t count, std::initializer_list<const void*> ptrs) {
+  for (const void* p : ptrs)
+    if (reinterpret_cast<uintptr_t>(p) & 15u) return 0;
+  return count / 4;
 }
 
 // One block per plane at a time (planes are small: 13x13 ... 55x55), so all index arithmetic is 32-bit and the
@@ -226,7 +265,8 @@ int cct_sgd_step(cct_ctx* ctx, size_t count, float* w, float* g, float* h, float
   if (!ctx || !w || !g || !h) return CCT_ERR_INVALID;
   if (!count) return CCT_OK;
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
-  sgd_kernel<<<grid_for(ctx, count, 256), 256, 0, ctx->stream>>>(count, w, g, h, lr, momentum, lambda);
+  sgd_kernel<<<grid_for(ctx, (count + 3) / 4, 256), 256, 0, ctx->stream>>>(count, vec_groups(count, {w, g, h}), w, g, h, lr,
+                                                                        momentum, lambda);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }
@@ -234,7 +274,7 @@ int cct_sgd_step(cct_ctx* ctx, size_t count, float* w, float* g, float* h, float
 int cct_relu_forward(cct_ctx* ctx, const float* X, float* Y, size_t count) {
   if (!ctx || !X || !Y) return CCT_ERR_INVALID;
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
-  relu_fwd_kernel<<<grid_for(ctx, count, 256), 256, 0, ctx->stream>>>(X, Y, count);
+  relu_fwd_kernel<<<grid_for(ctx, (count + 3) / 4, 256), 256, 0, ctx->stream>>>(X, Y, count, vec_groups(count, {X, Y}));
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }
@@ -242,7 +282,8 @@ int cct_relu_forward(cct_ctx* ctx, const float* X, float* Y, size_t count) {
 int cct_relu_backward(cct_ctx* ctx, const float* X, const float* dY, float* dX, size_t count) {
   if (!ctx || !X || !dY || !dX) return CCT_ERR_INVALID;
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
-  relu_bwd_kernel<<<grid_for(ctx, count, 256), 256, 0, ctx->stream>>>(X, dY, dX, count);
+  relu_bwd_kernel<<<grid_for(ctx, (count + 3) / 4, 256), 256, 0, ctx->stream>>>(X, dY, dX, count,
+                                                                                vec_groups(count, {X, dY, dX}));
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }
