@@ -228,6 +228,138 @@ def run_reference_arm(args, w, rank, world):
     print(json.dumps(line), flush=True)
 
 
+# The five convolution layers of CaffeNet at batch 256 per GPU (BASELINE config 4 without the LRN / FC / softmax layers,
+# which are outside this path): (name, D, n, o, k, s, p, g, pool behind the layer's ReLU or None, needs dX).
+CAFFENET_CONVS = [
+    ("conv1", 3, 227, 96, 11, 4, 0, 1, (3, 2), False),
+    ("conv2", 96, 27, 256, 5, 1, 2, 2, (3, 2), True),
+    ("conv3", 256, 13, 384, 3, 1, 1, 1, None, True),
+    ("conv4", 384, 13, 384, 3, 1, 1, 2, None, True),
+    ("conv5", 384, 13, 256, 3, 1, 1, 2, (3, 2), True),
+]
+
+
+def run_conv_stack(args, rank, world, local_rank):
+    """All five CaffeNet convolution layers as one step: forward (+ReLU), fused backward (pooled gradient and ReLU
+    masks folded in, conv1 without dX), gradient all-reduce (N>1) and SGD step per layer, on synthetic tensors of the
+    layers' own shapes (the layers between them - LRN, pooling forward, FC - are not part of this path)."""
+    import torch
+    import torch.distributed as dist
+    from caffecontroll_b200 import capi
+    from caffecontroll_b200.bridge import Context, ConvolutionBridge, Layer, LogicalCube
+    from caffecontroll_b200.parallel import DeviceOps, ParallelizedBridge, SolverParameter
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    stream = torch.cuda.current_stream()
+    ctx = Context(local_rank, stream=stream.cuda_stream)
+    lib, vp = ctx.lib, C.c_void_p
+    B = args.batch or 256
+    rng = np.random.default_rng(4000 + rank)
+    layers, flops = [], 0.0
+    for name, D, n, o, k, s_, p_, g, pool, needs_dx in CAFFENET_CONVS:
+        m = (n + 2 * p_ - k) // s_ + 1
+        X = rng.standard_normal((B, D, n, n), dtype=np.float32)
+        if name != "conv1":
+            X = np.maximum(X, 0)  # every later layer sees a ReLU output
+        xin = Layer(LogicalCube.from_numpy(ctx, X), LogicalCube(ctx, n, n, D, B))
+        out = Layer(LogicalCube(ctx, m, m, o, B), LogicalCube.from_numpy(ctx, rng.standard_normal((B, o, m, m), dtype=np.float32)))
+        conv = ConvolutionBridge(xin, out, k, s_, p_, g, True, algo=args.algo)
+        conv.needs_to_calc_backward_grad = needs_dx
+        conv.fuse_relu = True
+        conv.fuse_relu_backward = needs_dx
+        conv.p_model_cube.upload((0.01 * rng.standard_normal((o, D // g, k, k))).astype(np.float32))
+        conv.p_bias_cube.upload(np.zeros(o, np.float32) if name in ("conv1", "conv3") else np.ones(o, np.float32))
+        pb = ParallelizedBridge(conv, SolverParameter(SOLVER["base_lr"], "step", 0.1, 100000, momentum=SOLVER["momentum"],
+                                                      weight_decay=SOLVER["weight_decay"]), DeviceOps(ctx))
+        if pool:
+            pk, ps = pool
+            mp = (m - pk) // ps + 1
+            pooled, idx = LogicalCube(ctx, mp, mp, o, B), LogicalCube(ctx, mp, mp, o, B, np.int32)
+            dP = LogicalCube.from_numpy(ctx, rng.standard_normal((B, o, mp, mp), dtype=np.float32))
+            conv.forward()
+            capi.check(lib.cct_maxpool_forward(ctx.h, vp(out.p_data_cube.ptr), vp(pooled.ptr), vp(idx.ptr), B * o, m, pk, ps),
+                       "cct_maxpool_forward", ctx.h)
+            conv.fuse_pool_relu_backward(dP, idx, pk, ps)
+        F = 2.0 * o * (k * k * D // g) * m * m * B
+        flops += (3 if needs_dx else 2) * F
+        layers.append((name, pb, conv, F, needs_dx))
+
+    def step():
+        for _, pb, _, _, _ in layers:
+            pb.forward()
+        for _, pb, _, _, _ in reversed(layers):
+            pb.backward()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    per_layer = {}
+    for name, pb, conv, F, needs_dx in layers:
+        lib.cct_conv_plan_enable_timing(conv.plan, 1)
+    acc = {name: np.zeros(5) for name, *_ in layers}
+    reps = min(args.steps, 5)
+    for _ in range(reps):
+        step()
+        for name, pb, conv, F, needs_dx in layers:
+            t5 = (C.c_float * 5)()
+            capi.check(lib.cct_conv_plan_last_timings(conv.plan, t5), "timings", ctx.h)
+            acc[name] += np.array(list(t5))
+    clocks = sampler.stop() if rank == 0 else None
+    for name, pb, conv, F, needs_dx in layers:
+        k_ms = acc[name] / reps
+        per_layer[name] = {"forward_ms": k_ms[0] + k_ms[4], "wgrad_ms": k_ms[1] + k_ms[2], "dgrad_ms": k_ms[3] if needs_dx else None,
+                           "forward_tflops": F / (k_ms[0] * 1e-3) / 1e12, "wgrad_tflops": F / ((k_ms[1] + k_ms[2]) * 1e-3) / 1e12,
+                           "dgrad_tflops": F / (k_ms[3] * 1e-3) / 1e12 if needs_dx and k_ms[3] > 0 else None}
+    if rank == 0:
+        peaks = load_peaks()
+        peak = peaks["bf16_tflops"] / 6.0
+        tf = world * flops / (ms_step * 1e-3) / 1e12
+        line = {
+            "metric": METRIC, "value": world * B / (ms_step * 1e-3), "unit": "images/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "caffenet_convs (conv1-conv5, batch %d per GPU)" % B, "batch_per_gpu": B,
+                       "global_batch": B * world, "step": "per layer: forward (+ReLU), fused backward (pooled gradient and ReLU masks folded in; conv1 "
+                               "without dX), gradient all-reduce (N>1), SGD momentum step",
+                       "l2": "inputs larger than L2 (2.4 GB of activations and gradients per step)", "parallelism": "dp%d" % world},
+            "tflops": tf,
+            "roofline": {"bound": "tensor", "kernel": "all contraction kernels of the five layers", "achieved": tf / world,
+                         "peak": peak, "unit": "TFLOP/s", "frac": tf / world / peak, "traffic": None,
+                         "peak_source": "%s: bf16 burst %.1f TFLOP/s / 2 / 3 - of measured; sustained figure %.1f" %
+                                        (peaks["source"], peaks["bf16_tflops"], (peaks.get("bf16_tflops_sustained") or 0) / 6.0),
+                         "flops_per_step": flops, "layers": per_layer},
+            "cpu_baseline": None, "e2e": None, "clocks": clocks, "gpu_launches": None,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    ctx.close()
+
+
 def config_of(args, w, world):
     return {"workload": args.workload, "batch_per_gpu": w["B"], "global_batch": w["B"] * world,
             "in": "%dx%dx%d" % (w["D"], w["n"], w["n"]), "filters": "%d x %dx%d stride %d pad %d groups %d" %
@@ -246,13 +378,20 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="alexnet_conv1", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="alexnet_conv1", choices=sorted(WORKLOADS) + ["caffenet_convs"])
     ap.add_argument("--algo", type=int, default=0, help="0 auto, 1 SIMT fp32, 2 tcgen05 3xTF32")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (profiling on a small case)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.workload == "caffenet_convs":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the reference arm is timed per layer workload, not for the conv stack"}))
+            return
+        run_conv_stack(args, int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")),
+                       int(os.environ.get("LOCAL_RANK", "0")))
+        return
     w = dict(WORKLOADS[args.workload])
     if args.batch:
         w["B"] = args.batch
