@@ -302,7 +302,7 @@ int cct_conv_backward(cct_conv_plan* plan, const float* X, const float* W, const
   if (plan->G.bias && !db) return CCT_ERR_INVALID;
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
   if (plan->algo == CCT_ALGO_UMMA_3XTF32)
-    return umma_conv_backward(ctx, plan->umma, X, W, dY, dX, dW, db, 0, &plan->timer);
+    return umma_conv_backward(ctx, plan->umma, X, W, dY, dX, dW, db, &plan->timer);
   return simt_conv_backward(ctx, plan->G, X, W, dY, dX, dW, db, &plan->timer);
 }
 
@@ -323,11 +323,12 @@ int cct_conv_backward_fused(cct_conv_plan* plan, const float* X, const float* W,
     dY = plan->mask_dY;
   }
   if (!dY) return CCT_ERR_INVALID;
-  const int mask_dx = f->relu_mask_dx && dX;
-  if (plan->algo == CCT_ALGO_UMMA_3XTF32)
-    return umma_conv_backward(ctx, plan->umma, X, W, dY, dX, dW, db, mask_dx, &plan->timer);
-  int rc = simt_conv_backward(ctx, G, X, W, dY, dX, dW, db, &plan->timer);
-  if (rc == CCT_OK && mask_dx) rc = cct_relu_backward(ctx, X, dX, dX, (size_t)G.B * G.D * G.n * G.n);
+  // The ReLU bridge in front of the layer: dX *= [X > 0] as one HBM-bound pass behind the data-gradient kernel.
+  // (Folded into that kernel's epilogue it cost more than the pass: one extra load per accumulator column in the four
+  // epilogue warps made the epilogue the bottleneck of wide data gradients.)
+  int rc = plan->algo == CCT_ALGO_UMMA_3XTF32 ? umma_conv_backward(ctx, plan->umma, X, W, dY, dX, dW, db, &plan->timer)
+                                              : simt_conv_backward(ctx, G, X, W, dY, dX, dW, db, &plan->timer);
+  if (rc == CCT_OK && f->relu_mask_dx && dX) rc = cct_relu_backward(ctx, X, dX, dX, (size_t)G.B * G.D * G.n * G.n);
   return rc;
 }
 

@@ -68,4 +68,4 @@ bool umma_supported(const ConvGeom& G);
 int umma_conv_forward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W, const float* bias, float* Y,
                       int relu, PhaseTimer* t);
 int umma_conv_backward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W, const float* dY, float* dX,
-                       float* dW, float* db, int relu_mask_dx, PhaseTimer* t);
+                       float* dW, float* db, PhaseTimer* t);

@@ -22,7 +22,6 @@
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
-#include <type_traits>
 #include <vector>
 
 #include <cuda.h>
@@ -263,7 +262,6 @@ struct GatherParams {
   const MaskTap* taps; // [k_pad]
   const ColEnt* cols;  // [n_pad]
   const float* bias;  // indexed by output channel, or null
-  const float* sign_src;  // same shape as `out`, or null: outputs are zeroed where sign_src <= 0 (ReLU backward)
   int n_pix, q_h, q_w;                 // pixels = batch * q_h * q_w
   int iy_mul, iy_add, ix_mul, ix_add;  // tap origin in the gathered tensor: iy0 = qy*iy_mul + iy_add
   int in_lim;                          // gathered tensor is in_lim x in_lim per channel
@@ -675,7 +673,6 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
       float* op = P.out + (long long)b * P.out_batch_stride + (long long)ch0 * P.out_plane +
                   (long long)oy0 * P.out_pitch + ox0;
       const float* bias = s_bias + (P.n_bias ? ch0 : 0);  // zero padded: readable for every column of the tile
-      const float* sp = P.sign_src + (op - P.out);
       PROF_LAP(0);
       mbar_wait(acc_full + 8u * buf, (uint32_t)ause & 1u, failed, P.status, 0x200);
       tc_fence_after();
@@ -696,9 +693,8 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
         PROF_LAP(3);
         // Straight-line code: table and bias reads first, then predicated st.global (a generic store could alias
         // shared memory and would pin every following table read behind it; a branch per column costs more than
-        // the store it guards).  MASKED: the output is zeroed where the tensor `sign_src` is not positive.
-        auto store_chunk = [&](auto masked_tag) {
-          constexpr bool MASKED = decltype(masked_tag)::value;
+        // the store it guards).
+        if (!DBG(P, 128)) {
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             ColEnt ce[8];
@@ -709,28 +705,17 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
               ce[j] = s_cols[col];
               bv[j] = bias[col];
             }
-            uint32_t ok[8];
-            float sg[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               const int col = c * 16 + h * 8 + j;
               const uint32_t in_y = (unsigned)(oy0 + ce[j].cy) < (unsigned)P.out_lim ? 1u : 0u;
               const uint32_t in_x = (unsigned)(ox0 + ce[j].cx) < (unsigned)P.out_lim ? 1u : 0u;
-              ok[j] = live & (col < P.n ? 1u : 0u) & (unchecked | (in_y & in_x)) & (DBG(P, 32) ? 0u : 1u);
-              if (MASKED) sg[j] = ldg_if(sp + ce[j].off, ok[j]);
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
+              const uint32_t ok = live & (col < P.n ? 1u : 0u) & (unchecked | (in_y & in_x)) & (DBG(P, 32) ? 0u : 1u);
               float y = v[h * 8 + j] + bv[j];
               y = P.relu ? fmaxf(y, 0.f) : y;
-              if (MASKED) y = sg[j] > 0.f ? y : 0.f;
-              stg_if(op + ce[j].off, y, ok[j]);
+              stg_if(op + ce[j].off, y, ok);
             }
           }
-        };
-        if (!DBG(P, 128)) {
-          if (P.sign_src) store_chunk(std::true_type{});
-          else store_chunk(std::false_type{});
         }
         PROF_LAP(4);
       }
@@ -1610,7 +1595,7 @@ int umma_conv_forward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W,
 }
 
 int umma_conv_backward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W, const float* dY, float* dX,
-                       float* dW, float* db, int relu_mask_dx, PhaseTimer* t) {
+                       float* dW, float* db, PhaseTimer* t) {
   if (*ctx->status_host != 0) return CCT_ERR_TIMEOUT;
   const ConvGeom& G = p->G;
   // ---- weight + bias gradient
@@ -1682,7 +1667,6 @@ int umma_conv_backward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W
     CCT_CHECK_LAUNCH(ctx);
     GatherParams P{};
     P.in = dY; P.out = dX; P.bias = nullptr;
-    P.sign_src = relu_mask_dx ? X : nullptr;  // X has dX's shape: the ReLU in front of this layer, folded in
     P.n_pix = G.B * p->dgr_q * p->dgr_q; P.q_h = p->dgr_q; P.q_w = p->dgr_q;
     P.iy_mul = 1; P.iy_add = p->dgr_q0; P.ix_mul = 1; P.ix_add = p->dgr_q0;
     P.in_lim = G.m;

@@ -112,7 +112,7 @@ int cct_conv_backward(cct_conv_plan* plan, const float* X, const float* W, const
  *     int32 indices cct_maxpool_forward wrote, dP = gradient of the pooled tensor.  One HBM-bound pass into
  *     plan-owned scratch feeds both gradient kernels.
  *   - Input side.  relu_mask_dx != 0 writes dX * [X > 0] instead of dX: the ReLU bridge in front of this layer (whose
- *     output X is) folded into the data-gradient epilogue.
+ *     output X is), applied by one streaming pass right behind the data-gradient kernel.
  * f == NULL behaves like cct_conv_backward. */
 typedef struct cct_bwd_fusion {
   const float* A;
