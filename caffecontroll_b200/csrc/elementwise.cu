@@ -140,8 +140,9 @@ __device__ __forceinline__ uint32_t fast_div(uint32_t x, uint32_t d, uint32_t in
 // indices and gradients (into its slice of shared memory) and the first sixteen rows-worth of A (into registers) -
 // so a plane costs about two memory round trips; the window tests then run out of shared memory.
 constexpr int kPoolWarps = 8;  // warps (= planes in flight) per block
+constexpr int kPoolRows = 8;   // rows per step: their A values are loaded together
 template <int T, bool RELU>
-__global__ void __launch_bounds__(kPoolWarps * 32) maxpool_bwd_kernel(const float* __restrict__ A,
+__global__ void __launch_bounds__(kPoolWarps * 32, 5) maxpool_bwd_kernel(const float* __restrict__ A,
                                                                       const int32_t* __restrict__ idx,
                                                                       const float* __restrict__ dP,
                                                                       float* __restrict__ dA, int planes, int n, int m,
@@ -170,7 +171,7 @@ __global__ void __launch_bounds__(kPoolWarps * 32) maxpool_bwd_kernel(const floa
       s_idx[i] = __ldg(ip + i);
       s_dp[i] = __ldg(gp + i);
     }
-    // lane = column (in chunks of 32), sixteen rows per step with their A values loaded together: no division and no
+    // lane = column (in chunks of 32), eight rows per step with their A values loaded together: no division and no
     // global load inside the window tests.
     for (int w0 = 0; w0 < n; w0 += 32) {
       const int w = w0 + lane;
@@ -184,17 +185,17 @@ __global__ void __launch_bounds__(kPoolWarps * 32) maxpool_bwd_kernel(const floa
         pwv[jj] = wok && pw >= (int)(rw & 0xffffu);
         pwc[jj] = max(pw, 0);
       }
-      float av[16];
+      float av[kPoolRows];
       auto fetch = [&](int h0) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) av[j] = (RELU && wok && h0 + j < n) ? __ldg(a + (h0 + j) * n + w) : 1.f;
+        for (int j = 0; j < kPoolRows; ++j) av[j] = (RELU && wok && h0 + j < n) ? __ldg(a + (h0 + j) * n + w) : 1.f;
       };
       fetch(0);
       __syncwarp();  // staged values visible (first column chunk) / harmless afterwards
-      for (int h0 = 0; h0 < n; h0 += 16) {
-        float res[16];
+      for (int h0 = 0; h0 < n; h0 += kPoolRows) {
+        float res[kPoolRows];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
+        for (int j = 0; j < kPoolRows; ++j) {
           const int h = min(h0 + j, n - 1);
           const int here = h * n + w;
           const bool live = av[j] > 0.f;
@@ -205,12 +206,16 @@ __global__ void __launch_bounds__(kPoolWarps * 32) maxpool_bwd_kernel(const floa
 #pragma unroll
             for (int i = 0; i < T; ++i) {
               const int ph = ph1 - (T - 1) + i;
-              const bool phv = live && ph >= ph0;
-              const int base = max(ph, 0) * m;
+              if (ph >= ph0) {  // the same for every lane (h is): a uniform branch that skips the row's dead windows
+                const int base = ph * m;
 #pragma unroll
-              for (int jj = 0; jj < T; ++jj) {
-                const int at = base + pwc[jj];
-                acc += (phv && pwv[jj] && s_idx[at] == here) ? s_dp[at] : 0.f;
+                for (int jj = 0; jj < T; ++jj) {
+                  // both reads are unconditional (the index is always inside the slice), so there is no branch
+                  const int at = base + pwc[jj];
+                  const int32_t where = s_idx[at];
+                  const float g = s_dp[at];
+                  acc += (live && pwv[jj] && where == here) ? g : 0.f;
+                }
               }
             }
           } else if (live && wok) {
@@ -220,9 +225,9 @@ __global__ void __launch_bounds__(kPoolWarps * 32) maxpool_bwd_kernel(const floa
           }
           res[j] = acc;
         }
-        if (h0 + 16 < n) fetch(h0 + 16);  // next rows' A in flight while these results are stored
+        if (h0 + kPoolRows < n) fetch(h0 + kPoolRows);  // next rows' A in flight while these results are stored
 #pragma unroll
-        for (int j = 0; j < 16; ++j)
+        for (int j = 0; j < kPoolRows; ++j)
           if (wok && h0 + j < n) out[(h0 + j) * n + w] = res[j];
       }
     }
