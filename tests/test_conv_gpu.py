@@ -33,6 +33,8 @@ SHAPES = [
     (5, 48, 13, 40, 5, 1, 2, 1),    # K = 1200 like CaffeNet conv2, ragged pixel tile (845 pixels)
     (2, 16, 13, 272, 3, 1, 1, 1),   # 272 filters: two output-channel tiles of 136
     (2, 288, 6, 16, 3, 1, 1, 1),    # 288 input channels: two input-channel tiles in the data gradient
+    (2, 128, 10, 136, 3, 2, 1, 2),  # 576 lowered rows per group, stride 2, pad 1: weight gradient through the gather kernel
+    (2, 64, 8, 160, 3, 1, 1, 1),    # 160 filters in one tile: the one-CTA-per-SM shape, in all three passes
 ]
 
 
