@@ -120,6 +120,33 @@ def test_linearity_and_adjoint_at_larger_size(ctx):
     assert abs(lhs - float(np.sum(W.astype(np.float64) * dW))) <= TOL * abs(lhs) + 1e-3
 
 
+@pytest.mark.parametrize("cfg", [
+    ("AlexNet conv1 (BASELINE config 2)", 256, 3, 227, 96, 11, 4, 0, 1, "normal"),
+    ("CaffeNet conv2 (BASELINE config 3)", 256, 96, 27, 256, 5, 1, 2, 2, "relu"),
+])
+def test_full_size_configs_by_properties(ctx, port, cfg):
+    """The BASELINE layers at their full batch, where the CPU oracle would take minutes: images are independent in
+    Y and dX, so the first and last image are compared with the oracle run on those two images alone; dW and db couple
+    the whole batch and are pinned by the adjoint identity <conv(X), dY> = <X, dX> = <W, dW> (bias off in the
+    identity's forward) and by db = plane sums of dY in float64."""
+    from caffecontroll_b200 import conv_layer
+    name, B, D, n, o, k, s, p, g, dist = cfg
+    X, W, b, dY = make_inputs(2000 + n, B, D, n, o, k, s, p, g, relu_input=(dist == "relu"))
+    Y, dX, dW, db, _ = conv_layer(ctx, X, W, b, dY, k, s, p, g, algo=UMMA)
+    ends = [0, B - 1]
+    Xe, dYe = np.ascontiguousarray(X[ends]), np.ascontiguousarray(dY[ends])
+    Yr = port.conv_forward(Xe, W, b, k, s, p, g)
+    dXr, _, _ = port.conv_backward(Xe, W, dYe, k, s, p, g)
+    assert_close(Y[ends], Yr, name + ": Y of the first and last image")
+    assert_close(dX[ends], dXr, name + ": dX of the first and last image")
+    Y0 = Y - b.reshape(1, o, 1, 1)  # forward without bias, for the identity
+    lhs = float(np.sum(Y0.astype(np.float64) * dY))
+    assert abs(lhs - float(np.sum(X.astype(np.float64) * dX))) <= TOL * abs(lhs) + 1e-2
+    assert abs(lhs - float(np.sum(W.astype(np.float64) * dW.reshape(W.shape)))) <= TOL * abs(lhs) + 1e-2
+    db_ref = dY.astype(np.float64).sum(axis=(0, 2, 3))
+    assert maxnorm_rel(db.reshape(-1), db_ref.astype(np.float32)) <= TOL
+
+
 def test_backward_is_deterministic(ctx):
     from caffecontroll_b200 import conv_layer
     X, W, b, dY = make_inputs(15, 6, 16, 14, 24, 3, 1, 1, 1)
