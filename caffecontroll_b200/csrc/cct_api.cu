@@ -2,6 +2,8 @@
 #include <cstdio>
 #include <new>
 
+#include <algorithm>
+
 #include "cct_internal.h"
 
 struct cct_conv_plan {
@@ -16,6 +18,9 @@ struct cct_conv_plan {
   size_t staging_bytes = 0;
   bool staged_forward = false;  // sX / sW hold what the last cct_conv_forward_host uploaded
   float* mask_dY = nullptr;     // output gradient rebuilt from the pooled gradient (cct_conv_backward_fused), on first use
+  // Host-buffer calls move the batch in slices: slice c is uploaded (ev_in[c]), processed, downloaded (after ev_out[c]).
+  static constexpr int kSlices = 4;
+  cudaEvent_t ev_in[kSlices] = {}, ev_out[kSlices] = {}, ev_start = nullptr, ev_done = nullptr;
   PhaseTimer timer;
 };
 
@@ -52,7 +57,39 @@ int ensure_staging(cct_conv_plan* p) {
     CCT_CUDA(ctx, cudaMalloc((void**)slots[i], counts[i] * sizeof(float)));
     p->staging_bytes += counts[i] * sizeof(float);
   }
+  if (!ctx->copy_in) CCT_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->copy_in, cudaStreamNonBlocking));
+  if (!ctx->copy_out) CCT_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->copy_out, cudaStreamNonBlocking));
+  for (int c = 0; c < cct_conv_plan::kSlices; ++c) {
+    CCT_CUDA(ctx, cudaEventCreateWithFlags(&p->ev_in[c], cudaEventDisableTiming));
+    CCT_CUDA(ctx, cudaEventCreateWithFlags(&p->ev_out[c], cudaEventDisableTiming));
+  }
+  CCT_CUDA(ctx, cudaEventCreateWithFlags(&p->ev_start, cudaEventDisableTiming));
+  CCT_CUDA(ctx, cudaEventCreateWithFlags(&p->ev_done, cudaEventDisableTiming));
   return CCT_OK;
+}
+
+// Images per slice of the pipelined host-buffer calls (0: do not slice - tiny batches and the direct fp32 path).
+int slice_images(const cct_conv_plan* p) {
+  if (p->algo != CCT_ALGO_UMMA_3XTF32 || p->G.B < 2 * cct_conv_plan::kSlices) return 0;
+  return (p->G.B + cct_conv_plan::kSlices - 1) / cct_conv_plan::kSlices;
+}
+
+// Both side streams start behind whatever the context's stream has queued; at the end the context's stream waits for
+// the downloads, so that cct_sync() covers the whole call.
+int host_call_begin(cct_conv_plan* p) {
+  cct_ctx* ctx = p->ctx;
+  CCT_CUDA(ctx, cudaEventRecord(p->ev_start, ctx->stream));
+  CCT_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_in, p->ev_start, 0));
+  CCT_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_out, p->ev_start, 0));
+  return CCT_OK;
+}
+int host_call_end(cct_conv_plan* p) {
+  cct_ctx* ctx = p->ctx;
+  CCT_CUDA(ctx, cudaEventRecord(p->ev_done, ctx->copy_out));
+  CCT_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, p->ev_done, 0));
+  CCT_CUDA(ctx, cudaEventRecord(p->ev_done, ctx->copy_in));
+  CCT_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, p->ev_done, 0));
+  return cct_sync(ctx);
 }
 
 }  // namespace
@@ -118,6 +155,8 @@ int cct_ctx_destroy(cct_ctx* ctx) {
   if (!ctx) return CCT_ERR_INVALID;
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
+  if (ctx->copy_in) cudaStreamDestroy(ctx->copy_in);
+  if (ctx->copy_out) cudaStreamDestroy(ctx->copy_out);
   if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
   if (ctx->status_host) cudaFreeHost((void*)ctx->status_host);
   delete ctx;
@@ -243,6 +282,12 @@ int cct_conv_plan_destroy(cct_conv_plan* plan) {
   if (plan->umma) umma_plan_destroy(ctx, plan->umma);
   for (cudaEvent_t e : plan->timer.ev)
     if (e) cudaEventDestroy(e);
+  for (int c = 0; c < cct_conv_plan::kSlices; ++c) {
+    if (plan->ev_in[c]) cudaEventDestroy(plan->ev_in[c]);
+    if (plan->ev_out[c]) cudaEventDestroy(plan->ev_out[c]);
+  }
+  if (plan->ev_start) cudaEventDestroy(plan->ev_start);
+  if (plan->ev_done) cudaEventDestroy(plan->ev_done);
   float* slots[] = {plan->sX, plan->sW, plan->sb, plan->sY, plan->sdY, plan->sdX, plan->sdW, plan->sdb, plan->mask_dY};
   for (float* s : slots)
     if (s) cudaFree(s);
@@ -343,6 +388,35 @@ int cct_conv_forward_host(cct_conv_plan* plan, const float* hX, const float* hW,
   if (rc != CCT_OK) return rc;
   const size_t nx = (size_t)G.B * G.D * G.n * G.n, ny = (size_t)G.B * G.o * G.m * G.m,
                nw = (size_t)G.o * G.Dg * G.k * G.k;
+  const int per = slice_images(plan);
+  if (per > 0) {
+    // Upload, kernel and download of consecutive batch slices overlap: PCIe runs in both directions at once.
+    rc = host_call_begin(plan);
+    if (rc != CCT_OK) return rc;
+    const size_t ix = (size_t)G.D * G.n * G.n, iy = (size_t)G.o * G.m * G.m;  // elements per image
+    CCT_CUDA(ctx, cudaMemcpyAsync(plan->sW, hW, nw * 4, cudaMemcpyHostToDevice, ctx->copy_in));
+    if (G.bias) CCT_CUDA(ctx, cudaMemcpyAsync(plan->sb, hbias, (size_t)G.o * 4, cudaMemcpyHostToDevice, ctx->copy_in));
+    int slices = 0;
+    for (int b0 = 0; b0 < G.B; b0 += per, ++slices) {
+      const int nb = std::min(per, G.B - b0);
+      CCT_CUDA(ctx, cudaMemcpyAsync(plan->sX + b0 * ix, hX + b0 * ix, nb * ix * 4, cudaMemcpyHostToDevice, ctx->copy_in));
+      CCT_CUDA(ctx, cudaEventRecord(plan->ev_in[slices], ctx->copy_in));
+    }
+    PhaseTimer untimed;
+    slices = 0;
+    for (int b0 = 0; b0 < G.B; b0 += per, ++slices) {
+      const int nb = std::min(per, G.B - b0);
+      CCT_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, plan->ev_in[slices], 0));
+      rc = umma_conv_forward(ctx, plan->umma, plan->sX + b0 * ix, plan->sW, plan->sb, plan->sY + b0 * iy, relu, &untimed, nb,
+                             slices == 0);
+      if (rc != CCT_OK) return rc;
+      CCT_CUDA(ctx, cudaEventRecord(plan->ev_out[slices], ctx->stream));
+      CCT_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_out, plan->ev_out[slices], 0));
+      CCT_CUDA(ctx, cudaMemcpyAsync(hY + b0 * iy, plan->sY + b0 * iy, nb * iy * 4, cudaMemcpyDeviceToHost, ctx->copy_out));
+    }
+    plan->staged_forward = true;
+    return host_call_end(plan);
+  }
   CCT_CUDA(ctx, cudaMemcpyAsync(plan->sX, hX, nx * 4, cudaMemcpyHostToDevice, ctx->stream));
   CCT_CUDA(ctx, cudaMemcpyAsync(plan->sW, hW, nw * 4, cudaMemcpyHostToDevice, ctx->stream));
   if (G.bias) CCT_CUDA(ctx, cudaMemcpyAsync(plan->sb, hbias, (size_t)G.o * 4, cudaMemcpyHostToDevice, ctx->stream));
@@ -365,6 +439,41 @@ int cct_conv_backward_host(cct_conv_plan* plan, const float* hX, const float* hW
   if (rc != CCT_OK) return rc;
   const size_t nx = (size_t)G.B * G.D * G.n * G.n, ny = (size_t)G.B * G.o * G.m * G.m,
                nw = (size_t)G.o * G.Dg * G.k * G.k;
+  const int per = slice_images(plan);
+  if (per > 0) {
+    // dY arrives in slices; the data gradient of a slice runs as soon as the slice is there and its dX goes back while
+    // the next slice is still arriving; the weight gradient (the whole batch) follows the last slice.
+    rc = host_call_begin(plan);
+    if (rc != CCT_OK) return rc;
+    const size_t ix = (size_t)G.D * G.n * G.n, iy = (size_t)G.o * G.m * G.m;
+    if (hW) CCT_CUDA(ctx, cudaMemcpyAsync(plan->sW, hW, nw * 4, cudaMemcpyHostToDevice, ctx->copy_in));
+    if (hX) CCT_CUDA(ctx, cudaMemcpyAsync(plan->sX, hX, nx * 4, cudaMemcpyHostToDevice, ctx->copy_in));
+    int slices = 0;
+    for (int b0 = 0; b0 < G.B; b0 += per, ++slices) {
+      const int nb = std::min(per, G.B - b0);
+      CCT_CUDA(ctx, cudaMemcpyAsync(plan->sdY + b0 * iy, hdY + b0 * iy, nb * iy * 4, cudaMemcpyHostToDevice, ctx->copy_in));
+      CCT_CUDA(ctx, cudaEventRecord(plan->ev_in[slices], ctx->copy_in));
+    }
+    PhaseTimer untimed;
+    slices = 0;
+    for (int b0 = 0; b0 < G.B; b0 += per, ++slices) {
+      const int nb = std::min(per, G.B - b0);
+      CCT_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, plan->ev_in[slices], 0));
+      if (!hdX) continue;
+      rc = umma_conv_dgrad(ctx, plan->umma, plan->sW, plan->sdY + b0 * iy, plan->sdX + b0 * ix, &untimed, nb, slices == 0);
+      if (rc != CCT_OK) return rc;
+      CCT_CUDA(ctx, cudaEventRecord(plan->ev_out[slices], ctx->stream));
+      CCT_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_out, plan->ev_out[slices], 0));
+      CCT_CUDA(ctx, cudaMemcpyAsync(hdX + b0 * ix, plan->sdX + b0 * ix, nb * ix * 4, cudaMemcpyDeviceToHost, ctx->copy_out));
+    }
+    rc = umma_conv_wgrad(ctx, plan->umma, plan->sX, plan->sdY, plan->sdW, plan->sdb, &untimed);
+    if (rc != CCT_OK) return rc;
+    CCT_CUDA(ctx, cudaEventRecord(plan->ev_out[0], ctx->stream));
+    CCT_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_out, plan->ev_out[0], 0));
+    CCT_CUDA(ctx, cudaMemcpyAsync(hdW, plan->sdW, nw * 4, cudaMemcpyDeviceToHost, ctx->copy_out));
+    if (G.bias) CCT_CUDA(ctx, cudaMemcpyAsync(hdb, plan->sdb, (size_t)G.o * 4, cudaMemcpyDeviceToHost, ctx->copy_out));
+    return host_call_end(plan);
+  }
   if (hX) CCT_CUDA(ctx, cudaMemcpyAsync(plan->sX, hX, nx * 4, cudaMemcpyHostToDevice, ctx->stream));
   if (hW) CCT_CUDA(ctx, cudaMemcpyAsync(plan->sW, hW, nw * 4, cudaMemcpyHostToDevice, ctx->stream));
   CCT_CUDA(ctx, cudaMemcpyAsync(plan->sdY, hdY, ny * 4, cudaMemcpyHostToDevice, ctx->stream));

@@ -10,6 +10,8 @@ struct cct_ctx {
   int device = 0;
   cudaStream_t stream = nullptr;
   bool owns_stream = false;
+  // Side streams of the host-buffer entry points: uploads and downloads overlap each other and the kernels.
+  cudaStream_t copy_in = nullptr, copy_out = nullptr;
   int sm_count = 148;
   // One word in mapped pinned host memory that kernels set when a bounded wait runs out; read by cct_sync().
   volatile int* status_host = nullptr;
@@ -65,7 +67,12 @@ int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out);
 void umma_plan_destroy(cct_ctx* ctx, UmmaPlan* p);
 size_t umma_plan_workspace_bytes(const UmmaPlan* p);
 bool umma_supported(const ConvGeom& G);
+// `batch` > 0 restricts a call to the first `batch` images of the tensors it is given; `repack` = rewrite the packed
+// weight operand from W first (needed once per new W).
 int umma_conv_forward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W, const float* bias, float* Y,
-                      int relu, PhaseTimer* t);
+                      int relu, PhaseTimer* t, int batch = 0, bool repack = true);
 int umma_conv_backward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W, const float* dY, float* dX,
                        float* dW, float* db, PhaseTimer* t);
+int umma_conv_wgrad(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* dY, float* dW, float* db, PhaseTimer* t);
+int umma_conv_dgrad(cct_ctx* ctx, UmmaPlan* p, const float* W, const float* dY, float* dX, PhaseTimer* t, int batch,
+                    bool repack);

@@ -1561,20 +1561,23 @@ void launch_gather(cct_ctx* ctx, const GatherParams& P, const GatherProblem& gp)
 }  // namespace
 
 int umma_conv_forward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W, const float* bias, float* Y,
-                      int relu, PhaseTimer* t) {
+                      int relu, PhaseTimer* t, int batch, bool repack) {
   if (*ctx->status_host != 0) return CCT_ERR_TIMEOUT;  // an earlier bounded wait gave up: do not pile up behind it
   const ConvGeom& G = p->G;
   GatherProblem& f = p->fwd;
   const int vgroups = G.g * f.tiles;
-  t->begin(4, ctx->stream);
-  pack_fwd_kernel<<<pack_grid(ctx, f.w_half), 256, 0, ctx->stream>>>(W, f.w, f.w + f.w_half, vgroups, f.tiles, G.og, f.n,
-                                                                   f.n_pad, f.k_real, f.k_pad);
-  t->end(4, ctx->stream);
-  CCT_CHECK_LAUNCH(ctx);
+  const int B = batch > 0 ? batch : G.B;  // a leading slice of the batch (host-buffer calls pipeline over slices)
+  if (repack) {
+    t->begin(4, ctx->stream);
+    pack_fwd_kernel<<<pack_grid(ctx, f.w_half), 256, 0, ctx->stream>>>(W, f.w, f.w + f.w_half, vgroups, f.tiles, G.og,
+                                                                     f.n, f.n_pad, f.k_real, f.k_pad);
+    t->end(4, ctx->stream);
+    CCT_CHECK_LAUNCH(ctx);
+  }
   GatherParams P{};
   P.in = X; P.out = Y;
   P.bias = G.bias ? bias : nullptr;
-  P.n_pix = G.B * G.m * G.m; P.q_h = G.m; P.q_w = G.m;
+  P.n_pix = B * G.m * G.m; P.q_h = G.m; P.q_w = G.m;
   P.iy_mul = G.s; P.iy_add = -G.p; P.ix_mul = G.s; P.ix_add = -G.p;
   P.in_lim = G.n;
   P.tap_sign = 1; P.taps_per_axis = G.k;
@@ -1596,9 +1599,15 @@ int umma_conv_forward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W,
 
 int umma_conv_backward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W, const float* dY, float* dX,
                        float* dW, float* db, PhaseTimer* t) {
+  int rc = umma_conv_wgrad(ctx, p, X, dY, dW, db, t);
+  if (rc == CCT_OK && dX) rc = umma_conv_dgrad(ctx, p, W, dY, dX, t, 0, true);
+  return rc;
+}
+
+// Weight + bias gradient over the whole batch.
+int umma_conv_wgrad(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* dY, float* dW, float* db, PhaseTimer* t) {
   if (*ctx->status_host != 0) return CCT_ERR_TIMEOUT;
   const ConvGeom& G = p->G;
-  // ---- weight + bias gradient
   if (p->wg_gather) {
     const GatherProblem& f = p->fwd;
     GatherProblem& w = p->wgp;
@@ -1656,18 +1665,28 @@ int umma_conv_backward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W
     t->end(2, ctx->stream);
     CCT_CHECK_LAUNCH(ctx);
   }
-  // ---- data gradient
-  if (dX) {
+  return CCT_OK;
+}
+
+// Data gradient of the first `batch` images (0: all of them); `repack` rewrites the packed weights from W first.
+int umma_conv_dgrad(cct_ctx* ctx, UmmaPlan* p, const float* W, const float* dY, float* dX, PhaseTimer* t, int batch,
+                    bool repack) {
+  if (*ctx->status_host != 0) return CCT_ERR_TIMEOUT;
+  const ConvGeom& G = p->G;
+  const int B = batch > 0 ? batch : G.B;
+  {
     GatherProblem& d = p->dgr;
     const int vgroups = G.g * d.tiles;
     t->begin(3, ctx->stream);
-    pack_dgrad_kernel<<<pack_grid(ctx, d.w_half), 256, 0, ctx->stream>>>(W, d.w, d.w + d.w_half, vgroups, d.tiles, G.og,
-                                                                       G.Dg, G.k, G.s, p->dgr_taps, d.ch_tile, d.n,
-                                                                       d.n_pad, d.k_real, d.k_pad);
-    CCT_CHECK_LAUNCH(ctx);
+    if (repack) {
+      pack_dgrad_kernel<<<pack_grid(ctx, d.w_half), 256, 0, ctx->stream>>>(W, d.w, d.w + d.w_half, vgroups, d.tiles, G.og,
+                                                                         G.Dg, G.k, G.s, p->dgr_taps, d.ch_tile, d.n,
+                                                                         d.n_pad, d.k_real, d.k_pad);
+      CCT_CHECK_LAUNCH(ctx);
+    }
     GatherParams P{};
     P.in = dY; P.out = dX; P.bias = nullptr;
-    P.n_pix = G.B * p->dgr_q * p->dgr_q; P.q_h = p->dgr_q; P.q_w = p->dgr_q;
+    P.n_pix = B * p->dgr_q * p->dgr_q; P.q_h = p->dgr_q; P.q_w = p->dgr_q;
     P.iy_mul = 1; P.iy_add = p->dgr_q0; P.ix_mul = 1; P.ix_add = p->dgr_q0;
     P.in_lim = G.m;
     P.tap_sign = -1; P.taps_per_axis = p->dgr_taps;

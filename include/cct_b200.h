@@ -127,7 +127,9 @@ int cct_conv_backward_fused(cct_conv_plan* plan, const float* X, const float* W,
 /* Host-buffer forms of the two calls above, for callers that keep cubes in host memory as the reference's
  * ParallelizedBridge does (src/bridges/ParallelizedBridge_impl.hxx:538-671, 686-738, 779-830, 895-910,
  * 1071-1122): inputs are copied to plan-owned device buffers, the kernels run, results are copied back, and the
- * call returns after the results have landed.  Pinned host memory (cct_malloc_host) makes the copies asynchronous.
+ * call returns after the results have landed.  Pinned host memory (cct_malloc_host) makes the copies asynchronous;
+ * batches of eight images or more move in four slices on two side streams, so that the upload of one slice, the
+ * kernels of the previous one and the download of the one before overlap.
  * cct_conv_backward_host accepts hX == NULL and/or hW == NULL, meaning "the copy staged by the last
  * cct_conv_forward_host on this plan" (the reference keeps the input cube on the device between the two passes). */
 int cct_conv_forward_host(cct_conv_plan* plan, const float* hX, const float* hW, const float* hbias, float* hY,

@@ -156,10 +156,11 @@ def test_backward_is_deterministic(ctx):
         assert np.array_equal(u, v)
 
 
-def test_host_buffer_entry_points(ctx, port):
+@pytest.mark.parametrize("B", [4, 10, 16])  # 4: one piece; 10 and 16: pipelined in slices of 3 (last one short) and 4
+def test_host_buffer_entry_points(ctx, port, B):
     import ctypes as C
     from caffecontroll_b200 import capi
-    B, D, n, o, k, s, p, g = 4, 3, 20, 10, 5, 4, 2, 1
+    D, n, o, k, s, p, g = 3, 20, 10, 5, 4, 2, 1
     X, W, b, dY = make_inputs(16, B, D, n, o, k, s, p, g)
     lib = ctx.lib
     desc = capi.ConvDesc(B, D, n, o, k, s, p, g, 1, capi.ALGO_AUTO)
@@ -168,10 +169,20 @@ def test_host_buffer_entry_points(ctx, port):
     Y = np.empty((B, o, 5, 5), np.float32)
     dX, dW, db = np.empty_like(X), np.empty_like(W), np.empty_like(b)
     vp = lambda a: a.ctypes.data_as(C.c_void_p)
-    capi.check(lib.cct_conv_forward_host(plan, vp(X), vp(W), vp(b), vp(Y), 0), "forward_host", ctx.h)
-    capi.check(lib.cct_conv_backward_host(plan, vp(X), vp(W), vp(dY), vp(dX), vp(dW), vp(db)), "backward_host", ctx.h)
-    lib.cct_conv_plan_destroy(plan)
-    assert_close(Y, port.conv_forward(X, W, b, k, s, p, g), "Y")
+    Yr = port.conv_forward(X, W, b, k, s, p, g)
     dXr, dWr, dbr = port.conv_backward(X, W, dY, k, s, p, g)
-    for a, r, name in ((dX, dXr, "dX"), (dW, dWr, "dW"), (db, dbr, "db")):
-        assert_close(a, r, name)
+    for rnd in range(2):  # the second round reuses the staged X / W (NULL) and must not be disturbed by the first
+        Y.fill(np.nan); dX.fill(np.nan); dW.fill(np.nan); db.fill(np.nan)
+        capi.check(lib.cct_conv_forward_host(plan, vp(X), vp(W), vp(b), vp(Y), 0), "forward_host", ctx.h)
+        if rnd == 0:
+            capi.check(lib.cct_conv_backward_host(plan, vp(X), vp(W), vp(dY), vp(dX), vp(dW), vp(db)), "backward_host", ctx.h)
+        else:
+            capi.check(lib.cct_conv_backward_host(plan, None, None, vp(dY), vp(dX), vp(dW), vp(db)), "backward_host", ctx.h)
+        assert_close(Y, Yr, "Y")
+        for a, r, name in ((dX, dXr, "dX"), (dW, dWr, "dW"), (db, dbr, "db")):
+            assert_close(a, r, name)
+    # without dX
+    dW.fill(np.nan)
+    capi.check(lib.cct_conv_backward_host(plan, None, None, vp(dY), None, vp(dW), vp(db)), "backward_host", ctx.h)
+    assert_close(dW, dWr, "dW without dX")
+    lib.cct_conv_plan_destroy(plan)
