@@ -1047,12 +1047,51 @@ WgradKernel wgrad_pick(int subs, int n_pad) {
   return subs == 2 ? wgrad_pick_nb<2>(n_pad / 16) : wgrad_pick_nb<1>(n_pad / 16);
 }
 
-// dW[o][kk] and db[o] from the split partial sums, added in split order (deterministic).  One block per row
-// (channel tile, kk) of the partial sums, threads over the row's channels: no division per element, coalesced reads.
-__global__ void __launch_bounds__(128) wgrad_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dW,
+// dW[o][kk] and db[o] from the split partial sums, added in split order (deterministic).  One block per 32 x 32
+// tile of (kk, channel): the partial sums are read along the channels (their fastest index), the tile is turned in
+// shared memory, and dW is written along kk (its fastest index) - both sides coalesced, no division per element.
+__global__ void __launch_bounds__(256) wgrad_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dW,
                                                            float* __restrict__ db, int splits, int vgroups,
                                                            int tiles_per_group, int rows_pad, int n_real, int n_pad,
                                                            int k_real, int og) {
+  __shared__ float tile[32][33];
+  const int vg = blockIdx.z;
+  const int kk0 = blockIdx.x * 32, j0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  const int ch0 = (vg / tiles_per_group) * og + (vg % tiles_per_group) * n_real;
+  const size_t split_stride = (size_t)vgroups * rows_pad * n_pad;
+  const int last = db ? k_real : k_real - 1;  // the bias row exists only where the kernel produced it
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int kk = kk0 + ty + 8 * r, j = j0 + tx;
+    float acc = 0.f;
+    if (kk <= last && j < n_real) {
+      const float* src = partial + ((size_t)vg * rows_pad + kk) * n_pad + j;
+#pragma unroll 8
+      for (int s = 0; s < splits; ++s) acc += src[(size_t)s * split_stride];
+    }
+    tile[ty + 8 * r][tx] = acc;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int j = j0 + ty + 8 * r, kk = kk0 + tx;
+    if (j < n_real && kk <= last) {
+      const float v = tile[tx][ty + 8 * r];
+      if (kk < k_real)
+        dW[(size_t)(ch0 + j) * k_real + kk] = v;
+      else
+        db[ch0 + j] = v;
+    }
+  }
+}
+
+// The same reduction for small outputs, where 32 x 32 tiles would leave most SMs idle: one block per row (channel
+// tile, kk) of the partial sums, threads over the row's channels.
+__global__ void __launch_bounds__(128) wgrad_reduce_rows_kernel(const float* __restrict__ partial, float* __restrict__ dW,
+                                                                float* __restrict__ db, int splits, int vgroups,
+                                                                int tiles_per_group, int rows_pad, int n_real,
+                                                                int n_pad, int k_real, int og) {
   const int rows = vgroups * (k_real + 1);
   for (int r = blockIdx.x; r < rows; r += gridDim.x) {
     const int vg = r / (k_real + 1), kk = r - vg * (k_real + 1);
@@ -1121,18 +1160,14 @@ __global__ void __launch_bounds__(256) split_dy_kernel(const float* __restrict__
 
 // db[c] = sum over the batch of the plane sums (ConvolutionBridge_impl.hxx:575-599), in a fixed order.
 __global__ void bias_grad_kernel(const float* __restrict__ plane_sums, float* __restrict__ db, int batch, int channels) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  // one warp per channel: lane l adds images l, l + 32, ... in order, then a fixed shuffle tree
+  const int c = (int)((blockIdx.x * blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
   if (c >= channels) return;
-  float t0 = 0.f, t1 = 0.f, t2 = 0.f, t3 = 0.f;  // four interleaved chains: the loads of a group of four overlap
-  int b = 0;
-  for (; b + 3 < batch; b += 4) {
-    t0 += plane_sums[(size_t)b * channels + c];
-    t1 += plane_sums[(size_t)(b + 1) * channels + c];
-    t2 += plane_sums[(size_t)(b + 2) * channels + c];
-    t3 += plane_sums[(size_t)(b + 3) * channels + c];
-  }
-  for (; b < batch; ++b) t0 += plane_sums[(size_t)b * channels + c];
-  db[c] = (t0 + t1) + (t2 + t3);
+  float t = 0.f;
+  for (int b = lane; b < batch; b += 32) t += plane_sums[(size_t)b * channels + c];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  if (lane == 0) db[c] = t;
 }
 
 // ------------------------------------------------------------------------------------------ weight packing
@@ -1287,7 +1322,17 @@ int set_smem(cct_ctx* ctx, K kernel, size_t bytes) {
   return CCT_OK;
 }
 
-int reduce_grid(cct_ctx* ctx, int rows) { return std::max(1, std::min(rows, ctx->sm_count * 16)); }
+// Split reduction: tiles when they fill the machine, rows otherwise (both add in split order).
+void launch_wgrad_reduce(cct_ctx* ctx, const float* partial, float* dW, float* db, int splits, int vgroups,
+                         int tiles_per_group, int rows_pad, int n_real, int n_pad, int k_real, int og) {
+  const dim3 tiles((k_real + 1 + 31) / 32, (n_real + 31) / 32, vgroups);
+  if ((int)(tiles.x * tiles.y * tiles.z) >= ctx->sm_count)
+    wgrad_reduce_kernel<<<tiles, 256, 0, ctx->stream>>>(partial, dW, db, splits, vgroups, tiles_per_group, rows_pad,
+                                                       n_real, n_pad, k_real, og);
+  else
+    wgrad_reduce_rows_kernel<<<std::max(1, std::min(vgroups * (k_real + 1), ctx->sm_count * 16)), 128, 0, ctx->stream>>>(
+        partial, dW, db, splits, vgroups, tiles_per_group, rows_pad, n_real, n_pad, k_real, og);
+}
 
 int pack_grid(cct_ctx* ctx, size_t total) {
   size_t b = (total + 255) / 256;
@@ -1631,9 +1676,9 @@ int umma_conv_wgrad(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* dY, 
     t->end(1, ctx->stream);
     CCT_CHECK_LAUNCH(ctx);
     t->begin(2, ctx->stream);
-    wgrad_reduce_kernel<<<reduce_grid(ctx, vgroups * (f.k_real + 1)), 128, 0, ctx->stream>>>(
-        p->w_partial, dW, nullptr, p->wg_splits, vgroups, f.tiles, p->wg_mtiles * kTileM, f.n, f.n_pad, f.k_real, G.og);
-    if (G.bias) bias_grad_kernel<<<(G.o + 127) / 128, 128, 0, ctx->stream>>>(p->wg_plane_sums, db, G.B, G.o);
+    launch_wgrad_reduce(ctx, p->w_partial, dW, nullptr, p->wg_splits, vgroups, f.tiles, p->wg_mtiles * kTileM, f.n,
+                        f.n_pad, f.k_real, G.og);
+    if (G.bias) bias_grad_kernel<<<(G.o + 7) / 8, 256, 0, ctx->stream>>>(p->wg_plane_sums, db, G.B, G.o);
     t->end(2, ctx->stream);
     CCT_CHECK_LAUNCH(ctx);
   } else {
@@ -1659,9 +1704,8 @@ int umma_conv_wgrad(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* dY, 
     t->end(1, ctx->stream);
     CCT_CHECK_LAUNCH(ctx);
     t->begin(2, ctx->stream);
-    wgrad_reduce_kernel<<<reduce_grid(ctx, vgroups * (f.k_real + 1)), 128, 0, ctx->stream>>>(
-        p->w_partial, dW, G.bias ? db : nullptr, p->w_splits, vgroups, f.tiles, p->w_mtiles * kTileM, f.n, f.n_pad,
-        f.k_real, G.og);
+    launch_wgrad_reduce(ctx, p->w_partial, dW, G.bias ? db : nullptr, p->w_splits, vgroups, f.tiles,
+                        p->w_mtiles * kTileM, f.n, f.n_pad, f.k_real, G.og);
     t->end(2, ctx->stream);
     CCT_CHECK_LAUNCH(ctx);
   }
@@ -1819,8 +1863,8 @@ extern "C" int cct_conv_weight_grad_noalloc(cct_ctx* ctx, const cct_conv_desc* d
   P.dbg = 0;
   kernel<<<dim3(mgroups, splits, vgroups), kWgThreads, smem, ctx->stream>>>(P);
   CCT_CHECK_LAUNCH(ctx);
-  wgrad_reduce_kernel<<<reduce_grid(ctx, vgroups * (k_real + 1)), 128, 0, ctx->stream>>>(
-      partial, dW, G.bias ? db : nullptr, splits, vgroups, tiles, m_tiles * kTileM, n_real, n_pad, k_real, G.og);
+  launch_wgrad_reduce(ctx, partial, dW, G.bias ? db : nullptr, splits, vgroups, tiles, m_tiles * kTileM, n_real, n_pad,
+                      k_real, G.og);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }
