@@ -991,7 +991,7 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
       for (int kbl = 0; kbl < kblocks; ++kbl, ring.advance(P.stages)) {
         const int s = ring.idx;
         PROF_LAP(0);
-        mbar_wait<false>(full + 8u * s, (uint32_t)ring.use & 1u, failed, P.status, 0x40);
+        mbar_wait(full + 8u * s, (uint32_t)ring.use & 1u, failed, P.status, 0x40);  // parked: this thread mostly waits for the producers
         tc_fence_after();
         PROF_LAP(1);
         const uint32_t st = base + (uint32_t)s * L.stage_bytes;
