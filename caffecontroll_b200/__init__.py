@@ -5,6 +5,6 @@ capi.py (ctypes binding), bridge.py (mirror of the reference's LogicalCube / Lay
 interface) and parallel.py (ParallelizedBridge's batch partitioning over one process per GPU).
 """
 from . import capi  # noqa: F401
-from .bridge import Context, ConvolutionBridge, Layer, LogicalCube, conv_layer  # noqa: F401
+from .bridge import Context, ConvolutionBridge, FullyConnectedBridge, Layer, LogicalCube, conv_layer  # noqa: F401
 
-__all__ = ["capi", "Context", "ConvolutionBridge", "Layer", "LogicalCube", "conv_layer"]
+__all__ = ["capi", "Context", "ConvolutionBridge", "FullyConnectedBridge", "Layer", "LogicalCube", "conv_layer"]

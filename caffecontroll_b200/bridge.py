@@ -213,6 +213,21 @@ class ConvolutionBridge:
                 c.free()
 
 
+class FullyConnectedBridge(ConvolutionBridge):
+    """The reference's FullyConnectedBridge (src/bridges/FullyConnectedBridge_impl.hxx:201-202, 305-312) is a
+    convolution whose kernel covers the whole input.  Here it runs as a 1x1 convolution over the input viewed as
+    D*R*C channels of a single pixel: the same arithmetic on the same weight layout [o][d][r][c], through the same
+    plan, kernels and fusion options as ConvolutionBridge.  The output layer is B x num_output x 1 x 1."""
+
+    def __init__(self, p_input_layer, p_output_layer, bias_term=True, algo=capi.ALGO_AUTO, ctx=None):
+        x, dx = p_input_layer.p_data_cube, p_input_layer.p_gradient_cube
+        k = x.D * x.R * x.C
+        flat = Layer(LogicalCube(x.ctx, 1, 1, k, x.B, x.dtype, ptr=x.ptr),
+                     LogicalCube(dx.ctx, 1, 1, k, dx.B, dx.dtype, ptr=dx.ptr) if dx is not None else None)
+        super().__init__(flat, p_output_layer, 1, 1, 0, 1, bias_term, algo, ctx)
+        self.unflattened_input_layer = p_input_layer
+
+
 def conv_layer(ctx, X, W, bias, dY, kernel, stride=1, pad=0, group=1, needs_dx=True, algo=capi.ALGO_AUTO, relu=False):
     """Convenience for tests: numpy in, numpy out (Y, dX, dW, db) through a ConvolutionBridge."""
     B, D, n, _ = X.shape

@@ -47,6 +47,10 @@ __device__ unsigned long long g_prof[64];
 #define PROF_FLUSH(role, cond)
 #endif
 constexpr int kMaxTapsPerAxis = 15;
+// Longest accumulation chain of a weight-gradient partial sum, in k-blocks of 32 pixels.  Measured against a
+// double-accumulating CPU reference, AlexNet conv1's dW was off by 7.7e-5 (max-norm relative) with chains of 327
+// k-blocks, the error pointing towards zero (truncating accumulate), and it shrinks in proportion to the chain.
+constexpr int kMaxChainKblocks = 176;
 constexpr uint32_t kPadBit = 0x80000000u;  // never set in a pixel's validity mask: marks padding entries
 
 // One entry per reduction index of a gathered operand: element offset from the pixel's tap origin, and the tap's
@@ -1497,7 +1501,14 @@ int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out) {
     const int n_pix = G.B * G.m * G.m;
     p->w_kblocks_total = (n_pix + kBlockK - 1) / kBlockK;
     const int out_tiles = p->w_mgroups * G.g * f.tiles;
-    int splits = std::max(1, ctx->sm_count / out_tiles);
+    // Whole waves of CTAs (one CTA per SM), as few as keep a partial sum's accumulation chain within
+    // kMaxChainKblocks: the tensor core's fp32 accumulation truncates, so the error of a partial sum grows with the
+    // length of its chain, while the reduction over splits adds with proper rounding.
+    int splits = 1;
+    for (int waves = 1; waves <= 64; ++waves) {
+      splits = std::max(1, waves * ctx->sm_count / out_tiles);
+      if ((p->w_kblocks_total + splits - 1) / splits <= kMaxChainKblocks) break;
+    }
     splits = std::min(splits, std::max(1, p->w_kblocks_total / 8));  // at least 8 k-blocks per CTA
     p->w_kblocks_per_split = (p->w_kblocks_total + splits - 1) / splits;
     p->w_splits = (p->w_kblocks_total + p->w_kblocks_per_split - 1) / p->w_kblocks_per_split;
@@ -1521,6 +1532,7 @@ int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out) {
     const int base_tiles = vgroups * p->wg_mtiles;
     int splits = std::max(1, (4 * ctx->sm_count + base_tiles - 1) / base_tiles);
     splits = std::min(splits, std::max(1, kb_total / 16));
+    splits = std::max(splits, (kb_total + kMaxChainKblocks - 1) / kMaxChainKblocks);  // bounded accumulation chains
     p->wg_kps = (kb_total + splits - 1) / splits;
     p->wg_splits = (kb_total + p->wg_kps - 1) / p->wg_kps;
     w.k_pad = p->wg_kps * kBlockK;
