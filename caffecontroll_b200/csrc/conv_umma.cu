@@ -1091,26 +1091,40 @@ __global__ void __launch_bounds__(256) wgrad_reduce_kernel(const float* __restri
 }
 
 // The same reduction for small outputs, where 32 x 32 tiles would leave most SMs idle: one block per row (channel
-// tile, kk) of the partial sums, threads over the row's channels.
-__global__ void __launch_bounds__(128) wgrad_reduce_rows_kernel(const float* __restrict__ partial, float* __restrict__ dW,
+// tile, kk) of the partial sums; 32 channels x 8 interleaved slices of the splits per pass, the eight slice sums
+// added in a fixed order - the result does not depend on the grid, and a thread's chain is splits / 8 long.
+__global__ void __launch_bounds__(256) wgrad_reduce_rows_kernel(const float* __restrict__ partial, float* __restrict__ dW,
                                                                 float* __restrict__ db, int splits, int vgroups,
                                                                 int tiles_per_group, int rows_pad, int n_real,
                                                                 int n_pad, int k_real, int og) {
+  __shared__ float part[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int rows = vgroups * (k_real + 1);
+  const size_t split_stride = (size_t)vgroups * rows_pad * n_pad;
   for (int r = blockIdx.x; r < rows; r += gridDim.x) {
     const int vg = r / (k_real + 1), kk = r - vg * (k_real + 1);
-    if (kk == k_real && !db) continue;  // no bias row in the partial sums
+    if (kk == k_real && !db) continue;  // no bias row in the partial sums (uniform over the block)
     const int ch0 = (vg / tiles_per_group) * og + (vg % tiles_per_group) * n_real;
-    const size_t split_stride = (size_t)vgroups * rows_pad * n_pad;
-    for (int j = threadIdx.x; j < n_real; j += blockDim.x) {
-      const float* src = partial + ((size_t)vg * rows_pad + kk) * n_pad + j;
+    for (int j0 = 0; j0 < n_real; j0 += 32) {
+      const int j = j0 + tx;
       float acc = 0.f;
-#pragma unroll 8
-      for (int s = 0; s < splits; ++s) acc += src[(size_t)s * split_stride];
-      if (kk < k_real)
-        dW[(size_t)(ch0 + j) * k_real + kk] = acc;
-      else
-        db[ch0 + j] = acc;
+      if (j < n_real) {
+        const float* src = partial + ((size_t)vg * rows_pad + kk) * n_pad + j;
+#pragma unroll 4
+        for (int s = ty; s < splits; s += 8) acc += src[(size_t)s * split_stride];
+      }
+      __syncthreads();  // the previous pass has been read
+      part[ty][tx] = acc;
+      __syncthreads();
+      if (ty == 0 && j < n_real) {
+        float t = part[0][tx];
+#pragma unroll
+        for (int y = 1; y < 8; ++y) t += part[y][tx];
+        if (kk < k_real)
+          dW[(size_t)(ch0 + j) * k_real + kk] = t;
+        else
+          db[ch0 + j] = t;
+      }
     }
   }
 }
@@ -1334,7 +1348,7 @@ void launch_wgrad_reduce(cct_ctx* ctx, const float* partial, float* dW, float* d
     wgrad_reduce_kernel<<<tiles, 256, 0, ctx->stream>>>(partial, dW, db, splits, vgroups, tiles_per_group, rows_pad,
                                                        n_real, n_pad, k_real, og);
   else
-    wgrad_reduce_rows_kernel<<<std::max(1, std::min(vgroups * (k_real + 1), ctx->sm_count * 16)), 128, 0, ctx->stream>>>(
+    wgrad_reduce_rows_kernel<<<std::max(1, std::min(vgroups * (k_real + 1), ctx->sm_count * 8)), 256, 0, ctx->stream>>>(
         partial, dW, db, splits, vgroups, tiles_per_group, rows_pad, n_real, n_pad, k_real, og);
 }
 
