@@ -234,12 +234,98 @@ __global__ void __launch_bounds__(kPoolWarps * 32, 5) maxpool_bwd_kernel(const f
   }
 }
 
+// The same operation for ceil(k / s) <= 2 (3x3 / stride 2, 2x2 / stride 2, ...), where an element is covered by at most
+// four windows: a table built once per block lists every element's candidate windows in (ph, pw) order (unused slots
+// point at a sentinel entry that matches nothing), so the element loop is one table read and four compare / select /
+// add steps - no range or validity arithmetic - over the flat, fully coalesced plane.
+template <bool RELU>
+__global__ void __launch_bounds__(kPoolWarps * 32) maxpool_bwd4_kernel(const float* __restrict__ A,
+                                                                      const int32_t* __restrict__ idx,
+                                                                      const float* __restrict__ dP,
+                                                                      float* __restrict__ dA, int planes, int n, int m,
+                                                                      int k, int s, int slice) {
+  extern __shared__ uint32_t pool_smem[];
+  const int mm = m * m, nn = n * n;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  ushort4* cand = reinterpret_cast<ushort4*>(pool_smem);                                // [nn]
+  int32_t* s_idx = reinterpret_cast<int32_t*>(pool_smem + 2 * ((nn + 1) & ~1)) + warp * 2 * slice;  // [mm + 1]
+  float* s_dp = reinterpret_cast<float*>(s_idx + slice);                                // [mm + 1]
+  for (int e = threadIdx.x; e < nn; e += blockDim.x) {
+    const int h = e / n, w = e - h * n;
+    const int ph1 = min(h / s, m - 1), pw1 = min(w / s, m - 1);
+    const int ph0 = h < k ? 0 : (h - k) / s + 1, pw0 = w < k ? 0 : (w - k) / s + 1;
+    unsigned short c[4] = {(unsigned short)mm, (unsigned short)mm, (unsigned short)mm, (unsigned short)mm};
+    int cnt = 0;
+    for (int ph = ph0; ph <= ph1; ++ph)
+      for (int pw = pw0; pw <= pw1; ++pw) c[cnt++] = (unsigned short)(ph * m + pw);
+    cand[e] = make_ushort4(c[0], c[1], c[2], c[3]);
+  }
+  if (lane == 0) {  // the sentinel: an index no element has, and a gradient of zero
+    s_idx[mm] = -1;
+    s_dp[mm] = 0.f;
+  }
+  __syncthreads();
+  const int warp0 = blockIdx.x * kPoolWarps + warp, nwarps = gridDim.x * kPoolWarps;
+  for (int plane = warp0; plane < planes; plane += nwarps) {
+    const int32_t* ip = idx + (size_t)plane * mm;
+    const float* gp = dP + (size_t)plane * mm;
+    const float* a = RELU ? A + (size_t)plane * nn : nullptr;
+    float* out = dA + (size_t)plane * nn;
+    float av[8];
+    auto fetch = [&](int e0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int e = e0 + j * 32 + lane;
+        av[j] = (RELU && e < nn) ? __ldg(a + e) : 1.f;
+      }
+    };
+    fetch(0);
+    __syncwarp();  // the previous plane's tests are done with the slice
+    for (int i = lane; i < mm; i += 32) {
+      s_idx[i] = __ldg(ip + i);
+      s_dp[i] = __ldg(gp + i);
+    }
+    __syncwarp();
+    for (int e0 = 0; e0 < nn; e0 += 256) {
+      float res[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int e = min(e0 + j * 32 + lane, nn - 1);
+        const ushort4 c = cand[e];
+        const bool live = av[j] > 0.f;
+        float acc = 0.f;
+        acc += (live && s_idx[c.x] == e) ? s_dp[c.x] : 0.f;
+        acc += (live && s_idx[c.y] == e) ? s_dp[c.y] : 0.f;
+        acc += (live && s_idx[c.z] == e) ? s_dp[c.z] : 0.f;
+        acc += (live && s_idx[c.w] == e) ? s_dp[c.w] : 0.f;
+        res[j] = acc;
+      }
+      if (e0 + 256 < nn) fetch(e0 + 256);  // the next elements' A in flight while these results are stored
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int e = e0 + j * 32 + lane;
+        if (e < nn) out[e] = res[j];
+      }
+    }
+  }
+}
+
 template <bool RELU>
 int launch_maxpool_bwd(cct_ctx* ctx, const float* A, const int32_t* idx, const float* dP, float* dA, int planes, int n,
                        int m, int k, int s) {
   const int grid = plane_grid(ctx, (planes + kPoolWarps - 1) / kPoolWarps);
   const uint32_t inv_s = fast_div_magic((uint64_t)n, (uint32_t)s);
   const int taps = (k + s - 1) / s;
+  if (taps <= 2 && m * m < 65535) {
+    const int slice = (m * m + 1 + 31) & ~31;
+    const size_t smem4 = ((size_t)2 * ((n * n + 1) & ~1) + (size_t)kPoolWarps * 2 * slice) * 4;
+    if (smem4 <= 100 * 1024) {  // two blocks per SM still fit
+      if (smem4 > 48 * 1024)
+        CCT_CUDA(ctx, cudaFuncSetAttribute(maxpool_bwd4_kernel<RELU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem4));
+      maxpool_bwd4_kernel<RELU><<<grid, kPoolWarps * 32, smem4, ctx->stream>>>(A, idx, dP, dA, planes, n, m, k, s, slice);
+      return CCT_OK;
+    }
+  }
   const int mm_pad = (m * m + 31) & ~31;
   const size_t smem = ((size_t)((n + 31) & ~31) + (size_t)kPoolWarps * 2 * mm_pad) * 4;
   if (smem > 200 * 1024) {

@@ -16,7 +16,9 @@ def _cube(ctx, arr):
     return LogicalCube.from_numpy(ctx, arr)
 
 
-@pytest.mark.parametrize("shape", [(2, 3, 13, 3, 2), (2, 3, 10, 4, 2), (1, 2, 27, 3, 2), (3, 1, 7, 2, 1), (1, 1, 9, 3, 3)])
+# the last two have three and five windows per axis over an element: the kernels for overlapping pooling beyond 2x2
+@pytest.mark.parametrize("shape", [(2, 3, 13, 3, 2), (2, 3, 10, 4, 2), (1, 2, 27, 3, 2), (3, 1, 7, 2, 1), (1, 1, 9, 3, 3),
+                                   (2, 2, 9, 3, 1), (1, 2, 11, 5, 1)])
 def test_pool_and_relu_masks_match_oracle_bitwise(ctx, port, shape):
     from caffecontroll_b200 import capi
     B, D, n, k, s = shape
