@@ -826,7 +826,8 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
   constexpr uint32_t kATile = kTileM * 128u, kBTile = NB * 16u * 128u;
   constexpr int kNPad = NB * 16;
   // Narrow dY tiles run "dual": the lo tile sits right behind the hi tile, one MMA of width 2*kNPad covers both (an
-  // MMA costs about 90 cycles however narrow it is), and the epilogue adds the two halves of the accumulator.
+  // MMA costs the issuing thread about 75 cycles however narrow it is), and the epilogue adds the two halves of the
+  // accumulator.
   constexpr bool kDual = kNPad <= 64;  // operands from shared memory: an MMA wider than 128 is slower than two narrow ones
   constexpr int kAccCols = kDual ? 2 * kNPad : kNPad;
 
