@@ -6,6 +6,7 @@
 //   B200Driver                the slice of src/sched/DeviceDriver.h:56-274 the path needs
 //   ConvolutionBridge         src/bridges/ConvolutionBridge.h + AbstractBridge.h members (iR..oB, p_*_layer,
 //                             needs_to_calc_backward_grad, bias_term, model / bias / gradient cube accessors)
+//   FullyConnectedBridge      src/bridges/FullyConnectedBridge.h, over the convolution plan (kernel = whole input)
 //   SGDGradientUpdater        src/algorithms/GradientUpdater.h:154-193
 //   ParallelizedBridge        one partition per process: owns model, gradient and history, sums gradients through a
 //                             caller-supplied all-reduce (src/bridges/ParallelizedBridge_impl.hxx:876-971), then updates
@@ -204,6 +205,36 @@ class ConvolutionBridge : public PhysicalOperator {
   LogicalCube<float>* p_model_gradient_cube_ = nullptr;
   LogicalCube<float>* p_bias_cube_ = nullptr;
   LogicalCube<float>* p_bias_gradient_cube_ = nullptr;
+};
+
+// The reference's FullyConnectedBridge (src/bridges/FullyConnectedBridge_impl.hxx:201-202, 305-312) is a convolution
+// whose kernel covers the whole input.  Here: a ConvolutionBridge with a 1x1 kernel over the input viewed as D*R*C
+// channels of one pixel - the same arithmetic on the same weight layout [o][d][r][c].  Output layer: B x num_output
+// x 1 x 1.  Not tuned: a long reduction stays in one accumulator.
+class FullyConnectedBridge : public PhysicalOperator {
+ public:
+  FullyConnectedBridge(Layer* in, Layer* out, int num_output, bool bias_term, B200Driver* driver, int algo = CCT_ALGO_AUTO)
+      : flat_data_(in->p_data_cube->get_p_data(), 1, 1, in->p_data_cube->R * in->p_data_cube->C * in->p_data_cube->D,
+                   in->p_data_cube->B, driver),
+        flat_grad_(in->p_gradient_cube->get_p_data(), 1, 1,
+                   in->p_gradient_cube->R * in->p_gradient_cube->C * in->p_gradient_cube->D, in->p_gradient_cube->B, driver),
+        flat_(&flat_data_, &flat_grad_),
+        conv_(&flat_, out, params(num_output, bias_term), driver, algo) {}
+  ConvolutionBridge& as_convolution() { return conv_; }  // model / bias cubes, fusion switches
+  void forward() override { conv_.forward(); }
+  void backward() override { conv_.backward(); }
+
+ private:
+  static ConvolutionParameter params(int num_output, bool bias_term) {
+    ConvolutionParameter cp;
+    cp.num_output = num_output;
+    cp.kernel_size = 1;
+    cp.bias_term = bias_term;
+    return cp;
+  }
+  LogicalCube<float> flat_data_, flat_grad_;
+  Layer flat_;
+  ConvolutionBridge conv_;
 };
 
 // The solver fields the updater reads, with the reference's learning-rate policies (src/util.h:76-100).

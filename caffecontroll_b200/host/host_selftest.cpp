@@ -21,7 +21,7 @@ static void save(const std::string& path, const std::vector<float>& v) {
 }
 
 int main(int argc, char** argv) {
-  if (argc < 11) { std::cerr << "usage: host_selftest dir B D n o k s p g steps" << std::endl; return 2; }
+  if (argc < 11) { std::cerr << "usage: host_selftest dir B D n o k s p g steps [fc]" << std::endl; return 2; }
   const std::string dir = argv[1];
   const int B = atoi(argv[2]), D = atoi(argv[3]), n = atoi(argv[4]), o = atoi(argv[5]), k = atoi(argv[6]), s = atoi(argv[7]),
             p = atoi(argv[8]), g = atoi(argv[9]), steps = atoi(argv[10]);
@@ -55,6 +55,19 @@ int main(int argc, char** argv) {
   std::vector<float> hw(hdw.size()), hb(o);
   conv.get_model_cube()->copy_to_host(hw.data()); conv.get_bias_cube()->copy_to_host(hb.data());
   save(dir + "/Wnew.bin", hw); save(dir + "/bnew.bin", hb);
+  if (argc > 11 && std::string(argv[11]) == "fc") {
+    // kernel == input: the same layer through FullyConnectedBridge (a 1x1 convolution over the flattened input)
+    FullyConnectedBridge fc(&in, &out, o, true, &driver);
+    ConvolutionBridge& c = fc.as_convolution();
+    c.get_model_cube()->copy_from_host(load(dir + "/W.bin", c.get_model_cube()->n_elements).data());
+    c.get_bias_cube()->copy_from_host(load(dir + "/b.bin", o).data());
+    fc.forward();
+    fc.backward();
+    driver.device_sync();
+    y.copy_to_host(hy.data()); dx.copy_to_host(hdx.data());
+    c.get_model_grad_cube()->copy_to_host(hdw.data()); c.get_bias_grad_cube()->copy_to_host(hdb.data());
+    save(dir + "/Y_fc.bin", hy); save(dir + "/dX_fc.bin", hdx); save(dir + "/dW_fc.bin", hdw); save(dir + "/db_fc.bin", hdb);
+  }
   std::cout << "host_selftest ok" << std::endl;
   return 0;
 }

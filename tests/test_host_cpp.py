@@ -56,3 +56,23 @@ def test_host_mirror_matches_oracle(port, tmp_path):
         port.sgd_update(bc, db, hb, float(np.float32(lr * 2.0)), 0.9, 0.0)
     assert maxnorm_rel(rd("Wnew", W.shape), Wc) <= TOL
     assert maxnorm_rel(rd("bnew", (o,)), bc) <= TOL
+
+
+@pytest.mark.gpu
+def test_host_fully_connected_mirror_matches_oracle(port, tmp_path):
+    """kernel == input, so the layer is an inner product: the C++ FullyConnectedBridge mirror must reproduce what the
+    ConvolutionBridge mirror (and the oracle) give for it."""
+    exe = _build()
+    B, D, n, o, k, s, p, g = 6, 5, 4, 12, 4, 1, 0, 1
+    X, W, b, dY = make_inputs(56, B, D, n, o, k, s, p, g)
+    for name, arr in (("X", X), ("W", W), ("b", b), ("dY", dY)):
+        arr.tofile(os.path.join(str(tmp_path), name + ".bin"))
+    subprocess.run([exe, str(tmp_path)] + [str(v) for v in (B, D, n, o, k, s, p, g, 0)] + ["fc"], check=True)
+    rd = lambda name, shape: np.fromfile(os.path.join(str(tmp_path), name + ".bin"), np.float32).reshape(shape)
+    Yr = port.conv_forward(X, W, b, k, s, p, g)
+    dXr, dWr, dbr = port.conv_backward(X, W, dY, k, s, p, g)
+    for tag in ("", "_fc"):
+        assert_close(rd("Y" + tag, (B, o, 1, 1)), Yr, "Y" + tag)
+        assert_close(rd("dX" + tag, X.shape), dXr, "dX" + tag)
+        assert_close(rd("dW" + tag, W.shape), dWr, "dW" + tag)
+        assert_close(rd("db" + tag, (o,)), dbr, "db" + tag)
