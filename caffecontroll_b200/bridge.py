@@ -185,6 +185,7 @@ class ConvolutionBridge:
         """Fold the ReLU and max-pooling bridges that follow this layer into backward(): the output gradient is
         rebuilt from the pooled tensor's gradient and the pooling indices (MaxPoolingBridge::backward then
         ReLUBridge::backward in the reference) instead of being read from p_output_layer.p_gradient_cube."""
+        capi.check(self.lib.cct_conv_plan_reserve_fusion(self.plan), "cct_conv_plan_reserve_fusion", self.ctx.h)
         self.pool_fusion = (pooled_gradient_cube, max_index_cube, kernel_size, stride)
 
     def backward(self):

@@ -20,7 +20,8 @@ EXPORTS = [
     "cct_device_count", "cct_malloc", "cct_free", "cct_malloc_host", "cct_free_host", "cct_memcpy_h2d",
     "cct_memcpy_d2h", "cct_memcpy_d2d", "cct_memset", "cct_fill_f32", "cct_conv_plan_create",
     "cct_conv_plan_destroy", "cct_conv_out_size", "cct_conv_plan_algo", "cct_conv_plan_workspace_bytes",
-    "cct_conv_plan_enable_timing", "cct_conv_plan_last_timings", "cct_conv_forward", "cct_conv_backward", "cct_conv_backward_fused", "cct_conv_forward_host", "cct_conv_backward_host", "cct_conv_weight_grad_noalloc",
+    "cct_conv_plan_enable_timing", "cct_conv_plan_last_timings", "cct_conv_forward", "cct_conv_backward", "cct_conv_backward_fused",
+    "cct_conv_plan_reserve_fusion", "cct_selftest_bounded_wait", "cct_conv_forward_host", "cct_conv_backward_host", "cct_conv_weight_grad_noalloc",
     "cct_maxpool_forward", "cct_maxpool_backward", "cct_relu_forward", "cct_relu_backward",
     "cct_pool_relu_backward", "cct_sgd_step",
 ]
@@ -82,6 +83,8 @@ def load():
         "cct_conv_forward": [_vp, _vp, _vp, _vp, _vp, i],
         "cct_conv_backward": [_vp, _vp, _vp, _vp, _vp, _vp, _vp],
         "cct_conv_backward_fused": [_vp, _vp, _vp, _vp, C.POINTER(BwdFusion), _vp, _vp, _vp],
+        "cct_conv_plan_reserve_fusion": [_vp],
+        "cct_selftest_bounded_wait": [_vp, C.c_longlong],
         "cct_conv_forward_host": [_vp, _vp, _vp, _vp, _vp, i],
         "cct_conv_backward_host": [_vp, _vp, _vp, _vp, _vp, _vp, _vp],
         "cct_conv_weight_grad_noalloc": [_vp, C.POINTER(ConvDesc), _vp, _vp, _vp, _vp],

@@ -17,9 +17,10 @@ struct cct_conv_plan {
         *sdb = nullptr;
   size_t staging_bytes = 0;
   bool staged_forward = false;  // sX / sW hold what the last cct_conv_forward_host uploaded
-  float* mask_dY = nullptr;     // output gradient rebuilt from the pooled gradient (cct_conv_backward_fused), on first use
+  float* mask_dY = nullptr;     // output gradient rebuilt from the pooled gradient (cct_conv_plan_reserve_fusion)
+  bool staging_ready = false;   // every staging buffer, side stream and event below exists
   // Host-buffer calls move the batch in slices: slice c is uploaded (ev_in[c]), processed, downloaded (after ev_out[c]).
-  static constexpr int kSlices = 4;
+  static constexpr int kSlices = 8;
   cudaEvent_t ev_in[kSlices] = {}, ev_out[kSlices] = {}, ev_start = nullptr, ev_done = nullptr;
   PhaseTimer timer;
 };
@@ -45,26 +46,39 @@ int geom_from_desc(const cct_conv_desc* d, ConvGeom* G) {
   return CCT_OK;
 }
 
+// All or nothing: a failed allocation releases what this call allocated, so that a retry starts from scratch.
 int ensure_staging(cct_conv_plan* p) {
-  if (p->sX) return CCT_OK;
+  if (p->staging_ready) return CCT_OK;
   cct_ctx* ctx = p->ctx;
   const ConvGeom& G = p->G;
   const size_t nx = (size_t)G.B * G.D * G.n * G.n, ny = (size_t)G.B * G.o * G.m * G.m,
                nw = (size_t)G.o * G.Dg * G.k * G.k;
   float** slots[] = {&p->sX, &p->sW, &p->sb, &p->sY, &p->sdY, &p->sdX, &p->sdW, &p->sdb};
   const size_t counts[] = {nx, nw, (size_t)G.o, ny, ny, nx, nw, (size_t)G.o};
-  for (int i = 0; i < 8; ++i) {
-    CCT_CUDA(ctx, cudaMalloc((void**)slots[i], counts[i] * sizeof(float)));
-    p->staging_bytes += counts[i] * sizeof(float);
+  cudaError_t e = cudaSuccess;
+  size_t bytes = 0;
+  for (int i = 0; i < 8 && e == cudaSuccess; ++i) {
+    e = cudaMalloc((void**)slots[i], counts[i] * sizeof(float));
+    if (e == cudaSuccess) bytes += counts[i] * sizeof(float);
   }
-  if (!ctx->copy_in) CCT_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->copy_in, cudaStreamNonBlocking));
-  if (!ctx->copy_out) CCT_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->copy_out, cudaStreamNonBlocking));
-  for (int c = 0; c < cct_conv_plan::kSlices; ++c) {
-    CCT_CUDA(ctx, cudaEventCreateWithFlags(&p->ev_in[c], cudaEventDisableTiming));
-    CCT_CUDA(ctx, cudaEventCreateWithFlags(&p->ev_out[c], cudaEventDisableTiming));
+  if (e == cudaSuccess && !ctx->copy_in) e = cudaStreamCreateWithFlags(&ctx->copy_in, cudaStreamNonBlocking);
+  if (e == cudaSuccess && !ctx->copy_out) e = cudaStreamCreateWithFlags(&ctx->copy_out, cudaStreamNonBlocking);
+  for (int c = 0; c < cct_conv_plan::kSlices && e == cudaSuccess; ++c) {
+    if (!p->ev_in[c]) e = cudaEventCreateWithFlags(&p->ev_in[c], cudaEventDisableTiming);
+    if (e == cudaSuccess && !p->ev_out[c]) e = cudaEventCreateWithFlags(&p->ev_out[c], cudaEventDisableTiming);
   }
-  CCT_CUDA(ctx, cudaEventCreateWithFlags(&p->ev_start, cudaEventDisableTiming));
-  CCT_CUDA(ctx, cudaEventCreateWithFlags(&p->ev_done, cudaEventDisableTiming));
+  if (e == cudaSuccess && !p->ev_start) e = cudaEventCreateWithFlags(&p->ev_start, cudaEventDisableTiming);
+  if (e == cudaSuccess && !p->ev_done) e = cudaEventCreateWithFlags(&p->ev_done, cudaEventDisableTiming);
+  if (e != cudaSuccess) {
+    for (float** s : slots) {
+      if (*s) cudaFree(*s);
+      *s = nullptr;
+    }
+    ctx->last_error = std::string("staging for the host-buffer calls: ") + cudaGetErrorString(e);
+    return e == cudaErrorMemoryAllocation ? CCT_ERR_NOMEM : CCT_ERR_CUDA;
+  }
+  p->staging_bytes += bytes;
+  p->staging_ready = true;
   return CCT_OK;
 }
 
@@ -256,13 +270,13 @@ int cct_conv_plan_create(cct_ctx* ctx, const cct_conv_desc* desc, cct_conv_plan*
     ctx->last_error = "shape not supported by the tcgen05 path";
     return CCT_ERR_UNSUPPORTED;
   }
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
   cct_conv_plan* p = new (std::nothrow) cct_conv_plan();
   if (!p) return CCT_ERR_NOMEM;
   p->ctx = ctx;
   p->desc = *desc;
   p->G = G;
   p->algo = algo;
-  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
   if (algo == CCT_ALGO_UMMA_3XTF32) {
     const int rc2 = umma_plan_create(ctx, G, &p->umma);
     if (rc2 != CCT_OK) {
@@ -304,6 +318,19 @@ int cct_conv_plan_algo(const cct_conv_plan* plan, int* algo) {
 int cct_conv_plan_workspace_bytes(const cct_conv_plan* plan, size_t* bytes) {
   if (!plan || !bytes) return CCT_ERR_INVALID;
   *bytes = (plan->umma ? umma_plan_workspace_bytes(plan->umma) : 0) + plan->staging_bytes;
+  return CCT_OK;
+}
+
+int cct_conv_plan_reserve_fusion(cct_conv_plan* plan) {
+  if (!plan) return CCT_ERR_INVALID;
+  cct_ctx* ctx = plan->ctx;
+  const ConvGeom& G = plan->G;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (!plan->mask_dY) {
+    const size_t bytes = (size_t)G.B * G.o * G.m * G.m * sizeof(float);
+    CCT_CUDA(ctx, cudaMalloc((void**)&plan->mask_dY, bytes));
+    plan->staging_bytes += bytes;
+  }
   return CCT_OK;
 }
 
@@ -362,7 +389,10 @@ int cct_conv_backward_fused(cct_conv_plan* plan, const float* X, const float* W,
   if (f->dP) {
     // conv -> ReLU -> max-pool behind this layer: one pass builds the output gradient both kernels read.
     if (!f->A || !f->idx || f->pool_k <= 0 || f->pool_s <= 0 || f->pool_k > G.m) return CCT_ERR_INVALID;
-    if (!plan->mask_dY) CCT_CUDA(ctx, cudaMalloc((void**)&plan->mask_dY, (size_t)G.B * G.o * G.m * G.m * sizeof(float)));
+    if (!plan->mask_dY) {
+      ctx->last_error = "cct_conv_backward_fused with a pooled gradient needs cct_conv_plan_reserve_fusion(plan) first";
+      return CCT_ERR_INVALID;
+    }
     const int rc = cct_pool_relu_backward(ctx, f->A, f->idx, f->dP, plan->mask_dY, G.B * G.o, G.m, f->pool_k, f->pool_s);
     if (rc != CCT_OK) return rc;
     dY = plan->mask_dY;

@@ -33,19 +33,6 @@ namespace {
 constexpr int kTileM = 128;
 constexpr int kBlockK = 32;  // fp32 per k-block: one 128-byte swizzled row
 constexpr int kSmemLimit = 227 * 1024;
-#ifdef CCT_DBG
-#define DBG(P, bit) ((P).dbg & (bit))
-// Cycle accounting of debug builds: per role, cycles spent in each wait and in the work between waits.
-__device__ unsigned long long g_prof[64];
-#define PROF_DECL long long prof_t = clock64(); long long prof_acc[6] = {0, 0, 0, 0, 0, 0}
-#define PROF_LAP(i) do { const long long prof_n = clock64(); prof_acc[i] += prof_n - prof_t; prof_t = prof_n; } while (0)
-#define PROF_FLUSH(role, cond) do { if (cond) for (int prof_i = 0; prof_i < 6; ++prof_i) atomicAdd(&g_prof[(role) * 8 + prof_i], (unsigned long long)prof_acc[prof_i]); } while (0)
-#else
-#define DBG(P, bit) 0
-#define PROF_DECL
-#define PROF_LAP(i)
-#define PROF_FLUSH(role, cond)
-#endif
 constexpr int kMaxTapsPerAxis = 15;
 // Longest accumulation chain of a weight-gradient partial sum, in k-blocks of 32 pixels.  Measured against a
 // double-accumulating CPU reference, AlexNet conv1's dW was off by 7.7e-5 (max-norm relative) with chains of 327
@@ -162,8 +149,10 @@ __device__ __forceinline__ uint32_t mbar_try_wait_parked(uint32_t bar, uint32_t 
 // Bounded wait.  Returns false (and records `code` in the status word) after about 0.2 s without completion.
 // PARK = true: the many warps that mostly wait (producers, epilogue) park in hardware between polls; the MMA and TMA
 // threads, whose wake-up latency is on the critical path, poll.
+constexpr long long kWaitLimitCycles = 400000000LL;
 template <bool PARK = true>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, bool& failed, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, bool& failed, int* status, int code,
+                                          long long limit_cycles = kWaitLimitCycles) {
   if (failed) return false;
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
@@ -171,7 +160,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, bool& f
 #pragma unroll 1
     for (int i = 0; i < 256; ++i)
       if (PARK ? mbar_try_wait_parked(bar, parity, 20000u) : mbar_try_wait(bar, parity)) return true;
-    if (clock64() - t0 > 400000000LL) break;
+    if (clock64() - t0 > limit_cycles) break;
   }
   failed = true;
   *reinterpret_cast<volatile int*>(status) = code;
@@ -296,7 +285,6 @@ struct GatherParams {
   int wg_k, wg_kreal;         // kernel size, real rows of the lowered matrix
   int taps_smem;              // entries of `taps` staged in shared memory (0 in weight-gradient mode)
   int* status;
-  int dbg;
 };
 
 // Which tile a persistent CTA works on: channel tile, pixel tile (or M-tile), first k-block, split.
@@ -370,9 +358,8 @@ __host__ __device__ inline GatherSmem gather_smem(int n_pad, int k_pad, int b_st
 template <int SETS>
 __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
     gather_conv_kernel(const __grid_constant__ GatherParams P, const __grid_constant__ CUtensorMap w_map) {
-  constexpr int kProducerWarps = 4 * SETS, kMmaWarp = kProducerWarps, kTmaWarp = kMmaWarp + 1, kEpiWarp0 = kTmaWarp + 1;
+  constexpr int kProducerWarps = 4 * SETS, kMmaWarp = kProducerWarps, kTmaWarp = kMmaWarp + 1;
   constexpr int kGatherThreads = gather_threads(SETS);
-  (void)kEpiWarp0;  // named only by the cycle accounting of debug builds
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -480,7 +467,7 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
 #pragma unroll
         for (int e = 0; e < kBlockK; ++e) {
           const uint2 ent = slot[e];
-          v[e] = ldg_if_clear(in_px + (int)ent.x, DBG(P, 1) ? 0xffffffffu : ent.y, mask);
+          v[e] = ldg_if_clear(in_px + (int)ent.x, ent.y, mask);
         }
         return;
       }
@@ -488,7 +475,7 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
 #pragma unroll
       for (int e = 0; e < kBlockK; ++e) {
         const MaskTap tap = tp[e];
-        v[e] = ldg_if_bits(in_px + tap.off, DBG(P, 1) ? 0u : mask, tap.bits);
+        v[e] = ldg_if_bits(in_px + tap.off, mask, tap.bits);
       }
     };
     int tile_local = 0, kb = group;
@@ -498,7 +485,6 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
       prefetch_entries(kb);
       gather(kb);
     }
-    PROF_DECL;
     for (int it = group; it < my_stages; it += SETS) {
       const int sa = it & (P.a_stages - 1);  // a_stages is 2 or 4
       const uint32_t st_addr = lane_addr + (uint32_t)(sa * 64);
@@ -512,12 +498,10 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
         if (tile_local != before) setup_tile(tile_local);
         prefetch_entries(kb);
       }
-      PROF_LAP(0);
       // The A slot was last read by the MMAs of k-block it - a_stages.
       const int prev = it - P.a_stages;
       if (prev >= 0) mbar_wait(done_bar + 8u * (prev & 3), (uint32_t)(prev >> 2) & 1u, failed, P.status, 0x10);
       tc_fence_after();
-      PROF_LAP(1);
 #pragma unroll
       for (int c = 0; c < kBlockK / 8; ++c) {
         uint32_t hi[8], lo[8];
@@ -526,7 +510,6 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
         tmem_st8(st_addr + (uint32_t)(c * 8), hi);
         tmem_st8(st_addr + 32u + (uint32_t)(c * 8), lo);
       }
-      PROF_LAP(2);
       // With two stages the hand-over of a filled stage is on the critical path: arrive first, then fetch.
       if (P.a_stages == 2) {
         tmem_wait_st();
@@ -534,72 +517,57 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
         __syncwarp();
         if (lane == 0) mbar_arrive(ready_bar + 8u * (it & 3));
       }
-      PROF_LAP(4);
       if (has_next) gather(kb);  // loads in flight across the next wait
-      PROF_LAP(3);
       if (P.a_stages != 2) {
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(ready_bar + 8u * (it & 3));  // one arrival per warp: same-address arrivals serialise
       }
-      PROF_LAP(4);
     }
-    PROF_FLUSH(0, warp == 0 && lane == 0 && blockIdx.x == 0);
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issue
     if (lane == 0) {
       const uint32_t idesc = make_idesc(P.acc_cols);
       int tile_iter = 0;
       Ring ra, rb, rbar;  // A slot, weight slot, barrier pair of the current k-block
-      PROF_DECL;
       for (int t = blockIdx.x; t < P.total_tiles; t += gridDim.x, ++tile_iter) {
         const int buf = tile_iter & (P.acc_bufs - 1), ause = tile_iter >> (P.acc_bufs - 1);  // acc_bufs is 1 or 2
-        PROF_LAP(0);
         if (ause > 0) mbar_wait<false>(acc_empty + 8u * buf, (uint32_t)(ause - 1) & 1u, failed, P.status, 0x20);
         tc_fence_after();
-        PROF_LAP(1);
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * P.acc_cols);
         for (int kb = 0; kb < kblocks; ++kb) {
-          PROF_LAP(0);
           mbar_wait<false>(ready_bar + 8u * rbar.idx, (uint32_t)rbar.use & 1u, failed, P.status, 0x40);
           tc_fence_after();
-          PROF_LAP(2);
           const uint32_t b_hi = base + (uint32_t)rb.idx * L.b_stage_bytes, b_lo = b_hi + (uint32_t)P.n_pad * 128u;
           const uint64_t dbh = make_desc(b_hi), dbl = make_desc(b_lo);
           const uint32_t a_hi = tmem_base + a_col0 + (uint32_t)(ra.idx * 64), a_lo = a_hi + 32u;
-          if (!DBG(P, 4)) {
-            if (P.dual) {
-              // The lo tile sits right behind the hi tile: one descriptor spans both, so a single MMA of width
-              // 2*n_pad produces A*B_hi in the first n_pad columns and A*B_lo in the next (issuing an MMA costs
-              // this thread ~75 cycles however narrow it is, so two wide ones beat three narrow ones).
+          if (P.dual) {
+            // The lo tile sits right behind the hi tile: one descriptor spans both, so a single MMA of width
+            // 2*n_pad produces A*B_hi in the first n_pad columns and A*B_lo in the next (issuing an MMA costs
+            // this thread ~75 cycles however narrow it is, so two wide ones beat three narrow ones).
 #pragma unroll
-              for (int j = 0; j < kBlockK / 8; ++j) {
-                const uint64_t adv = (uint64_t)(j * 2);
-                umma_tf32_ts(d_tmem, a_lo + (uint32_t)(j * 8), dbh + adv, idesc, (kb == 0 && j == 0) ? 0u : 1u);
-                umma_tf32_ts(d_tmem, a_hi + (uint32_t)(j * 8), dbh + adv, idesc, 1u);
-              }
-            } else {
+            for (int j = 0; j < kBlockK / 8; ++j) {
+              const uint64_t adv = (uint64_t)(j * 2);
+              umma_tf32_ts(d_tmem, a_lo + (uint32_t)(j * 8), dbh + adv, idesc, (kb == 0 && j == 0) ? 0u : 1u);
+              umma_tf32_ts(d_tmem, a_hi + (uint32_t)(j * 8), dbh + adv, idesc, 1u);
+            }
+          } else {
 #pragma unroll
-              for (int j = 0; j < kBlockK / 8; ++j) {
-                const uint64_t adv = (uint64_t)(j * 2);
-                umma_tf32_ts(d_tmem, a_lo + (uint32_t)(j * 8), dbh + adv, idesc, (kb == 0 && j == 0) ? 0u : 1u);
-                umma_tf32_ts(d_tmem, a_hi + (uint32_t)(j * 8), dbl + adv, idesc, 1u);
-                umma_tf32_ts(d_tmem, a_hi + (uint32_t)(j * 8), dbh + adv, idesc, 1u);
-              }
+            for (int j = 0; j < kBlockK / 8; ++j) {
+              const uint64_t adv = (uint64_t)(j * 2);
+              umma_tf32_ts(d_tmem, a_lo + (uint32_t)(j * 8), dbh + adv, idesc, (kb == 0 && j == 0) ? 0u : 1u);
+              umma_tf32_ts(d_tmem, a_hi + (uint32_t)(j * 8), dbl + adv, idesc, 1u);
+              umma_tf32_ts(d_tmem, a_hi + (uint32_t)(j * 8), dbh + adv, idesc, 1u);
             }
           }
-          PROF_LAP(4);
           umma_commit(done_bar + 8u * rbar.idx);  // frees the A slot for the producers and the weight slot for the TMA thread
           ra.advance(P.a_stages);
           rb.advance(P.b_stages);
           rbar.advance(4);
-          PROF_LAP(5);
         }
         umma_commit(acc_full + 8u * buf);
       }
-      PROF_LAP(0);
-      PROF_FLUSH(1, blockIdx.x == 0);
     }
   } else if (warp == kTmaWarp) {
     // ------------------------------------------------------------------ weight tiles by TMA
@@ -627,7 +595,6 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     int tile_iter = 0;
-    PROF_DECL;
     for (int t = blockIdx.x; t < P.total_tiles; t += gridDim.x, ++tile_iter) {
       const TileId id = decode_tile(P, t, kblocks);
       const int vg = id.vg, ptile = id.ptile;
@@ -635,10 +602,8 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
       const int buf = tile_iter & (P.acc_bufs - 1), ause = tile_iter >> (P.acc_bufs - 1);
       if (P.wg) {
         // The accumulator is a 128-row slice of this split's partial sums: row-contiguous stores.
-        PROF_LAP(0);
         mbar_wait(acc_full + 8u * buf, (uint32_t)ause & 1u, failed, P.status, 0x200);
         tc_fence_after();
-        PROF_LAP(1);
         const uint32_t acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P.acc_cols);
         float* op = P.out + ((size_t)(id.split * P.wg_vgroups + vg) * P.wg_rows_pad + (size_t)ptile * kTileM + row) * P.n_pad;
         for (int c = 0; c < P.n_pad / 16; ++c) {
@@ -656,11 +621,9 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
             for (int j = 0; j < 4; ++j) o4[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
           }
         }
-        PROF_LAP(4);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(acc_empty + 8u * buf);
-        PROF_LAP(2);
         continue;
       }
       const int pix = ptile * kTileM + row;
@@ -677,10 +640,8 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
       float* op = P.out + (long long)b * P.out_batch_stride + (long long)ch0 * P.out_plane +
                   (long long)oy0 * P.out_pitch + ox0;
       const float* bias = s_bias + (P.n_bias ? ch0 : 0);  // zero padded: readable for every column of the tile
-      PROF_LAP(0);
       mbar_wait(acc_full + 8u * buf, (uint32_t)ause & 1u, failed, P.status, 0x200);
       tc_fence_after();
-      PROF_LAP(1);
       const uint32_t live = (pix < P.n_pix && !failed) ? 1u : 0u;
       const uint32_t unchecked = P.check_out ? 0u : 1u;
       const uint32_t acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * P.acc_cols);
@@ -694,41 +655,35 @@ __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
 #pragma unroll
           for (int j = 0; j < 16; ++j) v[j] += w[j];
         }
-        PROF_LAP(3);
         // Straight-line code: table and bias reads first, then predicated st.global (a generic store could alias
         // shared memory and would pin every following table read behind it; a branch per column costs more than
         // the store it guards).
-        if (!DBG(P, 128)) {
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            ColEnt ce[8];
-            float bv[8];
+        for (int h = 0; h < 2; ++h) {
+          ColEnt ce[8];
+          float bv[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const int col = c * 16 + h * 8 + j;
-              ce[j] = s_cols[col];
-              bv[j] = bias[col];
-            }
+          for (int j = 0; j < 8; ++j) {
+            const int col = c * 16 + h * 8 + j;
+            ce[j] = s_cols[col];
+            bv[j] = bias[col];
+          }
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const int col = c * 16 + h * 8 + j;
-              const uint32_t in_y = (unsigned)(oy0 + ce[j].cy) < (unsigned)P.out_lim ? 1u : 0u;
-              const uint32_t in_x = (unsigned)(ox0 + ce[j].cx) < (unsigned)P.out_lim ? 1u : 0u;
-              const uint32_t ok = live & (col < P.n ? 1u : 0u) & (unchecked | (in_y & in_x)) & (DBG(P, 32) ? 0u : 1u);
-              float y = v[h * 8 + j] + bv[j];
-              y = P.relu ? fmaxf(y, 0.f) : y;
-              stg_if(op + ce[j].off, y, ok);
-            }
+          for (int j = 0; j < 8; ++j) {
+            const int col = c * 16 + h * 8 + j;
+            const uint32_t in_y = (unsigned)(oy0 + ce[j].cy) < (unsigned)P.out_lim ? 1u : 0u;
+            const uint32_t in_x = (unsigned)(ox0 + ce[j].cx) < (unsigned)P.out_lim ? 1u : 0u;
+            const uint32_t ok = live & (col < P.n ? 1u : 0u) & (unchecked | (in_y & in_x));
+            float y = v[h * 8 + j] + bv[j];
+            y = P.relu ? fmaxf(y, 0.f) : y;
+            stg_if(op + ce[j].off, y, ok);
           }
         }
-        PROF_LAP(4);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty + 8u * buf);
-      PROF_LAP(2);
     }
-    PROF_FLUSH(2, warp == kEpiWarp0 && lane == 0 && blockIdx.x == 0);
   }
   tc_fence_before();
   __syncthreads();
@@ -773,9 +728,9 @@ struct WgradParams {
   int n_real, n_pad;
   int m_tiles, subs, stages;
   int ones_row;           // index of the all-ones row among the lowered-matrix rows
-  int kblocks_total, kblocks_per_split;
+  int kblocks_total, kblocks_per_split;  // end of this launch's k-block range, k-blocks per split
+  int kb_first;                          // first k-block of this launch (a later round of a launch sequence starts further in)
   int* status;
-  int dbg;
 };
 
 struct WgSmem {
@@ -844,7 +799,7 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
   tc_fence_after();
   uint32_t tmem_base;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
-  const int kb_begin = split * P.kblocks_per_split;
+  const int kb_begin = P.kb_first + split * P.kblocks_per_split;
   const int kb_end = min(P.kblocks_total, kb_begin + P.kblocks_per_split);
   const int kblocks = kb_end - kb_begin;  // >= 1 by construction of the grid
   bool failed = false;
@@ -887,7 +842,7 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
 #pragma unroll
         for (int i = 0; i < kARows; ++i) {
           const MaskTap tap = my_taps[kWgTapWarps * i];
-          va[i] = ldg_if_bits(xsrc + tap.off, DBG(P, 1) ? 0u : mask, tap.bits);
+          va[i] = ldg_if_bits(xsrc + tap.off, mask, tap.bits);
         }
         if (ones_i >= 0) {
 #pragma unroll
@@ -895,14 +850,11 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
         }
       };
       load_rows();
-      PROF_DECL;
       Ring ring;
       for (int kbl = 0; kbl < kblocks; ++kbl, ring.advance(P.stages)) {
         const int s = ring.idx, use = ring.use;
         uint8_t* st = lane_ptr + (size_t)s * L.stage_bytes;
-        PROF_LAP(0);
         if (use > 0) mbar_wait(empty + 8u * s, (uint32_t)(use - 1) & 1u, failed, P.status, 0x10);
-        PROF_LAP(1);
 #pragma unroll
         for (int i = 0; i < kARows; ++i) {  // tile i/8 (hi then lo), row warp + 16*(i%8)
           uint32_t h, l;
@@ -911,18 +863,14 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
           *reinterpret_cast<uint32_t*>(dst) = h;
           *reinterpret_cast<uint32_t*>(dst + kATile) = l;
         }
-        PROF_LAP(2);
         if (kbl + 1 < kblocks) {  // the next k-block's loads go in flight before the barrier work
           next_pixel();
           load_rows();
         }
-        PROF_LAP(3);
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(full + 8u * s);  // one arrival per warp: same-address arrivals serialise
-        PROF_LAP(4);
       }
-      PROF_FLUSH(4, warp == 0 && lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
     } else {
       // ---- dY rows: channel w8 + 8*i of the tile (hi then lo), behind the SUBS tap tiles of the stage
       const int w8 = warp - kWgTapWarps;
@@ -936,7 +884,7 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
         const bool ok = pix < P.n_pix;
         const float* dsrc = dyg + (long long)pb * P.dy_batch_stride + pr * P.m + pc;
 #pragma unroll
-        for (int i = 0; i < kDyRows; ++i) vb[i] = ldg_if(dsrc + i * dy_step, (ok && i < b_live && !DBG(P, 2)) ? 1u : 0u);
+        for (int i = 0; i < kDyRows; ++i) vb[i] = ldg_if(dsrc + i * dy_step, (ok && i < b_live) ? 1u : 0u);
       };
       load_rows();
       Ring ring;
@@ -991,41 +939,34 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
     // ------------------------------------------------------------------ MMA issue
     if (lane == 0) {
       const uint32_t idesc = make_idesc(kAccCols);
-      PROF_DECL;
       Ring ring;
       for (int kbl = 0; kbl < kblocks; ++kbl, ring.advance(P.stages)) {
         const int s = ring.idx;
-        PROF_LAP(0);
         mbar_wait(full + 8u * s, (uint32_t)ring.use & 1u, failed, P.status, 0x40);  // parked: this thread mostly waits for the producers
         tc_fence_after();
-        PROF_LAP(1);
         const uint32_t st = base + (uint32_t)s * L.stage_bytes;
         const uint32_t b_hi = st + SUBS * 2u * kATile, b_lo = b_hi + kBTile;
         const uint64_t dbh = make_desc(b_hi), dbl = make_desc(b_lo);
-        if (!DBG(P, 4)) {
-          for (int u = 0; u < subs; ++u) {
-            const uint32_t d_tmem = tmem_base + (uint32_t)(u * kAccCols);
-            const uint32_t a_hi = st + (uint32_t)u * 2u * kATile;
-            const uint64_t dah = make_desc(a_hi), dal = make_desc(a_hi + kATile);
+        for (int u = 0; u < subs; ++u) {
+          const uint32_t d_tmem = tmem_base + (uint32_t)(u * kAccCols);
+          const uint32_t a_hi = st + (uint32_t)u * 2u * kATile;
+          const uint64_t dah = make_desc(a_hi), dal = make_desc(a_hi + kATile);
 #pragma unroll
-            for (int j = 0; j < kBlockK / 8; ++j) {
-              const uint64_t adv = (uint64_t)(j * 2);
-              if (kDual) {
-                umma_tf32_ss(d_tmem, dal + adv, dbh + adv, idesc, (kbl == 0 && j == 0) ? 0u : 1u);
-                umma_tf32_ss(d_tmem, dah + adv, dbh + adv, idesc, 1u);
-              } else {
-                umma_tf32_ss(d_tmem, dal + adv, dbh + adv, idesc, (kbl == 0 && j == 0) ? 0u : 1u);
-                umma_tf32_ss(d_tmem, dah + adv, dbl + adv, idesc, 1u);
-                umma_tf32_ss(d_tmem, dah + adv, dbh + adv, idesc, 1u);
-              }
+          for (int j = 0; j < kBlockK / 8; ++j) {
+            const uint64_t adv = (uint64_t)(j * 2);
+            if (kDual) {
+              umma_tf32_ss(d_tmem, dal + adv, dbh + adv, idesc, (kbl == 0 && j == 0) ? 0u : 1u);
+              umma_tf32_ss(d_tmem, dah + adv, dbh + adv, idesc, 1u);
+            } else {
+              umma_tf32_ss(d_tmem, dal + adv, dbh + adv, idesc, (kbl == 0 && j == 0) ? 0u : 1u);
+              umma_tf32_ss(d_tmem, dah + adv, dbl + adv, idesc, 1u);
+              umma_tf32_ss(d_tmem, dah + adv, dbh + adv, idesc, 1u);
             }
           }
         }
         umma_commit(empty + 8u * s);
       }
       umma_commit(acc_full);
-      PROF_LAP(0);
-      PROF_FLUSH(5, blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
     }
   }
   tc_fence_before();
@@ -1058,7 +999,7 @@ WgradKernel wgrad_pick(int subs, int n_pad) {
 __global__ void __launch_bounds__(256) wgrad_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dW,
                                                            float* __restrict__ db, int splits, int vgroups,
                                                            int tiles_per_group, int rows_pad, int n_real, int n_pad,
-                                                           int k_real, int og) {
+                                                           int k_real, int og, int accumulate) {
   __shared__ float tile[32][33];
   const int vg = blockIdx.z;
   const int kk0 = blockIdx.x * 32, j0 = blockIdx.y * 32;
@@ -1083,10 +1024,8 @@ __global__ void __launch_bounds__(256) wgrad_reduce_kernel(const float* __restri
     const int j = j0 + ty + 8 * r, kk = kk0 + tx;
     if (j < n_real && kk <= last) {
       const float v = tile[tx][ty + 8 * r];
-      if (kk < k_real)
-        dW[(size_t)(ch0 + j) * k_real + kk] = v;
-      else
-        db[ch0 + j] = v;
+      float* dst = kk < k_real ? dW + (size_t)(ch0 + j) * k_real + kk : db + ch0 + j;
+      *dst = accumulate ? *dst + v : v;  // accumulate: a later round of splits adds to what the earlier rounds left
     }
   }
 }
@@ -1097,7 +1036,7 @@ __global__ void __launch_bounds__(256) wgrad_reduce_kernel(const float* __restri
 __global__ void __launch_bounds__(256) wgrad_reduce_rows_kernel(const float* __restrict__ partial, float* __restrict__ dW,
                                                                 float* __restrict__ db, int splits, int vgroups,
                                                                 int tiles_per_group, int rows_pad, int n_real,
-                                                                int n_pad, int k_real, int og) {
+                                                                int n_pad, int k_real, int og, int accumulate) {
   __shared__ float part[8][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int rows = vgroups * (k_real + 1);
@@ -1121,10 +1060,8 @@ __global__ void __launch_bounds__(256) wgrad_reduce_rows_kernel(const float* __r
         float t = part[0][tx];
 #pragma unroll
         for (int y = 1; y < 8; ++y) t += part[y][tx];
-        if (kk < k_real)
-          dW[(size_t)(ch0 + j) * k_real + kk] = t;
-        else
-          db[ch0 + j] = t;
+        float* dst = kk < k_real ? dW + (size_t)(ch0 + j) * k_real + kk : db + ch0 + j;
+        *dst = accumulate ? *dst + t : t;
       }
     }
   }
@@ -1237,16 +1174,6 @@ __global__ void pack_dgrad_kernel(const float* __restrict__ W, float* __restrict
   }
 }
 
-// Measurement knobs of debug builds (-DCCT_DBG): a bit mask from the environment that removes one pipeline part.
-int dbg_knobs() {
-#ifdef CCT_DBG
-  const char* e = getenv("CCT_DBG_KNOBS");
-  return e ? atoi(e) : 0;
-#else
-  return 0;
-#endif
-}
-
 int round_up(int v, int a) { return (v + a - 1) / a * a; }
 
 // Smallest number of equal channel tiles such that a tile spans at most `limit` accumulator columns.
@@ -1343,35 +1270,20 @@ int set_smem(cct_ctx* ctx, K kernel, size_t bytes) {
 
 // Split reduction: tiles when they fill the machine, rows otherwise (both add in split order).
 void launch_wgrad_reduce(cct_ctx* ctx, const float* partial, float* dW, float* db, int splits, int vgroups,
-                         int tiles_per_group, int rows_pad, int n_real, int n_pad, int k_real, int og) {
+                         int tiles_per_group, int rows_pad, int n_real, int n_pad, int k_real, int og,
+                         int accumulate = 0) {
   const dim3 tiles((k_real + 1 + 31) / 32, (n_real + 31) / 32, vgroups);
   if ((int)(tiles.x * tiles.y * tiles.z) >= ctx->sm_count)
     wgrad_reduce_kernel<<<tiles, 256, 0, ctx->stream>>>(partial, dW, db, splits, vgroups, tiles_per_group, rows_pad,
-                                                       n_real, n_pad, k_real, og);
+                                                       n_real, n_pad, k_real, og, accumulate);
   else
     wgrad_reduce_rows_kernel<<<std::max(1, std::min(vgroups * (k_real + 1), ctx->sm_count * 8)), 256, 0, ctx->stream>>>(
-        partial, dW, db, splits, vgroups, tiles_per_group, rows_pad, n_real, n_pad, k_real, og);
+        partial, dW, db, splits, vgroups, tiles_per_group, rows_pad, n_real, n_pad, k_real, og, accumulate);
 }
 
 int pack_grid(cct_ctx* ctx, size_t total) {
   size_t b = (total + 255) / 256;
   return (int)std::min<size_t>(std::max<size_t>(b, 1), (size_t)ctx->sm_count * 8);
-}
-
-bool wgrad_gather_allowed() {
-#ifdef CCT_DBG
-  const char* e = getenv("CCT_DBG_OLD_WGRAD");
-  if (e && atoi(e)) return false;
-#endif
-  return true;
-}
-
-bool two_ctas_allowed() {
-#ifdef CCT_DBG
-  const char* e = getenv("CCT_DBG_ONE_CTA");
-  if (e && atoi(e)) return false;
-#endif
-  return true;
 }
 
 // Tensor-memory and shared-memory budget of a gather problem, packed-weight buffer and its tensor map.
@@ -1396,7 +1308,7 @@ int finish_problem(cct_ctx* ctx, UmmaPlan* p, GatherProblem& gp, int vgroups, in
   // Accumulators of at most 128 columns leave room for two CTAs per SM: 256 columns each (accumulator + two A
   // slots) and half the shared memory (the SM holds 228 KB, 1 KB of it reserved per resident CTA).
   const int b_two = slots_that_fit(113 * 1024);
-  if (gp.acc_cols <= 128 && b_two >= 3 && two_ctas_allowed()) {
+  if (gp.acc_cols <= 128 && b_two >= 3) {
     gp.sets = 2; gp.tmem_cols = 256; gp.acc_bufs = 1; gp.a_stages = 2; gp.b_stages = b_two;
   }
   gp.smem = gather_smem(gp.n_pad, taps_smem, gp.b_stages, n_bias, gp.taps_smem == 0 ? 4 * gp.sets : 0).total + 1024;
@@ -1534,7 +1446,7 @@ int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out) {
   // It needs one extra pass over dY (split into hi / lo, 12 bytes moved per element), which pays when every dY
   // element takes part in many multiply-adds: measured faster from CaffeNet conv2 (1200 lowered rows) upwards,
   // slower for AlexNet conv1 (363 rows), so short lowered matrices keep the shared-memory kernel above.
-  if (rc == CCT_OK && wgrad_gather_allowed() && p->fwd.k_real >= 512) {
+  if (rc == CCT_OK && p->fwd.k_real >= 512) {
     const GatherProblem& f = p->fwd;
     GatherProblem& w = p->wgp;
     const int n_pix = G.B * G.m * G.m;
@@ -1571,10 +1483,14 @@ int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out) {
     }
     rc = upload(ctx, p, &p->wg_pix, t);
     if (rc == CCT_OK) rc = finish_problem(ctx, p, w, vgroups, 0);
-    if (rc == CCT_OK) CCT_CUDA(ctx, cudaMemsetAsync(w.w, 0, 2 * w.w_half * sizeof(float), ctx->stream));  // padded channel rows stay zero
+    if (rc == CCT_OK && cudaMemsetAsync(w.w, 0, 2 * w.w_half * sizeof(float), ctx->stream) != cudaSuccess) {  // padded channel rows stay zero
+      ctx->last_error = "cudaMemsetAsync of the pre-split dY buffer failed";
+      rc = CCT_ERR_CUDA;
+    }
     if (rc == CCT_OK && G.bias) rc = dev_alloc(ctx, p, &p->wg_plane_sums, (size_t)G.B * G.o);
     if (rc == CCT_OK) {
       cudaFree(p->w_partial);  // sized for the other kernel's split count
+      p->bytes -= (size_t)p->w_splits * vgroups * p->w_mtiles * kTileM * f.n_pad * sizeof(float);
       p->w_partial = nullptr;
       rc = dev_alloc(ctx, p, &p->w_partial, (size_t)p->wg_splits * vgroups * p->wg_mtiles * kTileM * f.n_pad);
     }
@@ -1616,7 +1532,6 @@ void fill_common(GatherParams& P, const GatherProblem& gp, cct_ctx* ctx, int vgr
   P.n_bias = P.bias ? n_bias : 0;
   P.lo_row_offset = vgroups * gp.n_pad;
   P.status = ctx->status_dev;
-  P.dbg = dbg_knobs();
 }
 
 // Persistent grid: one CTA per SM (4 producer sets) or two (2 sets).
@@ -1723,7 +1638,6 @@ int umma_conv_wgrad(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* dY, 
     P.ones_row = f.k_real;
     P.kblocks_total = p->w_kblocks_total; P.kblocks_per_split = p->w_kblocks_per_split;
     P.status = ctx->status_dev;
-    P.dbg = dbg_knobs();
     const int vgroups = G.g * f.tiles;
     dim3 grid(p->w_mgroups, p->w_splits, vgroups);
     t->begin(1, ctx->stream);
@@ -1835,7 +1749,7 @@ extern "C" int cct_conv_weight_grad_noalloc(cct_ctx* ctx, const cct_conv_desc* d
   }
   unsigned char* scratch = static_cast<unsigned char*>(g_noalloc_dev_ptr[ctx->device]);
 
-  // Same tiling rules as the plan-based path, with the split count additionally capped by the scratch size.
+  // Same tiling rules as the plan-based path.
   const int tiles = channel_tiles(G.og, 1);
   const int n_real = G.og / tiles, n_pad = round_up(n_real, 16);
   const int k_real = G.Dg * G.k * G.k;
@@ -1862,11 +1776,16 @@ extern "C" int cct_conv_weight_grad_noalloc(cct_ctx* ctx, const cct_conv_desc* d
   }
   const int n_pix = G.B * G.m * G.m;
   const int kblocks_total = (n_pix + kBlockK - 1) / kBlockK;
-  int splits = std::max(1, ctx->sm_count / (mgroups * vgroups));
-  splits = std::min(splits, std::max(1, kblocks_total / 8));
-  splits = std::min<size_t>(splits, (kNoAllocScratchBytes - taps_bytes) / split_bytes);
-  const int kblocks_per_split = (kblocks_total + splits - 1) / splits;
-  splits = (kblocks_total + kblocks_per_split - 1) / kblocks_per_split;
+  // Splits: one wave of CTAs, and - as in the plan-based path - enough of them that no partial sum's accumulation
+  // chain exceeds kMaxChainKblocks (the tensor core's fp32 accumulate truncates; the split reduction rounds).  When
+  // the array cannot hold that many partial-sum slices, the pixel range is covered in several rounds of (weight
+  // gradient kernel, reduction), each round reusing the slices and the later reductions adding to dW / db.
+  int want = std::max(1, ctx->sm_count / (mgroups * vgroups));
+  want = std::max(want, (kblocks_total + kMaxChainKblocks - 1) / kMaxChainKblocks);
+  want = std::min(want, std::max(1, kblocks_total / 8));  // at least 8 k-blocks per CTA (kMaxChainKblocks > 8)
+  const int kblocks_per_split = (kblocks_total + want - 1) / want;
+  const int total_splits = (kblocks_total + kblocks_per_split - 1) / kblocks_per_split;
+  const int slots = (int)std::min<size_t>((kNoAllocScratchBytes - taps_bytes) / split_bytes, (size_t)total_splits);
 
   MaskTap* taps = reinterpret_cast<MaskTap*>(scratch);
   float* partial = reinterpret_cast<float*>(scratch + taps_bytes);
@@ -1885,25 +1804,43 @@ extern "C" int cct_conv_weight_grad_noalloc(cct_ctx* ctx, const cct_conv_desc* d
   P.n_real = n_real; P.n_pad = n_pad;
   P.m_tiles = m_tiles; P.subs = subs; P.stages = stages;
   P.ones_row = k_real;
-  P.kblocks_total = kblocks_total; P.kblocks_per_split = kblocks_per_split;
+  P.kblocks_per_split = kblocks_per_split;
   P.status = ctx->status_dev;
-  P.dbg = 0;
-  kernel<<<dim3(mgroups, splits, vgroups), kWgThreads, smem, ctx->stream>>>(P);
-  CCT_CHECK_LAUNCH(ctx);
-  launch_wgrad_reduce(ctx, partial, dW, G.bias ? db : nullptr, splits, vgroups, tiles, m_tiles * kTileM, n_real, n_pad,
-                      k_real, G.og);
-  CCT_CHECK_LAUNCH(ctx);
+  for (int first = 0, round = 0; first < total_splits; first += slots, ++round) {
+    const int here = std::min(slots, total_splits - first);
+    P.kb_first = first * kblocks_per_split;
+    P.kblocks_total = std::min(kblocks_total, P.kb_first + here * kblocks_per_split);
+    kernel<<<dim3(mgroups, here, vgroups), kWgThreads, smem, ctx->stream>>>(P);
+    CCT_CHECK_LAUNCH(ctx);
+    launch_wgrad_reduce(ctx, partial, dW, G.bias ? db : nullptr, here, vgroups, tiles, m_tiles * kTileM, n_real, n_pad,
+                        k_real, G.og, round > 0);
+    CCT_CHECK_LAUNCH(ctx);
+  }
   return CCT_OK;
 }
 
-#ifdef CCT_DBG
-extern "C" int cct_dbg_read_prof(unsigned long long* out, int reset) {
-  cudaDeviceSynchronize();
-  if (cudaMemcpyFromSymbol(out, g_prof, sizeof(unsigned long long) * 64) != cudaSuccess) return 1;
-  if (reset) {
-    static unsigned long long zeros[64];
-    cudaMemcpyToSymbol(g_prof, zeros, sizeof zeros);
+// ------------------------------------------------------------------ the bounded wait, exercised on purpose
+namespace {
+// One warp waits - through the same mbar_wait the convolution kernels use - for a barrier phase that nothing will ever
+// complete, with a short limit.  The wait gives up, records `code` in the status word and the kernel returns
+// normally: no trap, no fault, the context stays usable.
+__global__ void bounded_wait_selftest_kernel(int* status, long long limit_cycles, int code) {
+  __shared__ __align__(8) unsigned long long bar_storage;
+  const uint32_t bar = smem_u32(&bar_storage);
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);
+    fence_mbar_init();
   }
-  return 0;
+  __syncthreads();
+  bool failed = false;
+  mbar_wait(bar, 0u, failed, status, code, limit_cycles);
 }
-#endif
+}  // namespace
+
+extern "C" int cct_selftest_bounded_wait(cct_ctx* ctx, long long limit_cycles) {
+  if (!ctx || limit_cycles <= 0 || limit_cycles > kWaitLimitCycles) return CCT_ERR_INVALID;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  bounded_wait_selftest_kernel<<<1, 32, 0, ctx->stream>>>(ctx->status_dev, limit_cycles, 0x7e57);
+  CCT_CHECK_LAUNCH(ctx);
+  return CCT_OK;
+}

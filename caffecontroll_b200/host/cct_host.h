@@ -172,6 +172,10 @@ class ConvolutionBridge : public PhysicalOperator {
   const float* pooled_gradient = nullptr;
   const int32_t* max_index = nullptr;
   int pool_kernel_size = 0, pool_stride = 0;
+  void fuse_pool_relu_backward(const float* pooled_grad, const int32_t* index, int kernel_size, int pool_stride_) {
+    p_driver->check(cct_conv_plan_reserve_fusion(plan_), "cct_conv_plan_reserve_fusion");
+    pooled_gradient = pooled_grad; max_index = index; pool_kernel_size = kernel_size; pool_stride = pool_stride_;
+  }
 
   void backward() override {
     float* dx = needs_to_calc_backward_grad ? p_input_layer->p_gradient_cube->get_p_data() : nullptr;

@@ -110,7 +110,7 @@ int cct_conv_backward(cct_conv_plan* plan, const float* X, const float* W, const
  *         dY = (A > 0) * maxpool_backward(dP, idx)
  *     A = this layer's forward output [batch][out_depth][m][m] (pre- or post-ReLU: only its sign is used), idx = the
  *     int32 indices cct_maxpool_forward wrote, dP = gradient of the pooled tensor.  One HBM-bound pass into
- *     plan-owned scratch feeds both gradient kernels.
+ *     plan-owned scratch (cct_conv_plan_reserve_fusion) feeds both gradient kernels.
  *   - Input side.  relu_mask_dx != 0 writes dX * [X > 0] instead of dX: the ReLU bridge in front of this layer (whose
  *     output X is), applied by one streaming pass right behind the data-gradient kernel.
  * f == NULL behaves like cct_conv_backward. */
@@ -123,12 +123,16 @@ typedef struct cct_bwd_fusion {
 } cct_bwd_fusion;
 int cct_conv_backward_fused(cct_conv_plan* plan, const float* X, const float* W, const float* dY,
                             const cct_bwd_fusion* f, float* dX, float* dW, float* db);
+/* Allocates the plan-owned buffer (one tensor of the layer's output size) that cct_conv_backward_fused fills when it
+ * is given a pooled gradient.  Call it once, next to cct_conv_plan_create, for every plan that will be used that way:
+ * cct_conv_backward_fused itself never allocates and returns CCT_ERR_INVALID if the buffer is missing. */
+int cct_conv_plan_reserve_fusion(cct_conv_plan* plan);
 
 /* Host-buffer forms of the two calls above, for callers that keep cubes in host memory as the reference's
  * ParallelizedBridge does (src/bridges/ParallelizedBridge_impl.hxx:538-671, 686-738, 779-830, 895-910,
  * 1071-1122): inputs are copied to plan-owned device buffers, the kernels run, results are copied back, and the
  * call returns after the results have landed.  Pinned host memory (cct_malloc_host) makes the copies asynchronous;
- * batches of eight images or more move in four slices on two side streams, so that the upload of one slice, the
+ * batches of sixteen images or more move in eight slices on two side streams, so that the upload of one slice, the
  * kernels of the previous one and the download of the one before overlap.
  * cct_conv_backward_host accepts hX == NULL and/or hW == NULL, meaning "the copy staged by the last
  * cct_conv_forward_host on this plan" (the reference keeps the input cube on the device between the two passes). */
@@ -145,14 +149,20 @@ int cct_conv_backward_host(cct_conv_plan* plan, const float* hX, const float* hW
  * row table and the split partial sums) in a 16 MiB array that is part of the library image on every device that
  * loads it.  It calls no cudaMalloc / cudaFree and no allocating library routine; X, dY, dW, db are the caller's
  * device buffers as in cct_conv_backward (dW, db overwritten; db ignored without bias_term).
- *   - Limit: table + one split of partial sums must fit in 16 MiB, else CCT_ERR_UNSUPPORTED with the needed size in
- *     cct_last_error_string; larger layers simply run with fewer splits than the plan-based path would use.
- *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress); make that first call
- *     before starting any stream capture.
+ *   - Limit: the row table plus one split's partial sums must fit in 16 MiB, else CCT_ERR_UNSUPPORTED with the needed
+ *     size in cct_last_error_string.  The pixel range is cut into the same bounded accumulation chains as in the
+ *     plan-based path (at most 176 blocks of 32 pixels per partial sum); when the array cannot hold all the splits at
+ *     once they are processed in rounds that reuse the slices, each round's reduction adding to dW / db.
+ *   - The 16 MiB come into being when the library's device code is first loaded on a device, which with lazy module
+ *     loading can be this call itself.  Make one call of it (or any plan-based convolution call) on every device
+ *     BEFORE the pool takes the device or the no-allocation section starts; a failure at that point surfaces as
+ *     CCT_ERR_NOMEM or CCT_ERR_CUDA from this function.  The same first call looks up the array's device address
+ *     (cudaGetSymbolAddress) and should precede any stream capture.
  *   - All calls on a device share the one array and it keeps the previous call's contents (nothing in it needs to
- *     start at zero: every slot that is read is written first by the same call).  Two calls that overlap on the GPU —
- *     different streams or contexts of the same device — race on it; serialise them.
- * Results equal cct_conv_backward's dW, db up to the rounding of a different split count. */
+ *     start at zero: every slot that is read is written first by the same call).  Two calls that overlap on the GPU -
+ *     different streams or contexts of the same device - race on it; serialise them.
+ * Results equal cct_conv_backward's dW, db up to the rounding of a different split count; both hold the 1e-4
+ * tolerance against the CPU path at the BASELINE sizes (tests/test_zz_no_alloc.py). */
 int cct_conv_weight_grad_noalloc(cct_ctx* ctx, const cct_conv_desc* desc, const float* X, const float* dY, float* dW,
                                  float* db);
 
@@ -163,6 +173,13 @@ int cct_conv_weight_grad_noalloc(cct_ctx* ctx, const cct_conv_desc* desc, const 
  * (its Report objects hold host wall-clock: src/Report.h:13-91). */
 int cct_conv_plan_enable_timing(cct_conv_plan* plan, int enable);
 int cct_conv_plan_last_timings(cct_conv_plan* plan, float ms[5]);
+
+/* Failure-path self-test (no counterpart in the reference, whose kernels never wait on anything): launches one warp
+ * that waits, through the same bounded wait the convolution kernels use, on a barrier nothing completes, with a limit
+ * of `limit_cycles` SM clock cycles (at most the kernels' own limit).  The wait runs out, the kernel returns normally,
+ * and the next cct_sync on the context reports CCT_ERR_TIMEOUT and clears the status word; calls made after that run
+ * as usual.  Nothing traps or faults. */
+int cct_selftest_bounded_wait(cct_ctx* ctx, long long limit_cycles);
 
 /* ---- adjacent layers whose backward masks feed the convolution backward ---- */
 /* DeviceDriver::maxpool_forward / maxpool_backward (src/sched/DeviceDriver_CPU.cpp:369-421): windows k x k,

@@ -156,7 +156,7 @@ def test_backward_is_deterministic(ctx):
         assert np.array_equal(u, v)
 
 
-@pytest.mark.parametrize("B", [4, 10, 16])  # 4: one piece; 10 and 16: pipelined in slices of 3 (last one short) and 4
+@pytest.mark.parametrize("B", [4, 20, 16])  # 4: one piece; 20 and 16: pipelined in slices of 3 (last one short) and 2
 def test_host_buffer_entry_points(ctx, port, B):
     import ctypes as C
     from caffecontroll_b200 import capi

@@ -36,6 +36,7 @@ def _run(ctx, port, shape, algo):
     desc = capi.ConvDesc(B, D, n, o, k, s, p, g, 1, algo)
     plan = C.c_void_p()
     capi.check(lib.cct_conv_plan_create(ctx.h, C.byref(desc), C.byref(plan)), "plan", ctx.h)
+    capi.check(lib.cct_conv_plan_reserve_fusion(plan), "reserve", ctx.h)
     cX, cW, cb, cdP = (LogicalCube.from_numpy(ctx, a) for a in (X, W, bias, dP))
     cY = LogicalCube(ctx, m, m, o, B)
     cPool, cidx = LogicalCube(ctx, mp, mp, o, B), LogicalCube(ctx, mp, mp, o, B, np.int32)
@@ -102,6 +103,9 @@ def test_fused_backward_argument_checks(ctx):
     f = capi.BwdFusion(None, None, buf.ptr, 3, 2, 0)  # dP without A / idx
     rc = lib.cct_conv_backward_fused(plan, vp(buf.ptr), vp(buf.ptr), None, C.byref(f), None, vp(buf.ptr), vp(buf.ptr))
     assert rc == capi.CCT_ERR_INVALID
+    f = capi.BwdFusion(buf.ptr, buf.ptr, buf.ptr, 3, 2, 0)  # a pooled gradient without cct_conv_plan_reserve_fusion
+    rc = lib.cct_conv_backward_fused(plan, vp(buf.ptr), vp(buf.ptr), None, C.byref(f), None, vp(buf.ptr), vp(buf.ptr))
+    assert rc == capi.CCT_ERR_INVALID and b"reserve_fusion" in lib.cct_last_error_string(ctx.h)
     f = capi.BwdFusion(None, None, None, 0, 0, 1)  # neither dY nor dP
     rc = lib.cct_conv_backward_fused(plan, vp(buf.ptr), vp(buf.ptr), None, C.byref(f), None, vp(buf.ptr), vp(buf.ptr))
     assert rc == capi.CCT_ERR_INVALID
