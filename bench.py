@@ -64,20 +64,78 @@ def synth(w, seed):
     return X, W, bias, dY
 
 
-# dram__bytes_read.sum per launch of each contraction kernel in the ncu capture of the batch-64 AlexNet conv1 case
-# (profiles/alexnet_conv1_b64_ncu_full.md).  Reads equal the pass's input bytes and grow with the batch.
-NCU_DRAM_READ_B64 = {"alexnet_conv1": {"forward": 39.9e6, "wgrad": 116.4e6, "dgrad": 74.7e6}}
-
-
 def dram_traffic(workload, w, pass_name, batch):
-    """DRAM bytes per launch of one pass: measured reads scaled to this batch plus the pass's output bytes."""
-    table = NCU_DRAM_READ_B64.get(workload)
-    if table is None:
-        return None
+    """DRAM bytes per launch of one pass, from the ncu captures summarised in profiles/dram_traffic.json: measured
+    reads of the small-case capture scaled to this batch (they grow in proportion) plus the pass's output bytes (the
+    small case's outputs stay in L2, so its write counter undercounts).  (None, None) for a pass never captured."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    try:
+        with open(path) as f:
+            table = json.load(f)
+    except OSError:
+        return None, None
+    entry = table.get(workload, {}).get(pass_name)
+    if not entry:
+        return None, None
     m = (w["n"] + 2 * w["p"] - w["k"]) // w["s"] + 1
     out_elems = {"forward": batch * w["o"] * m * m, "dgrad": batch * w["D"] * w["n"] * w["n"],
                  "wgrad": w["o"] * (w["D"] // w["g"]) * w["k"] * w["k"] + w["o"]}[pass_name]
-    return table[pass_name] * batch / 64.0 + 4.0 * out_elems
+    return entry["dram_read_bytes"] * batch / float(entry["batch"]) + 4.0 * out_elems, entry["source"]
+
+
+def measure_tf32_peak(seconds=2.0):
+    """Dense TF32 matmul throughput of this GPU, measured like the bf16 figures of MEASURED_PEAKS.json: a library
+    8192^3 matmul with TF32 inputs, best of 10 (burst) and back to back for `seconds` (sustained).  Only a roofline
+    denominator: nothing on the measured path calls a library GEMM."""
+    import torch
+    n = 8192
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        a = torch.randn(n, n, device="cuda")
+        b = torch.randn(n, n, device="cuda")
+        c = torch.empty(n, n, device="cuda")
+        for _ in range(3):
+            torch.matmul(a, b, out=c)
+        torch.cuda.synchronize()
+        best = float("inf")
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch.matmul(a, b, out=c)
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        reps = max(10, int(seconds * 1e3 / best))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            torch.matmul(a, b, out=c)
+        e1.record()
+        torch.cuda.synchronize()
+        sustained = e0.elapsed_time(e1) / reps
+        del a, b, c
+        torch.cuda.empty_cache()
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    flops = 2.0 * n ** 3
+    return flops / (best * 1e-3) / 1e12, flops / (sustained * 1e-3) / 1e12
+
+
+def tensor_roofline(peaks, measure=True):
+    """fp32-equivalent 3xTF32 roofline in TFLOP/s: the measured TF32 matmul rate / 3 (three MMAs per product)."""
+    out = {"bf16_burst": peaks["bf16_tflops"], "bf16_sustained": peaks.get("bf16_tflops_sustained")}
+    if measure:
+        burst, sustained = measure_tf32_peak()
+        out.update(tf32_burst=burst, tf32_sustained=sustained, peak=burst / 3.0, peak_sustained=sustained / 3.0,
+                   source="TF32 8192^3 library matmul measured in this run: burst %.1f, sustained %.1f TFLOP/s; / 3 for "
+                          "3xTF32 - of measured (bf16 in MEASURED_PEAKS.json: %.1f burst)" %
+                          (burst, sustained, peaks["bf16_tflops"]))
+    else:
+        out.update(tf32_burst=None, tf32_sustained=None, peak=peaks["bf16_tflops"] / 6.0,
+                   peak_sustained=(peaks.get("bf16_tflops_sustained") or 0) / 6.0,
+                   source="%s: bf16 burst %.1f TFLOP/s / 2 (assumed TF32 rate) / 3" % (peaks["source"], peaks["bf16_tflops"]))
+    return out
 
 
 def load_peaks():
@@ -226,6 +284,31 @@ def run_reference_arm(args, w, rank, world):
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def preheat(step, warmup, seconds, stream, world, dev):
+    """Untimed warm-up: at least `warmup` steps and at least `seconds` of device time, so that the timed steps that
+    follow run at the clocks and power state of a long job and not in a cold burst.  Returns the steps run (the same
+    on every rank: the count is agreed through a MAX all-reduce of one rank-local calibration)."""
+    import torch
+    import torch.distributed as dist
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n0 = max(warmup, 3)
+    e0.record(stream)
+    for _ in range(n0):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    per = max(e0.elapsed_time(e1) / n0, 1e-3)
+    more = max(0, int(seconds * 1e3 / per) - n0)
+    if world > 1:
+        t = torch.tensor([more], device=dev, dtype=torch.int64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        more = int(t.item())
+    for _ in range(more):
+        step()
+    torch.cuda.synchronize()
+    return n0 + more
 
 
 # The five convolution layers of CaffeNet at batch 256 per GPU (BASELINE config 4 without the LRN / FC / softmax layers,
@@ -381,6 +464,8 @@ def main():
     ap.add_argument("--workload", default="alexnet_conv1", choices=sorted(WORKLOADS) + ["caffenet_convs"])
     ap.add_argument("--algo", type=int, default=0, help="0 auto, 1 SIMT fp32, 2 tcgen05 3xTF32")
     ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--preheat-s", type=float, default=1.0,
+                    help="untimed warm-up runs until at least this much device time has passed (and --warmup steps)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (profiling on a small case)")
     args = ap.parse_args()
@@ -473,8 +558,8 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        step()
+    roof = tensor_roofline(load_peaks(), measure=(rank == 0))
+    warm_steps = preheat(step, args.warmup, args.preheat_s, stream, world, dev)
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -508,19 +593,18 @@ def main():
     F = gemm_flops(w)
     passes = {"forward": k_ms[0], "wgrad": k_ms[1], "dgrad": k_ms[3]}
     wg_gather = (D // g) * k * k >= 512  # the library's rule: long lowered matrices take the gather-kernel weight gradient
-    peaks = load_peaks()
-    tensor_peak = peaks["bf16_tflops"] / 2.0 / 3.0  # TF32 = 1/2 bf16 rate; 3 MMAs per product
+    tensor_peak = roof["peak"]
     dom = max(passes, key=lambda x: passes[x])
     ach = F / (passes[dom] * 1e-3) / 1e12 if passes[dom] > 0 else 0.0
+    traffic, traffic_source = dram_traffic(args.workload, w, dom, B) if algo.value == 2 else (None, None)
     roofline = {
         "bound": "tensor", "kernel": {"forward": "gather_conv_kernel (forward)", "dgrad": "gather_conv_kernel (data gradient)",
                                       "wgrad": "split_dy_kernel + gather_conv_kernel (weight gradient)" if wg_gather else "wgrad_kernel"}[dom] if algo.value == 2 else "simt_%s" % dom,
         "pass": dom, "achieved": ach, "peak": tensor_peak, "unit": "TFLOP/s", "frac": ach / tensor_peak,
-        "traffic": dram_traffic(args.workload, w, dom, B) if algo.value == 2 else None,
-        "traffic_source": "ncu dram__bytes_read.sum of the batch-64 capture scaled by batch/64, plus the pass's "
-                          "output bytes (the batch-64 outputs stayed in L2, so its write counter undercounts)",
-        "peak_source": "%s: bf16 burst %.1f TFLOP/s / 2 (TF32 rate) / 3 (3xTF32) — of measured" %
-                       (peaks["source"], peaks["bf16_tflops"]),
+        "traffic": traffic,
+        "peak_source": roof["source"], "peak_sustained": roof["peak_sustained"],
+        "frac_of_sustained": ach / roof["peak_sustained"] if roof["peak_sustained"] else None,
+        "whole_step_frac": (3 * F / (ms_step * 1e-3) / 1e12) / tensor_peak,
         "flops_per_launch": F, "ms_per_launch": passes[dom],
         "timing": "CUDA events around each kernel group on the launching stream, mean of %d steps run right after the "
                   "timed region" % prof_steps,
@@ -528,6 +612,9 @@ def main():
                       "forward_repack": k_ms[4]},
         "passes_tflops": {p: (F / (v * 1e-3) / 1e12 if v > 0 else None) for p, v in passes.items()},
     }
+    if traffic is not None:
+        roofline["traffic_source"] = ("ncu dram__bytes_read.sum of the small-case capture scaled by the batch ratio, plus "
+                                      "the pass's output bytes: " + traffic_source)
 
     # End to end through the host-buffer C-ABI calls: pinned host memory, copies inside the timed region.
     hX, hW, hb, hdY = (torch.from_numpy(a).pin_memory() for a in (X, W, bias, dY))
@@ -566,7 +653,7 @@ def main():
         launches_per_step = (2 + (6 if wg_gather else 4) + 2) if algo.value == 2 else (1 + 3 + 2)
         line = {
             "metric": METRIC, "value": world * B / (ms_step * 1e-3), "unit": "images/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "steps": args.steps, "warmup": warm_steps, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": dict(config_of(args, w, world), algo={1: "simt_fp32", 2: "tcgen05_3xtf32"}[algo.value]),
             "tflops": world * 3 * F / (ms_step * 1e-3) / 1e12,
