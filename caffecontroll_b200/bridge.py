@@ -214,19 +214,115 @@ class ConvolutionBridge:
                 c.free()
 
 
-class FullyConnectedBridge(ConvolutionBridge):
-    """The reference's FullyConnectedBridge (src/bridges/FullyConnectedBridge_impl.hxx:201-202, 305-312) is a
-    convolution whose kernel covers the whole input.  Here it runs as a 1x1 convolution over the input viewed as
-    D*R*C channels of a single pixel: the same arithmetic on the same weight layout [o][d][r][c], through the same
-    plan, kernels and fusion options as ConvolutionBridge.  The output layer is B x num_output x 1 x 1."""
+class FullyConnectedBridge:
+    """The reference's FullyConnectedBridge (src/bridges/FullyConnectedBridge_impl.hxx:171-235, 257-330): Y = X W^T + b
+    over the flattened input, weight layout [o][d][r][c].  Runs on the fully connected plan of the C ABI (tensor-core
+    GEMMs that read X, W and dY in place); layers whose feature counts are not multiples of 4, and
+    algo=ALGO_SIMT_FP32, run as a 1x1 convolution over the input viewed as D*R*C channels of one pixel instead.
+    The output layer is B x num_output x 1 x 1.
+
+    Fusion switches (the bridges around the layer in CaffeNet): fuse_relu clamps the output at 0; dropout_mask /
+    dropout_scale (a device cube of uint32, one per output element) applies DropoutBridge's forward; on the input
+    side fuse_relu_backward and input_dropout_mask / input_dropout_scale fold ReLUBridge::backward and
+    DropoutBridge::backward of the bridges in front of the layer into the input gradient."""
 
     def __init__(self, p_input_layer, p_output_layer, bias_term=True, algo=capi.ALGO_AUTO, ctx=None):
-        x, dx = p_input_layer.p_data_cube, p_input_layer.p_gradient_cube
-        k = x.D * x.R * x.C
-        flat = Layer(LogicalCube(x.ctx, 1, 1, k, x.B, x.dtype, ptr=x.ptr),
-                     LogicalCube(dx.ctx, 1, 1, k, dx.B, dx.dtype, ptr=dx.ptr) if dx is not None else None)
-        super().__init__(flat, p_output_layer, 1, 1, 0, 1, bias_term, algo, ctx)
-        self.unflattened_input_layer = p_input_layer
+        x, y = p_input_layer.p_data_cube, p_output_layer.p_data_cube
+        self.p_input_layer, self.p_output_layer = p_input_layer, p_output_layer
+        self.ctx = ctx or x.ctx
+        self.lib = self.ctx.lib
+        self.iR, self.iC, self.iD, self.iB = x.R, x.C, x.D, x.B
+        self.oR, self.oC, self.oD, self.oB = y.R, y.C, y.D, y.B
+        if (self.oR, self.oC, self.oB) != (1, 1, self.iB):
+            raise ValueError("output layer must be B x num_output x 1 x 1")
+        self.in_features = x.D * x.R * x.C
+        self.bias_term = bias_term
+        self.needs_to_calc_backward_grad = True
+        self.fuse_relu = False
+        self.fuse_relu_backward = False
+        self.dropout_mask, self.dropout_scale = None, 1.0
+        self.input_dropout_mask, self.input_dropout_scale = None, 1.0
+        self.plan, self._conv = None, None
+        use_plan = algo == capi.ALGO_UMMA_3XTF32 or (algo == capi.ALGO_AUTO and self.in_features % 4 == 0 and
+                                                      self.oD % 4 == 0)
+        if use_plan:
+            plan = C.c_void_p()
+            capi.check(self.lib.cct_fc_plan_create(self.ctx.h, self.iB, self.in_features, self.oD, int(bias_term),
+                                                   C.byref(plan)), "cct_fc_plan_create", self.ctx.h)
+            self.plan = plan
+            self.p_model_cube = LogicalCube(self.ctx, x.R, x.C, x.D, self.oD)
+            self.p_model_gradient_cube = LogicalCube(self.ctx, x.R, x.C, x.D, self.oD)
+            self.p_bias_cube = LogicalCube(self.ctx, 1, 1, self.oD, 1) if bias_term else None
+            self.p_bias_gradient_cube = LogicalCube(self.ctx, 1, 1, self.oD, 1) if bias_term else None
+        else:
+            dx = p_input_layer.p_gradient_cube
+            k = self.in_features
+            flat = Layer(LogicalCube(x.ctx, 1, 1, k, x.B, x.dtype, ptr=x.ptr),
+                         LogicalCube(dx.ctx, 1, 1, k, dx.B, dx.dtype, ptr=dx.ptr) if dx is not None else None)
+            self._conv = ConvolutionBridge(flat, p_output_layer, 1, 1, 0, 1, bias_term, algo, ctx)
+            c = self._conv
+            self.p_model_cube, self.p_model_gradient_cube = c.p_model_cube, c.p_model_gradient_cube
+            self.p_bias_cube, self.p_bias_gradient_cube = c.p_bias_cube, c.p_bias_gradient_cube
+
+    @property
+    def algo(self):
+        return capi.ALGO_UMMA_3XTF32 if self.plan else self._conv.algo
+
+    def get_model_cube(self):
+        return self.p_model_cube
+
+    def get_bias_cube(self):
+        return self.p_bias_cube
+
+    def get_model_grad_cube(self):
+        return self.p_model_gradient_cube
+
+    def get_bias_grad_cube(self):
+        return self.p_bias_gradient_cube
+
+    def forward(self):
+        if self._conv:
+            if self.dropout_mask is not None:
+                raise ValueError("dropout fusion needs the fully connected plan")
+            self._conv.fuse_relu = self.fuse_relu
+            self._conv.forward()
+            return
+        vp = C.c_void_p
+        mask = self.dropout_mask.ptr if self.dropout_mask is not None else None
+        capi.check(self.lib.cct_fc_forward(self.plan, vp(self.p_input_layer.p_data_cube.ptr), vp(self.p_model_cube.ptr),
+                                           vp(self.p_bias_cube.ptr) if self.bias_term else None,
+                                           vp(self.p_output_layer.p_data_cube.ptr), int(self.fuse_relu), mask,
+                                           float(self.dropout_scale)), "cct_fc_forward", self.ctx.h)
+
+    def backward(self):
+        if self._conv:
+            if self.input_dropout_mask is not None:
+                raise ValueError("dropout fusion needs the fully connected plan")
+            self._conv.needs_to_calc_backward_grad = self.needs_to_calc_backward_grad
+            self._conv.fuse_relu_backward = self.fuse_relu_backward
+            self._conv.backward()
+            return
+        vp = C.c_void_p
+        dx = self.p_input_layer.p_gradient_cube.ptr if self.needs_to_calc_backward_grad else None
+        mask = self.input_dropout_mask.ptr if self.input_dropout_mask is not None else None
+        capi.check(self.lib.cct_fc_backward(self.plan, vp(self.p_input_layer.p_data_cube.ptr), vp(self.p_model_cube.ptr),
+                                            vp(self.p_output_layer.p_gradient_cube.ptr), dx,
+                                            vp(self.p_model_gradient_cube.ptr),
+                                            vp(self.p_bias_gradient_cube.ptr) if self.bias_term else None,
+                                            int(self.fuse_relu_backward), mask, float(self.input_dropout_scale)),
+                   "cct_fc_backward", self.ctx.h)
+
+    def close(self):
+        if self._conv:
+            self._conv.close()
+            self._conv = None
+            return
+        if self.plan:
+            self.lib.cct_fc_plan_destroy(self.plan)
+            self.plan = None
+        for c in (self.p_model_cube, self.p_model_gradient_cube, self.p_bias_cube, self.p_bias_gradient_cube):
+            if c is not None:
+                c.free()
 
 
 def conv_layer(ctx, X, W, bias, dY, kernel, stride=1, pad=0, group=1, needs_dx=True, algo=capi.ALGO_AUTO, relu=False):

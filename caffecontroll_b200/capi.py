@@ -24,6 +24,11 @@ EXPORTS = [
     "cct_conv_plan_reserve_fusion", "cct_selftest_bounded_wait", "cct_conv_forward_host", "cct_conv_backward_host", "cct_conv_weight_grad_noalloc",
     "cct_maxpool_forward", "cct_maxpool_backward", "cct_relu_forward", "cct_relu_backward",
     "cct_pool_relu_backward", "cct_sgd_step",
+    "cct_fc_plan_create", "cct_fc_plan_destroy", "cct_fc_plan_workspace_bytes", "cct_fc_forward", "cct_fc_backward",
+    "cct_fc_plan_enable_timing", "cct_fc_plan_last_timings",
+    "cct_comm_unique_id", "cct_comm_init_rank", "cct_comm_destroy", "cct_comm_size", "cct_allreduce_sum_begin",
+    "cct_comm_wait", "cct_allreduce_sum",
+    "cct_lrn_forward", "cct_lrn_backward", "cct_dropout_apply", "cct_dropout_mask", "cct_softmax_loss_forward", "cct_softmax_loss_backward",
 ]
 
 
@@ -94,6 +99,26 @@ def load():
         "cct_relu_backward": [_vp, _vp, _vp, _vp, sz],
         "cct_pool_relu_backward": [_vp, _vp, _vp, _vp, _vp, i, i, i, i],
         "cct_sgd_step": [_vp, sz, _vp, _vp, _vp, f, f, f],
+        "cct_comm_unique_id": [C.c_char_p],
+        "cct_comm_init_rank": [_vp, i, i, C.c_char_p, C.POINTER(_vp)],
+        "cct_comm_destroy": [_vp],
+        "cct_comm_size": [_vp, C.POINTER(i), C.POINTER(i)],
+        "cct_allreduce_sum_begin": [_vp, _vp, sz],
+        "cct_comm_wait": [_vp],
+        "cct_allreduce_sum": [_vp, _vp, sz],
+        "cct_lrn_forward": [_vp, _vp, _vp, _vp, i, i, i, i, f, f],
+        "cct_lrn_backward": [_vp, _vp, _vp, _vp, _vp, _vp, i, i, i, i, f, f],
+        "cct_dropout_apply": [_vp, _vp, _vp, f, _vp, sz],
+        "cct_dropout_mask": [_vp, _vp, sz, f, C.c_uint64, C.c_uint64],
+        "cct_softmax_loss_forward": [_vp, _vp, _vp, _vp, _vp, _vp, i, i],
+        "cct_softmax_loss_backward": [_vp, _vp, _vp, _vp, i, i, f],
+        "cct_fc_plan_create": [_vp, i, i, i, i, C.POINTER(_vp)],
+        "cct_fc_plan_destroy": [_vp],
+        "cct_fc_plan_workspace_bytes": [_vp, C.POINTER(sz)],
+        "cct_fc_forward": [_vp, _vp, _vp, _vp, _vp, i, _vp, f],
+        "cct_fc_backward": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, i, _vp, f],
+        "cct_fc_plan_enable_timing": [_vp, i],
+        "cct_fc_plan_last_timings": [_vp, C.POINTER(C.c_float)],
     }
     for name, args in sigs.items():
         fn = getattr(L, name)

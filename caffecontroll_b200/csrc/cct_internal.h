@@ -76,3 +76,6 @@ int umma_conv_backward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W
 int umma_conv_wgrad(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* dY, float* dW, float* db, PhaseTimer* t);
 int umma_conv_dgrad(cct_ctx* ctx, UmmaPlan* p, const float* W, const float* dY, float* dX, PhaseTimer* t, int batch,
                     bool repack);
+
+// ---- max pooling forward with the plane staged in shared memory (layers.cu)
+int maxpool_forward_staged(cct_ctx* ctx, const float* X, float* Y, int32_t* idx, int planes, int n, int m, int k, int s);

@@ -385,8 +385,9 @@ int cct_maxpool_forward(cct_ctx* ctx, const float* X, float* Y, int32_t* idx, in
   if (!ctx || !X || !Y || !idx || !pool_args_ok(planes, n, k, s)) return CCT_ERR_INVALID;
   const int m = (n - k) / s + 1;
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
-  maxpool_fwd_kernel<<<plane_grid(ctx, planes), 256, 0, ctx->stream>>>(X, Y, idx, planes, n, m, k,
-                                                                                        s);
+  // planes that fit in shared memory are staged there (one HBM read per element); larger ones read through L1
+  if ((size_t)n * n * sizeof(float) <= 200 * 1024) return maxpool_forward_staged(ctx, X, Y, idx, planes, n, m, k, s);
+  maxpool_fwd_kernel<<<plane_grid(ctx, planes), 256, 0, ctx->stream>>>(X, Y, idx, planes, n, m, k, s);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }

@@ -1,0 +1,285 @@
+// The remaining CaffeNet bridges between the contractions, as HBM-bound kernels: local response normalisation
+// (LRNBridge), dropout (DropoutBridge), softmax with loss (SoftmaxLossBridge) and max pooling forward with the plane
+// staged in shared memory.  Each kernel notes the bytes it moves per element; grids are multiples of the SM count.
+#include <float.h>
+
+#include <algorithm>
+
+#include "cct_internal.h"
+
+namespace {
+
+inline int ew_grid(cct_ctx* ctx, size_t work, int threads) {
+  const size_t blocks = (work + threads - 1) / threads;
+  return (int)std::max<size_t>(1, std::min<size_t>(blocks, (size_t)ctx->sm_count * 16));
+}
+
+// ---------------------------------------------------------------------------------------------------- LRN
+// Across-channel normalisation (src/bridges/LRNBridge_impl.hxx:46-120, src/kernels/lrn.hxx:38-124):
+//   scale[b][d][p] = 1 + (alpha / local_size) * sum_{|c - d| <= local_size / 2} X[b][c][p]^2,   Y = X / scale^beta.
+// One thread per (image, position), walking over the channels with the last local_size squares in registers: consecutive
+// threads read consecutive positions of one channel plane (coalesced).  4 B read + 8 B written per element (Y and
+// scale; the backward pass reads scale instead of recomputing a nine-channel window).
+template <int LOCAL>
+__global__ void lrn_fwd_kernel(const float* __restrict__ X, float* __restrict__ Y, float* __restrict__ scale,
+                               size_t positions, int D, int plane, float alpha_over_size, float beta) {
+  constexpr int W = LOCAL / 2;
+  for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < positions; t += (size_t)gridDim.x * blockDim.x) {
+    const size_t b = t / plane, p = t - b * plane;
+    const float* x = X + b * (size_t)D * plane + p;
+    float* y = Y + b * (size_t)D * plane + p;
+    float* sc = scale + b * (size_t)D * plane + p;
+    float win[LOCAL];  // x[d - W .. d + W]
+#pragma unroll
+    for (int i = 0; i < LOCAL; ++i) win[i] = (i - W - 1 >= 0 && i - W - 1 < D) ? x[(size_t)(i - W - 1) * plane] : 0.f;
+    for (int d = 0; d < D; ++d) {
+#pragma unroll
+      for (int i = 0; i + 1 < LOCAL; ++i) win[i] = win[i + 1];
+      win[LOCAL - 1] = d + W < D ? x[(size_t)(d + W) * plane] : 0.f;
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < LOCAL; ++i) sum += win[i] * win[i];
+      const float s = alpha_over_size * sum + 1.f;
+      sc[(size_t)d * plane] = s;
+      y[(size_t)d * plane] = win[W] / powf(s, beta);
+    }
+  }
+}
+
+// Any odd window: the squares are re-read (they sit in L1 from the previous channels' steps).
+__global__ void lrn_fwd_generic_kernel(const float* __restrict__ X, float* __restrict__ Y, float* __restrict__ scale,
+                                       size_t positions, int D, int plane, int local, float alpha_over_size, float beta) {
+  const int w = local / 2;
+  for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < positions; t += (size_t)gridDim.x * blockDim.x) {
+    const size_t b = t / plane, p = t - b * plane;
+    const size_t base = b * (size_t)D * plane + p;
+    for (int d = 0; d < D; ++d) {
+      float sum = 0.f;
+      for (int c = max(0, d - w); c <= min(D - 1, d + w); ++c) {
+        const float v = X[base + (size_t)c * plane];
+        sum += v * v;
+      }
+      const float s = alpha_over_size * sum + 1.f;
+      scale[base + (size_t)d * plane] = s;
+      Y[base + (size_t)d * plane] = X[base + (size_t)d * plane] / powf(s, beta);
+    }
+  }
+}
+
+// LRNBridge::backward (src/kernels/lrn.hxx:134-180) as a gather: the reference scatters, for every output channel o,
+//   dX[c] += dY[o] * ([c == o] / scale[o]^beta - 2 beta (alpha / size) X[o] X[c] / scale[o]^(beta + 1))   for |c - o| <= w;
+// collected per input channel c:
+//   dX[c] = dY[c] / scale[c]^beta - 2 beta (alpha / size) X[c] * sum_{|o - c| <= w} dY[o] Y[o] / scale[o]
+// (Y[o] = X[o] / scale[o]^beta, so no power is needed inside the window).  16 B read + 4 B written per element; the
+// window terms of neighbouring channels come from L1.
+__global__ void lrn_bwd_kernel(const float* __restrict__ X, const float* __restrict__ Y, const float* __restrict__ scale,
+                               const float* __restrict__ dY, float* __restrict__ dX, size_t positions, int D, int plane,
+                               int local, float alpha_over_size, float beta) {
+  const int w = local / 2;
+  const float coef = 2.f * beta * alpha_over_size;
+  for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < positions; t += (size_t)gridDim.x * blockDim.x) {
+    const size_t b = t / plane, p = t - b * plane;
+    const size_t base = b * (size_t)D * plane + p;
+    for (int c = 0; c < D; ++c) {
+      float acc = 0.f;
+      for (int o = max(0, c - w); o <= min(D - 1, c + w); ++o) {
+        const size_t at = base + (size_t)o * plane;
+        acc += dY[at] * Y[at] / scale[at];
+      }
+      const size_t at = base + (size_t)c * plane;
+      dX[at] = dY[at] / powf(scale[at], beta) - coef * X[at] * acc;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ dropout
+// DropoutBridge forward in training and backward (src/bridges/DropoutBridge_impl.hxx:71-74, 150-170): the same
+// element-wise product with the mask (one unsigned int per element, non-zero = keep) and the scale 1 / (1 - ratio).
+__global__ void dropout_kernel(const float* __restrict__ in, const uint32_t* __restrict__ mask, float scale,
+                               float* __restrict__ out, size_t count) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = in[i] * (float)(mask[i] != 0u) * scale;
+}
+
+// A fresh keep / drop mask on the device: element i of stream (seed, call) keeps its value with probability
+// 1 - ratio.  Counter-based (a 64-bit mix of seed, call counter and index), so the result does not depend on the grid
+// and a (seed, call) pair reproduces its mask.  The reference's GPU path thresholds cuRAND integers the same way
+// (src/bridges/DropoutBridge_impl.hxx:100-104); its CPU path draws from boost::bernoulli on mt19937 - masks differ
+// between the two there as well, which is why parity runs inject the CPU oracle's mask instead.
+__global__ void dropout_mask_kernel(uint32_t* __restrict__ mask, size_t count, uint32_t threshold, uint64_t key) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x) {
+    uint64_t z = key + (uint64_t)i * 0x9E3779B97F4A7C15ull;  // splitmix64 finaliser
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    mask[i] = (uint32_t)(z >> 32) >= threshold ? 1u : 0u;
+  }
+}
+
+// -------------------------------------------------------------------------------------------- softmax loss
+// SoftmaxLossBridge (src/kernels/softmax.hxx:17-50): per image prob = exp(x - max) / sum, loss -= log(max(prob[label],
+// FLT_MIN)).  One warp per image; the per-image losses are added in image order by one thread afterwards, so the
+// result does not depend on the grid.  Labels are floats, as in the reference's label cube.
+__global__ void softmax_fwd_kernel(const float* __restrict__ X, const float* __restrict__ labels, float* __restrict__ prob,
+                                   float* __restrict__ image_loss, int B, int C) {
+  const int lane = threadIdx.x & 31;
+  const int img = (int)((blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5);
+  if (img >= B) return;
+  const float* x = X + (size_t)img * C;
+  float* pr = prob + (size_t)img * C;
+  float mx = -FLT_MAX;
+  for (int i = lane; i < C; i += 32) mx = fmaxf(mx, x[i]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f;
+  for (int i = lane; i < C; i += 32) sum += expf(x[i] - mx);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  for (int i = lane; i < C; i += 32) pr[i] = expf(x[i] - mx) / sum;
+  __syncwarp();
+  if (lane == 0) {
+    const int label = (int)labels[img];
+    const float p = (label >= 0 && label < C) ? expf(x[label] - mx) / sum : 0.f;
+    image_loss[img] = -logf(fmaxf(p, FLT_MIN));
+  }
+}
+
+__global__ void sum_in_order_kernel(const float* __restrict__ v, float* __restrict__ out, int n) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    float acc = 0.f;
+    for (int i = 0; i < n; ++i) acc += v[i];
+    *out = acc;
+  }
+}
+
+// Gradient of the loss with respect to the bridge's input (src/kernels/softmax.hxx:62-80):
+// dX = (prob - onehot(label)) * scale, scale = 1 / (batch the loss is averaged over).
+__global__ void softmax_bwd_kernel(const float* __restrict__ prob, const float* __restrict__ labels,
+                                   float* __restrict__ dX, size_t total, int C, float scale) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t img = i / C;
+    const int c = (int)(i - img * C);
+    dX[i] = (prob[i] - (c == (int)labels[img] ? 1.f : 0.f)) * scale;
+  }
+}
+
+// ----------------------------------------------------------------------------- max pooling forward, staged
+// MaxPoolingBridge::forward (src/sched/DeviceDriver_CPU.cpp:369-400): windows clipped at the border, rows then columns,
+// strict '>' so the first maximum wins; idx = offset inside the plane.  One block per plane at a time: the plane is
+// copied to shared memory with coalesced loads (every input element crosses HBM -> SM once), the windows are read
+// from there, Y and idx leave in coalesced runs.  4 B read per input element + 8 B written per output element.
+__global__ void __launch_bounds__(256) maxpool_fwd_staged_kernel(const float* __restrict__ X, float* __restrict__ Y,
+                                                                 int32_t* __restrict__ idx, int planes, int n, int m,
+                                                                 int k, int s) {
+  extern __shared__ float plane_smem[];
+  const int nn = n * n, mm = m * m;
+  for (int plane = blockIdx.x; plane < planes; plane += gridDim.x) {
+    const float* in = X + (size_t)plane * nn;
+    __syncthreads();  // the previous plane's windows have been read
+    for (int i = threadIdx.x; i < nn; i += blockDim.x) plane_smem[i] = __ldg(in + i);
+    __syncthreads();
+    for (int t = threadIdx.x; t < mm; t += blockDim.x) {
+      const int ph = t / m, pw = t - ph * m;
+      const int he = min(ph * s + k, n), we = min(pw * s + k, n);
+      float best = -FLT_MAX;
+      int where = 0;
+      for (int h = ph * s; h < he; ++h)
+        for (int w = pw * s; w < we; ++w) {
+          const float v = plane_smem[h * n + w];
+          if (v > best) { best = v; where = h * n + w; }
+        }
+      Y[(size_t)plane * mm + t] = best;
+      idx[(size_t)plane * mm + t] = where;
+    }
+  }
+}
+
+}  // namespace
+
+int maxpool_forward_staged(cct_ctx* ctx, const float* X, float* Y, int32_t* idx, int planes, int n, int m, int k, int s) {
+  const size_t smem = (size_t)n * n * sizeof(float);
+  if (smem > 200 * 1024) return CCT_ERR_UNSUPPORTED;
+  if (smem > 48 * 1024)
+    CCT_CUDA(ctx, cudaFuncSetAttribute(maxpool_fwd_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(8, (200 * 1024) / std::max<size_t>(smem, 1)));
+  const int grid = std::max(1, std::min(planes, ctx->sm_count * per_sm));
+  maxpool_fwd_staged_kernel<<<grid, 256, smem, ctx->stream>>>(X, Y, idx, planes, n, m, k, s);
+  CCT_CHECK_LAUNCH(ctx);
+  return CCT_OK;
+}
+
+extern "C" {
+
+int cct_lrn_forward(cct_ctx* ctx, const float* X, float* Y, float* scale, int batch, int depth, int plane, int local_size,
+                    float alpha, float beta) {
+  if (!ctx || !X || !Y || !scale || batch <= 0 || depth <= 0 || plane <= 0 || local_size <= 0 || !(local_size & 1))
+    return CCT_ERR_INVALID;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  const size_t positions = (size_t)batch * plane;
+  const int grid = ew_grid(ctx, positions, 128);
+  const float aos = alpha / (float)local_size;
+  if (local_size == 5)
+    lrn_fwd_kernel<5><<<grid, 128, 0, ctx->stream>>>(X, Y, scale, positions, depth, plane, aos, beta);
+  else if (local_size == 3)
+    lrn_fwd_kernel<3><<<grid, 128, 0, ctx->stream>>>(X, Y, scale, positions, depth, plane, aos, beta);
+  else
+    lrn_fwd_generic_kernel<<<grid, 128, 0, ctx->stream>>>(X, Y, scale, positions, depth, plane, local_size, aos, beta);
+  CCT_CHECK_LAUNCH(ctx);
+  return CCT_OK;
+}
+
+int cct_lrn_backward(cct_ctx* ctx, const float* X, const float* Y, const float* scale, const float* dY, float* dX,
+                     int batch, int depth, int plane, int local_size, float alpha, float beta) {
+  if (!ctx || !X || !Y || !scale || !dY || !dX || batch <= 0 || depth <= 0 || plane <= 0 || local_size <= 0 ||
+      !(local_size & 1))
+    return CCT_ERR_INVALID;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  const size_t positions = (size_t)batch * plane;
+  lrn_bwd_kernel<<<ew_grid(ctx, positions, 128), 128, 0, ctx->stream>>>(X, Y, scale, dY, dX, positions, depth, plane,
+                                                                       local_size, alpha / (float)local_size, beta);
+  CCT_CHECK_LAUNCH(ctx);
+  return CCT_OK;
+}
+
+int cct_dropout_apply(cct_ctx* ctx, const float* in, const uint32_t* mask, float scale, float* out, size_t count) {
+  if (!ctx || !in || !mask || !out) return CCT_ERR_INVALID;
+  if (!count) return CCT_OK;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  dropout_kernel<<<ew_grid(ctx, count, 256), 256, 0, ctx->stream>>>(in, mask, scale, out, count);
+  CCT_CHECK_LAUNCH(ctx);
+  return CCT_OK;
+}
+
+int cct_dropout_mask(cct_ctx* ctx, uint32_t* mask, size_t count, float ratio, uint64_t seed, uint64_t call) {
+  if (!ctx || !mask || !(ratio >= 0.f && ratio < 1.f)) return CCT_ERR_INVALID;
+  if (!count) return CCT_OK;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  const uint32_t threshold = (uint32_t)std::min(4294967295.0, (double)ratio * 4294967296.0);
+  const uint64_t key = (seed * 0xD1342543DE82EF95ull + 0x632BE59BD9B4E019ull) ^ (call * 0xDA942042E4DD58B5ull);
+  dropout_mask_kernel<<<ew_grid(ctx, count, 256), 256, 0, ctx->stream>>>(mask, count, threshold, key);
+  CCT_CHECK_LAUNCH(ctx);
+  return CCT_OK;
+}
+
+int cct_softmax_loss_forward(cct_ctx* ctx, const float* X, const float* labels, float* prob, float* image_loss,
+                             float* loss, int batch, int classes) {
+  if (!ctx || !X || !labels || !prob || !image_loss || !loss || batch <= 0 || classes <= 0) return CCT_ERR_INVALID;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  softmax_fwd_kernel<<<(batch + 3) / 4, 128, 0, ctx->stream>>>(X, labels, prob, image_loss, batch, classes);
+  CCT_CHECK_LAUNCH(ctx);
+  sum_in_order_kernel<<<1, 32, 0, ctx->stream>>>(image_loss, loss, batch);
+  CCT_CHECK_LAUNCH(ctx);
+  return CCT_OK;
+}
+
+int cct_softmax_loss_backward(cct_ctx* ctx, const float* prob, const float* labels, float* dX, int batch, int classes,
+                              float scale) {
+  if (!ctx || !prob || !labels || !dX || batch <= 0 || classes <= 0) return CCT_ERR_INVALID;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  const size_t total = (size_t)batch * classes;
+  softmax_bwd_kernel<<<ew_grid(ctx, total, 256), 256, 0, ctx->stream>>>(prob, labels, dX, total, classes, scale);
+  CCT_CHECK_LAUNCH(ctx);
+  return CCT_OK;
+}
+
+}  // extern "C"

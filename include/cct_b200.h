@@ -174,6 +174,31 @@ int cct_conv_weight_grad_noalloc(cct_ctx* ctx, const cct_conv_desc* desc, const 
 int cct_conv_plan_enable_timing(cct_conv_plan* plan, int enable);
 int cct_conv_plan_last_timings(cct_conv_plan* plan, float ms[5]);
 
+/* ---- the fully connected bridge: replaces FullyConnectedBridge::forward/backward
+ *      (src/bridges/FullyConnectedBridge_impl.hxx:171-235, 257-330) and the driver calls they make (sgemm_new,
+ *      backward_bias_fc: src/sched/DeviceDriver_GPU.cu:1142-1160).  X is [batch][in_features] (a cube of any R x C x D
+ *      with R*C*D = in_features, flattened as the reference does), W is [out_features][in_features], Y is
+ *      [batch][out_features].  in_features and out_features must be multiples of 4.  The three contractions run as
+ *      3xTF32 on the tensor cores with the operands read in place by TMA (nothing is transposed or packed). ---- */
+typedef struct cct_fc_plan cct_fc_plan;
+int cct_fc_plan_create(cct_ctx* ctx, int batch, int in_features, int out_features, int bias_term, cct_fc_plan** out);
+int cct_fc_plan_destroy(cct_fc_plan* plan);
+int cct_fc_plan_workspace_bytes(const cct_fc_plan* plan, size_t* bytes);
+/* Y = X * W^T + bias.  relu != 0 clamps at 0 (the ReLU bridge behind the layer); drop_mask != NULL then multiplies by
+ * (mask != 0) * drop_scale (DropoutBridge::forward in training, src/bridges/DropoutBridge_impl.hxx:71-74: the mask
+ * holds one unsigned int per output element, drop_scale = 1 / (1 - dropout_ratio)). */
+int cct_fc_forward(cct_fc_plan* plan, const float* X, const float* W, const float* bias, float* Y, int relu,
+                   const uint32_t* drop_mask, float drop_scale);
+/* dW = dY^T * X and db = column sums of dY (both overwritten); dX = dY * W when dX != NULL.  The bridges in front of the
+ * layer can be folded into dX: in_drop_mask != NULL multiplies dX by (mask != 0) * in_drop_scale (DropoutBridge::backward),
+ * in_relu != 0 by [X > 0] (ReLUBridge::backward; X is this layer's input, i.e. the output of those bridges). */
+int cct_fc_backward(cct_fc_plan* plan, const float* X, const float* W, const float* dY, float* dX, float* dW, float* db,
+                    int in_relu, const uint32_t* in_drop_mask, float in_drop_scale);
+/* Per-kernel-group device times of the most recent calls (as cct_conv_plan_last_timings): ms[0] forward, ms[1] weight
+ * and bias gradient, ms[3] data gradient. */
+int cct_fc_plan_enable_timing(cct_fc_plan* plan, int enable);
+int cct_fc_plan_last_timings(cct_fc_plan* plan, float ms[5]);
+
 /* Failure-path self-test (no counterpart in the reference, whose kernels never wait on anything): launches one warp
  * that waits, through the same bounded wait the convolution kernels use, on a barrier nothing completes, with a limit
  * of `limit_cycles` SM clock cycles (at most the kernels' own limit).  The wait runs out, the kernel returns normally,
@@ -196,6 +221,53 @@ int cct_relu_backward(cct_ctx* ctx, const float* X, const float* dY, float* dX, 
  *   dA[plane][h][w] = (A > 0) * sum over windows (ph,pw) covering (h,w) with idx == h*n+w of dP[plane][ph][pw]. */
 int cct_pool_relu_backward(cct_ctx* ctx, const float* A, const int32_t* idx, const float* dP, float* dA, int planes,
                            int n, int k, int s);
+
+/* ---- gradient summation across the partitions of the mini-batch: replaces the device-to-host gather and the serial
+ *      host-side sum of ParallelizedBridge::backward (src/bridges/ParallelizedBridge_impl.hxx:876-971) by an NCCL
+ *      all-reduce(SUM, fp32) over NVLink.  One communicator per context (= per GPU / rank); NCCL is loaded at run time
+ *      the first time a communicator of more than one rank is created.  Rank 0 obtains an id with cct_comm_unique_id and
+ *      hands its bytes to every rank by whatever channel the launcher offers (a file, MPI, a TCP store); every rank then
+ *      calls cct_comm_init_rank (collective: it returns once all ranks have joined).
+ *      cct_allreduce_sum_begin orders the reduction behind the work already queued on the context's stream and runs it
+ *      on the communicator's own stream, so that kernels enqueued afterwards (the backward pass of the layers below)
+ *      overlap it; cct_comm_wait makes the context's stream wait for every reduction begun so far - call it before the
+ *      SGD step that reads the buffers.  cct_allreduce_sum = begin + wait.  nranks == 1 makes all of them no-ops. ---- */
+#define CCT_COMM_ID_BYTES 128
+typedef struct cct_comm cct_comm;
+int cct_comm_unique_id(unsigned char id[CCT_COMM_ID_BYTES]);
+int cct_comm_init_rank(cct_ctx* ctx, int nranks, int rank, const unsigned char id[CCT_COMM_ID_BYTES], cct_comm** out);
+int cct_comm_destroy(cct_comm* comm);
+int cct_comm_size(const cct_comm* comm, int* nranks, int* rank);
+int cct_allreduce_sum_begin(cct_comm* comm, float* buf, size_t count);
+int cct_comm_wait(cct_comm* comm);
+int cct_allreduce_sum(cct_comm* comm, float* buf, size_t count);
+
+/* ---- the other bridges of a CaffeNet iteration, as HBM-bound kernels ---- */
+/* LRNBridge (across channels; src/bridges/LRNBridge_impl.hxx:46-190, src/kernels/lrn.hxx:38-180, exact pow as in the
+ * reference's test build): scale = 1 + (alpha / local_size) * sum over the local_size channels around d of X^2,
+ * Y = X / scale^beta.  X, Y, scale, dY, dX are [batch][depth][plane] with plane = R * C; local_size is odd.
+ * The backward pass needs X, Y and scale of the forward pass. */
+int cct_lrn_forward(cct_ctx* ctx, const float* X, float* Y, float* scale, int batch, int depth, int plane, int local_size,
+                    float alpha, float beta);
+int cct_lrn_backward(cct_ctx* ctx, const float* X, const float* Y, const float* scale, const float* dY, float* dX,
+                     int batch, int depth, int plane, int local_size, float alpha, float beta);
+/* DropoutBridge in training, forward and backward alike (src/bridges/DropoutBridge_impl.hxx:71-74):
+ * out = in * (mask != 0) * scale, one unsigned int of mask per element, scale = 1 / (1 - dropout_ratio).  The mask is
+ * the caller's (the reference draws it on the host, src/bridges/DropoutBridge_impl.hxx:62-66); in == out is allowed. */
+int cct_dropout_apply(cct_ctx* ctx, const float* in, const uint32_t* mask, float scale, float* out, size_t count);
+/* Draws a mask on the device: element i is 1 with probability 1 - ratio (as GPUDriver::rand_uint_initialize followed by
+ * the threshold test does, src/bridges/DropoutBridge_impl.hxx:100-104).  Counter-based: (seed, call) fixes the mask,
+ * whatever the launch shape; use a new `call` value every iteration. */
+int cct_dropout_mask(cct_ctx* ctx, uint32_t* mask, size_t count, float ratio, uint64_t seed, uint64_t call);
+/* SoftmaxLossBridge (src/kernels/softmax.hxx:17-80; host-only in the reference): prob[b][c] = softmax of X[b][:],
+ * *loss = sum over images of -log(max(prob[b][label], FLT_MIN)) (image_loss: `batch` floats of scratch that receive
+ * the per-image terms).  labels holds one float per image, as the reference's label cube does.  The backward pass
+ * writes dX = (prob - onehot(label)) * scale; the reference uses scale = 1 / batch (with data parallelism: the batch
+ * of the whole job, so that the partitions' gradients add up). */
+int cct_softmax_loss_forward(cct_ctx* ctx, const float* X, const float* labels, float* prob, float* image_loss,
+                             float* loss, int batch, int classes);
+int cct_softmax_loss_backward(cct_ctx* ctx, const float* prob, const float* labels, float* dX, int batch, int classes,
+                              float scale);
 
 /* ---- parameter update: SGDGradientUpdater::update (src/algorithms/GradientUpdater.h:154-193) as one kernel:
  *      g += lambda*w (if lambda != 0);  h = lr*g + momentum*h;  w -= h. ---- */

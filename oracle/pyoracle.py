@@ -133,6 +133,15 @@ class Reference:
         L.cctref_relu.argtypes = [C.c_int] * 3 + [_fp, _fp, _fp, _fp]
         L.cctref_blas_config.restype = C.c_char_p
         L.cctref_default_partitions.argtypes = [C.c_int]
+        _up = C.POINTER(C.c_uint)
+        for name, args in (("cctref_lrn", [C.c_int] * 4 + [C.c_float] * 2 + [_fp] * 4 + [C.c_int]),
+                           ("cctref_dropout", [C.c_int] * 3 + [C.c_float, C.c_int, _fp, _fp, _up, _fp, _fp, C.c_int]),
+                           ("cctref_fc", [C.c_int] * 4 + [_fp] * 8 + [C.c_int] * 2),
+                           ("cctref_softmax_loss", [C.c_int] * 2 + [_fp] * 5 + [C.c_int])):
+            fn = getattr(L, name, None)
+            if fn is not None:  # a library built before these wrappers existed lacks them
+                fn.argtypes = args
+                fn.restype = C.c_double
 
     def hardware_concurrency(self):
         return int(self.lib.cctref_hardware_concurrency())
@@ -217,12 +226,100 @@ class Reference:
         self.lib.cctref_maxpool(B, D, n, k, s, _p(X), _p(Y), _p(idx), _p(dY), _p(dX))
         return Y, idx, dX
 
+    def lrn(self, X, local_size, alpha, beta, dY=None, time_iters=0):
+        """Y, dX (None without dY), median seconds of fwd(+bwd) when time_iters > 0."""
+        B, D, n, _ = X.shape
+        Y = np.empty_like(X)
+        dX = np.empty_like(X) if dY is not None else None
+        sec = self.lib.cctref_lrn(B, D, n, local_size, alpha, beta, _p(X), _p(Y), _p(dY), _p(dX), time_iters)
+        return Y, dX, sec
+
+    def dropout(self, X, ratio, seed, dY=None, time_iters=0):
+        """Y, the mask the bridge drew (uint32, 0 / 1), dX, seconds."""
+        B, D, n, _ = X.shape
+        Y = np.empty_like(X)
+        mask = np.empty(X.shape, np.uint32)
+        dX = np.empty_like(X) if dY is not None else None
+        sec = self.lib.cctref_dropout(B, D, n, ratio, seed, _p(X), _p(Y), mask.ctypes.data_as(C.POINTER(C.c_uint)),
+                                      _p(dY), _p(dX), time_iters)
+        return Y, mask, dX, sec
+
+    def fc(self, X, W, bias, dY=None, blas_threads=1, time_iters=0):
+        """Y, dX, dW, db, seconds through the reference's FullyConnectedBridge."""
+        B, D, n, _ = X.shape
+        o = W.shape[0]
+        Y = np.empty((B, o, 1, 1), _f)
+        dX = np.empty_like(X) if dY is not None else None
+        dW = np.empty_like(W) if dY is not None else None
+        db = np.empty((o,), _f) if (dY is not None and bias is not None) else None
+        sec = self.lib.cctref_fc(B, D, n, o, _p(X), _p(W), _p(bias), _p(Y), _p(dY), _p(dX), _p(dW), _p(db), blas_threads,
+                                 time_iters)
+        return Y, dX, dW, db, sec
+
+    def softmax_loss(self, X, labels, time_iters=0):
+        """prob, loss (summed over the batch), dX (scaled by 1 / batch), seconds."""
+        B = X.shape[0]
+        Cn = X.size // B
+        prob, dX = np.empty_like(X), np.empty_like(X)
+        loss = C.c_float()
+        lab = np.ascontiguousarray(labels, dtype=_f)
+        sec = self.lib.cctref_softmax_loss(B, Cn, _p(X), _p(lab), _p(prob), C.byref(loss), _p(dX), time_iters)
+        return prob, float(loss.value), dX, sec
+
     def relu(self, X, dY=None):
         B, D, n, _ = X.shape
         Y = np.empty_like(X)
         dX = np.empty_like(X) if dY is not None else None
         self.lib.cctref_relu(B, D, n, _p(X), _p(Y), _p(dY), _p(dX))
         return Y, dX
+
+
+# ---- numpy restatements of the remaining CaffeNet bridges (float64 inside, so they can serve as the "truth" side)
+
+def np_lrn_forward(X, local_size, alpha, beta):
+    """LRNBridge::forward (src/kernels/lrn.hxx:38-124): scale = 1 + alpha/size * sum of squares over the window of
+    local_size channels; Y = X / scale^beta.  Returns (Y, scale) as float32."""
+    X64 = X.astype(np.float64)
+    B, D = X.shape[:2]
+    w = local_size // 2
+    sq = X64 * X64
+    ssum = np.zeros_like(X64)
+    for d in range(D):
+        ssum[:, d] = sq[:, max(0, d - w):min(D, d + w + 1)].sum(axis=1)
+    scale = 1.0 + (alpha / local_size) * ssum
+    return (X64 / scale ** beta).astype(_f), scale.astype(_f)
+
+
+def np_lrn_backward(X, dY, local_size, alpha, beta):
+    """LRNBridge::backward (src/kernels/lrn.hxx:134-180), collected per input channel."""
+    X64, dY64 = X.astype(np.float64), dY.astype(np.float64)
+    B, D = X.shape[:2]
+    w = local_size // 2
+    sq = X64 * X64
+    scale = np.ones_like(X64)
+    for d in range(D):
+        scale[:, d] += (alpha / local_size) * sq[:, max(0, d - w):min(D, d + w + 1)].sum(axis=1)
+    t = dY64 * X64 * scale ** (-beta - 1.0)
+    dX = dY64 * scale ** (-beta)
+    for c in range(D):
+        dX[:, c] -= 2.0 * beta * (alpha / local_size) * X64[:, c] * t[:, max(0, c - w):min(D, c + w + 1)].sum(axis=1)
+    return dX.astype(_f)
+
+
+def np_softmax_loss(X, labels, scale=None):
+    """SoftmaxLossBridge (src/kernels/softmax.hxx:17-80): prob, summed loss, gradient (prob - onehot) * scale
+    (scale defaults to 1 / batch)."""
+    B = X.shape[0]
+    X64 = X.reshape(B, -1).astype(np.float64)
+    e = np.exp(X64 - X64.max(axis=1, keepdims=True))
+    prob = e / e.sum(axis=1, keepdims=True)
+    lab = labels.astype(np.int64).reshape(B)
+    tiny = np.finfo(np.float32).tiny
+    loss = float(-np.log(np.maximum(prob[np.arange(B), lab], tiny)).sum())
+    g = prob.copy()
+    g[np.arange(B), lab] -= 1.0
+    g *= (1.0 / B) if scale is None else scale
+    return prob.astype(_f).reshape(X.shape), loss, g.astype(_f).reshape(X.shape)
 
 
 _port = None

@@ -6,6 +6,7 @@
 //   ParallelizedBridge<float, ConvolutionBridge>  (src/bridges/ParallelizedBridge.h:303-320)
 //   ConvolutionBridge<..., CPUDriver>             (src/bridges/ConvolutionBridge_impl.hxx:294-373, 551-628)
 //   MaxPoolingBridge / ReLUBridge                 (src/bridges/MaxPoolingBridge_impl.hxx, ReLUBridge_impl.hxx)
+//   LRNBridge / DropoutBridge / FullyConnectedBridge / SoftmaxLossBridge   (src/bridges/*_impl.hxx)
 // and copies caller buffers in and out of the reference's cubes.  Only tests, the smoke check and the
 // CPU-baseline leg of the benchmark may load the resulting library.
 #include <chrono>
@@ -18,6 +19,10 @@
 #include "bridges/ConvolutionBridge.h"
 #include "bridges/MaxPoolingBridge.h"
 #include "bridges/ReLUBridge.h"
+#include "bridges/LRNBridge.h"
+#include "bridges/DropoutBridge.h"
+#include "bridges/FullyConnectedBridge.h"
+#include "bridges/SoftmaxLossBridge.h"
 
 namespace {
 
@@ -44,6 +49,25 @@ struct PoolWithIndex : MaxPoolingBridge<float, Layout_CRDB, float, Layout_CRDB, 
 
 double now_s() {
   return std::chrono::duration<double>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+
+// Runs fwd (+ bwd when `with_backward`) of a bridge once for the results, then `iters` more times for the clock;
+// returns the median seconds of one fwd+bwd pair (0 when iters == 0).
+template <class Bridge>
+static double run_and_time(Bridge& br, bool with_backward, int iters, void (*after_first)(void*), void* arg) {
+  br.forward();
+  if (with_backward) br.backward();
+  if (after_first) after_first(arg);
+  std::vector<double> tt;
+  for (int i = 0; i < iters; ++i) {
+    const double t0 = now_s();
+    br.forward();
+    if (with_backward) br.backward();
+    tt.push_back(now_s() - t0);
+  }
+  if (tt.empty()) return 0.0;
+  std::sort(tt.begin(), tt.end());
+  return tt[tt.size() / 2];
 }
 
 }  // namespace
@@ -211,4 +235,102 @@ void cctref_relu(int B, int D, int n, const float* X, float* Y, const float* dY,
   }
 }
 
+// Across-channel LRN through the reference bridge: Y from X, then dX from dY (pass dY == NULL to skip).
+double cctref_lrn(int B, int D, int n, int local_size, float alpha, float beta, const float* X, float* Y,
+                  const float* dY, float* dX, int time_iters) {
+  Cube &x = *new Cube(n, n, D, B), &dx = *new Cube(n, n, D, B), &y = *new Cube(n, n, D, B), &dy = *new Cube(n, n, D, B);
+  CubeLayer lin(&x, &dx), lout(&y, &dy);
+  cnn::LayerParameter lp;
+  lp.lrn_.local_size_ = local_size; lp.lrn_.alpha_ = alpha; lp.lrn_.beta_ = beta;
+  cnn::SolverParameter sp;
+  CPUDriver drv;
+  LRNBridge<float, Layout_CRDB, float, Layout_CRDB, CPUDriver> br(&lin, &lout, &lp, &sp, &drv);
+  std::memcpy(x.get_p_data(), X, sizeof(float) * x.n_elements);
+  if (dY) std::memcpy(dy.get_p_data(), dY, sizeof(float) * dy.n_elements);
+  br.forward();
+  std::memcpy(Y, y.get_p_data(), sizeof(float) * y.n_elements);
+  if (dY && dX) {
+    br.backward();
+    std::memcpy(dX, dx.get_p_data(), sizeof(float) * dx.n_elements);
+  }
+  return time_iters > 0 ? run_and_time(br, dY != NULL, time_iters, NULL, NULL) : 0.0;
+}
+
+// Dropout (training phase) through the reference bridge: the bridge draws its own mask from mt19937(seed); the mask
+// it used is returned so that the same one can be given to the implementation under test.
+double cctref_dropout(int B, int D, int n, float ratio, int seed, const float* X, float* Y, unsigned int* mask,
+                      const float* dY, float* dX, int time_iters) {
+  Cube &x = *new Cube(n, n, D, B), &dx = *new Cube(n, n, D, B), &y = *new Cube(n, n, D, B), &dy = *new Cube(n, n, D, B);
+  CubeLayer lin(&x, &dx), lout(&y, &dy);
+  cnn::LayerParameter lp;
+  lp.dropout_.ratio_ = ratio;
+  cnn::SolverParameter sp;
+  sp.random_seed_ = seed;
+  CPUDriver drv;
+  DropoutBridge<float, Layout_CRDB, float, Layout_CRDB, CPUDriver> br(&lin, &lout, &lp, &sp, &drv);
+  std::memcpy(x.get_p_data(), X, sizeof(float) * x.n_elements);
+  br.forward();
+  std::memcpy(Y, y.get_p_data(), sizeof(float) * y.n_elements);
+  if (mask) std::memcpy(mask, br.mask_cube->get_p_data(), sizeof(unsigned int) * x.n_elements);
+  if (dY && dX) {
+    std::memcpy(dy.get_p_data(), dY, sizeof(float) * dy.n_elements);
+    br.backward();
+    std::memcpy(dX, dx.get_p_data(), sizeof(float) * dx.n_elements);
+  }
+  return time_iters > 0 ? run_and_time(br, dY != NULL, time_iters, NULL, NULL) : 0.0;
+}
+
+// Fully connected layer through the reference bridge (no SGD step: the bare bridge has no updater).
+double cctref_fc(int B, int D, int n, int o, const float* X, const float* W, const float* bias, float* Y, const float* dY,
+                 float* dX, float* dW, float* db, int blas_threads, int time_iters) {
+  Cube &x = *new Cube(n, n, D, B), &dx = *new Cube(n, n, D, B), &y = *new Cube(1, 1, o, B), &dy = *new Cube(1, 1, o, B);
+  CubeLayer lin(&x, &dx), lout(&y, &dy);
+  cnn::LayerParameter lp;
+  lp.ip_.num_output_ = o;
+  lp.ip_.bias_term_ = bias != NULL;
+  cnn::SolverParameter sp;
+  sp.random_seed_ = 1;
+  CPUDriver drv;
+  std::streambuf* keep = std::cout.rdbuf(nullptr);
+  FullyConnectedBridge<float, Layout_CRDB, float, Layout_CRDB, CPUDriver> br(&lin, &lout, &lp, &sp, &drv);
+  std::cout.rdbuf(keep);
+  std::cout.clear();
+  br.run_with_n_threads = blas_threads > 0 ? blas_threads : 1;
+  std::memcpy(br.get_model_cube()->get_p_data(), W, sizeof(float) * (size_t)o * D * n * n);
+  if (bias) std::memcpy(br.get_bias_cube()->get_p_data(), bias, sizeof(float) * o);
+  std::memcpy(x.get_p_data(), X, sizeof(float) * x.n_elements);
+  br.forward();
+  if (Y) std::memcpy(Y, y.get_p_data(), sizeof(float) * y.n_elements);
+  if (dY) {
+    std::memcpy(dy.get_p_data(), dY, sizeof(float) * dy.n_elements);
+    br.backward();
+    if (dX) std::memcpy(dX, dx.get_p_data(), sizeof(float) * dx.n_elements);
+    if (dW) std::memcpy(dW, br.get_model_grad_cube()->get_p_data(), sizeof(float) * (size_t)o * D * n * n);
+    if (db && bias) std::memcpy(db, br.get_bias_grad_cube()->get_p_data(), sizeof(float) * o);
+  }
+  return time_iters > 0 ? run_and_time(br, dY != NULL, time_iters, NULL, NULL) : 0.0;
+}
+
+// Softmax with loss through the reference bridge: prob (the bridge's output cube), the summed loss, and the gradient
+// with respect to the input (scaled by 1 / B as the bridge does).
+double cctref_softmax_loss(int B, int C, const float* X, const float* labels, float* prob, float* loss, float* dX,
+                           int time_iters) {
+  Cube &x = *new Cube(1, 1, C, B), &dx = *new Cube(1, 1, C, B), &y = *new Cube(1, 1, C, B), &dy = *new Cube(1, 1, C, B);
+  CubeLayer lin(&x, &dx), lout(&y, &dy);
+  Cube lab(1, 1, 1, B);
+  CPUDriver drv;
+  SoftmaxLossBridge<float, Layout_CRDB, float, Layout_CRDB, CPUDriver> br(&lin, &lout, &lab, &drv);
+  std::memcpy(x.get_p_data(), X, sizeof(float) * x.n_elements);
+  std::memcpy(lab.get_p_data(), labels, sizeof(float) * B);
+  br.forward();
+  if (prob) std::memcpy(prob, y.get_p_data(), sizeof(float) * y.n_elements);
+  if (loss) *loss = br.get_loss();
+  if (dX) {
+    br.backward();
+    std::memcpy(dX, dx.get_p_data(), sizeof(float) * dx.n_elements);
+  }
+  return time_iters > 0 ? run_and_time(br, dX != NULL, time_iters, NULL, NULL) : 0.0;
+}
+
 }  // extern "C"
+
