@@ -18,7 +18,7 @@ _ERR_NAMES = {1: "CCT_ERR_INVALID", 2: "CCT_ERR_CUDA", 3: "CCT_ERR_NOMEM", 4: "C
 EXPORTS = [
     "cct_ctx_create", "cct_ctx_create_on_stream", "cct_ctx_destroy", "cct_sync", "cct_last_error_string",
     "cct_device_count", "cct_malloc", "cct_free", "cct_malloc_host", "cct_free_host", "cct_memcpy_h2d",
-    "cct_memcpy_d2h", "cct_memcpy_d2d", "cct_memset", "cct_fill_f32", "cct_conv_plan_create",
+    "cct_memcpy_d2h", "cct_memcpy_d2d", "cct_memset", "cct_fill_f32", "cct_fill_random", "cct_conv_plan_create",
     "cct_conv_plan_destroy", "cct_conv_out_size", "cct_conv_plan_algo", "cct_conv_plan_workspace_bytes",
     "cct_conv_plan_enable_timing", "cct_conv_plan_last_timings", "cct_conv_forward", "cct_conv_backward", "cct_conv_backward_fused",
     "cct_conv_plan_reserve_fusion", "cct_selftest_bounded_wait", "cct_conv_forward_host", "cct_conv_backward_host", "cct_conv_weight_grad_noalloc",
@@ -78,6 +78,7 @@ def load():
         "cct_memcpy_d2d": [_vp, _vp, _vp, sz],
         "cct_memset": [_vp, _vp, i, sz],
         "cct_fill_f32": [_vp, _vp, sz, f],
+        "cct_fill_random": [_vp, _vp, sz, i, f, f, C.c_long],
         "cct_conv_plan_create": [_vp, C.POINTER(ConvDesc), C.POINTER(_vp)],
         "cct_conv_plan_destroy": [_vp],
         "cct_conv_out_size": [C.POINTER(ConvDesc), C.POINTER(i)],

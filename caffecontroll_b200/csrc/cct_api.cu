@@ -3,6 +3,9 @@
 #include <new>
 
 #include <algorithm>
+#include <cmath>
+#include <random>
+#include <vector>
 
 #include "cct_internal.h"
 
@@ -243,6 +246,33 @@ int cct_memset(cct_ctx* ctx, void* dptr, int byte_value, size_t bytes) {
   if (!bytes) return CCT_OK;
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
   CCT_CUDA(ctx, cudaMemsetAsync(dptr, byte_value, bytes, ctx->stream));
+  return CCT_OK;
+}
+
+// The reference's fillers run on the host with the C++ standard generators (CPUDriver::sgaussian_initialize,
+// sinitialize_xavier, sbernoulli_initialize: src/sched/DeviceDriver_CPU.cpp:661-699); the same calls here produce
+// the same numbers for the same seed, and the result is uploaded.
+int cct_fill_random(cct_ctx* ctx, float* dptr, size_t count, int kind, float a, float b, long seed) {
+  if (!ctx || (!dptr && count) || kind < CCT_FILL_GAUSSIAN || kind > CCT_FILL_BERNOULLI) return CCT_ERR_INVALID;
+  if (!count) return CCT_OK;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  std::vector<float> host(count);
+  std::random_device rd;
+  std::mt19937 gen(seed == -1 ? rd() : (unsigned)seed);
+  if (kind == CCT_FILL_GAUSSIAN) {
+    std::normal_distribution<float> dist(a, b);
+    for (size_t i = 0; i < count; ++i) host[i] = dist(gen);
+  } else if (kind == CCT_FILL_XAVIER) {
+    if (!(a > 0.f)) return CCT_ERR_INVALID;
+    const float scale = (float)std::sqrt(3.0 / (size_t)a);
+    std::uniform_real_distribution<float> dist(-scale, scale);
+    for (size_t i = 0; i < count; ++i) host[i] = dist(gen);
+  } else {
+    std::bernoulli_distribution dist(a);
+    for (size_t i = 0; i < count; ++i) host[i] = dist(gen);
+  }
+  CCT_CUDA(ctx, cudaMemcpyAsync(dptr, host.data(), count * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+  CCT_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // `host` goes out of scope
   return CCT_OK;
 }
 

@@ -62,6 +62,15 @@ int cct_memcpy_d2d(cct_ctx* ctx, void* dst, const void* src, size_t bytes);
 int cct_memset(cct_ctx* ctx, void* dptr, int byte_value, size_t bytes);
 /* DeviceDriver::sconstant_initialize (src/sched/DeviceDriver.h:236, DeviceDriver_GPU.cu:1189-1200). */
 int cct_fill_f32(cct_ctx* ctx, float* dptr, size_t count, float value);
+/* The weight / bias fillers a bridge constructor applies (ConvolutionBridge::initialize_logical_cube,
+ * src/bridges/ConvolutionBridge_impl.hxx:250-267; CPUDriver::sgaussian_initialize, sinitialize_xavier,
+ * sbernoulli_initialize, src/sched/DeviceDriver_CPU.cpp:661-699): std::mt19937(seed) feeding the standard
+ * distributions on the host, uploaded to dptr; seed == -1 takes a random seed (solver.random_seed's default).
+ *   CCT_FILL_GAUSSIAN : a = mean, b = std            CCT_FILL_XAVIER : a = fan_in (elements / n_batch), uniform in
+ *   +-sqrt(3 / fan_in)                               CCT_FILL_BERNOULLI : a = p
+ * With the same C++ standard library the values equal the reference's for the same seed ("constant" is cct_fill_f32). */
+enum { CCT_FILL_GAUSSIAN = 0, CCT_FILL_XAVIER = 1, CCT_FILL_BERNOULLI = 2 };
+int cct_fill_random(cct_ctx* ctx, float* dptr, size_t count, int kind, float a, float b, long seed);
 
 /* ---- the convolution bridge: replaces ConvolutionBridge::forward/backward
  *      (src/bridges/ConvolutionBridge_impl.hxx:294-500, 551-773) together with the driver entry points they

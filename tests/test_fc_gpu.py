@@ -49,7 +49,7 @@ def _run(ctx, X, W, b, dY, algo, relu=False, mask=None, scale=1.0, in_relu=False
     fc.forward()
     fc.backward()
     ctx.sync()
-    res = (out.p_data_cube.download(), xin.p_gradient_cube.download(), fc.p_model_gradient_cube.download(),
+    res = (out.p_data_cube.download(), xin.p_gradient_cube.download(), fc.p_model_gradient_cube.download().reshape(W.shape),
            fc.p_bias_gradient_cube.download().reshape(-1) if b is not None else None, fc.algo)
     fc.close()
     for layer in (xin, out):
