@@ -443,6 +443,350 @@ def run_conv_stack(args, rank, world, local_rank):
     ctx.close()
 
 
+def caffenet_layer_table():
+    """(name, kind, geometry) of every CaffeNet layer at the bench's shapes, for the reference arm."""
+    return [
+        ("conv1", "conv", dict(D=3, n=227, o=96, k=11, s=4, p=0, g=1, needs_dx=False)),
+        ("relu1", "relu", dict(D=96, n=55)), ("pool1", "pool", dict(D=96, n=55)), ("norm1", "lrn", dict(D=96, n=27)),
+        ("conv2", "conv", dict(D=96, n=27, o=256, k=5, s=1, p=2, g=2, needs_dx=True)),
+        ("relu2", "relu", dict(D=256, n=27)), ("pool2", "pool", dict(D=256, n=27)), ("norm2", "lrn", dict(D=256, n=13)),
+        ("conv3", "conv", dict(D=256, n=13, o=384, k=3, s=1, p=1, g=1, needs_dx=True)), ("relu3", "relu", dict(D=384, n=13)),
+        ("conv4", "conv", dict(D=384, n=13, o=384, k=3, s=1, p=1, g=2, needs_dx=True)), ("relu4", "relu", dict(D=384, n=13)),
+        ("conv5", "conv", dict(D=384, n=13, o=256, k=3, s=1, p=1, g=2, needs_dx=True)), ("relu5", "relu", dict(D=256, n=13)),
+        ("pool5", "pool", dict(D=256, n=13)),
+        ("fc6", "fc", dict(D=256, n=6, o=4096)), ("relu6", "relu", dict(D=4096, n=1)), ("drop6", "dropout", dict(D=4096, n=1)),
+        ("fc7", "fc", dict(D=4096, n=1, o=4096)), ("relu7", "relu", dict(D=4096, n=1)), ("drop7", "dropout", dict(D=4096, n=1)),
+        ("fc8", "fc", dict(D=4096, n=1, o=1000)), ("loss", "softmax", dict(D=1000, n=1)),
+    ]
+
+
+def caffenet_reference_seconds(B, iters, log=None):
+    """Seconds of one CaffeNet iteration (forward + backward of every layer) on the host cores through the reference's
+    own CPU bridges, one bridge at a time on synthetic tensors of the layer's shapes: convolutions through its
+    ParallelizedBridge with the partition count DeepNet uses (grouped layers as one bridge per channel slice - the
+    reference bridge has no group concept), fully connected layers with all hardware threads in BLAS as DeepNet gives
+    them, the parameter-free bridges as plain bridges.  Median of `iters` passes per layer; returns (total, per layer)."""
+    from oracle import pyoracle
+    ref = pyoracle.reference()
+    if ref is None:
+        return None, None
+    rng = np.random.default_rng(99)
+    parts = ref.default_partitions(B)
+    hc = ref.hardware_concurrency()
+    per = {}
+    for name, kind, g in caffenet_layer_table():
+        D, n = g["D"], g["n"]
+        X = np.maximum(rng.standard_normal((B, D, n, n), dtype=np.float32), 0) if name != "conv1" else \
+            rng.standard_normal((B, D, n, n), dtype=np.float32)
+        if kind == "conv":
+            o, k, s_, p_, grp = g["o"], g["k"], g["s"], g["p"], g["g"]
+            m = (n + 2 * p_ - k) // s_ + 1
+            W = (0.01 * rng.standard_normal((o, D // grp, k, k))).astype(np.float32)
+            bias = np.zeros(o, np.float32)
+            dY = rng.standard_normal((B, o, m, m), dtype=np.float32)
+            Dg, og = D // grp, o // grp
+            sec = 0.0
+            for gi in range(grp):
+                sec += ref.conv_time(np.ascontiguousarray(X[:, gi * Dg:(gi + 1) * Dg]), np.ascontiguousarray(W[gi * og:(gi + 1) * og]),
+                                     np.ascontiguousarray(bias[gi * og:(gi + 1) * og]),
+                                     np.ascontiguousarray(dY[:, gi * og:(gi + 1) * og]), k, s_, p_, parts, g["needs_dx"], 1, iters)[0]
+        elif kind == "relu":
+            t0 = time.perf_counter()
+            for _ in range(iters):
+                ref.relu(X, dY=X)
+            sec = (time.perf_counter() - t0) / iters
+        elif kind == "pool":
+            m = (n - 3) // 2 + 1
+            dY = rng.standard_normal((B, D, m, m), dtype=np.float32)
+            t0 = time.perf_counter()
+            for _ in range(iters):
+                ref.maxpool(X, 3, 2, dY=dY)
+            sec = (time.perf_counter() - t0) / iters
+        elif kind == "lrn":
+            sec = ref.lrn(X, 5, 1e-4, 0.75, dY=X, time_iters=iters)[2]
+        elif kind == "fc":
+            o = g["o"]
+            W = (0.01 * rng.standard_normal((o, D, n, n))).astype(np.float32)
+            dY = rng.standard_normal((B, o, 1, 1), dtype=np.float32)
+            sec = ref.fc(X, W, np.ones(o, np.float32), dY=dY, blas_threads=hc, time_iters=iters)[4]
+        elif kind == "dropout":
+            sec = ref.dropout(X, 0.5, 1, dY=X, time_iters=iters)[3]
+        else:
+            labels = rng.integers(0, D, B).astype(np.float32)
+            sec = ref.softmax_loss(X, labels, time_iters=iters)[3]
+        per[name] = sec
+        if log:
+            log("  reference %-6s %8.1f ms" % (name, sec * 1e3))
+    return sum(per.values()), per
+
+
+def run_caffenet(args, rank, world, local_rank):
+    """BASELINE configs 4 (one GPU) and 5 (2 / 4 / 8 GPUs): one CaffeNet training iteration - forward, backward, gradient
+    all-reduce over NCCL (N > 1), SGD momentum step - at batch 256 per GPU on synthetic 3 x 227 x 227 images, built from
+    the package's prototxt by the network builder."""
+    import torch
+    import torch.distributed as dist
+    from caffecontroll_b200 import capi
+    from caffecontroll_b200.bridge import Context, LogicalCube
+    from caffecontroll_b200.net import Net, parse_prototxt, solver_from_message
+    from caffecontroll_b200.parallel import Communicator, DeviceOps
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    B = args.batch or 256
+    if world > 1:
+        # torch.distributed (gloo, host side) only carries the NCCL id and the timing reductions; the gradient sums are
+        # NCCL all-reduces issued by the library's own communicator
+        dist.init_process_group("gloo")
+    stream = torch.cuda.current_stream()
+    ctx = Context(local_rank, stream=stream.cuda_stream)
+    comm = None
+    if world > 1:
+        ids = [Communicator.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        comm = Communicator(ctx, world, rank, ids[0])
+    ops = DeviceOps(ctx, comm=comm)
+    nets_dir = os.path.join(ROOT, "caffecontroll_b200", "nets")
+    with open(os.path.join(nets_dir, "caffenet_train.prototxt")) as f:
+        net_param = parse_prototxt(f.read())
+    with open(os.path.join(nets_dir, "caffenet_solver.prototxt")) as f:
+        solver = solver_from_message(parse_prototxt(f.read()))
+    net = Net(ctx, net_param, solver, B, ops=ops, loss_batch=B * world, algo=args.algo)
+    rng = np.random.default_rng(5000 + rank)
+    X = rng.standard_normal((B, 3, 227, 227), dtype=np.float32)
+    labels = rng.integers(0, 1000, B).astype(np.float32)
+    net.set_input(X, labels)
+    flops = net.flops_forward + net.flops_backward
+    lib, vp = ctx.lib, C.c_void_p
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    roof = tensor_roofline(load_peaks(), measure=(rank == 0))
+    warm_steps = preheat(net.step, args.warmup, args.preheat_s, stream, 1, dev)
+    loss0 = net.get_loss()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for _ in range(args.steps):
+        net.step()
+    e1.record(stream)
+    barrier()
+    ms_step = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+    loss1 = net.get_loss()
+
+    # ---- per-layer device times: the same steps again with events around every bridge pass
+    prof_steps = max(1, min(args.steps, 5))
+    names = net.names
+    fwd_ms, bwd_ms = np.zeros(len(names)), np.zeros(len(names))
+    plan_ms = {}
+    for i, br in enumerate(net.bridges):
+        if net.types[i] == "Convolution":
+            lib.cct_conv_plan_enable_timing(br.plan, 1)
+        elif net.types[i] == "InnerProduct" and br.plan:
+            lib.cct_fc_plan_enable_timing(br.plan, 1)
+    upd_ms = 0.0
+    for _ in range(prof_steps):
+        evs = []
+        for i, br in enumerate(net.bridges):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream); br.forward(); b.record(stream)
+            evs.append(("f", i, a, b))
+        for i in range(len(net.bridges) - 1, -1, -1):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            (net.pbridges[i] if i in net.pbridges else net.bridges[i]).backward()
+            b.record(stream)
+            evs.append(("b", i, a, b))
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        ops.allreduce_wait()
+        for i in sorted(net.pbridges, reverse=True):
+            net.pbridges[i].apply_update()
+        b.record(stream)
+        torch.cuda.synchronize()
+        upd_ms += a.elapsed_time(b)
+        for kind, i, a, b in evs:
+            (fwd_ms if kind == "f" else bwd_ms)[i] += a.elapsed_time(b)
+        for i, br in enumerate(net.bridges):
+            t5 = (C.c_float * 5)()
+            if net.types[i] == "Convolution":
+                lib.cct_conv_plan_last_timings(br.plan, t5)
+            elif net.types[i] == "InnerProduct" and br.plan:
+                lib.cct_fc_plan_last_timings(br.plan, t5)
+            else:
+                continue
+            plan_ms[i] = plan_ms.get(i, np.zeros(5)) + np.array(list(t5))
+    fwd_ms /= prof_steps; bwd_ms /= prof_steps; upd_ms /= prof_steps
+    layers, contraction = {}, []
+    hbm = load_peaks()["hbm_gbs"]
+    for i, name in enumerate(names):
+        rec = {"type": net.types[i], "forward_ms": float(fwd_ms[i]), "backward_ms": float(bwd_ms[i])}
+        if i in plan_ms:
+            k = plan_ms[i] / prof_steps
+            br = net.bridges[i]
+            F = (2.0 * br.oD * (br.K * br.K * br.iD // br.group) * br.oR * br.oC * B if net.types[i] == "Convolution"
+                 else 2.0 * br.oD * br.in_features * B)
+            rec.update(forward_kernel_ms=float(k[0]), wgrad_kernel_ms=float(k[1] + k[2]), dgrad_kernel_ms=float(k[3]),
+                       gflop_per_pass=F / 1e9)
+            for pname, ms in (("forward", k[0]), ("wgrad", k[1] + k[2]), ("dgrad", k[3])):
+                if ms > 0:
+                    rec[pname + "_tflops"] = F / (ms * 1e-3) / 1e12
+                    contraction.append((ms, F, "%s %s" % (name, pname)))
+        layers[name] = rec
+    dom_ms, dom_F, dom_name = max(contraction) if contraction else (0.0, 0.0, "")
+    hbm_passes = {}
+    for i, name in enumerate(names):  # the HBM-bound bridges: algorithmic bytes over measured time
+        br, t = net.bridges[i], net.types[i]
+        n_in = br.iB * br.iD * br.iR * br.iC
+        n_out = br.oB * br.oD * br.oR * br.oC
+        if t == "Pooling":
+            hbm_passes[name + " forward"] = (4.0 * n_in + 8.0 * n_out, fwd_ms[i])
+        elif t == "LRN":
+            hbm_passes[name + " forward"] = (12.0 * n_in, fwd_ms[i])
+            hbm_passes[name + " backward"] = (20.0 * n_in, bwd_ms[i])
+    hbm_table = {k: {"ms": float(ms), "bytes": b, "achieved_gbs": b / ms / 1e6, "frac": b / ms / 1e6 / hbm}
+                 for k, (b, ms) in hbm_passes.items() if ms > 0}
+
+    # ---- end to end: every step uploads its images and labels from pinned host memory and reads the loss back
+    hX = torch.from_numpy(X).pin_memory()
+    hL = torch.from_numpy(labels).pin_memory()
+    copy_stream = torch.cuda.Stream()
+    cctx = Context(local_rank, stream=copy_stream.cuda_stream)
+    stage = [LogicalCube(ctx, 227, 227, 3, B), LogicalCube(ctx, 227, 227, 3, B)]
+    stage_l = [LogicalCube(ctx, 1, 1, 1, B), LogicalCube(ctx, 1, 1, 1, B)]
+    main_ptr, main_labels_ptr = net.input.p_data_cube.ptr, net.labels.ptr
+    up_done = [torch.cuda.Event(), torch.cuda.Event()]
+    used = [torch.cuda.Event(), torch.cuda.Event()]
+
+    def upload(slot):  # next batch -> staging buffer `slot`, on the copy stream
+        copy_stream.wait_event(used[slot])
+        capi.check(lib.cct_memcpy_h2d(cctx.h, vp(stage[slot].ptr), vp(hX.data_ptr()), X.nbytes), "h2d", cctx.h)
+        capi.check(lib.cct_memcpy_h2d(cctx.h, vp(stage_l[slot].ptr), vp(hL.data_ptr()), labels.nbytes), "h2d", cctx.h)
+        up_done[slot].record(copy_stream)
+
+    def e2e_step(slot):
+        stream.wait_event(up_done[slot])
+        net.input.p_data_cube.ptr, net.labels.ptr = stage[slot].ptr, stage_l[slot].ptr
+        net.loss_bridge.p_data_labels = net.labels
+        net.step()
+        used[slot].record(stream)
+        upload(slot ^ 1)  # the next step's batch travels while this step computes
+        return net.get_loss()  # device -> host read of the step's result
+
+    for e in used:
+        e.record(stream)
+    upload(0)
+    e2e_step(0)
+    barrier()
+    t0 = time.perf_counter()
+    for it in range(args.e2e_steps):
+        e2e_step((it + 1) & 1)
+    torch.cuda.synchronize()
+    e2e_s = max_over_ranks((time.perf_counter() - t0) / args.e2e_steps)
+    net.input.p_data_cube.ptr, net.labels.ptr = main_ptr, main_labels_ptr
+    torch.cuda.synchronize()
+
+    if rank == 0:
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            total, per = caffenet_reference_seconds(B, 1)
+            if total:
+                from oracle import pyoracle
+                ref = pyoracle.reference()
+                cpu = dict(value=B / total, unit="images/s", cores=ref.hardware_concurrency(), kind="reference",
+                           sample="one forward + backward pass of every CaffeNet layer over a %d-image batch through the "
+                                  "reference's CPU bridges, one bridge at a time (convolutions: %d partitions x 1 BLAS thread; "
+                                  "fully connected: %d BLAS threads), times summed; %s" %
+                                  (B, ref.default_partitions(B), ref.hardware_concurrency(), ref.blas_config()),
+                           seconds_per_step=total)
+        tf = world * flops / (ms_step * 1e-3) / 1e12
+        ach = dom_F / (dom_ms * 1e-3) / 1e12 if dom_ms > 0 else 0.0
+        line = {
+            "metric": METRIC, "value": world * B / (ms_step * 1e-3), "unit": "images/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warm_steps, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "caffenet (BASELINE config %d: full CaffeNet iteration, batch %d per GPU)" % (4 if world == 1 else 5, B),
+                       "batch_per_gpu": B, "global_batch": B * world,
+                       "step": "forward + backward of all 23 layers + NCCL all-reduce of the %.1f M parameter gradients (N>1, "
+                               "begun per layer, overlapping the layers below) + SGD momentum step" % (net.num_parameters() / 1e6),
+                       "fusions": net.fused, "l2": "inputs larger than L2 (%.1f GB of activations and gradients per step)" %
+                       (sum(c.n_elements * 4 for c in net._cubes) / 1e9), "parallelism": "dp%d" % world},
+            "tflops": tf, "flops_per_step": flops,
+            "roofline": {"bound": "tensor", "kernel": dom_name, "achieved": ach, "peak": roof["peak"], "unit": "TFLOP/s",
+                         "frac": ach / roof["peak"] if roof["peak"] else None, "traffic": None,
+                         "peak_source": roof["source"], "peak_sustained": roof["peak_sustained"],
+                         "frac_of_sustained": ach / roof["peak_sustained"] if roof["peak_sustained"] else None,
+                         "whole_step_achieved": tf / world, "whole_step_frac": tf / world / roof["peak"],
+                         "whole_step_frac_of_sustained": tf / world / roof["peak_sustained"] if roof["peak_sustained"] else None,
+                         "flops_per_launch": dom_F, "ms_per_launch": dom_ms,
+                         "timing": "CUDA events on the launching stream around every kernel group, mean of %d steps run "
+                                   "right after the timed region" % prof_steps},
+            "layers": layers, "update_ms": upd_ms, "hbm_bound_passes": hbm_table,
+            "loss": {"after_warmup": loss0, "after_timed_steps": loss1},
+            "cpu_baseline": cpu,
+            "e2e": {"value": world * B / e2e_s, "unit": "images/s", "h2d_bytes_per_step": int(X.nbytes + labels.nbytes),
+                    "d2h_bytes_per_step": 4, "ms_per_step": e2e_s * 1e3, "steps": args.e2e_steps,
+                    "how": "each step: images and labels copied from pinned host memory (double-buffered on a copy stream), "
+                           "the iteration, the loss read back"},
+            "clocks": clocks, "gpu_launches": net.launches_per_step() * args.steps,
+            "allreduce_bytes_per_step": 4 * net.num_parameters() if world > 1 else 0,
+        }
+        if cpu:
+            cpu.pop("seconds_per_step", None)
+        print(json.dumps(line), flush=True)
+    for c in stage + stage_l:
+        c.free()
+    cctx.close()
+    net.close()
+    if comm is not None:
+        comm.close()
+    if world > 1:
+        dist.destroy_process_group()
+    ctx.close()
+
+
+def run_caffenet_reference_arm(args, rank, world):
+    if rank != 0:
+        return
+    B = args.batch or 256
+    log = lambda m: print(m, file=sys.stderr, flush=True)
+    total, per = caffenet_reference_seconds(B, max(1, args.steps), log)
+    if total is None:
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libcct_ref.so (the reference's CPU code) is not built"}))
+        return
+    from oracle import pyoracle
+    ref = pyoracle.reference()
+    val = B / total
+    cpu = dict(value=val, unit="images/s", cores=ref.hardware_concurrency(), kind="reference",
+               sample="each step = forward + backward of every CaffeNet layer over one %d-image batch through the reference's "
+                      "CPU bridges, one bridge at a time, median of %d passes per layer, times summed (convolutions: %d "
+                      "partitions x 1 BLAS thread, fully connected: %d BLAS threads); %s" %
+                      (B, max(1, args.steps), ref.default_partitions(B), ref.hardware_concurrency(), ref.blas_config()))
+    line = {"impl": "reference", "metric": METRIC, "value": val, "unit": "images/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": total * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "caffenet (BASELINE config %d: full CaffeNet iteration, batch %d per GPU)" % (4 if world == 1 else 5, B),
+                       "batch_per_gpu": B, "global_batch": B * world, "parallelism": "dp%d" % world},
+            "layers_ms": {k: v * 1e3 for k, v in per.items()}, "cpu_baseline": cpu,
+            "e2e": {"value": val, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
 def config_of(args, w, world):
     return {"workload": args.workload, "batch_per_gpu": w["B"], "global_batch": w["B"] * world,
             "in": "%dx%dx%d" % (w["D"], w["n"], w["n"]), "filters": "%d x %dx%d stride %d pad %d groups %d" %
@@ -458,10 +802,10 @@ def config_of(args, w, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="alexnet_conv1", choices=sorted(WORKLOADS) + ["caffenet_convs"])
+    ap.add_argument("--workload", default="caffenet", choices=["caffenet"] + sorted(WORKLOADS) + ["caffenet_convs"])
     ap.add_argument("--algo", type=int, default=0, help="0 auto, 1 SIMT fp32, 2 tcgen05 3xTF32")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--preheat-s", type=float, default=1.0,
@@ -470,6 +814,13 @@ def main():
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (profiling on a small case)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.workload == "caffenet":
+        env = [int(os.environ.get(k, d)) for k, d in (("RANK", "0"), ("WORLD_SIZE", "1"), ("LOCAL_RANK", "0"))]
+        if args.impl == "reference":
+            run_caffenet_reference_arm(args, env[0], env[1])
+        else:
+            run_caffenet(args, env[0], env[1], env[2])
+        return
     if args.workload == "caffenet_convs":
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "the reference arm is timed per layer workload, not for the conv stack"}))

@@ -25,6 +25,7 @@ class Context:
                        "cct_ctx_create_on_stream")
         self.h = h
         self.device = device
+        self.stream = stream  # the cudaStream_t the context enqueues on when the caller supplied one, else None
 
     def close(self):
         if self.h:

@@ -11,6 +11,8 @@ LIB_PATH = os.environ.get("CCT_B200_LIB") or os.path.join(HERE, "libcct_b200.so"
 
 CCT_OK, CCT_ERR_INVALID, CCT_ERR_CUDA, CCT_ERR_NOMEM, CCT_ERR_TIMEOUT, CCT_ERR_UNSUPPORTED = range(6)
 ALGO_AUTO, ALGO_SIMT_FP32, ALGO_UMMA_3XTF32 = 0, 1, 2
+FILL_GAUSSIAN, FILL_XAVIER, FILL_BERNOULLI = 0, 1, 2
+COMM_ID_BYTES = 128
 _ERR_NAMES = {1: "CCT_ERR_INVALID", 2: "CCT_ERR_CUDA", 3: "CCT_ERR_NOMEM", 4: "CCT_ERR_TIMEOUT",
               5: "CCT_ERR_UNSUPPORTED"}
 

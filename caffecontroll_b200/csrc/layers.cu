@@ -17,22 +17,32 @@ inline int ew_grid(cct_ctx* ctx, size_t work, int threads) {
 // ---------------------------------------------------------------------------------------------------- LRN
 // Across-channel normalisation (src/bridges/LRNBridge_impl.hxx:46-120, src/kernels/lrn.hxx:38-124):
 //   scale[b][d][p] = 1 + (alpha / local_size) * sum_{|c - d| <= local_size / 2} X[b][c][p]^2,   Y = X / scale^beta.
-// One thread per (image, position), walking over the channels with the last local_size squares in registers: consecutive
-// threads read consecutive positions of one channel plane (coalesced).  4 B read + 8 B written per element (Y and
-// scale; the backward pass reads scale instead of recomputing a nine-channel window).
+// One thread per (image, chunk of kLrnChunk channels, position): consecutive threads read consecutive positions of one
+// channel plane (coalesced), a thread walks over its chunk with the window's squares in registers and reads
+// local_size / 2 channels of halo on either side (they come from L1 / L2: the neighbouring chunk's thread block reads
+// them as its own).  Splitting the channels keeps the grid large on the late layers (13 x 13 planes).  4 B read + 8 B
+// written per element (Y and scale; the backward pass reads scale instead of recomputing a nine-channel window).
+constexpr int kLrnChunk = 16;
+
 template <int LOCAL>
-__global__ void lrn_fwd_kernel(const float* __restrict__ X, float* __restrict__ Y, float* __restrict__ scale,
-                               size_t positions, int D, int plane, float alpha_over_size, float beta) {
+__global__ void __launch_bounds__(128) lrn_fwd_kernel(const float* __restrict__ X, float* __restrict__ Y,
+                                                      float* __restrict__ scale, size_t items, int D, int chunks, int plane,
+                                                      float alpha_over_size, float beta) {
   constexpr int W = LOCAL / 2;
-  for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < positions; t += (size_t)gridDim.x * blockDim.x) {
-    const size_t b = t / plane, p = t - b * plane;
+  for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < items; t += (size_t)gridDim.x * blockDim.x) {
+    const size_t bc = t / plane, p = t - bc * plane;
+    const size_t b = bc / chunks;
+    const int d0 = (int)(bc - b * chunks) * kLrnChunk, d1 = min(D, d0 + kLrnChunk);
     const float* x = X + b * (size_t)D * plane + p;
     float* y = Y + b * (size_t)D * plane + p;
     float* sc = scale + b * (size_t)D * plane + p;
-    float win[LOCAL];  // x[d - W .. d + W]
+    float win[LOCAL];  // x[d - W .. d + W], one step behind at loop entry
 #pragma unroll
-    for (int i = 0; i < LOCAL; ++i) win[i] = (i - W - 1 >= 0 && i - W - 1 < D) ? x[(size_t)(i - W - 1) * plane] : 0.f;
-    for (int d = 0; d < D; ++d) {
+    for (int i = 0; i < LOCAL; ++i) {
+      const int c = d0 + i - W - 1;
+      win[i] = (c >= 0 && c < D) ? x[(size_t)c * plane] : 0.f;
+    }
+    for (int d = d0; d < d1; ++d) {
 #pragma unroll
       for (int i = 0; i + 1 < LOCAL; ++i) win[i] = win[i + 1];
       win[LOCAL - 1] = d + W < D ? x[(size_t)(d + W) * plane] : 0.f;
@@ -48,12 +58,15 @@ __global__ void lrn_fwd_kernel(const float* __restrict__ X, float* __restrict__ 
 
 // Any odd window: the squares are re-read (they sit in L1 from the previous channels' steps).
 __global__ void lrn_fwd_generic_kernel(const float* __restrict__ X, float* __restrict__ Y, float* __restrict__ scale,
-                                       size_t positions, int D, int plane, int local, float alpha_over_size, float beta) {
+                                       size_t items, int D, int chunks, int plane, int local, float alpha_over_size,
+                                       float beta) {
   const int w = local / 2;
-  for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < positions; t += (size_t)gridDim.x * blockDim.x) {
-    const size_t b = t / plane, p = t - b * plane;
+  for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < items; t += (size_t)gridDim.x * blockDim.x) {
+    const size_t bc = t / plane, p = t - bc * plane;
+    const size_t b = bc / chunks;
+    const int d0 = (int)(bc - b * chunks) * kLrnChunk, d1 = min(D, d0 + kLrnChunk);
     const size_t base = b * (size_t)D * plane + p;
-    for (int d = 0; d < D; ++d) {
+    for (int d = d0; d < d1; ++d) {
       float sum = 0.f;
       for (int c = max(0, d - w); c <= min(D - 1, d + w); ++c) {
         const float v = X[base + (size_t)c * plane];
@@ -70,17 +83,54 @@ __global__ void lrn_fwd_generic_kernel(const float* __restrict__ X, float* __res
 //   dX[c] += dY[o] * ([c == o] / scale[o]^beta - 2 beta (alpha / size) X[o] X[c] / scale[o]^(beta + 1))   for |c - o| <= w;
 // collected per input channel c:
 //   dX[c] = dY[c] / scale[c]^beta - 2 beta (alpha / size) X[c] * sum_{|o - c| <= w} dY[o] Y[o] / scale[o]
-// (Y[o] = X[o] / scale[o]^beta, so no power is needed inside the window).  16 B read + 4 B written per element; the
-// window terms of neighbouring channels come from L1.
-__global__ void lrn_bwd_kernel(const float* __restrict__ X, const float* __restrict__ Y, const float* __restrict__ scale,
-                               const float* __restrict__ dY, float* __restrict__ dX, size_t positions, int D, int plane,
-                               int local, float alpha_over_size, float beta) {
+// (Y[o] = X[o] / scale[o]^beta, so no power is needed inside the window, and dY[c] / scale[c]^beta = dY[c] Y[c] / X[c]
+// needs none either - but X may be 0, so the power is taken once per element).  Same decomposition as the forward
+// kernel, the window terms t[o] = dY[o] Y[o] / scale[o] held in registers.  16 B read + 4 B written per element.
+template <int LOCAL>
+__global__ void __launch_bounds__(128) lrn_bwd_kernel(const float* __restrict__ X, const float* __restrict__ Y,
+                                                      const float* __restrict__ scale, const float* __restrict__ dY,
+                                                      float* __restrict__ dX, size_t items, int D, int chunks, int plane,
+                                                      float alpha_over_size, float beta) {
+  constexpr int W = LOCAL / 2;
+  const float coef = 2.f * beta * alpha_over_size;
+  for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < items; t += (size_t)gridDim.x * blockDim.x) {
+    const size_t bc = t / plane, p = t - bc * plane;
+    const size_t b = bc / chunks;
+    const int d0 = (int)(bc - b * chunks) * kLrnChunk, d1 = min(D, d0 + kLrnChunk);
+    const size_t base = b * (size_t)D * plane + p;
+    auto term = [&](int c) {
+      if (c < 0 || c >= D) return 0.f;
+      const size_t at = base + (size_t)c * plane;
+      return dY[at] * Y[at] / scale[at];
+    };
+    float win[LOCAL];
+#pragma unroll
+    for (int i = 0; i < LOCAL; ++i) win[i] = term(d0 + i - W - 1);
+    for (int c = d0; c < d1; ++c) {
+#pragma unroll
+      for (int i = 0; i + 1 < LOCAL; ++i) win[i] = win[i + 1];
+      win[LOCAL - 1] = term(c + W);
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < LOCAL; ++i) acc += win[i];
+      const size_t at = base + (size_t)c * plane;
+      dX[at] = dY[at] / powf(scale[at], beta) - coef * X[at] * acc;
+    }
+  }
+}
+
+__global__ void lrn_bwd_generic_kernel(const float* __restrict__ X, const float* __restrict__ Y,
+                                       const float* __restrict__ scale, const float* __restrict__ dY,
+                                       float* __restrict__ dX, size_t items, int D, int chunks, int plane, int local,
+                                       float alpha_over_size, float beta) {
   const int w = local / 2;
   const float coef = 2.f * beta * alpha_over_size;
-  for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < positions; t += (size_t)gridDim.x * blockDim.x) {
-    const size_t b = t / plane, p = t - b * plane;
+  for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < items; t += (size_t)gridDim.x * blockDim.x) {
+    const size_t bc = t / plane, p = t - bc * plane;
+    const size_t b = bc / chunks;
+    const int d0 = (int)(bc - b * chunks) * kLrnChunk, d1 = min(D, d0 + kLrnChunk);
     const size_t base = b * (size_t)D * plane + p;
-    for (int c = 0; c < D; ++c) {
+    for (int c = d0; c < d1; ++c) {
       float acc = 0.f;
       for (int o = max(0, c - w); o <= min(D - 1, c + w); ++o) {
         const size_t at = base + (size_t)o * plane;
@@ -164,32 +214,54 @@ __global__ void softmax_bwd_kernel(const float* __restrict__ prob, const float* 
 }
 
 // ----------------------------------------------------------------------------- max pooling forward, staged
-// MaxPoolingBridge::forward (src/sched/DeviceDriver_CPU.cpp:369-400): windows clipped at the border, rows then columns,
-// strict '>' so the first maximum wins; idx = offset inside the plane.  One block per plane at a time: the plane is
-// copied to shared memory with coalesced loads (every input element crosses HBM -> SM once), the windows are read
-// from there, Y and idx leave in coalesced runs.  4 B read per input element + 8 B written per output element.
+// MaxPoolingBridge::forward (src/sched/DeviceDriver_CPU.cpp:369-400): rows then columns, strict '>' so the first maximum
+// wins; idx = offset inside the plane.  Output size by floor and no padding, so every window lies inside the plane
+// ((m - 1) s + k <= n) and no clipping is needed.  One block per plane at a time: the plane is copied to shared memory
+// with coalesced loads (every input element crosses HBM -> SM once, four loads in flight per thread), the windows are
+// read from there, Y and idx leave in coalesced runs.  K, S > 0 fix the window at compile time (straight-line
+// compare / select chain); K = 0 keeps run-time loops.  4 B read per input element + 8 B written per output element.
+template <int K, int S>
 __global__ void __launch_bounds__(256) maxpool_fwd_staged_kernel(const float* __restrict__ X, float* __restrict__ Y,
                                                                  int32_t* __restrict__ idx, int planes, int n, int m,
-                                                                 int k, int s) {
+                                                                 int k_rt, int s_rt) {
   extern __shared__ float plane_smem[];
   const int nn = n * n, mm = m * m;
+  const int k = K > 0 ? K : k_rt, s = S > 0 ? S : s_rt;
   for (int plane = blockIdx.x; plane < planes; plane += gridDim.x) {
     const float* in = X + (size_t)plane * nn;
     __syncthreads();  // the previous plane's windows have been read
-    for (int i = threadIdx.x; i < nn; i += blockDim.x) plane_smem[i] = __ldg(in + i);
+    int i = threadIdx.x;
+    for (; i + 3 * 256 < nn; i += 4 * 256) {
+      const float a = __ldg(in + i), b = __ldg(in + i + 256), c = __ldg(in + i + 512), d = __ldg(in + i + 768);
+      plane_smem[i] = a; plane_smem[i + 256] = b; plane_smem[i + 512] = c; plane_smem[i + 768] = d;
+    }
+    for (; i < nn; i += 256) plane_smem[i] = __ldg(in + i);
     __syncthreads();
-    for (int t = threadIdx.x; t < mm; t += blockDim.x) {
+    for (int t = threadIdx.x; t < mm; t += 256) {
       const int ph = t / m, pw = t - ph * m;
-      const int he = min(ph * s + k, n), we = min(pw * s + k, n);
+      const int origin = ph * s * n + pw * s;
+      const float* win = plane_smem + origin;
       float best = -FLT_MAX;
       int where = 0;
-      for (int h = ph * s; h < he; ++h)
-        for (int w = pw * s; w < we; ++w) {
-          const float v = plane_smem[h * n + w];
-          if (v > best) { best = v; where = h * n + w; }
-        }
+      if (K > 0) {
+#pragma unroll
+        for (int h = 0; h < K; ++h)
+#pragma unroll
+          for (int w = 0; w < K; ++w) {
+            const float v = win[h * n + w];
+            const bool better = v > best;
+            best = better ? v : best;
+            where = better ? h * n + w : where;
+          }
+      } else {
+        for (int h = 0; h < k; ++h)
+          for (int w = 0; w < k; ++w) {
+            const float v = win[h * n + w];
+            if (v > best) { best = v; where = h * n + w; }
+          }
+      }
       Y[(size_t)plane * mm + t] = best;
-      idx[(size_t)plane * mm + t] = where;
+      idx[(size_t)plane * mm + t] = origin + where;
     }
   }
 }
@@ -199,11 +271,12 @@ __global__ void __launch_bounds__(256) maxpool_fwd_staged_kernel(const float* __
 int maxpool_forward_staged(cct_ctx* ctx, const float* X, float* Y, int32_t* idx, int planes, int n, int m, int k, int s) {
   const size_t smem = (size_t)n * n * sizeof(float);
   if (smem > 200 * 1024) return CCT_ERR_UNSUPPORTED;
-  if (smem > 48 * 1024)
-    CCT_CUDA(ctx, cudaFuncSetAttribute(maxpool_fwd_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  auto kernel = (k == 3 && s == 2) ? maxpool_fwd_staged_kernel<3, 2> : (k == 2 && s == 2) ? maxpool_fwd_staged_kernel<2, 2>
+                                                                                         : maxpool_fwd_staged_kernel<0, 0>;
+  if (smem > 48 * 1024) CCT_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(8, (200 * 1024) / std::max<size_t>(smem, 1)));
   const int grid = std::max(1, std::min(planes, ctx->sm_count * per_sm));
-  maxpool_fwd_staged_kernel<<<grid, 256, smem, ctx->stream>>>(X, Y, idx, planes, n, m, k, s);
+  kernel<<<grid, 256, smem, ctx->stream>>>(X, Y, idx, planes, n, m, k, s);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }
@@ -215,15 +288,16 @@ int cct_lrn_forward(cct_ctx* ctx, const float* X, float* Y, float* scale, int ba
   if (!ctx || !X || !Y || !scale || batch <= 0 || depth <= 0 || plane <= 0 || local_size <= 0 || !(local_size & 1))
     return CCT_ERR_INVALID;
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
-  const size_t positions = (size_t)batch * plane;
-  const int grid = ew_grid(ctx, positions, 128);
+  const int chunks = (depth + kLrnChunk - 1) / kLrnChunk;
+  const size_t items = (size_t)batch * chunks * plane;
+  const int grid = ew_grid(ctx, items, 128);
   const float aos = alpha / (float)local_size;
   if (local_size == 5)
-    lrn_fwd_kernel<5><<<grid, 128, 0, ctx->stream>>>(X, Y, scale, positions, depth, plane, aos, beta);
+    lrn_fwd_kernel<5><<<grid, 128, 0, ctx->stream>>>(X, Y, scale, items, depth, chunks, plane, aos, beta);
   else if (local_size == 3)
-    lrn_fwd_kernel<3><<<grid, 128, 0, ctx->stream>>>(X, Y, scale, positions, depth, plane, aos, beta);
+    lrn_fwd_kernel<3><<<grid, 128, 0, ctx->stream>>>(X, Y, scale, items, depth, chunks, plane, aos, beta);
   else
-    lrn_fwd_generic_kernel<<<grid, 128, 0, ctx->stream>>>(X, Y, scale, positions, depth, plane, local_size, aos, beta);
+    lrn_fwd_generic_kernel<<<grid, 128, 0, ctx->stream>>>(X, Y, scale, items, depth, chunks, plane, local_size, aos, beta);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }
@@ -234,9 +308,17 @@ int cct_lrn_backward(cct_ctx* ctx, const float* X, const float* Y, const float* 
       !(local_size & 1))
     return CCT_ERR_INVALID;
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
-  const size_t positions = (size_t)batch * plane;
-  lrn_bwd_kernel<<<ew_grid(ctx, positions, 128), 128, 0, ctx->stream>>>(X, Y, scale, dY, dX, positions, depth, plane,
-                                                                       local_size, alpha / (float)local_size, beta);
+  const int chunks = (depth + kLrnChunk - 1) / kLrnChunk;
+  const size_t items = (size_t)batch * chunks * plane;
+  const int grid = ew_grid(ctx, items, 128);
+  const float aos = alpha / (float)local_size;
+  if (local_size == 5)
+    lrn_bwd_kernel<5><<<grid, 128, 0, ctx->stream>>>(X, Y, scale, dY, dX, items, depth, chunks, plane, aos, beta);
+  else if (local_size == 3)
+    lrn_bwd_kernel<3><<<grid, 128, 0, ctx->stream>>>(X, Y, scale, dY, dX, items, depth, chunks, plane, aos, beta);
+  else
+    lrn_bwd_generic_kernel<<<grid, 128, 0, ctx->stream>>>(X, Y, scale, dY, dX, items, depth, chunks, plane, local_size, aos,
+                                                        beta);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }

@@ -396,6 +396,31 @@ class Net:
     def num_parameters(self):
         return sum(pb.count for pb in self.pbridges.values())
 
+    def launches_per_step(self):
+        """Kernels one forward + backward + update launches, counted from the structure of the calls: convolution
+        forward = weight pack + contraction; its backward = weight gradient (dY split + contraction + split reduction +
+        bias sums for lowered matrices of 512 rows or more, else contraction + reduction), data gradient (pack +
+        contraction), plus one pass per folded mask; fully connected = contraction + reduction per pass, bias sums;
+        one kernel per parameter-free bridge pass; two SGD kernels per parameterised layer."""
+        n = 0
+        for i, br in enumerate(self.bridges):
+            t = self.types[i]
+            if t == "Convolution":
+                wg = 4 if (br.iD // br.group) * br.K * br.K >= 512 else 2
+                n += 2 + wg + (2 if br.needs_to_calc_backward_grad else 0)
+                n += (1 if br.pool_fusion is not None else 0) + (1 if br.fuse_relu_backward and br.needs_to_calc_backward_grad else 0)
+            elif t == "InnerProduct":
+                n += 2 + 2 + (2 if br.needs_to_calc_backward_grad else 0)
+            elif t == "SoftmaxWithLoss":
+                n += 3
+            elif t == "Dropout":
+                n += 1 + (0 if br.skip_forward else 1) + (0 if br.skip_backward else 1)
+            elif t == "Pooling":
+                n += 1 + (0 if br.skip_backward else 1)
+            else:
+                n += (0 if br.skip_forward else 1) + (0 if br.skip_backward else 1)
+        return n + 2 * len(self.pbridges)
+
     def close(self):
         self.ctx.sync()
         for br in self.bridges:

@@ -61,18 +61,48 @@ def get_learning_rate(policy, base_lr, gamma, it, stepsize, power, max_iter):
     return float(np.float32(rate))
 
 
-class DeviceOps:
-    """Gradient sum and SGD step on the GPU: torch.distributed (NCCL) over a zero-copy view, cct_sgd_step."""
+class Communicator:
+    """cct_comm: the NCCL communicator of the C ABI (one per context).  `unique_id` is the 128-byte id rank 0 made with
+    Communicator.unique_id() and handed to every rank; nranks == 1 needs none and never loads NCCL."""
 
-    def __init__(self, ctx, group=None):
-        self.ctx, self.group = ctx, group
+    def __init__(self, ctx, nranks=1, rank=0, unique_id=None):
+        self.ctx, self.nranks, self.rank = ctx, nranks, rank
+        h = C.c_void_p()
+        capi.check(ctx.lib.cct_comm_init_rank(ctx.h, nranks, rank, unique_id, C.byref(h)), "cct_comm_init_rank", ctx.h)
+        self.h = h
+
+    @staticmethod
+    def unique_id():
+        buf = C.create_string_buffer(capi.COMM_ID_BYTES)
+        capi.check(capi.load().cct_comm_unique_id(buf), "cct_comm_unique_id")
+        return buf.raw
+
+    def close(self):
+        if self.h:
+            self.ctx.lib.cct_comm_destroy(self.h)
+            self.h = None
+
+
+class DeviceOps:
+    """Gradient sum and SGD step on the GPU.  The sum is an NCCL all-reduce issued through the C ABI's communicator
+    (on its own stream, overlapping the kernels queued after it) when one is given, else through torch.distributed on
+    torch's current stream - which must then be the stream the context was created on."""
+
+    def __init__(self, ctx, group=None, comm=None):
+        self.ctx, self.group, self.comm = ctx, group, comm
+        self._checked_stream = False
 
     def world_size(self):
+        if self.comm is not None:
+            return self.comm.nranks
         import torch.distributed as dist
         return dist.get_world_size(self.group) if dist.is_available() and dist.is_initialized() else 1
 
     def alloc(self, count):
         return self.ctx.malloc(4 * count)
+
+    def free(self, ptr):
+        self.ctx.free(ptr)
 
     def view(self, ptr, count):
         import torch
@@ -82,10 +112,32 @@ class DeviceOps:
 
         return torch.as_tensor(_Iface(), device="cuda:%d" % self.ctx.device)
 
-    def allreduce_sum(self, ptr, count):
-        if self.world_size() > 1:
+    def allreduce_begin(self, ptr, count):
+        """Starts the sum of `count` floats at `ptr` over all ranks, ordered behind the work queued so far."""
+        if self.comm is not None:
+            capi.check(self.ctx.lib.cct_allreduce_sum_begin(self.comm.h, C.c_void_p(ptr), count), "cct_allreduce_sum_begin",
+                       self.ctx.h)
+        elif self.world_size() > 1:
+            import torch
             import torch.distributed as dist
+            if not self._checked_stream:
+                # the collective runs on torch's current stream; the kernels that produce and consume the buffer run on
+                # the context's stream: without a communicator of its own the two must be one stream
+                cur = torch.cuda.current_stream(self.ctx.device).cuda_stream
+                if self.ctx.stream != cur:
+                    raise RuntimeError("DeviceOps without a Communicator needs a Context created on torch's current "
+                                       "stream (Context(device, stream=torch.cuda.current_stream().cuda_stream))")
+                self._checked_stream = True
             dist.all_reduce(self.view(ptr, count), group=self.group)
+
+    def allreduce_wait(self):
+        """Orders the context's stream behind every sum begun so far."""
+        if self.comm is not None:
+            capi.check(self.ctx.lib.cct_comm_wait(self.comm.h), "cct_comm_wait", self.ctx.h)
+
+    def allreduce_sum(self, ptr, count):
+        self.allreduce_begin(ptr, count)
+        self.allreduce_wait()
 
     def sgd_step(self, count, w, g, h, lr, momentum, lam):
         vp = C.c_void_p
@@ -94,6 +146,11 @@ class DeviceOps:
 
     def zero(self, ptr, count):
         self.ctx.fill(ptr, count, 0.0)
+
+    def copy(self, dst, src, count):
+        capi.check(self.ctx.lib.cct_memcpy_d2d(self.ctx.h, C.c_void_p(dst), C.c_void_p(src), 4 * count), "cct_memcpy_d2d",
+                   self.ctx.h)
+        self.ctx.sync()  # the source is freed right after
 
 
 class ParallelizedBridge:
@@ -104,14 +161,22 @@ class ParallelizedBridge:
     the pointer to its sub-bridges (ParallelizedBridge_impl.hxx:519-532).
     """
 
-    def __init__(self, bridge, solver, ops, lr_mult=(1.0, 2.0), decay_mult=(1.0, 0.0)):
+    def __init__(self, bridge, solver, ops, lr_mult=(1.0, 2.0), decay_mult=(1.0, 0.0), defer_update=False):
         self.bridge, self.solver, self.ops = bridge, solver, ops
+        self.defer_update = defer_update  # backward() only begins the gradient sum; the owner calls apply_update()
         self.n_w = bridge.p_model_cube.n_elements
         self.n_b = bridge.p_bias_cube.n_elements if bridge.bias_term else 0
         n = self.n_w + self.n_b
         self.count = n
         self.params, self.grads, self.hist = ops.alloc(n), ops.alloc(n), ops.alloc(n)
         ops.zero(self.hist, n)
+        # the sub-bridge's model and bias (already filled by its constructor's fillers) move into the flat buffer, as
+        # the reference's ParallelizedBridge copies sub-bridge 0's model into its own cube (ParallelizedBridge_impl.hxx:130-160)
+        copy = getattr(ops, "copy", None)
+        if copy is not None:
+            copy(self.params, bridge.p_model_cube.ptr, self.n_w)
+            if self.n_b:
+                copy(self.params + 4 * self.n_w, bridge.p_bias_cube.ptr, self.n_b)
         self._repoint(bridge.p_model_cube, self.params)
         self._repoint(bridge.p_model_gradient_cube, self.grads)
         if self.n_b:
@@ -144,7 +209,19 @@ class ParallelizedBridge:
 
     def backward(self):
         self.bridge.backward()
-        self.ops.allreduce_sum(self.grads, self.count)  # gradients are summed, not averaged (:916-955)
+        begin = getattr(self.ops, "allreduce_begin", None)
+        if begin is None:  # an ops object with the blocking form only
+            self.ops.allreduce_sum(self.grads, self.count)
+        else:
+            begin(self.grads, self.count)  # gradients are summed, not averaged (:916-955)
+        if not self.defer_update:
+            wait = getattr(self.ops, "allreduce_wait", None)
+            if begin is not None and wait is not None:
+                wait()
+            self.apply_update()
+
+    def apply_update(self):
+        """The SGD step on the summed gradients (the caller has waited for the sum when updates are deferred)."""
         if not self.update_model_gradients:
             return
         s = self.solver
@@ -158,3 +235,16 @@ class ParallelizedBridge:
             self.ops.sgd_step(self.n_b, self.params + off, self.grads + off, self.hist + off,
                               float(np.float32(base * self.lr_mult[1])), s.momentum,
                               float(np.float32(s.weight_decay * self.decay_mult[1])))
+
+    def get_model_grad_cube(self):
+        return self.bridge.p_model_gradient_cube
+
+    def get_bias_grad_cube(self):
+        return self.bridge.p_bias_gradient_cube
+
+    def close(self):
+        free = getattr(self.ops, "free", None)
+        if free is not None:
+            for p in (self.params, self.grads, self.hist):
+                free(p)
+        self.params = self.grads = self.hist = None

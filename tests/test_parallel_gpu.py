@@ -31,31 +31,38 @@ def _expected(port, steps):
     return W, b
 
 
-def _run_rank(rank, world, device, steps):
+def _run_rank(rank, world, device, steps, unique_id=None):
+    """One rank's partition.  With `unique_id` the gradient sum goes through the library's own NCCL communicator
+    (cct_comm_*), else through torch.distributed on torch's stream."""
     from caffecontroll_b200 import Context, ConvolutionBridge, Layer, LogicalCube
-    from caffecontroll_b200.parallel import DeviceOps, ParallelizedBridge, SolverParameter, partition_batch
+    from caffecontroll_b200.parallel import Communicator, DeviceOps, ParallelizedBridge, SolverParameter, partition_batch
     B, D, n, o, k, s, p, g = SHAPE
     m = (n + 2 * p - k) // s + 1
     X, W, b, dY = make_inputs(91, B, D, n, o, k, s, p, g)
     start, size = partition_batch(B, world)[rank]
     stream = None
-    if world > 1:
+    if world > 1 and unique_id is None:
         import torch
         torch.cuda.set_device(device)
         stream = torch.cuda.current_stream().cuda_stream
     ctx = Context(device, stream=stream)
+    comm = Communicator(ctx, world, rank, unique_id) if unique_id is not None else None
     xin = Layer(LogicalCube.from_numpy(ctx, X[start:start + size]), LogicalCube(ctx, n, n, D, size))
     out = Layer(LogicalCube(ctx, m, m, o, size), LogicalCube.from_numpy(ctx, dY[start:start + size]))
     br = ConvolutionBridge(xin, out, k, s, p, g, True)
     br.needs_to_calc_backward_grad = False
-    pb = ParallelizedBridge(br, SolverParameter(LR, "step", 0.1, 100000, momentum=MOM, weight_decay=WD), DeviceOps(ctx))
+    pb = ParallelizedBridge(br, SolverParameter(LR, "step", 0.1, 100000, momentum=MOM, weight_decay=WD),
+                            DeviceOps(ctx, comm=comm))
     br.p_model_cube.upload(W)
     br.p_bias_cube.upload(b)
     for _ in range(steps):
         pb.forward()
         pb.backward()
     ctx.sync()
-    return br.p_model_cube.download(), br.p_bias_cube.download().ravel()
+    res = br.p_model_cube.download(), br.p_bias_cube.download().ravel()
+    if comm is not None:
+        comm.close()
+    return res
 
 
 def test_single_rank_step_matches_oracle(port):
@@ -92,3 +99,53 @@ def test_two_nccl_ranks_match_oracle_on_whole_batch(port, tmp_path):
     b0 = np.load(os.path.join(str(tmp_path), "b_0.npy"))
     assert np.array_equal(W0, W1)
     assert maxnorm_rel(W0, We) <= TOL and maxnorm_rel(b0, be) <= TOL
+
+
+def _comm_rank(rank, world, id_path, out_dir):
+    """No torch.distributed at all: rank 0 writes the NCCL id to a file, the others read it."""
+    import time
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    from caffecontroll_b200.parallel import Communicator
+    if rank == 0:
+        uid = Communicator.unique_id()
+        with open(id_path + ".tmp", "wb") as f:
+            f.write(uid)
+        os.replace(id_path + ".tmp", id_path)
+    else:
+        for _ in range(600):
+            if os.path.exists(id_path):
+                break
+            time.sleep(0.05)
+        with open(id_path, "rb") as f:
+            uid = f.read()
+    W, b = _run_rank(rank, world, rank, 2, unique_id=uid)
+    np.save(os.path.join(out_dir, "W_%d.npy" % rank), W)
+    np.save(os.path.join(out_dir, "b_%d.npy" % rank), b)
+
+
+def test_two_ranks_through_the_c_abi_communicator_match_oracle(port, tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    mp.spawn(_comm_rank, args=(2, os.path.join(str(tmp_path), "nccl_id"), str(tmp_path)), nprocs=2, join=True)
+    We, be = _expected(port, 2)
+    W0, W1 = (np.load(os.path.join(str(tmp_path), "W_%d.npy" % r)) for r in (0, 1))
+    b0 = np.load(os.path.join(str(tmp_path), "b_0.npy"))
+    assert np.array_equal(W0, W1)
+    assert maxnorm_rel(W0, We) <= TOL and maxnorm_rel(b0, be) <= TOL
+
+
+def test_single_rank_communicator_is_a_no_op(ctx):
+    from caffecontroll_b200.parallel import Communicator, DeviceOps
+    comm = Communicator(ctx, 1, 0, None)
+    ops = DeviceOps(ctx, comm=comm)
+    buf = ops.alloc(16)
+    ctx.fill(buf, 16, 3.0)
+    ops.allreduce_sum(buf, 16)
+    ctx.sync()
+    out = np.empty(16, np.float32)
+    ctx.d2h(out, buf)
+    assert np.all(out == 3.0)
+    ops.free(buf)
+    comm.close()
