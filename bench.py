@@ -286,29 +286,29 @@ def run_reference_arm(args, w, rank, world):
     print(json.dumps(line), flush=True)
 
 
-def preheat(step, warmup, seconds, stream, world, dev):
+def preheat(step, warmup, seconds, stream, agree=None):
     """Untimed warm-up: at least `warmup` steps and at least `seconds` of device time, so that the timed steps that
-    follow run at the clocks and power state of a long job and not in a cold burst.  Returns the steps run (the same
-    on every rank: the count is agreed through a MAX all-reduce of one rank-local calibration)."""
+    follow run at the clocks and power state of a long job and not in a cold burst.  Returns the steps run.  With
+    several ranks every rank must run the same number of steps (each holds collectives): `agree(n)` returns the
+    maximum of n over the ranks."""
     import torch
-    import torch.distributed as dist
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     n0 = max(warmup, 3)
+    for _ in range(2):  # the first steps carry one-off costs (module loading, communicator set-up)
+        step()
     e0.record(stream)
-    for _ in range(n0):
+    for _ in range(n0 - 2 if n0 > 2 else 1):
         step()
     e1.record(stream)
     torch.cuda.synchronize()
-    per = max(e0.elapsed_time(e1) / n0, 1e-3)
+    per = max(e0.elapsed_time(e1) / max(n0 - 2, 1), 1e-3)
     more = max(0, int(seconds * 1e3 / per) - n0)
-    if world > 1:
-        t = torch.tensor([more], device=dev, dtype=torch.int64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        more = int(t.item())
+    if agree is not None:
+        more = agree(more)
     for _ in range(more):
         step()
     torch.cuda.synchronize()
-    return n0 + more
+    return max(n0, 3) + more
 
 
 # The five convolution layers of CaffeNet at batch 256 per GPU (BASELINE config 4 without the LRN / FC / softmax layers,
@@ -572,7 +572,7 @@ def run_caffenet(args, rank, world, local_rank):
         return float(t.item())
 
     roof = tensor_roofline(load_peaks(), measure=(rank == 0))
-    warm_steps = preheat(net.step, args.warmup, args.preheat_s, stream, 1, dev)
+    warm_steps = preheat(net.step, args.warmup, args.preheat_s, stream, lambda n: int(max_over_ranks(float(n))))
     loss0 = net.get_loss()
     barrier()
     sampler = ClockSampler(local_rank)
@@ -910,7 +910,14 @@ def main():
         torch.cuda.synchronize()
 
     roof = tensor_roofline(load_peaks(), measure=(rank == 0))
-    warm_steps = preheat(step, args.warmup, args.preheat_s, stream, world, dev)
+    def agree(n):
+        if world == 1:
+            return n
+        t = torch.tensor([n], device=dev, dtype=torch.int64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return int(t.item())
+
+    warm_steps = preheat(step, args.warmup, args.preheat_s, stream, agree)
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:

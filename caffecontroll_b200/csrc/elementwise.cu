@@ -70,6 +70,13 @@ __global__ void sgd_kernel(size_t count, size_t vec, float* __restrict__ w, floa
   }
 }
 
+// y = alpha x + beta y (12 B moved per element): the saxpy / saxpby calls of the reference's SGD updater
+// (src/algorithms/GradientUpdater.h:163-181), for callers that keep its three-call update.
+__global__ void saxpby_kernel(size_t count, float alpha, const float* __restrict__ x, float beta, float* __restrict__ y) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x)
+    y[i] = __fadd_rn(__fmul_rn(alpha, x[i]), __fmul_rn(beta, y[i]));
+}
+
 __global__ void relu_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, size_t count, size_t vec) {
   const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, nthreads = (size_t)gridDim.x * blockDim.x;
   for (size_t i = tid; i < vec; i += nthreads) {
@@ -358,6 +365,15 @@ int cct_sgd_step(cct_ctx* ctx, size_t count, float* w, float* g, float* h, float
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
   sgd_kernel<<<grid_for(ctx, (count + 3) / 4, 256), 256, 0, ctx->stream>>>(count, vec_groups(count, {w, g, h}), w, g, h, lr,
                                                                         momentum, lambda);
+  CCT_CHECK_LAUNCH(ctx);
+  return CCT_OK;
+}
+
+int cct_saxpby(cct_ctx* ctx, size_t count, float alpha, const float* x, float beta, float* y) {
+  if (!ctx || ((!x || !y) && count)) return CCT_ERR_INVALID;
+  if (!count) return CCT_OK;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  saxpby_kernel<<<grid_for(ctx, count, 256), 256, 0, ctx->stream>>>(count, alpha, x, beta, y);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }

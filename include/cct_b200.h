@@ -281,6 +281,10 @@ int cct_softmax_loss_backward(cct_ctx* ctx, const float* prob, const float* labe
 /* ---- parameter update: SGDGradientUpdater::update (src/algorithms/GradientUpdater.h:154-193) as one kernel:
  *      g += lambda*w (if lambda != 0);  h = lr*g + momentum*h;  w -= h. ---- */
 int cct_sgd_step(cct_ctx* ctx, size_t count, float* w, float* g, float* h, float lr, float momentum, float lambda);
+/* y = alpha * x + beta * y on device vectors: DeviceDriver::math_saxpy (beta = 1) and math_saxpby
+ * (src/sched/DeviceDriver.h:197-206), the calls the reference's SGDGradientUpdater makes when it is instantiated on a
+ * device driver unchanged. */
+int cct_saxpby(cct_ctx* ctx, size_t count, float alpha, const float* x, float beta, float* y);
 
 #ifdef __cplusplus
 }
