@@ -24,6 +24,11 @@ inline int ew_grid(cct_ctx* ctx, size_t work, int threads) {
 // written per element (Y and scale; the backward pass reads scale instead of recomputing a nine-channel window).
 constexpr int kLrnChunk = 16;
 
+// s^(-beta) for s >= 1: exp2(-beta log2 s) on the special-function units (ex2.approx / lg2.approx, each within ~2 ulp:
+// relative error below 1e-6 for the scales and exponents of a normalisation layer, two orders under the path's tolerance;
+// powf costs some thirty instructions and made these kernels compute-bound).
+__device__ __forceinline__ float inv_pow(float s, float beta) { return exp2f(-beta * __log2f(s)); }
+
 template <int LOCAL>
 __global__ void __launch_bounds__(128) lrn_fwd_kernel(const float* __restrict__ X, float* __restrict__ Y,
                                                       float* __restrict__ scale, size_t items, int D, int chunks, int plane,
@@ -51,7 +56,7 @@ __global__ void __launch_bounds__(128) lrn_fwd_kernel(const float* __restrict__ 
       for (int i = 0; i < LOCAL; ++i) sum += win[i] * win[i];
       const float s = alpha_over_size * sum + 1.f;
       sc[(size_t)d * plane] = s;
-      y[(size_t)d * plane] = win[W] / powf(s, beta);
+      y[(size_t)d * plane] = win[W] * inv_pow(s, beta);
     }
   }
 }
@@ -101,7 +106,7 @@ __global__ void __launch_bounds__(128) lrn_bwd_kernel(const float* __restrict__ 
     auto term = [&](int c) {
       if (c < 0 || c >= D) return 0.f;
       const size_t at = base + (size_t)c * plane;
-      return dY[at] * Y[at] / scale[at];
+      return __fdividef(dY[at] * Y[at], scale[at]);
     };
     float win[LOCAL];
 #pragma unroll
@@ -114,7 +119,7 @@ __global__ void __launch_bounds__(128) lrn_bwd_kernel(const float* __restrict__ 
 #pragma unroll
       for (int i = 0; i < LOCAL; ++i) acc += win[i];
       const size_t at = base + (size_t)c * plane;
-      dX[at] = dY[at] / powf(scale[at], beta) - coef * X[at] * acc;
+      dX[at] = dY[at] * inv_pow(scale[at], beta) - coef * X[at] * acc;
     }
   }
 }
@@ -223,24 +228,29 @@ __global__ void softmax_bwd_kernel(const float* __restrict__ prob, const float* 
 template <int K, int S>
 __global__ void __launch_bounds__(256) maxpool_fwd_staged_kernel(const float* __restrict__ X, float* __restrict__ Y,
                                                                  int32_t* __restrict__ idx, int planes, int n, int m,
-                                                                 int k_rt, int s_rt) {
+                                                                 int k_rt, int s_rt, int group) {
+  // `group` consecutive planes (contiguous in memory) are staged and pooled together, so that small planes (13 x 13)
+  // still give every thread of the block work.
   extern __shared__ float plane_smem[];
   const int nn = n * n, mm = m * m;
   const int k = K > 0 ? K : k_rt, s = S > 0 ? S : s_rt;
-  for (int plane = blockIdx.x; plane < planes; plane += gridDim.x) {
-    const float* in = X + (size_t)plane * nn;
-    __syncthreads();  // the previous plane's windows have been read
+  for (int p0 = blockIdx.x * group; p0 < planes; p0 += gridDim.x * group) {
+    const int g = min(group, planes - p0);
+    const float* in = X + (size_t)p0 * nn;
+    const int total_in = g * nn, total_out = g * mm;
+    __syncthreads();  // the previous group's windows have been read
     int i = threadIdx.x;
-    for (; i + 3 * 256 < nn; i += 4 * 256) {
+    for (; i + 3 * 256 < total_in; i += 4 * 256) {
       const float a = __ldg(in + i), b = __ldg(in + i + 256), c = __ldg(in + i + 512), d = __ldg(in + i + 768);
       plane_smem[i] = a; plane_smem[i + 256] = b; plane_smem[i + 512] = c; plane_smem[i + 768] = d;
     }
-    for (; i < nn; i += 256) plane_smem[i] = __ldg(in + i);
+    for (; i < total_in; i += 256) plane_smem[i] = __ldg(in + i);
     __syncthreads();
-    for (int t = threadIdx.x; t < mm; t += 256) {
-      const int ph = t / m, pw = t - ph * m;
+    for (int t = threadIdx.x; t < total_out; t += 256) {
+      const int pl = t / mm, r = t - pl * mm;
+      const int ph = r / m, pw = r - ph * m;
       const int origin = ph * s * n + pw * s;
-      const float* win = plane_smem + origin;
+      const float* win = plane_smem + pl * nn + origin;
       float best = -FLT_MAX;
       int where = 0;
       if (K > 0) {
@@ -260,8 +270,8 @@ __global__ void __launch_bounds__(256) maxpool_fwd_staged_kernel(const float* __
             if (v > best) { best = v; where = h * n + w; }
           }
       }
-      Y[(size_t)plane * mm + t] = best;
-      idx[(size_t)plane * mm + t] = origin + where;
+      Y[(size_t)p0 * mm + t] = best;
+      idx[(size_t)p0 * mm + t] = origin + where;
     }
   }
 }
@@ -269,14 +279,17 @@ __global__ void __launch_bounds__(256) maxpool_fwd_staged_kernel(const float* __
 }  // namespace
 
 int maxpool_forward_staged(cct_ctx* ctx, const float* X, float* Y, int32_t* idx, int planes, int n, int m, int k, int s) {
-  const size_t smem = (size_t)n * n * sizeof(float);
-  if (smem > 200 * 1024) return CCT_ERR_UNSUPPORTED;
+  const size_t plane_bytes = (size_t)n * n * sizeof(float);
+  if (plane_bytes > 200 * 1024) return CCT_ERR_UNSUPPORTED;
+  const int group = (int)std::max<size_t>(1, std::min<size_t>(16, (12 * 1024) / plane_bytes));  // ~12 KB staged per block
+  const size_t smem = plane_bytes * group;
   auto kernel = (k == 3 && s == 2) ? maxpool_fwd_staged_kernel<3, 2> : (k == 2 && s == 2) ? maxpool_fwd_staged_kernel<2, 2>
                                                                                          : maxpool_fwd_staged_kernel<0, 0>;
   if (smem > 48 * 1024) CCT_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(8, (200 * 1024) / std::max<size_t>(smem, 1)));
-  const int grid = std::max(1, std::min(planes, ctx->sm_count * per_sm));
-  kernel<<<grid, 256, smem, ctx->stream>>>(X, Y, idx, planes, n, m, k, s);
+  const int blocks_needed = (planes + group - 1) / group;
+  const int grid = std::max(1, std::min(blocks_needed, ctx->sm_count * per_sm));
+  kernel<<<grid, 256, smem, ctx->stream>>>(X, Y, idx, planes, n, m, k, s, group);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }

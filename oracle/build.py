@@ -72,10 +72,55 @@ def build_reference(force=False):
     return out
 
 
+def _read_floats(path):
+    import numpy as np
+    with open(path) as f:
+        return np.array(f.read().split(), dtype=np.float32)
+
+
+def build_adaptor_test(force=False):
+    """The reference-tree adaptor (caffecontroll_b200/host/reference_adaptor/*.h) compiled against the reference's own
+    headers in place, with the oracle's three shim headers, into oracle/_ref/adaptor_fixture_test; beside it the
+    reference's text fixtures of tests/test_parallelized_convolution.cpp converted to raw fp32 files (git-ignored, they
+    travel with the built program).  Only possible where the reference tree is mounted."""
+    ref = os.environ.get(REF_ENV, DEFAULT_REF)
+    src_dir = os.path.join(ref, "src")
+    out_dir = os.path.join(HERE, "_ref")
+    exe = os.path.join(out_dir, "adaptor_fixture_test")
+    if not os.path.isdir(src_dir):
+        return exe if os.path.exists(exe) else None
+    root = os.path.dirname(HERE)
+    adaptor = os.path.join(root, "caffecontroll_b200", "host", "reference_adaptor")
+    main_cpp = os.path.join(root, "tests", "adaptor_fixture_main.cpp")
+    lib_dir = os.path.join(root, "caffecontroll_b200")
+    deps = [main_cpp, os.path.join(root, "include", "cct_b200.h")] + glob.glob(os.path.join(adaptor, "*.h")) + \
+        glob.glob(os.path.join(HERE, "shim", "**", "*.h*"), recursive=True)
+    os.makedirs(out_dir, exist_ok=True)
+    if force or not _newer(exe, deps):
+        blas = scipy_openblas()
+        ref_srcs = [os.path.join(src_dir, p) for p in
+                    ("sched/DeviceDriver_CPU.cpp", "util.cpp", "timer.cpp", "DeepNetConfig.cpp")]
+        _run(["g++", "-std=c++11", "-O2", "-w", "-pthread", "-D_USE_OPENBLAS", "-include", "climits", "-include", "algorithm",
+              "-I" + os.path.join(HERE, "shim", "inc"), "-I" + src_dir, "-I" + adaptor, "-I" + os.path.join(root, "include"),
+              "-o", exe, main_cpp] + ref_srcs +
+             [blas, "-Wl,-rpath," + os.path.dirname(blas), "-L" + lib_dir, "-lcct_b200", "-Wl,-rpath,$ORIGIN/../../caffecontroll_b200"])
+    fix = os.path.join(out_dir, "conv_fixture")
+    tests = os.path.join(ref, "tests")
+    names = {"X": "input/conv_forward_in.txt", "W_fwd": "input/conv_model.txt", "W_bwd": "input/conv_backward_model.txt",
+             "b": "input/conv_bias_in.txt", "Y": "output/conv_forward.txt", "dX": "output/conv_backward.txt",
+             "b_new": "output/conv_bias.txt", "W_new": "output/conv_weights.txt"}
+    if os.path.isdir(tests) and (force or not os.path.exists(os.path.join(fix, "W_new.bin"))):
+        os.makedirs(fix, exist_ok=True)
+        for key, rel in names.items():
+            _read_floats(os.path.join(tests, rel)).tofile(os.path.join(fix, key + ".bin"))
+    return exe
+
+
 def main():
     force = "--force" in sys.argv
     print("port     :", build_port(force))
     print("reference:", build_reference(force))
+    print("adaptor  :", build_adaptor_test(force))
 
 
 if __name__ == "__main__":
