@@ -393,6 +393,34 @@ class Net:
             if f.read(1):
                 raise ValueError("model file is longer than the network's parameters")
 
+    # ---- snapshots (src/DeepNet.h:268-328): the model file, the momentum history in the same order, and the iteration
+    def write_snapshot(self, prefix):
+        """Writes <prefix>.MODEL, <prefix>.HISTORY and <prefix>.ITER."""
+        self.write_model_to_file(prefix + ".MODEL")
+        with open(prefix + ".HISTORY", "wb") as f:
+            for _, pb in self.param_bridges():
+                w, b = pb.history_host()
+                w.tofile(f)
+                if b is not None:
+                    b.tofile(f)
+        it = max([pb.current_iter for pb in self.pbridges.values()] or [0])
+        with open(prefix + ".ITER", "w") as f:
+            f.write("%d\n" % it)
+
+    def read_snapshot(self, prefix):
+        self.read_model_from_file(prefix + ".MODEL")
+        with open(prefix + ".HISTORY", "rb") as f:
+            for name, pb in self.param_bridges():
+                w = np.fromfile(f, np.float32, pb.n_w)
+                b = np.fromfile(f, np.float32, pb.n_b) if pb.n_b else None
+                if w.size != pb.n_w or (b is not None and b.size != pb.n_b):
+                    raise ValueError("history file ends inside layer %r" % name)
+                pb.set_history_host(w, b)
+        with open(prefix + ".ITER") as f:
+            it = int(f.read().split()[0])
+        for pb in self.pbridges.values():
+            pb.set_current_iter(it)
+
     def num_parameters(self):
         return sum(pb.count for pb in self.pbridges.values())
 

@@ -32,6 +32,35 @@ def partition_batch(global_batch, n_partitions):
     return out
 
 
+def partition_by_proportions(global_batch, proportions):
+    """GPU batch sizes from per-GPU batch proportions, the reference's placement fields gpu_{0..3}_batch_proportion
+    (src/parser/cnn.proto:249-256; any number of GPUs here).  As ParallelizedBridge::update_scheduler_partitions_for_curr_B
+    does (src/bridges/ParallelizedBridge.h:615-719): GPU i takes trunc(proportion_i * batch) images, GPUs whose share
+    comes out as zero are dropped, and the images left over by the truncation are spread over the GPUs in use, the
+    remainder of that division going to the first one.  Returns [(gpu index, start, size)] with contiguous slices in
+    GPU order.  The reference hands whatever the proportions do not cover to CPU partitions; there is no CPU path here,
+    so proportions that leave more than the truncation's leftovers uncovered are refused."""
+    if global_batch <= 0 or not proportions or any(p < 0 for p in proportions):
+        raise ValueError("need a positive batch and non-negative proportions")
+    sizes = [(i, int(p * global_batch)) for i, p in enumerate(proportions)]
+    sizes = [(i, n) for i, n in sizes if n > 0]
+    if not sizes:
+        raise ValueError("no GPU receives any image")
+    left = global_batch - sum(n for _, n in sizes)
+    if left < 0:
+        raise ValueError("proportions add up to more than the batch")
+    if left >= len(proportions) + 1 and sum(proportions) < 1.0 - 1e-6:
+        raise ValueError("proportions leave %d of %d images to CPU partitions, which are not built (no CPU fallback)" %
+                         (left, global_batch))
+    per, extra = left // len(sizes), left % len(sizes)
+    out, start = [], 0
+    for j, (i, n) in enumerate(sizes):
+        n += per + (extra if j == 0 else 0)
+        out.append((i, start, n))
+        start += n
+    return out
+
+
 class SolverParameter:
     """The solver fields the updater reads (src/algorithms/GradientUpdater.h:60-120, src/util.h:76-100)."""
 
@@ -238,6 +267,20 @@ class ParallelizedBridge:
 
     def get_model_grad_cube(self):
         return self.bridge.p_model_gradient_cube
+
+    # momentum history to / from the host (force_device_to_host_*_history_copy, src/bridges/ParallelizedBridge.h:482-507)
+    def history_host(self):
+        ctx = self.bridge.ctx
+        ctx.sync()
+        h = np.empty(self.count, np.float32)
+        ctx.d2h(h, self.hist)
+        return h[:self.n_w].copy(), (h[self.n_w:].copy() if self.n_b else None)
+
+    def set_history_host(self, w_hist, b_hist=None):
+        ctx = self.bridge.ctx
+        h = np.concatenate([np.ascontiguousarray(w_hist, np.float32).ravel()] +
+                           ([np.ascontiguousarray(b_hist, np.float32).ravel()] if self.n_b else []))
+        ctx.h2d(self.hist, h)
 
     def get_bias_grad_cube(self):
         return self.bridge.p_bias_gradient_cube

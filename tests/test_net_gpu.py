@@ -155,3 +155,33 @@ def test_iteration_matches_reference_bridges_and_unfused_net(ctx, nets, referenc
         assert_close(pb.get_bias_cube().download().reshape(-1), want_b.astype(np.float32), "updated bias " + name)
     for (name, pf), (_, pp) in zip(fused.param_bridges(), plain.param_bridges()):
         assert maxnorm_rel(pf.get_model_cube().download(), pp.get_model_cube().download()) <= 1e-5
+
+
+def test_snapshot_round_trip_resumes_the_same_trajectory(ctx, tmp_path):
+    """MODEL / HISTORY / ITER written after two steps and read into a fresh net: the third step is bit-identical."""
+    net_param, solver = parse_prototxt(NET), solver_from_message(parse_prototxt(SOLVER))
+    rng = np.random.default_rng(77)
+    X = rng.standard_normal((B, 3, 67, 67), dtype=np.float32)
+    labels = rng.integers(0, 12, B).astype(np.float32)
+    mask = (rng.random((B, 64, 1, 1)) < 0.5).astype(np.uint32)
+    a, b = Net(ctx, net_param, solver, B), Net(ctx, net_param, solver, B)
+    for net in (a, b):
+        for i, br in enumerate(net.bridges):
+            if net.types[i] == "Dropout":
+                br.set_mask(mask)
+        net.set_input(X, labels)
+    a.step()
+    a.step()
+    prefix = os.path.join(str(tmp_path), "snap")
+    a.write_snapshot(prefix)
+    assert open(prefix + ".ITER").read().split() == ["2"]
+    assert os.path.getsize(prefix + ".HISTORY") == os.path.getsize(prefix + ".MODEL") == 4 * a.num_parameters()
+    b.read_snapshot(prefix)
+    a.step()
+    b.step()
+    ctx.sync()
+    for (name, pa), (_, pb) in zip(a.param_bridges(), b.param_bridges()):
+        assert np.array_equal(pa.get_model_cube().download(), pb.get_model_cube().download()), name
+        assert np.array_equal(pa.history_host()[0], pb.history_host()[0]), name
+    a.close()
+    b.close()

@@ -12,7 +12,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-from caffecontroll_b200.parallel import ParallelizedBridge, SolverParameter, get_learning_rate, partition_batch  # noqa: E402
+from caffecontroll_b200.parallel import (ParallelizedBridge, SolverParameter, get_learning_rate, partition_batch,  # noqa: E402
+                                         partition_by_proportions)
 from tests.parity import make_inputs, maxnorm_rel  # noqa: E402
 
 SHAPE = (6, 3, 9, 5, 3, 2, 1, 1)  # B, D, n, o, k, s, p, g
@@ -25,6 +26,21 @@ def test_partition_batch_is_contiguous_and_complete():
     assert partition_batch(3, 3) == [(0, 1), (1, 1), (2, 1)]
     with pytest.raises(ValueError):
         partition_batch(2, 3)
+
+
+def test_partition_by_proportions_follows_the_reference_rules():
+    # the reference's own 4-GPU AlexNet placement: 0.25 each
+    assert partition_by_proportions(256, [0.25] * 4) == [(i, 64 * i, 64) for i in range(4)]
+    assert partition_by_proportions(2048, [0.125] * 8) == [(i, 256 * i, 256) for i in range(8)]
+    # unequal shares; a GPU whose share truncates to zero is dropped
+    assert partition_by_proportions(256, [0.5, 0.25, 0.25, 0.0]) == [(0, 0, 128), (1, 128, 64), (2, 192, 64)]
+    # truncation leftovers: spread over the GPUs in use, the remainder to the first (3 x 85 = 255 of 256)
+    assert partition_by_proportions(256, [1 / 3.0] * 3) == [(0, 0, 86), (1, 86, 85), (2, 171, 85)]
+    assert partition_by_proportions(10, [0.75, 0.25]) == [(0, 0, 8), (1, 8, 2)]
+    with pytest.raises(ValueError):
+        partition_by_proportions(256, [0.25, 0.25])  # half the batch would go to CPU partitions: not built
+    with pytest.raises(ValueError):
+        partition_by_proportions(256, [0.75, 0.75])
 
 
 def test_learning_rate_matches_oracle(port):

@@ -31,7 +31,7 @@ def _expected(port, steps):
     return W, b
 
 
-def _run_rank(rank, world, device, steps, unique_id=None):
+def _run_rank(rank, world, device, steps, unique_id=None, proportions=None):
     """One rank's partition.  With `unique_id` the gradient sum goes through the library's own NCCL communicator
     (cct_comm_*), else through torch.distributed on torch's stream."""
     from caffecontroll_b200 import Context, ConvolutionBridge, Layer, LogicalCube
@@ -39,7 +39,11 @@ def _run_rank(rank, world, device, steps, unique_id=None):
     B, D, n, o, k, s, p, g = SHAPE
     m = (n + 2 * p - k) // s + 1
     X, W, b, dY = make_inputs(91, B, D, n, o, k, s, p, g)
-    start, size = partition_batch(B, world)[rank]
+    if proportions is None:
+        start, size = partition_batch(B, world)[rank]
+    else:  # unequal shares, as the reference's gpu_N_batch_proportion fields give them
+        from caffecontroll_b200.parallel import partition_by_proportions
+        _, start, size = partition_by_proportions(B, proportions)[rank]
     stream = None
     if world > 1 and unique_id is None:
         import torch
@@ -118,7 +122,7 @@ def _comm_rank(rank, world, id_path, out_dir):
             time.sleep(0.05)
         with open(id_path, "rb") as f:
             uid = f.read()
-    W, b = _run_rank(rank, world, rank, 2, unique_id=uid)
+    W, b = _run_rank(rank, world, rank, 2, unique_id=uid, proportions=[0.75, 0.25])  # 6 + 2 of the 8 images
     np.save(os.path.join(out_dir, "W_%d.npy" % rank), W)
     np.save(os.path.join(out_dir, "b_%d.npy" % rank), b)
 
