@@ -8,15 +8,17 @@
 //                             needs_to_calc_backward_grad, bias_term, model / bias / gradient cube accessors)
 //   FullyConnectedBridge      src/bridges/FullyConnectedBridge.h, over the convolution plan (kernel = whole input)
 //   SGDGradientUpdater        src/algorithms/GradientUpdater.h:154-193
-//   ParallelizedBridge        one partition per process: owns model, gradient and history, sums gradients through a
-//                             caller-supplied all-reduce (src/bridges/ParallelizedBridge_impl.hxx:876-971), then updates
+//   Communicator              the C ABI's NCCL communicator (cct_comm_*): one per driver / GPU
+//   ParallelizedBridge        one partition per GPU (one per process, or one per host thread as the reference's
+//                             PhysicalStratum runs them): owns model, gradient and history, sums gradients over the
+//                             partitions with an NCCL all-reduce (in place of src/bridges/ParallelizedBridge_impl.hxx:876-971:
+//                             device-to-host gather + serial CPU sum), then updates on the device
 // Errors: the reference's convention is print + assert(false) (src/sched/DeviceDriver.h:48-51); here the failing call
 // prints the library's message and aborts, unless a handler was installed with B200Driver::set_error_handler.
 #pragma once
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
-#include <functional>
 #include <string>
 #include <vector>
 
@@ -211,34 +213,71 @@ class ConvolutionBridge : public PhysicalOperator {
   LogicalCube<float>* p_bias_gradient_cube_ = nullptr;
 };
 
-// The reference's FullyConnectedBridge (src/bridges/FullyConnectedBridge_impl.hxx:201-202, 305-312) is a convolution
-// whose kernel covers the whole input.  Here: a ConvolutionBridge with a 1x1 kernel over the input viewed as D*R*C
-// channels of one pixel - the same arithmetic on the same weight layout [o][d][r][c].  Output layer: B x num_output
-// x 1 x 1.  Not tuned: a long reduction stays in one accumulator.
+// The reference's FullyConnectedBridge (src/bridges/FullyConnectedBridge_impl.hxx:171-235, 257-330): Y = X W^T + b over
+// the flattened input, weights [o][d][r][c].  Runs on the C ABI's fully connected plan (three tensor-core GEMMs that read
+// X, W and dY in place); feature counts must be multiples of 4.  Output layer: B x num_output x 1 x 1.
 class FullyConnectedBridge : public PhysicalOperator {
  public:
-  FullyConnectedBridge(Layer* in, Layer* out, int num_output, bool bias_term, B200Driver* driver, int algo = CCT_ALGO_AUTO)
-      : flat_data_(in->p_data_cube->get_p_data(), 1, 1, in->p_data_cube->R * in->p_data_cube->C * in->p_data_cube->D,
-                   in->p_data_cube->B, driver),
-        flat_grad_(in->p_gradient_cube->get_p_data(), 1, 1,
-                   in->p_gradient_cube->R * in->p_gradient_cube->C * in->p_gradient_cube->D, in->p_gradient_cube->B, driver),
-        flat_(&flat_data_, &flat_grad_),
-        conv_(&flat_, out, params(num_output, bias_term), driver, algo) {}
-  ConvolutionBridge& as_convolution() { return conv_; }  // model / bias cubes, fusion switches
-  void forward() override { conv_.forward(); }
-  void backward() override { conv_.backward(); }
+  Layer* const p_input_layer;
+  Layer* const p_output_layer;
+  B200Driver* const p_driver;
+  const bool bias_term;
+  bool needs_to_calc_backward_grad = true;
+  bool fuse_relu = false;           // clamp the output at 0 (the ReLU bridge behind the layer)
+  bool fuse_relu_backward = false;  // input gradient times [input > 0] (the ReLU bridge in front)
+
+  FullyConnectedBridge(Layer* in, Layer* out, int num_output, bool bias, B200Driver* driver)
+      : p_input_layer(in), p_output_layer(out), p_driver(driver), bias_term(bias),
+        in_features_(in->p_data_cube->R * in->p_data_cube->C * in->p_data_cube->D) {
+    const LogicalCube<float>* x = in->p_data_cube;
+    if (out->p_data_cube->B != x->B || (int)(out->p_data_cube->n_elements / x->B) != num_output)
+      driver->check(CCT_ERR_INVALID, "FullyConnectedBridge: output layer must be B x num_output x 1 x 1");
+    driver->check(cct_fc_plan_create(driver->ctx(), (int)x->B, (int)in_features_, num_output, bias ? 1 : 0, &plan_),
+                  "cct_fc_plan_create");
+    p_model_cube_ = new LogicalCube<float>(x->R, x->C, x->D, num_output, driver);
+    p_model_gradient_cube_ = new LogicalCube<float>(x->R, x->C, x->D, num_output, driver);
+    if (bias) {
+      p_bias_cube_ = new LogicalCube<float>(1, 1, num_output, 1, driver);
+      p_bias_gradient_cube_ = new LogicalCube<float>(1, 1, num_output, 1, driver);
+      p_bias_cube_->reset_cube(0.f);
+    }
+  }
+  ~FullyConnectedBridge() {
+    if (plan_) cct_fc_plan_destroy(plan_);
+    delete p_model_cube_; delete p_model_gradient_cube_; delete p_bias_cube_; delete p_bias_gradient_cube_;
+  }
+  LogicalCube<float>* get_model_cube() { return p_model_cube_; }
+  LogicalCube<float>* get_bias_cube() { return p_bias_cube_; }
+  LogicalCube<float>* get_model_grad_cube() { return p_model_gradient_cube_; }
+  LogicalCube<float>* get_bias_grad_cube() { return p_bias_gradient_cube_; }
+  void set_model_cube(float* p) { p_model_cube_->set_p_data(p); }
+  void set_bias_cube(float* p) { if (p_bias_cube_) p_bias_cube_->set_p_data(p); }
+  void set_model_grad_cube(float* p) { p_model_gradient_cube_->set_p_data(p); }
+  void set_bias_grad_cube(float* p) { if (p_bias_gradient_cube_) p_bias_gradient_cube_->set_p_data(p); }
+
+  void forward() override {
+    p_driver->check(cct_fc_forward(plan_, p_input_layer->p_data_cube->get_p_data(), p_model_cube_->get_p_data(),
+                                   bias_term ? p_bias_cube_->get_p_data() : nullptr,
+                                   p_output_layer->p_data_cube->get_p_data(), fuse_relu ? 1 : 0, nullptr, 1.f),
+                    "cct_fc_forward");
+  }
+  void backward() override {
+    p_driver->check(cct_fc_backward(plan_, p_input_layer->p_data_cube->get_p_data(), p_model_cube_->get_p_data(),
+                                    p_output_layer->p_gradient_cube->get_p_data(),
+                                    needs_to_calc_backward_grad ? p_input_layer->p_gradient_cube->get_p_data() : nullptr,
+                                    p_model_gradient_cube_->get_p_data(),
+                                    bias_term ? p_bias_gradient_cube_->get_p_data() : nullptr, fuse_relu_backward ? 1 : 0,
+                                    nullptr, 1.f),
+                    "cct_fc_backward");
+  }
 
  private:
-  static ConvolutionParameter params(int num_output, bool bias_term) {
-    ConvolutionParameter cp;
-    cp.num_output = num_output;
-    cp.kernel_size = 1;
-    cp.bias_term = bias_term;
-    return cp;
-  }
-  LogicalCube<float> flat_data_, flat_grad_;
-  Layer flat_;
-  ConvolutionBridge conv_;
+  size_t in_features_;
+  cct_fc_plan* plan_ = nullptr;
+  LogicalCube<float>* p_model_cube_ = nullptr;
+  LogicalCube<float>* p_model_gradient_cube_ = nullptr;
+  LogicalCube<float>* p_bias_cube_ = nullptr;
+  LogicalCube<float>* p_bias_gradient_cube_ = nullptr;
 };
 
 // The solver fields the updater reads, with the reference's learning-rate policies (src/util.h:76-100).
@@ -286,16 +325,39 @@ class SGDGradientUpdater {
   LogicalCube<float> history_;
 };
 
-// One process = one batch partition.  forward()/backward() run the sub-bridge; backward() then sums the model and bias
-// gradients over all partitions through `allreduce_sum` (NULL: single partition) and applies the SGD update, identical
-// on every partition.  Model and bias (and their gradients) are contiguous (W | bias) so one all-reduce covers both.
-class ParallelizedBridge : public PhysicalOperator {
+// The C ABI's communicator: NCCL all-reduce of gradients over the partitions.  Rank 0 calls unique_id() and hands the
+// bytes to the other ranks (threads of one process, or processes through any channel); nranks == 1 needs no id.
+class Communicator {
  public:
-  typedef std::function<void(float* device_buffer, size_t count)> AllReduceSum;
-  ParallelizedBridge(ConvolutionBridge* sub, const SolverParameter* solver, B200Driver* driver,
-                     AllReduceSum allreduce_sum = nullptr, float model_lr_mult = 1.f, float model_decay_mult = 1.f,
-                     float bias_lr_mult = 2.f, float bias_decay_mult = 0.f)
-      : sub_(sub), p_driver_(driver), allreduce_(allreduce_sum), n_w_(sub->get_model_cube()->n_elements),
+  static std::vector<unsigned char> unique_id() {
+    std::vector<unsigned char> id(CCT_COMM_ID_BYTES);
+    if (cct_comm_unique_id(id.data()) != CCT_OK) { std::fprintf(stderr, "cct_b200: NCCL is not available\n"); std::abort(); }
+    return id;
+  }
+  Communicator(B200Driver* driver, int nranks, int rank, const unsigned char* id) : driver_(driver) {
+    driver->check(cct_comm_init_rank(driver->ctx(), nranks, rank, id, &comm_), "cct_comm_init_rank");
+  }
+  ~Communicator() { if (comm_) cct_comm_destroy(comm_); }
+  Communicator(const Communicator&) = delete;
+  void allreduce_sum_begin(float* buf, size_t count) { driver_->check(cct_allreduce_sum_begin(comm_, buf, count), "cct_allreduce_sum_begin"); }
+  void wait() { driver_->check(cct_comm_wait(comm_), "cct_comm_wait"); }
+
+ private:
+  B200Driver* driver_;
+  cct_comm* comm_ = nullptr;
+};
+
+// One batch partition on one GPU.  forward()/backward() run the sub-bridge; backward() then sums the model and bias
+// gradients over all partitions (`comm`, NULL: single partition) and applies the SGD update, identical on every
+// partition.  Model and bias (and their gradients) are contiguous (W | bias) so one all-reduce covers both.
+// SubBridge: ConvolutionBridge or FullyConnectedBridge.
+template <class SubBridge>
+class ParallelizedBridgeT : public PhysicalOperator {
+ public:
+  ParallelizedBridgeT(SubBridge* sub, const SolverParameter* solver, B200Driver* driver, Communicator* comm = nullptr,
+                      float model_lr_mult = 1.f, float model_decay_mult = 1.f, float bias_lr_mult = 2.f,
+                      float bias_decay_mult = 0.f)
+      : sub_(sub), p_driver_(driver), comm_(comm), n_w_(sub->get_model_cube()->n_elements),
         n_b_(sub->bias_term ? sub->get_bias_cube()->n_elements : 0), params_(n_w_ + n_b_, 1, 1, 1, driver),
         grads_(n_w_ + n_b_, 1, 1, 1, driver),
         p_grad_updater(n_w_, params_.get_p_data(), solver, model_lr_mult, model_decay_mult, driver),
@@ -313,21 +375,25 @@ class ParallelizedBridge : public PhysicalOperator {
   void forward() override { sub_->forward(); }
   void backward() override {
     sub_->backward();
-    if (allreduce_) allreduce_(grads_.get_p_data(), n_w_ + n_b_);
+    if (comm_) {
+      comm_->allreduce_sum_begin(grads_.get_p_data(), n_w_ + n_b_);  // gradients are summed, not averaged (:916-955)
+      comm_->wait();
+    }
     if (!update_model_gradients) return;
     p_grad_updater.update(grads_.get_p_data());
     if (n_b_) p_grad_updater_bias.update(grads_.get_p_data() + n_w_);
   }
 
  private:
-  ConvolutionBridge* sub_;
+  SubBridge* sub_;
   B200Driver* p_driver_;
-  AllReduceSum allreduce_;
+  Communicator* comm_;
   size_t n_w_, n_b_;
   LogicalCube<float> params_, grads_;
 
  public:
   SGDGradientUpdater p_grad_updater, p_grad_updater_bias;
 };
+typedef ParallelizedBridgeT<ConvolutionBridge> ParallelizedBridge;
 
 }  // namespace cct

@@ -1,8 +1,13 @@
 // Runs one convolution layer through the C++ bridge mirror (cct_host.h): forward, backward, and optionally the
 // ParallelizedBridge's SGD step.  Inputs and outputs are raw fp32 files in a directory, so a test harness can feed the
 // same tensors to a CPU checker:
-//   host_selftest <dir> B D n o k s p g steps
+//   host_selftest <dir> B D n o k s p g steps [fc | ranks=N]
 // reads  X.bin W.bin b.bin dY.bin ; writes Y.bin dX.bin dW.bin db.bin Wnew.bin bnew.bin
+//   fc       additionally runs the same tensors through FullyConnectedBridge (needs k == n: an inner product)
+//   ranks=N  additionally splits the batch over N GPUs, one host thread and one B200Driver per GPU (as the reference's
+//            PhysicalStratum runs its partitions), gradients summed by the C ABI's NCCL communicator; writes
+//            Wnew_r<rank>.bin / bnew_r<rank>.bin after `steps` updates - every rank must hold the single-GPU result
+#include <thread>
 #include <fstream>
 #include <iostream>
 
@@ -55,18 +60,46 @@ int main(int argc, char** argv) {
   std::vector<float> hw(hdw.size()), hb(o);
   conv.get_model_cube()->copy_to_host(hw.data()); conv.get_bias_cube()->copy_to_host(hb.data());
   save(dir + "/Wnew.bin", hw); save(dir + "/bnew.bin", hb);
-  if (argc > 11 && std::string(argv[11]) == "fc") {
-    // kernel == input: the same layer through FullyConnectedBridge (a 1x1 convolution over the flattened input)
+  const std::string mode = argc > 11 ? argv[11] : "";
+  if (mode == "fc") {
+    // kernel == input: the same layer through FullyConnectedBridge (tensor-core GEMMs over the flattened input)
     FullyConnectedBridge fc(&in, &out, o, true, &driver);
-    ConvolutionBridge& c = fc.as_convolution();
-    c.get_model_cube()->copy_from_host(load(dir + "/W.bin", c.get_model_cube()->n_elements).data());
-    c.get_bias_cube()->copy_from_host(load(dir + "/b.bin", o).data());
+    fc.get_model_cube()->copy_from_host(load(dir + "/W.bin", fc.get_model_cube()->n_elements).data());
+    fc.get_bias_cube()->copy_from_host(load(dir + "/b.bin", o).data());
     fc.forward();
     fc.backward();
     driver.device_sync();
     y.copy_to_host(hy.data()); dx.copy_to_host(hdx.data());
-    c.get_model_grad_cube()->copy_to_host(hdw.data()); c.get_bias_grad_cube()->copy_to_host(hdb.data());
+    fc.get_model_grad_cube()->copy_to_host(hdw.data()); fc.get_bias_grad_cube()->copy_to_host(hdb.data());
     save(dir + "/Y_fc.bin", hy); save(dir + "/dX_fc.bin", hdx); save(dir + "/dW_fc.bin", hdw); save(dir + "/db_fc.bin", hdb);
+  }
+  if (mode.compare(0, 6, "ranks=") == 0) {
+    const int ranks = atoi(mode.c_str() + 6);
+    if (ranks < 2 || B % ranks) { std::cerr << "ranks must be >= 2 and divide the batch" << std::endl; return 2; }
+    const std::vector<unsigned char> id = Communicator::unique_id();
+    const std::vector<float> hX = load(dir + "/X.bin", x.n_elements), hdY = load(dir + "/dY.bin", dy.n_elements),
+                             hW = load(dir + "/W.bin", hdw.size()), hb0 = load(dir + "/b.bin", o);
+    const int Bp = B / ranks;
+    std::vector<std::thread> threads;
+    for (int r = 0; r < ranks; ++r)
+      threads.emplace_back([&, r]() {
+        B200Driver drv(r);
+        Communicator comm(&drv, ranks, r, id.data());
+        LogicalCube<float> px(n, n, D, Bp, &drv), pdx(n, n, D, Bp, &drv), py(m, m, o, Bp, &drv), pdy(m, m, o, Bp, &drv);
+        Layer pin(&px, &pdx), pout(&py, &pdy);
+        ConvolutionBridge sub(&pin, &pout, cp, &drv);
+        ParallelizedBridge pb(&sub, &solver, &drv, &comm);
+        px.copy_from_host(hX.data() + (size_t)r * px.n_elements);    // contiguous batch slices, partition r
+        pdy.copy_from_host(hdY.data() + (size_t)r * pdy.n_elements);
+        sub.get_model_cube()->copy_from_host(hW.data());
+        sub.get_bias_cube()->copy_from_host(hb0.data());
+        for (int i = 0; i < steps; ++i) { pb.forward(); pb.backward(); }
+        drv.device_sync();
+        std::vector<float> w(hW.size()), b(o);
+        sub.get_model_cube()->copy_to_host(w.data()); sub.get_bias_cube()->copy_to_host(b.data());
+        save(dir + "/Wnew_r" + std::to_string(r) + ".bin", w); save(dir + "/bnew_r" + std::to_string(r) + ".bin", b);
+      });
+    for (auto& t : threads) t.join();
   }
   std::cout << "host_selftest ok" << std::endl;
   return 0;

@@ -76,3 +76,26 @@ def test_host_fully_connected_mirror_matches_oracle(port, tmp_path):
         assert_close(rd("dX" + tag, X.shape), dXr, "dX" + tag)
         assert_close(rd("dW" + tag, W.shape), dWr, "dW" + tag)
         assert_close(rd("db" + tag, (o,)), dbr, "db" + tag)
+
+
+@pytest.mark.gpu
+def test_host_mirror_two_gpus_one_thread_each(port, tmp_path):
+    """The C++ ParallelizedBridge with the C ABI's NCCL communicator, no Python and no torch in the data path: two host
+    threads, one GPU each, half the batch each; after two SGD steps both hold the parameters of the single-GPU run."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    exe = _build()
+    B, D, n, o, k, s, p, g = 8, 6, 13, 10, 3, 1, 1, 1
+    X, W, b, dY = make_inputs(57, B, D, n, o, k, s, p, g)
+    for name, arr in (("X", X), ("W", W), ("b", b), ("dY", dY)):
+        arr.tofile(os.path.join(str(tmp_path), name + ".bin"))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    subprocess.run([exe, str(tmp_path)] + [str(v) for v in (B, D, n, o, k, s, p, g, 2)] + ["ranks=2"], check=True, env=env,
+                   timeout=300)
+    rd = lambda name, shape: np.fromfile(os.path.join(str(tmp_path), name + ".bin"), np.float32).reshape(shape)
+    W1, b1 = rd("Wnew", W.shape), rd("bnew", (o,))
+    for r in (0, 1):
+        assert maxnorm_rel(rd("Wnew_r%d" % r, W.shape), W1) <= TOL
+        assert maxnorm_rel(rd("bnew_r%d" % r, (o,)), b1) <= TOL
+    assert np.array_equal(rd("Wnew_r0", W.shape), rd("Wnew_r1", W.shape))
