@@ -1,7 +1,7 @@
 // Direct convolution in fp32 FMA arithmetic (CCT_ALGO_SIMT_FP32).
 //
-// Used for shapes that are too small to fill a tensor-core tile (LeNet conv1: K = 25, 20 filters) and as an
-// on-device cross-check of the tcgen05 path at full size.  Every output element is reduced by one thread (forward,
+// CCT_ALGO_AUTO picks it only where the tcgen05 path does not apply (kernels wider than 15, tables beyond shared
+// memory); tests ask for it by name as a second on-device implementation to cross-check the tcgen05 path at full size.  Every output element is reduced by one thread (forward,
 // data gradient) or one thread block (weight and bias gradients) in a fixed order, so results are deterministic.
 #include "cct_internal.h"
 

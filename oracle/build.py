@@ -15,7 +15,12 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REF_ENV = "CCT_REFERENCE_ROOT"
-DEFAULT_REF = "/root/reference"
+
+
+def reference_root():
+    """The reference source tree: the directory CCT_REFERENCE_ROOT names, else a checkout called `reference` beside
+    this repository (absent on machines that only run the prebuilt checkers)."""
+    return os.environ.get(REF_ENV) or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 
 def _run(cmd):
@@ -50,7 +55,7 @@ def build_port(force=False):
 
 
 def build_reference(force=False):
-    ref = os.environ.get(REF_ENV, DEFAULT_REF)
+    ref = reference_root()
     src_dir = os.path.join(ref, "src")
     out_dir = os.path.join(HERE, "_ref")
     out = os.path.join(out_dir, "libcct_ref.so")
@@ -83,7 +88,7 @@ def build_adaptor_test(force=False):
     headers in place, with the oracle's three shim headers, into oracle/_ref/adaptor_fixture_test; beside it the
     reference's text fixtures of tests/test_parallelized_convolution.cpp converted to raw fp32 files (git-ignored, they
     travel with the built program).  Only possible where the reference tree is mounted."""
-    ref = os.environ.get(REF_ENV, DEFAULT_REF)
+    ref = reference_root()
     src_dir = os.path.join(ref, "src")
     out_dir = os.path.join(HERE, "_ref")
     exe = os.path.join(out_dir, "adaptor_fixture_test")

@@ -25,7 +25,7 @@ def _build():
 
 def test_adaptor_compiles_against_the_reference_headers():
     from oracle import build as obuild
-    ref = os.environ.get(obuild.REF_ENV, obuild.DEFAULT_REF)
+    ref = obuild.reference_root()
     if not os.path.isdir(os.path.join(ref, "src")):
         pytest.skip("the reference tree is not mounted here")
     exe = _build()

@@ -9,9 +9,10 @@ import os
 import numpy as np
 import pytest
 
+from oracle.build import reference_root
 from tests.parity import assert_close, make_inputs, maxnorm_rel
 
-REF_TESTS = os.path.join(os.environ.get("CCT_REFERENCE_ROOT", "/root/reference"), "tests")
+REF_TESTS = os.path.join(reference_root(), "tests")
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "conv_golden.npz")
 needs_ref_tree = pytest.mark.skipif(not os.path.isdir(REF_TESTS), reason="reference tree not mounted")
 
