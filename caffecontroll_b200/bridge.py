@@ -182,12 +182,14 @@ class ConvolutionBridge:
                                              self.p_output_layer.p_data_cube.ptr, int(self.fuse_relu)),
                    "cct_conv_forward", self.ctx.h)
 
-    def fuse_pool_relu_backward(self, pooled_gradient_cube, max_index_cube, kernel_size, stride):
+    def fuse_pool_relu_backward(self, pooled_gradient_cube, max_index_cube, kernel_size, stride, pooled_data_cube=None):
         """Fold the ReLU and max-pooling bridges that follow this layer into backward(): the output gradient is
         rebuilt from the pooled tensor's gradient and the pooling indices (MaxPoolingBridge::backward then
-        ReLUBridge::backward in the reference) instead of being read from p_output_layer.p_gradient_cube."""
+        ReLUBridge::backward in the reference) instead of being read from p_output_layer.p_gradient_cube.  With
+        `pooled_data_cube` (the pooling bridge's output, still as the forward pass wrote it when backward() runs) the
+        ReLU mask is read from it instead of from this layer's much larger output: same result, fewer bytes."""
         capi.check(self.lib.cct_conv_plan_reserve_fusion(self.plan), "cct_conv_plan_reserve_fusion", self.ctx.h)
-        self.pool_fusion = (pooled_gradient_cube, max_index_cube, kernel_size, stride)
+        self.pool_fusion = (pooled_gradient_cube, max_index_cube, kernel_size, stride, pooled_data_cube)
 
     def backward(self):
         dx = self.p_input_layer.p_gradient_cube.ptr if self.needs_to_calc_backward_grad else None
@@ -197,11 +199,12 @@ class ConvolutionBridge:
             capi.check(self.lib.cct_conv_backward(self.plan, x, w, self.p_output_layer.p_gradient_cube.ptr, dx, dw, db),
                        "cct_conv_backward", self.ctx.h)
             return
-        f = capi.BwdFusion(None, None, None, 0, 0, int(self.fuse_relu_backward))
+        f = capi.BwdFusion(None, None, None, 0, 0, int(self.fuse_relu_backward), None)
         dy = self.p_output_layer.p_gradient_cube.ptr
         if self.pool_fusion is not None:
-            dp, idx, k, s = self.pool_fusion
+            dp, idx, k, s, pooled = self.pool_fusion
             f.A, f.idx, f.dP, f.pool_k, f.pool_s = self.p_output_layer.p_data_cube.ptr, idx.ptr, dp.ptr, k, s
+            f.P = pooled.ptr if pooled is not None else None
             dy = None
         capi.check(self.lib.cct_conv_backward_fused(self.plan, x, w, dy, C.byref(f), dx, dw, db),
                    "cct_conv_backward_fused", self.ctx.h)

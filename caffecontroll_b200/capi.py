@@ -25,7 +25,7 @@ EXPORTS = [
     "cct_conv_plan_enable_timing", "cct_conv_plan_last_timings", "cct_conv_forward", "cct_conv_backward", "cct_conv_backward_fused",
     "cct_conv_plan_reserve_fusion", "cct_selftest_bounded_wait", "cct_conv_forward_host", "cct_conv_backward_host", "cct_conv_weight_grad_noalloc",
     "cct_maxpool_forward", "cct_maxpool_backward", "cct_relu_forward", "cct_relu_backward",
-    "cct_pool_relu_backward", "cct_sgd_step", "cct_saxpby",
+    "cct_pool_relu_backward", "cct_sgd_step", "cct_saxpby", "cct_l1_update",
     "cct_fc_plan_create", "cct_fc_plan_destroy", "cct_fc_plan_workspace_bytes", "cct_fc_forward", "cct_fc_backward",
     "cct_fc_plan_enable_timing", "cct_fc_plan_last_timings",
     "cct_comm_unique_id", "cct_comm_init_rank", "cct_comm_destroy", "cct_comm_size", "cct_allreduce_sum_begin",
@@ -43,7 +43,7 @@ class CctError(RuntimeError):
 class BwdFusion(C.Structure):
     """cct_bwd_fusion: what cct_conv_backward_fused folds into the backward pass."""
     _fields_ = [("A", C.c_void_p), ("idx", C.c_void_p), ("dP", C.c_void_p), ("pool_k", C.c_int), ("pool_s", C.c_int),
-                ("relu_mask_dx", C.c_int)]
+                ("relu_mask_dx", C.c_int), ("P", C.c_void_p)]
 
 
 class ConvDesc(C.Structure):
@@ -103,6 +103,7 @@ def load():
         "cct_pool_relu_backward": [_vp, _vp, _vp, _vp, _vp, i, i, i, i],
         "cct_sgd_step": [_vp, sz, _vp, _vp, _vp, f, f, f],
         "cct_saxpby": [_vp, sz, f, _vp, f, _vp],
+        "cct_l1_update": [_vp, sz, _vp, f, _vp],
         "cct_comm_unique_id": [C.c_char_p],
         "cct_comm_init_rank": [_vp, i, i, C.c_char_p, C.POINTER(_vp)],
         "cct_comm_destroy": [_vp],

@@ -418,12 +418,13 @@ int cct_conv_backward_fused(cct_conv_plan* plan, const float* X, const float* W,
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
   if (f->dP) {
     // conv -> ReLU -> max-pool behind this layer: one pass builds the output gradient both kernels read.
-    if (!f->A || !f->idx || f->pool_k <= 0 || f->pool_s <= 0 || f->pool_k > G.m) return CCT_ERR_INVALID;
+    if ((!f->A && !f->P) || !f->idx || f->pool_k <= 0 || f->pool_s <= 0 || f->pool_k > G.m) return CCT_ERR_INVALID;
     if (!plan->mask_dY) {
       ctx->last_error = "cct_conv_backward_fused with a pooled gradient needs cct_conv_plan_reserve_fusion(plan) first";
       return CCT_ERR_INVALID;
     }
-    const int rc = cct_pool_relu_backward(ctx, f->A, f->idx, f->dP, plan->mask_dY, G.B * G.o, G.m, f->pool_k, f->pool_s);
+    const int rc = f->P ? pool_relu_backward_pooled(ctx, f->P, f->idx, f->dP, plan->mask_dY, G.B * G.o, G.m, f->pool_k, f->pool_s)
+                        : cct_pool_relu_backward(ctx, f->A, f->idx, f->dP, plan->mask_dY, G.B * G.o, G.m, f->pool_k, f->pool_s);
     if (rc != CCT_OK) return rc;
     dY = plan->mask_dY;
   }

@@ -78,4 +78,6 @@ int umma_conv_dgrad(cct_ctx* ctx, UmmaPlan* p, const float* W, const float* dY, 
                     bool repack);
 
 // ---- max pooling forward with the plane staged in shared memory (layers.cu)
+int pool_relu_backward_pooled(cct_ctx* ctx, const float* P, const int32_t* idx, const float* dP, float* dA, int planes,
+                              int n, int k, int s);
 int maxpool_forward_staged(cct_ctx* ctx, const float* X, float* Y, int32_t* idx, int planes, int n, int m, int k, int s);

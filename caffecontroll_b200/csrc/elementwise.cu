@@ -77,6 +77,13 @@ __global__ void saxpby_kernel(size_t count, float alpha, const float* __restrict
     y[i] = __fadd_rn(__fmul_rn(alpha, x[i]), __fmul_rn(beta, y[i]));
 }
 
+// g += lambda * sign(w) with sign(0) = -1: DeviceDriver::L1_update as the host driver computes it
+// (src/sched/DeviceDriver_CPU.cpp:111-117), the L1 branch of the SGD updater.
+__global__ void l1_update_kernel(size_t count, float* __restrict__ g, float lambda, const float* __restrict__ w) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x)
+    g[i] = __fadd_rn(g[i], w[i] > 0.f ? lambda : -lambda);
+}
+
 __global__ void relu_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, size_t count, size_t vec) {
   const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, nthreads = (size_t)gridDim.x * blockDim.x;
   for (size_t i = tid; i < vec; i += nthreads) {
@@ -152,6 +159,7 @@ template <int T, bool RELU>
 __global__ void __launch_bounds__(kPoolWarps * 32, 5) maxpool_bwd_kernel(const float* __restrict__ A,
                                                                       const int32_t* __restrict__ idx,
                                                                       const float* __restrict__ dP,
+                                                                      const float* __restrict__ P,
                                                                       float* __restrict__ dA, int planes, int n, int m,
                                                                       int k, int s, uint32_t inv_s, int mm_pad) {
   extern __shared__ uint32_t pool_smem[];
@@ -176,7 +184,9 @@ __global__ void __launch_bounds__(kPoolWarps * 32, 5) maxpool_bwd_kernel(const f
     __syncwarp();  // the previous plane's window tests are done with the shared slice
     for (int i = lane; i < mm; i += 32) {
       s_idx[i] = __ldg(ip + i);
-      s_dp[i] = __ldg(gp + i);
+      // With the pooled tensor P given, the ReLU mask is applied here: the element a window points at holds exactly
+      // that window's maximum, so [A > 0] at the element equals [P > 0] at the window.
+      s_dp[i] = (P == nullptr || __ldg(P + (size_t)plane * mm + i) > 0.f) ? __ldg(gp + i) : 0.f;
     }
     // lane = column (in chunks of 32), eight rows per step with their A values loaded together: no division and no
     // global load inside the window tests.
@@ -249,6 +259,7 @@ template <bool RELU>
 __global__ void __launch_bounds__(kPoolWarps * 32) maxpool_bwd4_kernel(const float* __restrict__ A,
                                                                       const int32_t* __restrict__ idx,
                                                                       const float* __restrict__ dP,
+                                                                      const float* __restrict__ P,
                                                                       float* __restrict__ dA, int planes, int n, int m,
                                                                       int k, int s, int slice) {
   extern __shared__ uint32_t pool_smem[];
@@ -290,7 +301,9 @@ __global__ void __launch_bounds__(kPoolWarps * 32) maxpool_bwd4_kernel(const flo
     __syncwarp();  // the previous plane's tests are done with the slice
     for (int i = lane; i < mm; i += 32) {
       s_idx[i] = __ldg(ip + i);
-      s_dp[i] = __ldg(gp + i);
+      // With the pooled tensor P given, the ReLU mask is applied here: the element a window points at holds exactly
+      // that window's maximum, so [A > 0] at the element equals [P > 0] at the window.
+      s_dp[i] = (P == nullptr || __ldg(P + (size_t)plane * mm + i) > 0.f) ? __ldg(gp + i) : 0.f;
     }
     __syncwarp();
     for (int e0 = 0; e0 < nn; e0 += 256) {
@@ -319,7 +332,7 @@ __global__ void __launch_bounds__(kPoolWarps * 32) maxpool_bwd4_kernel(const flo
 
 template <bool RELU>
 int launch_maxpool_bwd(cct_ctx* ctx, const float* A, const int32_t* idx, const float* dP, float* dA, int planes, int n,
-                       int m, int k, int s) {
+                       int m, int k, int s, const float* P = nullptr) {
   const int grid = plane_grid(ctx, (planes + kPoolWarps - 1) / kPoolWarps);
   const uint32_t inv_s = fast_div_magic((uint64_t)n, (uint32_t)s);
   const int taps = (k + s - 1) / s;
@@ -329,7 +342,7 @@ int launch_maxpool_bwd(cct_ctx* ctx, const float* A, const int32_t* idx, const f
     if (smem4 <= 100 * 1024) {  // two blocks per SM still fit
       if (smem4 > 48 * 1024)
         CCT_CUDA(ctx, cudaFuncSetAttribute(maxpool_bwd4_kernel<RELU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem4));
-      maxpool_bwd4_kernel<RELU><<<grid, kPoolWarps * 32, smem4, ctx->stream>>>(A, idx, dP, dA, planes, n, m, k, s, slice);
+      maxpool_bwd4_kernel<RELU><<<grid, kPoolWarps * 32, smem4, ctx->stream>>>(A, idx, dP, P, dA, planes, n, m, k, s, slice);
       return CCT_OK;
     }
   }
@@ -342,11 +355,26 @@ int launch_maxpool_bwd(cct_ctx* ctx, const float* A, const int32_t* idx, const f
   auto kernel = taps == 1 ? maxpool_bwd_kernel<1, RELU> : taps == 2 ? maxpool_bwd_kernel<2, RELU>
               : taps == 3 ? maxpool_bwd_kernel<3, RELU> : maxpool_bwd_kernel<0, RELU>;
   if (smem > 48 * 1024) CCT_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kernel<<<grid, kPoolWarps * 32, smem, ctx->stream>>>(A, idx, dP, dA, planes, n, m, k, s, inv_s, mm_pad);
+  kernel<<<grid, kPoolWarps * 32, smem, ctx->stream>>>(A, idx, dP, P, dA, planes, n, m, k, s, inv_s, mm_pad);
   return CCT_OK;
 }
 
 }  // namespace
+
+static int pool_args_ok(int planes, int n, int k, int s) { return planes > 0 && n > 0 && k > 0 && s > 0 && k <= n; }
+
+// cct_pool_relu_backward with the ReLU mask taken from the pooled tensor P instead of the full-size activation A
+// (bit-identical: see the staging loop of the kernels); reads planes * m * m values where the other reads planes * n * n.
+int pool_relu_backward_pooled(cct_ctx* ctx, const float* P, const int32_t* idx, const float* dP, float* dA, int planes,
+                              int n, int k, int s) {
+  if (!ctx || !P || !idx || !dP || !dA || !pool_args_ok(planes, n, k, s)) return CCT_ERR_INVALID;
+  const int m = (n - k) / s + 1;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  const int rc = launch_maxpool_bwd<false>(ctx, nullptr, idx, dP, dA, planes, n, m, k, s, P);
+  if (rc != CCT_OK) return rc;
+  CCT_CHECK_LAUNCH(ctx);
+  return CCT_OK;
+}
 
 extern "C" {
 
@@ -378,6 +406,15 @@ int cct_saxpby(cct_ctx* ctx, size_t count, float alpha, const float* x, float be
   return CCT_OK;
 }
 
+int cct_l1_update(cct_ctx* ctx, size_t count, float* g, float lambda, const float* w) {
+  if (!ctx || ((!g || !w) && count)) return CCT_ERR_INVALID;
+  if (!count) return CCT_OK;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  l1_update_kernel<<<grid_for(ctx, count, 256), 256, 0, ctx->stream>>>(count, g, lambda, w);
+  CCT_CHECK_LAUNCH(ctx);
+  return CCT_OK;
+}
+
 int cct_relu_forward(cct_ctx* ctx, const float* X, float* Y, size_t count) {
   if (!ctx || !X || !Y) return CCT_ERR_INVALID;
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
@@ -395,7 +432,6 @@ int cct_relu_backward(cct_ctx* ctx, const float* X, const float* dY, float* dX, 
   return CCT_OK;
 }
 
-static int pool_args_ok(int planes, int n, int k, int s) { return planes > 0 && n > 0 && k > 0 && s > 0 && k <= n; }
 
 int cct_maxpool_forward(cct_ctx* ctx, const float* X, float* Y, int32_t* idx, int planes, int n, int k, int s) {
   if (!ctx || !X || !Y || !idx || !pool_args_ok(planes, n, k, s)) return CCT_ERR_INVALID;

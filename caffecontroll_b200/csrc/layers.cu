@@ -33,30 +33,31 @@ template <int LOCAL>
 __global__ void __launch_bounds__(128) lrn_fwd_kernel(const float* __restrict__ X, float* __restrict__ Y,
                                                       float* __restrict__ scale, size_t items, int D, int chunks, int plane,
                                                       float alpha_over_size, float beta) {
-  constexpr int W = LOCAL / 2;
+  constexpr int W = LOCAL / 2, SPAN = kLrnChunk + 2 * W;
   for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < items; t += (size_t)gridDim.x * blockDim.x) {
     const size_t bc = t / plane, p = t - bc * plane;
     const size_t b = bc / chunks;
-    const int d0 = (int)(bc - b * chunks) * kLrnChunk, d1 = min(D, d0 + kLrnChunk);
-    const float* x = X + b * (size_t)D * plane + p;
-    float* y = Y + b * (size_t)D * plane + p;
-    float* sc = scale + b * (size_t)D * plane + p;
-    float win[LOCAL];  // x[d - W .. d + W], one step behind at loop entry
+    const int d0 = (int)(bc - b * chunks) * kLrnChunk;
+    const size_t base = b * (size_t)D * plane + p;
+    // the chunk and its halo, all loads issued before the first use (a thread keeps SPAN requests in flight)
+    float x[SPAN];
 #pragma unroll
-    for (int i = 0; i < LOCAL; ++i) {
-      const int c = d0 + i - W - 1;
-      win[i] = (c >= 0 && c < D) ? x[(size_t)c * plane] : 0.f;
+    for (int i = 0; i < SPAN; ++i) {
+      const int c = d0 + i - W;
+      x[i] = (c >= 0 && c < D) ? __ldg(X + base + (size_t)c * plane) : 0.f;
     }
-    for (int d = d0; d < d1; ++d) {
 #pragma unroll
-      for (int i = 0; i + 1 < LOCAL; ++i) win[i] = win[i + 1];
-      win[LOCAL - 1] = d + W < D ? x[(size_t)(d + W) * plane] : 0.f;
-      float sum = 0.f;
+    for (int j = 0; j < kLrnChunk; ++j) {
+      const int d = d0 + j;
+      if (d < D) {
+        float sum = 0.f;
 #pragma unroll
-      for (int i = 0; i < LOCAL; ++i) sum += win[i] * win[i];
-      const float s = alpha_over_size * sum + 1.f;
-      sc[(size_t)d * plane] = s;
-      y[(size_t)d * plane] = win[W] * inv_pow(s, beta);
+        for (int i = 0; i < LOCAL; ++i) sum += x[j + i] * x[j + i];
+        const float s = alpha_over_size * sum + 1.f;
+        const size_t at = base + (size_t)d * plane;
+        scale[at] = s;
+        Y[at] = x[j + W] * inv_pow(s, beta);
+      }
     }
   }
 }
@@ -96,30 +97,36 @@ __global__ void __launch_bounds__(128) lrn_bwd_kernel(const float* __restrict__ 
                                                       const float* __restrict__ scale, const float* __restrict__ dY,
                                                       float* __restrict__ dX, size_t items, int D, int chunks, int plane,
                                                       float alpha_over_size, float beta) {
-  constexpr int W = LOCAL / 2;
+  constexpr int W = LOCAL / 2, SPAN = kLrnChunk + 2 * W;
   const float coef = 2.f * beta * alpha_over_size;
   for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < items; t += (size_t)gridDim.x * blockDim.x) {
     const size_t bc = t / plane, p = t - bc * plane;
     const size_t b = bc / chunks;
-    const int d0 = (int)(bc - b * chunks) * kLrnChunk, d1 = min(D, d0 + kLrnChunk);
+    const int d0 = (int)(bc - b * chunks) * kLrnChunk;
     const size_t base = b * (size_t)D * plane + p;
-    auto term = [&](int c) {
-      if (c < 0 || c >= D) return 0.f;
-      const size_t at = base + (size_t)c * plane;
-      return __fdividef(dY[at] * Y[at], scale[at]);
-    };
-    float win[LOCAL];
+    // every load of the chunk and its halo is issued before the first use
+    float gy[SPAN], yy[SPAN], sc[SPAN], xx[kLrnChunk];
 #pragma unroll
-    for (int i = 0; i < LOCAL; ++i) win[i] = term(d0 + i - W - 1);
-    for (int c = d0; c < d1; ++c) {
+    for (int i = 0; i < SPAN; ++i) {
+      const int c = d0 + i - W;
+      const bool in = c >= 0 && c < D;
+      const size_t at = base + (size_t)(in ? c : 0) * plane;
+      gy[i] = in ? __ldg(dY + at) : 0.f;
+      yy[i] = in ? __ldg(Y + at) : 0.f;
+      sc[i] = in ? __ldg(scale + at) : 1.f;
+    }
 #pragma unroll
-      for (int i = 0; i + 1 < LOCAL; ++i) win[i] = win[i + 1];
-      win[LOCAL - 1] = term(c + W);
-      float acc = 0.f;
+    for (int j = 0; j < kLrnChunk; ++j) xx[j] = d0 + j < D ? __ldg(X + base + (size_t)(d0 + j) * plane) : 0.f;
 #pragma unroll
-      for (int i = 0; i < LOCAL; ++i) acc += win[i];
-      const size_t at = base + (size_t)c * plane;
-      dX[at] = dY[at] * inv_pow(scale[at], beta) - coef * X[at] * acc;
+    for (int i = 0; i < SPAN; ++i) yy[i] = __fdividef(gy[i] * yy[i], sc[i]);  // the window terms
+#pragma unroll
+    for (int j = 0; j < kLrnChunk; ++j) {
+      if (d0 + j < D) {
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < LOCAL; ++i) acc += yy[j + i];
+        dX[base + (size_t)(d0 + j) * plane] = gy[j + W] * inv_pow(sc[j + W], beta) - coef * xx[j] * acc;
+      }
     }
   }
 }

@@ -63,6 +63,9 @@ public:
   void math_saxpby(const int nElements, const float alpha, const float * X, const float beta, float * Y) const {
     check(cct_saxpby(ctx_, nElements, alpha, X, beta, Y), "cct_saxpby");
   }
+  void L1_update(const int n_elements, float * const p_gradient, const float lambda, const float * const p_model) {
+    check(cct_l1_update(ctx_, n_elements, p_gradient, lambda, p_model), "cct_l1_update");
+  }
   void set_num_threads(const int nThreads) {}
   void sgemm(const enum CBLAS_ORDER order, CBLAS_TRANSPOSE TA, CBLAS_TRANSPOSE TB, int M, int N, int K, float alpha,
              float * pA, int LDA, float * pB, int LDB, float beta, float * pC, int LDC) {

@@ -308,7 +308,11 @@ class Net:
             if T[i] == "Convolution" and T[nxt] == "Pooling":
                 pool = B[nxt]
                 br.fuse_relu = True
-                br.fuse_pool_relu_backward(pool.p_output_layer.p_gradient_cube, pool.max_index, pool.kernel_size, pool.stride)
+                # the pooled tensor gives the ReLU mask unless a later in-place layer overwrites it before backward
+                after = nxt + 1
+                pooled_intact = not (after < len(B) and self.in_place[after] and B[after].p_input_layer is pool.p_output_layer)
+                br.fuse_pool_relu_backward(pool.p_output_layer.p_gradient_cube, pool.max_index, pool.kernel_size, pool.stride,
+                                           pool.p_output_layer.p_data_cube if pooled_intact else None)
                 B[r].skip_forward = B[r].skip_backward = pool.skip_backward = True
                 self.fused.append("%s+%s(+%s backward)" % (self.names[i], self.names[r], self.names[nxt]))
             elif T[nxt] in ("Convolution", "InnerProduct") and tensor_core(B[nxt]):

@@ -168,8 +168,14 @@ class DeviceOps:
         self.allreduce_begin(ptr, count)
         self.allreduce_wait()
 
-    def sgd_step(self, count, w, g, h, lr, momentum, lam):
+    def sgd_step(self, count, w, g, h, lr, momentum, lam, regularization_type="L2"):
+        """SGDGradientUpdater::update (src/algorithms/GradientUpdater.h:154-193): "L2" adds lam * w to the gradient,
+        "L1" lam * sign(w) (DeviceDriver::L1_update), then the momentum step; any other type applies no decay, as there."""
         vp = C.c_void_p
+        if lam != 0.0 and regularization_type == "L1":
+            capi.check(self.ctx.lib.cct_l1_update(self.ctx.h, count, vp(g), lam, vp(w)), "cct_l1_update", self.ctx.h)
+        if regularization_type != "L2":
+            lam = 0.0
         capi.check(self.ctx.lib.cct_sgd_step(self.ctx.h, count, vp(w), vp(g), vp(h), lr, momentum, lam), "cct_sgd_step",
                    self.ctx.h)
 
@@ -258,12 +264,12 @@ class ParallelizedBridge:
         base = get_learning_rate(s.lr_policy, s.base_lr, s.gamma, float(self.current_iter), float(s.stepsize), s.power,
                                  float(s.max_iter))
         self.ops.sgd_step(self.n_w, self.params, self.grads, self.hist, float(np.float32(base * self.lr_mult[0])),
-                          s.momentum, float(np.float32(s.weight_decay * self.decay_mult[0])))
+                          s.momentum, float(np.float32(s.weight_decay * self.decay_mult[0])), s.regularization_type)
         if self.n_b:
             off = 4 * self.n_w
             self.ops.sgd_step(self.n_b, self.params + off, self.grads + off, self.hist + off,
                               float(np.float32(base * self.lr_mult[1])), s.momentum,
-                              float(np.float32(s.weight_decay * self.decay_mult[1])))
+                              float(np.float32(s.weight_decay * self.decay_mult[1])), s.regularization_type)
 
     def get_model_grad_cube(self):
         return self.bridge.p_model_gradient_cube

@@ -119,7 +119,10 @@ int cct_conv_backward(cct_conv_plan* plan, const float* X, const float* W, const
  *         dY = (A > 0) * maxpool_backward(dP, idx)
  *     A = this layer's forward output [batch][out_depth][m][m] (pre- or post-ReLU: only its sign is used), idx = the
  *     int32 indices cct_maxpool_forward wrote, dP = gradient of the pooled tensor.  One HBM-bound pass into
- *     plan-owned scratch (cct_conv_plan_reserve_fusion) feeds both gradient kernels.
+ *     plan-owned scratch (cct_conv_plan_reserve_fusion) feeds both gradient kernels.  If P, the pooled tensor
+ *     cct_maxpool_forward wrote, is given as well (or instead of A), the sign is taken from it - the element a window
+ *     points at holds that window's maximum, so the result is bit-identical - and A, (m / pooled size)^2 times larger,
+ *     is not read.
  *   - Input side.  relu_mask_dx != 0 writes dX * [X > 0] instead of dX: the ReLU bridge in front of this layer (whose
  *     output X is), applied by one streaming pass right behind the data-gradient kernel.
  * f == NULL behaves like cct_conv_backward. */
@@ -129,6 +132,7 @@ typedef struct cct_bwd_fusion {
   const float* dP;
   int pool_k, pool_s;
   int relu_mask_dx;
+  const float* P; /* optional, see above; NULL = take the sign from A */
 } cct_bwd_fusion;
 int cct_conv_backward_fused(cct_conv_plan* plan, const float* X, const float* W, const float* dY,
                             const cct_bwd_fusion* f, float* dX, float* dW, float* db);
@@ -285,6 +289,10 @@ int cct_sgd_step(cct_ctx* ctx, size_t count, float* w, float* g, float* h, float
  * (src/sched/DeviceDriver.h:197-206), the calls the reference's SGDGradientUpdater makes when it is instantiated on a
  * device driver unchanged. */
 int cct_saxpby(cct_ctx* ctx, size_t count, float alpha, const float* x, float beta, float* y);
+/* g += lambda * sign(w), sign(0) = -1: DeviceDriver::L1_update (src/sched/DeviceDriver.h:114-117,
+ * src/sched/DeviceDriver_CPU.cpp:111-117), the updater's step for regularization_type "L1"; follow it with
+ * cct_sgd_step(..., lambda = 0). */
+int cct_l1_update(cct_ctx* ctx, size_t count, float* g, float lambda, const float* w);
 
 #ifdef __cplusplus
 }

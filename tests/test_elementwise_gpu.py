@@ -87,6 +87,25 @@ def test_sgd_step_matches_oracle_bitwise(ctx, port):
     assert np.array_equal(ch.download().ravel(), h)
 
 
+def test_l1_regularised_update_matches_reference_rule(ctx, port):
+    """regularization_type "L1": g += lambda * (w > 0 ? 1 : -1) (src/sched/DeviceDriver_CPU.cpp:111-117), then the
+    momentum step without decay; through DeviceOps.sgd_step, the call ParallelizedBridge makes."""
+    from caffecontroll_b200.parallel import DeviceOps
+    rng = np.random.default_rng(23)
+    n = 70001
+    w, g, h = (rng.standard_normal(n).astype(np.float32) for _ in range(3))
+    w[::7] = 0.0
+    cw, cg, ch = _cube(ctx, w), _cube(ctx, g), _cube(ctx, h)
+    lam = np.float32(0.0005)
+    DeviceOps(ctx).sgd_step(n, cw.ptr, cg.ptr, ch.ptr, 0.01, 0.9, float(lam), "L1")
+    g = (g + np.where(w > 0, lam, -lam)).astype(np.float32)
+    port.sgd_update(w, g, h, 0.01, 0.9, 0.0)
+    ctx.sync()
+    assert np.array_equal(cg.download().ravel(), g)
+    assert np.array_equal(ch.download().ravel(), h)
+    assert np.array_equal(cw.download().ravel(), w)
+
+
 def test_fill_and_empty_sizes(ctx):
     from caffecontroll_b200 import capi
     c = LogicalCube(ctx, 5, 7, 3, 2)

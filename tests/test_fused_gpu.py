@@ -53,6 +53,13 @@ def _run(ctx, port, shape, algo):
                                                vp(cdb.ptr)), "bwd fused", ctx.h)
         ctx.sync()
         out[mask_dx] = (cdX.download(), cdW.download(), cdb.download())
+    # the same with the ReLU mask taken from the pooled tensor instead of the layer's output: bit-identical
+    f = capi.BwdFusion(None, cidx.ptr, cdP.ptr, pk, ps, 0, cPool.ptr)
+    capi.check(lib.cct_conv_backward_fused(plan, vp(cX.ptr), vp(cW.ptr), None, C.byref(f), vp(cdX.ptr), vp(cdW.ptr),
+                                           vp(cdb.ptr)), "bwd fused, pooled mask", ctx.h)
+    ctx.sync()
+    for got, want in zip((cdX.download(), cdW.download(), cdb.download()), out[0]):
+        assert np.array_equal(got, want)
     # the ReLU mask alone, on a caller-supplied dY
     _, idx0 = port.maxpool_forward(Yg, pk, ps)
     cdY = LogicalCube.from_numpy(ctx, port.relu_backward(Yg, port.maxpool_backward(dP, idx0, m)))

@@ -84,7 +84,8 @@ class HostOps:
             import torch.distributed as dist
             dist.all_reduce(torch.from_numpy(self.view(ptr, count)))
 
-    def sgd_step(self, count, w, g, h, lr, momentum, lam):
+    def sgd_step(self, count, w, g, h, lr, momentum, lam, regularization_type="L2"):
+        assert regularization_type == "L2"
         self.port.sgd_update(self.view(w, count), self.view(g, count), self.view(h, count), lr, momentum, lam)
 
 
