@@ -252,81 +252,78 @@ __global__ void __launch_bounds__(kPoolWarps * 32, 5) maxpool_bwd_kernel(const f
 }
 
 // The same operation for ceil(k / s) <= 2 (3x3 / stride 2, 2x2 / stride 2, ...), where an element is covered by at most
-// four windows: a table built once per block lists every element's candidate windows in (ph, pw) order (unused slots
-// point at a sentinel entry that matches nothing), so the element loop is one table read and four compare / select /
-// add steps - no range or validity arithmetic - over the flat, fully coalesced plane.
+// four windows, turned around: the block walks over the WINDOWS of a group of planes (a quarter as many as elements
+// for 3x3 / 2), and each window drops its gradient into the slot (window row - first covering row, window column -
+// first covering column) of the element it points at, in a shared-memory plane of four slots per element.  A slot has
+// exactly one possible writer, so there is no read-modify-write; adding an element's four slots in slot order is the
+// (ph, pw) order of the reference's scatter, empty slots adding 0.f.  The output is then written (and the slots
+// zeroed again) by a flat, coalesced sweep, while the next group's indices and gradients are already in flight.
+// Reads idx, dP (and P or A) once, writes dA once; shared-memory work per element: four words read and zeroed.
+constexpr int kSlotThreads = 256;
+constexpr int kSlotWin = 4;  // windows per thread and group: a group has at most kSlotThreads * kSlotWin windows
 template <bool RELU>
-__global__ void __launch_bounds__(kPoolWarps * 32) maxpool_bwd4_kernel(const float* __restrict__ A,
-                                                                      const int32_t* __restrict__ idx,
-                                                                      const float* __restrict__ dP,
-                                                                      const float* __restrict__ P,
-                                                                      float* __restrict__ dA, int planes, int n, int m,
-                                                                      int k, int s, int slice) {
-  extern __shared__ uint32_t pool_smem[];
-  const int mm = m * m, nn = n * n;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  ushort4* cand = reinterpret_cast<ushort4*>(pool_smem);                                // [nn]
-  int32_t* s_idx = reinterpret_cast<int32_t*>(pool_smem + 2 * ((nn + 1) & ~1)) + warp * 2 * slice;  // [mm + 1]
-  float* s_dp = reinterpret_cast<float*>(s_idx + slice);                                // [mm + 1]
-  for (int e = threadIdx.x; e < nn; e += blockDim.x) {
-    const int h = e / n, w = e - h * n;
-    const int ph1 = min(h / s, m - 1), pw1 = min(w / s, m - 1);
-    const int ph0 = h < k ? 0 : (h - k) / s + 1, pw0 = w < k ? 0 : (w - k) / s + 1;
-    unsigned short c[4] = {(unsigned short)mm, (unsigned short)mm, (unsigned short)mm, (unsigned short)mm};
-    int cnt = 0;
-    for (int ph = ph0; ph <= ph1; ++ph)
-      for (int pw = pw0; pw <= pw1; ++pw) c[cnt++] = (unsigned short)(ph * m + pw);
-    cand[e] = make_ushort4(c[0], c[1], c[2], c[3]);
-  }
-  if (lane == 0) {  // the sentinel: an index no element has, and a gradient of zero
-    s_idx[mm] = -1;
-    s_dp[mm] = 0.f;
-  }
+__global__ void __launch_bounds__(kSlotThreads) maxpool_bwd_slots_kernel(
+    const float* __restrict__ A, const int32_t* __restrict__ idx, const float* __restrict__ dP,
+    const float* __restrict__ P, float* __restrict__ dA, int planes, int n, int m, int k, int s, int group,
+    uint32_t inv_mm, uint32_t inv_m, uint32_t inv_n) {
+  extern __shared__ float slot_smem[];
+  const int mm = m * m, nn = n * n, tid = threadIdx.x;
+  const int span = group * nn;
+  float* slots = slot_smem;                              // [4 slots][group][nn]: neighbouring elements, neighbouring banks
+  int* first = reinterpret_cast<int*>(slots + 4 * span);  // [n]: first window that covers a coordinate
+  for (int c = tid; c < n; c += kSlotThreads) first[c] = c < k ? 0 : (c - k) / s + 1;
+  for (int j = tid; j < 4 * span; j += kSlotThreads) slots[j] = 0.f;
   __syncthreads();
-  const int warp0 = blockIdx.x * kPoolWarps + warp, nwarps = gridDim.x * kPoolWarps;
-  for (int plane = warp0; plane < planes; plane += nwarps) {
-    const int32_t* ip = idx + (size_t)plane * mm;
-    const float* gp = dP + (size_t)plane * mm;
-    const float* a = RELU ? A + (size_t)plane * nn : nullptr;
-    float* out = dA + (size_t)plane * nn;
-    float av[8];
-    auto fetch = [&](int e0) {
+  const int ngroups = (planes + group - 1) / group;
+  int32_t e_r[kSlotWin];
+  float g_r[kSlotWin];
+  auto fetch = [&](int grp) {
+    const int p0 = grp * group, count = min(group, planes - p0) * mm;
+    const size_t off = (size_t)p0 * mm;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int e = e0 + j * 32 + lane;
-        av[j] = (RELU && e < nn) ? __ldg(a + e) : 1.f;
-      }
-    };
-    fetch(0);
-    __syncwarp();  // the previous plane's tests are done with the slice
-    for (int i = lane; i < mm; i += 32) {
-      s_idx[i] = __ldg(ip + i);
-      // With the pooled tensor P given, the ReLU mask is applied here: the element a window points at holds exactly
-      // that window's maximum, so [A > 0] at the element equals [P > 0] at the window.
-      s_dp[i] = (P == nullptr || __ldg(P + (size_t)plane * mm + i) > 0.f) ? __ldg(gp + i) : 0.f;
-    }
-    __syncwarp();
-    for (int e0 = 0; e0 < nn; e0 += 256) {
-      float res[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int e = min(e0 + j * 32 + lane, nn - 1);
-        const ushort4 c = cand[e];
-        const bool live = av[j] > 0.f;
-        float acc = 0.f;
-        acc += (live && s_idx[c.x] == e) ? s_dp[c.x] : 0.f;
-        acc += (live && s_idx[c.y] == e) ? s_dp[c.y] : 0.f;
-        acc += (live && s_idx[c.z] == e) ? s_dp[c.z] : 0.f;
-        acc += (live && s_idx[c.w] == e) ? s_dp[c.w] : 0.f;
-        res[j] = acc;
-      }
-      if (e0 + 256 < nn) fetch(e0 + 256);  // the next elements' A in flight while these results are stored
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int e = e0 + j * 32 + lane;
-        if (e < nn) out[e] = res[j];
+    for (int w = 0; w < kSlotWin; ++w) {
+      const int i = tid + w * kSlotThreads;
+      e_r[w] = -1;
+      g_r[w] = 0.f;
+      if (i < count) {
+        e_r[w] = __ldg(idx + off + i);
+        const float g = __ldg(dP + off + i);
+        // With the pooled tensor P given, the ReLU mask is applied here: the element a window points at holds exactly
+        // that window's maximum, so [A > 0] at the element equals [P > 0] at the window.
+        g_r[w] = (P == nullptr || __ldg(P + off + i) > 0.f) ? g : 0.f;
       }
     }
+  };
+  int grp = blockIdx.x;
+  if (grp < ngroups) fetch(grp);
+  for (; grp < ngroups; grp += gridDim.x) {
+    const int p0 = grp * group, np = min(group, planes - p0);
+#pragma unroll
+    for (int w = 0; w < kSlotWin; ++w) {
+      if (e_r[w] >= 0) {
+        const uint32_t i = (uint32_t)(tid + w * kSlotThreads);
+        const uint32_t pl = fast_div(i, (uint32_t)mm, inv_mm), wi = i - pl * mm;
+        const uint32_t ph = fast_div(wi, (uint32_t)m, inv_m), pw = wi - ph * m;
+        const uint32_t e = (uint32_t)e_r[w];
+        const uint32_t h = fast_div(e, (uint32_t)n, inv_n), c = e - h * n;
+        const int slot = ((int)ph - first[h]) * 2 + ((int)pw - first[c]);
+        slots[slot * span + (int)(pl * nn + e)] = g_r[w];
+      }
+    }
+    __syncthreads();
+    if (grp + (int)gridDim.x < ngroups) fetch(grp + gridDim.x);  // in flight during the sweep below
+    const size_t obase = (size_t)p0 * nn;
+    for (int j = tid; j < np * nn; j += kSlotThreads) {
+      float acc = 0.f;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        acc += slots[q * span + j];
+        slots[q * span + j] = 0.f;
+      }
+      if (RELU) acc = __ldg(A + obase + j) > 0.f ? acc : 0.f;
+      dA[obase + j] = acc;
+    }
+    __syncthreads();
   }
 }
 
@@ -336,15 +333,20 @@ int launch_maxpool_bwd(cct_ctx* ctx, const float* A, const int32_t* idx, const f
   const int grid = plane_grid(ctx, (planes + kPoolWarps - 1) / kPoolWarps);
   const uint32_t inv_s = fast_div_magic((uint64_t)n, (uint32_t)s);
   const int taps = (k + s - 1) / s;
-  if (taps <= 2 && m * m < 65535) {
-    const int slice = (m * m + 1 + 31) & ~31;
-    const size_t smem4 = ((size_t)2 * ((n * n + 1) & ~1) + (size_t)kPoolWarps * 2 * slice) * 4;
-    if (smem4 <= 100 * 1024) {  // two blocks per SM still fit
-      if (smem4 > 48 * 1024)
-        CCT_CUDA(ctx, cudaFuncSetAttribute(maxpool_bwd4_kernel<RELU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem4));
-      maxpool_bwd4_kernel<RELU><<<grid, kPoolWarps * 32, smem4, ctx->stream>>>(A, idx, dP, P, dA, planes, n, m, k, s, slice);
-      return CCT_OK;
-    }
+  constexpr int kSlotSmemCap = 56 * 1024;  // four blocks per SM
+  if (taps <= 2 && m * m <= kSlotThreads * kSlotWin && (size_t)n * n * 16 + (size_t)n * 4 <= kSlotSmemCap) {
+    const int nn = n * n, mm = m * m;
+    const int group = std::max(1, std::min({planes, (int)((kSlotSmemCap - n * 4) / ((size_t)nn * 16)),
+                                            kSlotThreads * kSlotWin / mm}));
+    const size_t smem = (size_t)group * nn * 16 + (size_t)n * 4;
+    if (smem > 48 * 1024)
+      CCT_CUDA(ctx, cudaFuncSetAttribute(maxpool_bwd_slots_kernel<RELU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int ngroups = (planes + group - 1) / group;
+    const int blocks = std::max(1, std::min(ngroups, ctx->sm_count * 4));
+    maxpool_bwd_slots_kernel<RELU><<<blocks, kSlotThreads, smem, ctx->stream>>>(
+        A, idx, dP, P, dA, planes, n, m, k, s, group, fast_div_magic((uint64_t)kSlotThreads * kSlotWin, (uint32_t)mm),
+        fast_div_magic((uint64_t)mm, (uint32_t)m), fast_div_magic((uint64_t)nn, (uint32_t)n));
+    return CCT_OK;
   }
   const int mm_pad = (m * m + 31) & ~31;
   const size_t smem = ((size_t)((n + 31) & ~31) + (size_t)kPoolWarps * 2 * mm_pad) * 4;

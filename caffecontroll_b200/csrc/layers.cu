@@ -23,6 +23,7 @@ inline int ew_grid(cct_ctx* ctx, size_t work, int threads) {
 // them as its own).  Splitting the channels keeps the grid large on the late layers (13 x 13 planes).  4 B read + 8 B
 // written per element (Y and scale; the backward pass reads scale instead of recomputing a nine-channel window).
 constexpr int kLrnChunk = 16;
+constexpr int kLrnBwdChunk = 8;
 
 // s^(-beta) for s >= 1: exp2(-beta log2 s) on the special-function units (ex2.approx / lg2.approx, each within ~2 ulp:
 // relative error below 1e-6 for the scales and exponents of a normalisation layer, two orders under the path's tolerance;
@@ -97,6 +98,7 @@ __global__ void __launch_bounds__(128) lrn_bwd_kernel(const float* __restrict__ 
                                                       const float* __restrict__ scale, const float* __restrict__ dY,
                                                       float* __restrict__ dX, size_t items, int D, int chunks, int plane,
                                                       float alpha_over_size, float beta) {
+  constexpr int kLrnChunk = kLrnBwdChunk;  // four arrays are read here: a shorter chunk keeps the registers in check
   constexpr int W = LOCAL / 2, SPAN = kLrnChunk + 2 * W;
   const float coef = 2.f * beta * alpha_over_size;
   for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < items; t += (size_t)gridDim.x * blockDim.x) {
@@ -232,6 +234,7 @@ __global__ void softmax_bwd_kernel(const float* __restrict__ prob, const float* 
 // with coalesced loads (every input element crosses HBM -> SM once, four loads in flight per thread), the windows are
 // read from there, Y and idx leave in coalesced runs.  K, S > 0 fix the window at compile time (straight-line
 // compare / select chain); K = 0 keeps run-time loops.  4 B read per input element + 8 B written per output element.
+constexpr int kPoolFetch = 12;  // 256 * 12 elements: one 55 x 55 plane, four 27 x 27, sixteen 13 x 13
 template <int K, int S>
 __global__ void __launch_bounds__(256) maxpool_fwd_staged_kernel(const float* __restrict__ X, float* __restrict__ Y,
                                                                  int32_t* __restrict__ idx, int planes, int n, int m,
@@ -241,18 +244,43 @@ __global__ void __launch_bounds__(256) maxpool_fwd_staged_kernel(const float* __
   extern __shared__ float plane_smem[];
   const int nn = n * n, mm = m * m;
   const int k = K > 0 ? K : k_rt, s = S > 0 ? S : s_rt;
+  // Groups of up to 256 * kPoolFetch elements travel through registers: the next group's loads are issued before the
+  // current group's windows are evaluated, so they are in flight during the compare chains and the stores.
+  const bool via_regs = group * nn <= 256 * kPoolFetch;
+  float r[kPoolFetch];
+  auto fetch = [&](int p0) {
+    const int total_in = min(group, planes - p0) * nn;
+    const float* in = X + (size_t)p0 * nn;
+#pragma unroll
+    for (int j = 0; j < kPoolFetch; ++j) {
+      const int i = threadIdx.x + j * 256;
+      r[j] = i < total_in ? __ldg(in + i) : 0.f;
+    }
+  };
+  if (via_regs && (int)blockIdx.x * group < planes) fetch(blockIdx.x * group);
   for (int p0 = blockIdx.x * group; p0 < planes; p0 += gridDim.x * group) {
     const int g = min(group, planes - p0);
     const float* in = X + (size_t)p0 * nn;
     const int total_in = g * nn, total_out = g * mm;
     __syncthreads();  // the previous group's windows have been read
-    int i = threadIdx.x;
-    for (; i + 3 * 256 < total_in; i += 4 * 256) {
-      const float a = __ldg(in + i), b = __ldg(in + i + 256), c = __ldg(in + i + 512), d = __ldg(in + i + 768);
-      plane_smem[i] = a; plane_smem[i + 256] = b; plane_smem[i + 512] = c; plane_smem[i + 768] = d;
+    if (via_regs) {
+#pragma unroll
+      for (int j = 0; j < kPoolFetch; ++j) {
+        const int i = threadIdx.x + j * 256;
+        if (i < total_in) plane_smem[i] = r[j];
+      }
+      __syncthreads();
+      const int next = p0 + gridDim.x * group;
+      if (next < planes) fetch(next);
+    } else {
+      int i = threadIdx.x;
+      for (; i + 3 * 256 < total_in; i += 4 * 256) {
+        const float a = __ldg(in + i), b = __ldg(in + i + 256), c = __ldg(in + i + 512), d = __ldg(in + i + 768);
+        plane_smem[i] = a; plane_smem[i + 256] = b; plane_smem[i + 512] = c; plane_smem[i + 768] = d;
+      }
+      for (; i < total_in; i += 256) plane_smem[i] = __ldg(in + i);
+      __syncthreads();
     }
-    for (; i < total_in; i += 256) plane_smem[i] = __ldg(in + i);
-    __syncthreads();
     for (int t = threadIdx.x; t < total_out; t += 256) {
       const int pl = t / mm, r = t - pl * mm;
       const int ph = r / m, pw = r - ph * m;
@@ -328,7 +356,9 @@ int cct_lrn_backward(cct_ctx* ctx, const float* X, const float* Y, const float* 
       !(local_size & 1))
     return CCT_ERR_INVALID;
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
-  const int chunks = (depth + kLrnChunk - 1) / kLrnChunk;
+  const bool fixed = local_size == 5 || local_size == 3;
+  const int chunk = fixed ? kLrnBwdChunk : kLrnChunk;
+  const int chunks = (depth + chunk - 1) / chunk;
   const size_t items = (size_t)batch * chunks * plane;
   const int grid = ew_grid(ctx, items, 128);
   const float aos = alpha / (float)local_size;
