@@ -83,6 +83,21 @@ def dram_traffic(workload, w, pass_name, batch):
     return entry["dram_read_bytes"] * batch / float(entry["batch"]) + 4.0 * out_elems, entry["source"]
 
 
+def caffenet_traffic(kernel, batch):
+    """DRAM bytes (read + write) of one launch of a CaffeNet kernel group ("conv2 dgrad", "fc6 forward", ...) from the
+    batch-256 ncu capture summarised under profiles/, scaled by the batch ratio.  (None, None) if never captured."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
+            table = json.load(f).get("caffenet", {})
+    except OSError:
+        return None, None
+    layer, _, what = kernel.partition(" ")
+    entry = table.get("%s %s" % (layer, {"wgrad": "weight gradient", "dgrad": "data gradient"}.get(what, what)))
+    if not entry:
+        return None, None
+    return (entry["dram_read_bytes"] + entry["dram_write_bytes"]) * batch / float(entry["batch"]), entry["source"]
+
+
 def measure_tf32_peak(seconds=2.0):
     """Dense TF32 matmul throughput of this GPU, measured like the bf16 figures of MEASURED_PEAKS.json: a library
     8192^3 matmul with TF32 inputs, best of 10 (burst) and back to back for `seconds` (sustained).  Only a roofline
@@ -716,6 +731,7 @@ def run_caffenet(args, rank, world, local_rank):
                            seconds_per_step=total)
         tf = world * flops / (ms_step * 1e-3) / 1e12
         ach = dom_F / (dom_ms * 1e-3) / 1e12 if dom_ms > 0 else 0.0
+        dom_traffic, dom_traffic_source = caffenet_traffic(dom_name, B)
         line = {
             "metric": METRIC, "value": world * B / (ms_step * 1e-3), "unit": "images/s", "n_gpus": world,
             "steps": args.steps, "warmup": warm_steps, "ms_per_step": ms_step, "higher_is_better": True,
@@ -728,7 +744,7 @@ def run_caffenet(args, rank, world, local_rank):
                        (sum(c.n_elements * 4 for c in net._cubes) / 1e9), "parallelism": "dp%d" % world},
             "tflops": tf, "flops_per_step": flops,
             "roofline": {"bound": "tensor", "kernel": dom_name, "achieved": ach, "peak": roof["peak"], "unit": "TFLOP/s",
-                         "frac": ach / roof["peak"] if roof["peak"] else None, "traffic": None,
+                         "frac": ach / roof["peak"] if roof["peak"] else None, "traffic": dom_traffic,
                          "peak_source": roof["source"], "peak_sustained": roof["peak_sustained"],
                          "frac_of_sustained": ach / roof["peak_sustained"] if roof["peak_sustained"] else None,
                          "whole_step_achieved": tf / world, "whole_step_frac": tf / world / roof["peak"],
@@ -748,6 +764,9 @@ def run_caffenet(args, rank, world, local_rank):
         }
         if cpu:
             cpu.pop("seconds_per_step", None)
+        if dom_traffic is not None:
+            line["roofline"]["traffic_source"] = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of this kernel at "
+                                                  "batch 256, scaled by the batch ratio: " + dom_traffic_source)
         print(json.dumps(line), flush=True)
     for c in stage + stage_l:
         c.free()

@@ -258,22 +258,33 @@ __global__ void fc_reduce_dgrad_kernel(const float* __restrict__ partial, int sp
   }
 }
 
-// db[o] = sum_b dY[b][o], images added in order (FullyConnectedBridge_impl.hxx:298: backward_bias_fc).  Sixteen rows
-// are loaded before they are added, so a thread keeps sixteen requests in flight instead of one.
-__global__ void fc_bias_grad_kernel(const float* __restrict__ dY, float* __restrict__ db, int B, int O) {
-  const int o = blockIdx.x * blockDim.x + threadIdx.x;
-  if (o >= O) return;
+// db[o] = sum_b dY[b][o] (FullyConnectedBridge_impl.hxx:298: backward_bias_fc).  A block of 32 x 8 threads owns 32
+// outputs: thread (x, y) adds the images y, y + 8, ... in order with sixteen loads in flight, then the eight partial sums
+// of an output are added in a fixed order - deterministic, and two memory round trips instead of B.
+__global__ void __launch_bounds__(256) fc_bias_grad_kernel(const float* __restrict__ dY, float* __restrict__ db, int B, int O) {
+  __shared__ float part[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int o = blockIdx.x * 32 + tx;
   float acc = 0.f;
-  int b = 0;
-  for (; b + 16 <= B; b += 16) {
-    float v[16];
+  if (o < O) {
+    int b = ty;
+    for (; b + 8 * 15 < B; b += 8 * 16) {
+      float v[16];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) v[j] = __ldg(dY + (size_t)(b + j) * O + o);
+      for (int j = 0; j < 16; ++j) v[j] = __ldg(dY + (size_t)(b + 8 * j) * O + o);
 #pragma unroll
-    for (int j = 0; j < 16; ++j) acc += v[j];
+      for (int j = 0; j < 16; ++j) acc += v[j];
+    }
+    for (; b < B; b += 8) acc += dY[(size_t)b * O + o];
   }
-  for (; b < B; ++b) acc += dY[(size_t)b * O + o];
-  db[o] = acc;
+  part[ty][tx] = acc;
+  __syncthreads();
+  if (ty == 0 && o < O) {
+    float t = part[0][tx];
+#pragma unroll
+    for (int y = 1; y < 8; ++y) t += part[y][tx];
+    db[o] = t;
+  }
 }
 
 int fc_round_up(int v, int a) { return (v + a - 1) / a * a; }
@@ -451,7 +462,7 @@ int cct_fc_backward(cct_fc_plan* plan, const float* X, const float* W, const flo
     plan->timer.begin(1, ctx->stream);
     rc = fc_launch(ctx, P, a_map, b_map);
     if (rc != CCT_OK) return rc;
-    if (plan->bias) fc_bias_grad_kernel<<<(O + 31) / 32, 32, 0, ctx->stream>>>(dY, db, B, O);
+    if (plan->bias) fc_bias_grad_kernel<<<(O + 31) / 32, 256, 0, ctx->stream>>>(dY, db, B, O);
     plan->timer.end(1, ctx->stream);
     CCT_CHECK_LAUNCH(ctx);
   }
