@@ -327,12 +327,83 @@ __global__ void __launch_bounds__(kSlotThreads) maxpool_bwd_slots_kernel(
   }
 }
 
+// 3x3 windows with stride 2 (the pooling layers of AlexNet / CaffeNet) without shared memory or synchronisation: one
+// thread owns a 2 x 2 block of elements (rows 2a, 2a+1; columns 2b, 2b+1).  Only the windows (a-1 .. a) x (b-1 .. b) can
+// point into it - four index / gradient pairs for four outputs, read through L1, which neighbouring threads share -
+// and each element visits its windows in (ph, pw) order like the reference's scatter:
+//   (2a, 2b): all four;  (2a, 2b+1): (a-1, b), (a, b);  (2a+1, 2b): (a, b-1), (a, b);  (2a+1, 2b+1): (a, b).
+template <bool RELU>
+__global__ void __launch_bounds__(256) maxpool_bwd_3x3s2_kernel(const float* __restrict__ A, const int32_t* __restrict__ idx,
+                                                                const float* __restrict__ dP, const float* __restrict__ P,
+                                                                float* __restrict__ dA, uint32_t items, int n, int m,
+                                                                int half, uint32_t inv_half) {
+  const int nn = n * n, mm = m * m;
+  for (uint32_t t = blockIdx.x * blockDim.x + threadIdx.x; t < items; t += gridDim.x * blockDim.x) {
+    const uint32_t row = fast_div(t, (uint32_t)half, inv_half);  // = plane * half + a
+    const int b = (int)(t - row * half);
+    const size_t plane = fast_div(row, (uint32_t)half, inv_half);
+    const int a = (int)(row - (uint32_t)plane * half);
+    const int32_t* ip = idx + plane * mm;
+    const float* gp = dP + plane * mm;
+    const float* pp = P ? P + plane * mm : nullptr;
+    int32_t wi[2][2];
+    float wg[2][2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int ph = a - 1 + i, pw = b - 1 + j;
+        const bool ok = ph >= 0 && ph < m && pw >= 0 && pw < m;
+        const int at = ok ? ph * m + pw : 0;
+        wi[i][j] = ok ? __ldg(ip + at) : -1;
+        float g = ok ? __ldg(gp + at) : 0.f;
+        // With the pooled tensor P given, the ReLU mask is applied here: the element a window points at holds exactly
+        // that window's maximum, so [A > 0] at the element equals [P > 0] at the window.
+        if (pp != nullptr && ok && !(__ldg(pp + at) > 0.f)) g = 0.f;
+        wg[i][j] = g;
+      }
+    const int h0 = 2 * a, w0 = 2 * b;
+    const int e00 = h0 * n + w0, e01 = e00 + 1, e10 = e00 + n, e11 = e10 + 1;
+    float r00 = 0.f, r01 = 0.f, r10 = 0.f, r11 = 0.f;
+    r00 += wi[0][0] == e00 ? wg[0][0] : 0.f;
+    r00 += wi[0][1] == e00 ? wg[0][1] : 0.f;
+    r00 += wi[1][0] == e00 ? wg[1][0] : 0.f;
+    r00 += wi[1][1] == e00 ? wg[1][1] : 0.f;
+    r01 += wi[0][1] == e01 ? wg[0][1] : 0.f;
+    r01 += wi[1][1] == e01 ? wg[1][1] : 0.f;
+    r10 += wi[1][0] == e10 ? wg[1][0] : 0.f;
+    r10 += wi[1][1] == e10 ? wg[1][1] : 0.f;
+    r11 += wi[1][1] == e11 ? wg[1][1] : 0.f;
+    const bool wide = w0 + 1 < n, tall = h0 + 1 < n;
+    float* out = dA + plane * nn;
+    if (RELU) {
+      const float* ap = A + plane * nn;
+      r00 = __ldg(ap + e00) > 0.f ? r00 : 0.f;
+      if (wide) r01 = __ldg(ap + e01) > 0.f ? r01 : 0.f;
+      if (tall) r10 = __ldg(ap + e10) > 0.f ? r10 : 0.f;
+      if (wide && tall) r11 = __ldg(ap + e11) > 0.f ? r11 : 0.f;
+    }
+    out[e00] = r00;
+    if (wide) out[e01] = r01;
+    if (tall) out[e10] = r10;
+    if (wide && tall) out[e11] = r11;
+  }
+}
+
 template <bool RELU>
 int launch_maxpool_bwd(cct_ctx* ctx, const float* A, const int32_t* idx, const float* dP, float* dA, int planes, int n,
                        int m, int k, int s, const float* P = nullptr) {
   const int grid = plane_grid(ctx, (planes + kPoolWarps - 1) / kPoolWarps);
   const uint32_t inv_s = fast_div_magic((uint64_t)n, (uint32_t)s);
   const int taps = (k + s - 1) / s;
+  const int half = (n + 1) / 2;
+  if (k == 3 && s == 2 && (size_t)planes * half * half < (1ull << 31)) {
+    const size_t items = (size_t)planes * half * half;
+    const int blocks = (int)std::max<size_t>(1, std::min<size_t>((items + 255) / 256, (size_t)ctx->sm_count * 16));
+    maxpool_bwd_3x3s2_kernel<RELU><<<blocks, 256, 0, ctx->stream>>>(A, idx, dP, P, dA, (uint32_t)items, n, m, half,
+                                                                    fast_div_magic(items, (uint32_t)half));
+    return CCT_OK;
+  }
   constexpr int kSlotSmemCap = 56 * 1024;  // four blocks per SM
   if (taps <= 2 && m * m <= kSlotThreads * kSlotWin && (size_t)n * n * 16 + (size_t)n * 4 <= kSlotSmemCap) {
     const int nn = n * n, mm = m * m;
