@@ -1,14 +1,16 @@
 #!/usr/bin/env python
-"""Benchmark of the convolution hot path: forward + backward (dX, dW, db) + gradient all-reduce (N > 1) + SGD step
-of one convolution layer on synthetic data, one process per GPU.
+"""Benchmark of the convolution hot path and of the CaffeNet training iteration built around it, on synthetic data,
+one process per GPU.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload alexnet_conv1|caffenet_conv2|lenet_conv1]
+    python bench.py [--gpus N] [--steps K] [--warmup W]           # one CaffeNet iteration, 256 images per GPU (default)
+    python bench.py --workload alexnet_conv1|caffenet_conv2|lenet_conv1   # one convolution layer: forward + backward + SGD
     python bench.py --impl reference ...      # the reference's own CPU code (oracle/_ref) on the host cores
 
-Prints ONE JSON line (rank 0).  `value` is whole-job images/s with inputs resident in HBM; `e2e` is the same metric
-through the host-buffer C-ABI calls (pinned host memory, copies inside the timed region); `roofline` describes the
-slowest of the three contraction passes against the 3xTF32 tensor roofline; `cpu_baseline` is the reference CPU path
-timed on this box's host cores in the same run.
+Prints ONE JSON line (rank 0).  `value` is whole-job images/s with inputs resident in HBM, device-timed, maximum over
+ranks; `e2e` is the same metric with every step's inputs uploaded from pinned host memory and the loss (or the host-buffer
+calls' outputs) read back inside the timed region; `roofline` describes the slowest contraction kernel group against
+the 3xTF32 tensor roofline measured in the same run; `cpu_baseline` is the reference CPU path timed on this box's host
+cores in the same run.
 """
 import argparse
 import ctypes as C

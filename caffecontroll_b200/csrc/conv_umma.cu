@@ -812,6 +812,209 @@ __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_const
   if (warp == 0) tmem_dealloc(tmem_base, 512);
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// The same weight gradient with the operands' roles exchanged, for lowered matrices of 257 .. 384 rows (with the
+// all-ones row) and at most 128 output channels per tile - AlexNet / CaffeNet conv1:
+//     D[channel][row] = sum over pixels of dY[channel][pixel] * lowered[row][pixel].
+// The small operand (dY: 128 lanes = channels, 32 pixels per k-block) goes through TENSOR memory, so the MMAs read only
+// the lowered rows from shared memory, 192 of them per instruction (two accumulators of 192 columns): per k-block 24
+// MMAs of 96 cycles each, none paying the shared-memory-A surcharge, where wgrad_kernel issues 36 of 91, and one CTA
+// covers all rows, so dY is staged once per k-block for the whole SM.
+//   warps 0-23  tap producers: warp w stages rows w, w+24, ... (16 rows) of the 384-row tile exactly as wgrad_kernel's.
+//   warps 24-27 dY: warp 24+q owns channels 32q .. 32q+31 (= its tensor-memory lanes): coalesced loads with lane = pixel,
+//               a turn through a private 32 x 33 shared-memory tile, then lane = channel: split and tcgen05.st.
+//               After the last k-block the same warps write the accumulators out (lane = channel = fastest index of the
+//               partial-sum buffer).
+//   warp 28     one thread issues the MMAs.
+// The partial sums have wgrad_kernel's layout ([split][tile][row][channel]), so the same reduction kernels follow.
+constexpr int kTsTapWarps = 24, kTsDyWarps = 4, kTsMmaWarp = kTsTapWarps + kTsDyWarps;
+constexpr int kTsThreads = (kTsMmaWarp + 1) * 32;  // 928
+constexpr int kTsRows = 384, kTsNTile = 192, kTsStages = 2, kTsRowsPerWarp = kTsRows / kTsTapWarps;  // 16
+constexpr uint32_t kTsTile = kTsRows * 128u;       // one of hi / lo of the lowered rows of a k-block
+constexpr uint32_t kTsStage = 2u * kTsTile;
+constexpr uint32_t kTsTapsOff = kTsStages * kTsStage, kTsTurnOff = kTsTapsOff + kTsRows * 8u,
+                   kTsBarsOff = kTsTurnOff + kTsDyWarps * 32u * 33u * 4u, kTsSmem = kTsBarsOff + 8u * (2 * kTsStages + 1) + 16u;
+
+__global__ void __launch_bounds__(kTsThreads, 1) wgrad_ts_kernel(const __grid_constant__ WgradParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bars = base + kTsBarsOff;
+  const uint32_t full = bars, empty = full + 8u * kTsStages, acc_full = empty + 8u * kTsStages, tmem_slot = acc_full + 8u;
+  MaskTap* s_taps = reinterpret_cast<MaskTap*>(base_ptr + kTsTapsOff);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int split = blockIdx.y, vg = blockIdx.z;
+  const int grp = vg / P.tiles_per_group, ntile = vg % P.tiles_per_group;
+  constexpr uint32_t kACol0 = 2 * kTsNTile;  // tensor memory: two accumulators of 192 columns, then 2 x 64 columns of A
+
+  for (int i = tid; i < kTsRows; i += kTsThreads) s_taps[i] = P.taps[i];
+  if (tid == 0) {
+    for (int s = 0; s < kTsStages; ++s) { mbar_init(full + 8u * s, kTsTapWarps + kTsDyWarps); mbar_init(empty + 8u * s, 1); }
+    mbar_init(acc_full, 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) tmem_alloc(tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+  const int kb_begin = P.kb_first + split * P.kblocks_per_split;
+  const int kb_end = min(P.kblocks_total, kb_begin + P.kblocks_per_split);
+  const int kblocks = kb_end - kb_begin;
+  bool failed = false;
+
+  if (warp < kTsMmaWarp) {
+    // this lane's pixel, advanced by 32 per k-block
+    int pix = kb_begin * kBlockK + lane;
+    int pb = pix / P.mm, pr, pc;
+    {
+      const int pin = pix - pb * P.mm;
+      pr = pin / P.m;
+      pc = pin - pr * P.m;
+    }
+    auto next_pixel = [&]() {
+      pix += kBlockK;
+      pc += kBlockK;
+      while (pc >= P.m) { pc -= P.m; ++pr; }
+      while (pr >= P.m) { pr -= P.m; ++pb; }
+    };
+    if (warp < kTsTapWarps) {
+      // ---- lowered rows warp + 24*i: row offsets 3072 bytes apart, all with the swizzle phase of row `warp`
+      const float* xg = P.x + (long long)grp * P.x_group_stride;
+      const bool mine = P.ones_row % kTsTapWarps == warp;
+      const int ones_i = mine ? P.ones_row / kTsTapWarps : -1;
+      uint8_t* lane_ptr = base_ptr + warp * 128 + ((((lane >> 2) ^ (warp & 7)) << 4) + (lane & 3) * 4);
+      const MaskTap* my_taps = s_taps + warp;
+      float va[kTsRowsPerWarp];
+      auto load_rows = [&]() {
+        const bool ok = pix < P.n_pix;
+        const int iy0 = pr * P.s - P.p, ix0 = pc * P.s - P.p;
+        const float* xsrc = xg + (long long)pb * P.x_batch_stride + (long long)iy0 * P.n + ix0;
+        const uint32_t mask =
+            ok ? (kWgValidBit | bit_range(-iy0, min(P.k, P.n - iy0)) | (bit_range(-ix0, min(P.k, P.n - ix0)) << 16))
+               : 0u;
+#pragma unroll
+        for (int i = 0; i < kTsRowsPerWarp; ++i) {
+          const MaskTap tap = my_taps[kTsTapWarps * i];
+          va[i] = ldg_if_bits(xsrc + tap.off, mask, tap.bits);
+        }
+        if (ones_i >= 0) {
+#pragma unroll
+          for (int i = 0; i < kTsRowsPerWarp; ++i) va[i] = i == ones_i ? (ok ? 1.f : 0.f) : va[i];
+        }
+      };
+      load_rows();
+      Ring ring;
+      for (int kbl = 0; kbl < kblocks; ++kbl, ring.advance(kTsStages)) {
+        const int s = ring.idx, use = ring.use;
+        uint8_t* st = lane_ptr + (size_t)s * kTsStage;
+        if (use > 0) mbar_wait(empty + 8u * s, (uint32_t)(use - 1) & 1u, failed, P.status, 0x3010);
+#pragma unroll
+        for (int i = 0; i < kTsRowsPerWarp; ++i) {
+          uint32_t h, l;
+          split_tf32_trunc(va[i], h, l);
+          uint8_t* dst = st + i * (kTsTapWarps * 128);
+          *reinterpret_cast<uint32_t*>(dst) = h;
+          *reinterpret_cast<uint32_t*>(dst + kTsTile) = l;
+        }
+        if (kbl + 1 < kblocks) {  // the next k-block's loads go in flight before the barrier work
+          next_pixel();
+          load_rows();
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full + 8u * s);
+      }
+    } else {
+      // ---- dY: channels 32q .. 32q+31 of the tile; tensor-memory lanes of the same numbers
+      const int q = warp - kTsTapWarps;
+      const float* dyg = P.dy + (long long)(grp * P.dy_group_channels + ntile * P.n_real + q * 32) * P.mm;
+      const int live = min(32, max(0, P.n_real - q * 32));  // real channels of this quadrant
+      float* turn = reinterpret_cast<float*>(base_ptr + kTsTurnOff) + q * (32 * 33);
+      const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + kACol0;
+      float vb[32];
+      auto load_rows = [&]() {
+        const bool ok = pix < P.n_pix;
+        const float* dsrc = dyg + (long long)pb * P.dy_batch_stride + pr * P.m + pc;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) vb[i] = ldg_if(dsrc + (long long)i * P.mm, (ok && i < live) ? 1u : 0u);
+      };
+      load_rows();
+      Ring ring;
+      for (int kbl = 0; kbl < kblocks; ++kbl, ring.advance(kTsStages)) {
+        const int s = ring.idx, use = ring.use;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) turn[i * 33 + lane] = vb[i];  // row = channel, column = pixel
+        __syncwarp();
+        if (kbl + 1 < kblocks) {
+          next_pixel();
+          load_rows();
+        }
+        // The stage's 64 tensor-memory columns were last read by the MMAs of k-block kbl - 2.
+        if (use > 0) mbar_wait(empty + 8u * s, (uint32_t)(use - 1) & 1u, failed, P.status, 0x3011);
+        tc_fence_after();
+        const uint32_t st_addr = lane_addr + (uint32_t)(s * 64);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {  // lane = channel now: its 32 pixels, eight at a time
+          uint32_t hi[8], lo[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) split_tf32_trunc(turn[lane * 33 + c * 8 + e], hi[e], lo[e]);
+          tmem_st8(st_addr + (uint32_t)(c * 8), hi);
+          tmem_st8(st_addr + 32u + (uint32_t)(c * 8), lo);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();  // also: every lane has read the tile before the next k-block overwrites it
+        if (lane == 0) mbar_arrive(full + 8u * s);
+      }
+      // ---- epilogue: lane = channel, one accumulator column = one lowered row
+      mbar_wait(acc_full, 0u, failed, P.status, 0x3020);
+      tc_fence_after();
+      const int ch = q * 32 + lane;
+      float* op = P.partial + ((size_t)split * gridDim.z + vg) * kTsRows * P.n_pad + ch;
+      for (int c = 0; c < kTsRows / 16; ++c) {
+        float acc[16];
+        tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 16), acc);
+        if (!failed && ch < P.n_pad) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) op[(size_t)(c * 16 + j) * P.n_pad] = acc[j];
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ MMA issue
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(kTsNTile);
+      Ring ring;
+      for (int kbl = 0; kbl < kblocks; ++kbl, ring.advance(kTsStages)) {
+        const int s = ring.idx;
+        mbar_wait(full + 8u * s, (uint32_t)ring.use & 1u, failed, P.status, 0x3040);
+        tc_fence_after();
+        const uint32_t st = base + (uint32_t)s * kTsStage;
+        const uint32_t a_hi = tmem_base + kACol0 + (uint32_t)(s * 64), a_lo = a_hi + 32u;
+#pragma unroll
+        for (int u = 0; u < kTsRows / kTsNTile; ++u) {
+          const uint32_t d_tmem = tmem_base + (uint32_t)(u * kTsNTile);
+          const uint64_t dbh = make_desc(st + (uint32_t)u * kTsNTile * 128u), dbl = make_desc(st + kTsTile + (uint32_t)u * kTsNTile * 128u);
+#pragma unroll
+          for (int j = 0; j < kBlockK / 8; ++j) {
+            const uint64_t adv = (uint64_t)(j * 2);
+            umma_tf32_ts(d_tmem, a_lo + (uint32_t)(j * 8), dbh + adv, idesc, (kbl == 0 && j == 0) ? 0u : 1u);
+            umma_tf32_ts(d_tmem, a_hi + (uint32_t)(j * 8), dbl + adv, idesc, 1u);
+            umma_tf32_ts(d_tmem, a_hi + (uint32_t)(j * 8), dbh + adv, idesc, 1u);
+          }
+        }
+        umma_commit(empty + 8u * s);
+      }
+      umma_commit(acc_full);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, 512);
+}
+
 typedef void (*WgradKernel)(const WgradParams);
 template <int SUBS>
 WgradKernel wgrad_pick_nb(int nb) {
@@ -1046,6 +1249,7 @@ struct UmmaPlan {
   // weight gradient
   int w_mtiles, w_subs, w_stages, w_mgroups, w_splits, w_kblocks_total, w_kblocks_per_split, w_npad;
   size_t w_smem = 0;
+  bool w_ts = false;  // weight gradient by wgrad_ts_kernel (dY through tensor memory) instead of wgrad_kernel
   MaskTap* w_taps = nullptr;
   float* w_partial = nullptr;
   // weight gradient through the gather kernel: lanes = rows of the lowered matrix, reduction over pixels, dY as the
@@ -1244,9 +1448,12 @@ int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out) {
         subs = u;
     p->w_subs = subs;
     p->w_mgroups = (p->w_mtiles + subs - 1) / subs;
+    // 257 .. 384 rows and one channel tile of at most 128: the role-exchanged kernel, one CTA for all rows
+    p->w_ts = p->w_mtiles * kTileM == kTsRows && f.n_pad <= kTileM;
+    if (p->w_ts) p->w_mgroups = 1;
     const uint32_t stage_bytes = wg_smem(f.n_pad, subs, 2).stage_bytes;
     p->w_stages = std::max(2, std::min(kWgMaxStages, (int)((kSmemLimit - 8192) / stage_bytes)));
-    p->w_smem = wg_smem(f.n_pad, subs, p->w_stages).total + 1024;
+    p->w_smem = p->w_ts ? kTsSmem + 1024 : wg_smem(f.n_pad, subs, p->w_stages).total + 1024;
     const int n_pix = G.B * G.m * G.m;
     p->w_kblocks_total = (n_pix + kBlockK - 1) / kBlockK;
     const int out_tiles = p->w_mgroups * G.g * f.tiles;
@@ -1321,6 +1528,7 @@ int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out) {
   if (rc == CCT_OK) rc = set_smem(ctx, gather_conv_kernel<4>, kSmemLimit);
   if (rc == CCT_OK) rc = set_smem(ctx, gather_conv_kernel<2>, 113 * 1024);
   if (rc == CCT_OK) rc = set_smem(ctx, wgrad_pick(p->w_subs, p->fwd.n_pad), kSmemLimit);
+  if (rc == CCT_OK && p->w_ts) rc = set_smem(ctx, wgrad_ts_kernel, kSmemLimit);
   if (rc != CCT_OK) {
     umma_plan_destroy(ctx, p);
     return rc;
@@ -1463,7 +1671,10 @@ int umma_conv_wgrad(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* dY, 
     const int vgroups = G.g * f.tiles;
     dim3 grid(p->w_mgroups, p->w_splits, vgroups);
     t->begin(1, ctx->stream);
-    wgrad_pick(p->w_subs, f.n_pad)<<<grid, kWgThreads, p->w_smem, ctx->stream>>>(P);
+    if (p->w_ts)
+      wgrad_ts_kernel<<<grid, kTsThreads, p->w_smem, ctx->stream>>>(P);
+    else
+      wgrad_pick(p->w_subs, f.n_pad)<<<grid, kWgThreads, p->w_smem, ctx->stream>>>(P);
     t->end(1, ctx->stream);
     CCT_CHECK_LAUNCH(ctx);
     t->begin(2, ctx->stream);

@@ -40,6 +40,7 @@ struct FcGemmParams {
   int n_pad;                // accumulator columns per tile: N rounded up (a multiple of 32 for MN-major B)
   int m_tiles, n_tiles, splits, kblocks_total, kblocks_per_split;
   int a_mn, b_mn;           // 1: the operand is MN-major (row index contiguous in memory)
+  int a_tmem;               // 1: the A operand is split into tensor memory (hi and lo), the MMAs read it from there
   int stages, acc_bufs;
   int* status;
 };
@@ -92,6 +93,7 @@ __global__ void __launch_bounds__(kFcThreads, 1)
   tc_fence_after();
   uint32_t tmem_base;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+  const uint32_t a_col0 = (uint32_t)(P.acc_bufs * P.n_pad);  // A stages (64 columns each) behind the accumulators
   const int total_tiles = P.m_tiles * P.n_tiles * P.splits;
   bool failed = false;
   // tile t -> (split, n-tile, m-tile), m-tile fastest; k-blocks [kb0, kb1)
@@ -134,6 +136,7 @@ __global__ void __launch_bounds__(kFcThreads, 1)
   } else if (warp == kFcMmaWarp) {
     if (lane == 0) {
       const uint32_t idesc = make_idesc(P.n_pad) | (P.a_mn ? 1u << 15 : 0u) | (P.b_mn ? 1u << 16 : 0u);
+      const uint32_t idesc_ts = make_idesc(P.n_pad) | (P.b_mn ? 1u << 16 : 0u);  // A from tensor memory: lanes x K
       Ring ring;
       int tile_iter = 0;
       for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile_iter) {
@@ -150,6 +153,19 @@ __global__ void __launch_bounds__(kFcThreads, 1)
           tc_fence_after();
           const uint32_t st = base + (uint32_t)s * L.stage_bytes;
           const uint32_t a_raw = st, a_lo = st + kFcATile, b_raw = st + 2u * kFcATile, b_lo = b_raw + L.b_tile_bytes;
+          if (P.a_tmem) {
+            const uint32_t t_hi = tmem_base + a_col0 + (uint32_t)(s * 64), t_lo = t_hi + 32u;
+#pragma unroll
+            for (int j = 0; j < kBlockK / 8; ++j) {
+              const uint64_t bh = P.b_mn ? make_desc_mn(b_raw + j * 1024u) : make_desc(b_raw) + (uint64_t)(j * 2);
+              const uint64_t bl = P.b_mn ? make_desc_mn(b_lo + j * 1024u) : make_desc(b_lo) + (uint64_t)(j * 2);
+              umma_tf32_ts(d_tmem, t_lo + (uint32_t)(j * 8), bh, idesc_ts, (kb == kb0 && j == 0) ? 0u : 1u);
+              umma_tf32_ts(d_tmem, t_hi + (uint32_t)(j * 8), bl, idesc_ts, 1u);
+              umma_tf32_ts(d_tmem, t_hi + (uint32_t)(j * 8), bh, idesc_ts, 1u);
+            }
+            umma_commit(empty_bar + 8u * s);
+            continue;
+          }
 #pragma unroll
           for (int j = 0; j < kBlockK / 8; ++j) {
             // K-major: 8 reduction indices = 32 bytes along the swizzled row; MN-major: 8 rows of 128 bytes
@@ -179,7 +195,45 @@ __global__ void __launch_bounds__(kFcThreads, 1)
         const int s = ring.idx;
         mbar_wait(raw_bar + 8u * s, (uint32_t)ring.use & 1u, failed, P.status, 0x1500);
         uint8_t* st = base_ptr + (size_t)s * L.stage_bytes;
-        for (int i = xt; i < a_vec + b_vec; i += kXThreads) {
+        if (P.a_tmem) {
+          // The stage's tensor-memory columns are free: the TMA thread refilled the stage only after the MMAs that read
+          // them had completed (empty barrier), and this thread has just seen that refill land.
+          tc_fence_after();
+          // A: thread = (row m of the tile = tensor-memory lane, half of the k-block's 32 reduction indices).  Its 16
+          // values come out of the swizzled tile the TMA wrote; hi and lo go to the stage's 64 tensor-memory columns.
+          const int q = warp & 3, half = (warp - kFcXformWarp0) >> 2;
+          const int m = q * 32 + lane;
+          float x[16];
+          if (P.a_mn) {
+            // 32 x 32 boxes, row = reduction index (128 bytes), 32-byte chunks XORed with the row index mod 4
+            const uint8_t* box = st + (size_t)(m >> 5) * 4096u;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const uint32_t k = (uint32_t)(half * 16 + i);
+              const uint32_t off = k * 128u + (uint32_t)(m & 31) * 4u;
+              x[i] = *reinterpret_cast<const float*>(box + (off ^ ((k & 3u) << 5)));
+            }
+          } else {
+            // rows of 128 bytes, 16-byte chunks XORed with the row index mod 8
+            const uint8_t* rowp = st + (size_t)m * 128u;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t c = (uint32_t)(half * 4 + i);
+              const float4 v4 = *reinterpret_cast<const float4*>(rowp + ((c ^ (uint32_t)(m & 7)) << 4));
+              x[4 * i] = v4.x; x[4 * i + 1] = v4.y; x[4 * i + 2] = v4.z; x[4 * i + 3] = v4.w;
+            }
+          }
+          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + a_col0 + (uint32_t)(s * 64 + half * 16);
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            uint32_t hi[8], lo[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) split_tf32_trunc(x[c * 8 + e], hi[e], lo[e]);
+            tmem_st8(taddr + (uint32_t)(c * 8), hi);
+            tmem_st8(taddr + 32u + (uint32_t)(c * 8), lo);
+          }
+        }
+        for (int i = P.a_tmem ? a_vec + xt : xt; i < a_vec + b_vec; i += kXThreads) {
           const bool in_a = i < a_vec;
           uint8_t* src = in_a ? st + (size_t)i * 16 : st + 2u * kFcATile + (size_t)(i - a_vec) * 16;
           const float4 x = *reinterpret_cast<const float4*>(src);
@@ -191,6 +245,10 @@ __global__ void __launch_bounds__(kFcThreads, 1)
           *reinterpret_cast<float4*>(src + (in_a ? kFcATile : L.b_tile_bytes)) = l;
         }
         fence_proxy_async_smem();
+        if (P.a_tmem) {
+          tmem_wait_st();
+          tc_fence_before();
+        }
         __syncwarp();
         if (lane == 0) mbar_arrive(lo_bar + 8u * s);
       }
@@ -335,9 +393,12 @@ void fc_pick_splits(cct_ctx* ctx, int tiles, int kblocks, int* splits, int* kps)
 }
 
 int fc_launch(cct_ctx* ctx, FcGemmParams& P, const CUtensorMap& a_map, const CUtensorMap& b_map) {
-  P.acc_bufs = 2 * P.n_pad <= 512 ? 2 : 1;
   const uint32_t stage = fc_smem(P.n_pad, 1).stage_bytes;
   P.stages = std::max(2, std::min(kFcMaxStages, (int)((kSmemLimit - 2048) / stage)));
+  // Tensor memory: 512 columns = accumulator buffers (+ 64 columns per stage for an A operand kept there).
+  const int a_cols = P.a_tmem ? P.stages * 64 : 0;
+  if (P.n_pad + a_cols > 512) { P.a_tmem = 0; }
+  P.acc_bufs = 2 * P.n_pad + (P.a_tmem ? a_cols : 0) <= 512 ? 2 : 1;
   const size_t smem = fc_smem(P.n_pad, P.stages).total + 1024;
   P.status = ctx->status_dev;
   const int tiles = P.m_tiles * P.n_tiles * P.splits;
@@ -420,7 +481,7 @@ int cct_fc_forward(cct_fc_plan* plan, const float* X, const float* W, const floa
   P.n_pad = fc_round_up(std::min(B, 256), 16);
   P.m_tiles = (O + kTileM - 1) / kTileM; P.n_tiles = (B + P.n_pad - 1) / P.n_pad;
   P.kblocks_total = (K + kBlockK - 1) / kBlockK; P.splits = plan->f_splits; P.kblocks_per_split = plan->f_kps;
-  P.a_mn = 0; P.b_mn = 0;
+  P.a_mn = 0; P.b_mn = 0; P.a_tmem = 1;
   P.out = plan->partial; P.ld_out = O; P.split_stride = (long long)B * O;
   CUtensorMap a_map, b_map;
   int rc = fc_make_map(ctx, &a_map, W, O, K, kTileM, false);
@@ -473,7 +534,7 @@ int cct_fc_backward(cct_fc_plan* plan, const float* X, const float* W, const flo
     P.n_pad = fc_round_up(std::min(B, 256), 16);
     P.m_tiles = (K + kTileM - 1) / kTileM; P.n_tiles = (B + P.n_pad - 1) / P.n_pad;
     P.kblocks_total = (O + kBlockK - 1) / kBlockK; P.splits = plan->d_splits; P.kblocks_per_split = plan->d_kps;
-    P.a_mn = 1; P.b_mn = 0;
+    P.a_mn = 1; P.b_mn = 0; P.a_tmem = 1;
     P.out = plan->partial; P.ld_out = K; P.split_stride = (long long)B * K;
     CUtensorMap a_map, b_map;
     rc = fc_make_map(ctx, &a_map, W, O, K, 32, true);

@@ -35,6 +35,8 @@ SHAPES = [
     (2, 288, 6, 16, 3, 1, 1, 1),    # 288 input channels: two input-channel tiles in the data gradient
     (2, 128, 10, 136, 3, 2, 1, 2),  # 576 lowered rows per group, stride 2, pad 1: weight gradient through the gather kernel
     (2, 64, 8, 160, 3, 1, 1, 1),    # 160 filters in one tile: the one-CTA-per-SM shape, in all three passes
+    (3, 10, 12, 100, 6, 1, 2, 1),   # 360 lowered rows, 100 filters, pad 2: weight gradient with dY through tensor memory
+    (2, 24, 9, 48, 5, 1, 2, 2),     # the same kernel on a grouped layer (300 rows and 24 filters per group)
 ]
 
 
