@@ -30,6 +30,7 @@ namespace {
 constexpr int kFcEpiWarps = 4, kFcTmaWarp = 4, kFcMmaWarp = 5, kFcXformWarp0 = 6, kFcXformWarps = 8;
 constexpr int kFcThreads = (kFcXformWarp0 + kFcXformWarps) * 32;  // 448
 constexpr int kFcMaxStages = 4;
+constexpr int kFcPrefetch = 6;  // k-blocks of A requested into L2 ahead of their loads
 constexpr int kFcMaxChainKblocks = 96;  // k-blocks of 32 per partial sum: the tensor core's fp32 accumulate truncates
 constexpr uint32_t kFcATile = kTileM * 128u;  // bytes of one 128 x 32 fp32 tile
 
@@ -42,16 +43,18 @@ struct FcGemmParams {
   int a_mn, b_mn;           // 1: the operand is MN-major (row index contiguous in memory)
   int a_tmem;               // 1: the A operand is split into tensor memory (hi and lo), the MMAs read it from there
   int stages, acc_bufs;
+  int tmem_cols;            // tensor-memory columns the CTA allocates: 512, or 256 when two CTAs share an SM
   int* status;
 };
 
 struct FcSmem {
-  uint32_t b_tile_bytes, stage_bytes, bars_off, total;
+  uint32_t b_tile_bytes, b_off, stage_bytes, bars_off, total;
 };
-__host__ __device__ inline FcSmem fc_smem(int n_pad, int stages) {
+__host__ __device__ inline FcSmem fc_smem(int n_pad, int stages, int a_tmem) {
   FcSmem L;
   L.b_tile_bytes = (uint32_t)n_pad * 128u;
-  L.stage_bytes = 2u * kFcATile + 2u * L.b_tile_bytes;  // A raw, A lo, B raw, B lo
+  L.b_off = (a_tmem ? 1u : 2u) * kFcATile;            // A raw, (A lo unless A's halves live in tensor memory,)
+  L.stage_bytes = L.b_off + 2u * L.b_tile_bytes;      // B raw, B lo
   L.bars_off = (uint32_t)stages * L.stage_bytes;
   L.total = L.bars_off + 8u * (3 * kFcMaxStages + 4) + 16u;
   return L;
@@ -65,13 +68,13 @@ __device__ __forceinline__ uint64_t make_desc_mn(uint32_t smem_addr) {
          (1ull << 46) | (1ull << 61);
 }
 
-__global__ void __launch_bounds__(kFcThreads, 1)
+__global__ void __launch_bounds__(kFcThreads, 2)
     fc_gemm_kernel(const __grid_constant__ FcGemmParams P, const __grid_constant__ CUtensorMap a_map,
                    const __grid_constant__ CUtensorMap b_map) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  const FcSmem L = fc_smem(P.n_pad, P.stages);
+  const FcSmem L = fc_smem(P.n_pad, P.stages, P.a_tmem);
   const uint32_t bars = base + L.bars_off;
   // raw[s]: the stage's TMA bytes have landed; lo[s]: the transform warps have written the lo tiles; empty[s]: the
   // stage's MMAs have finished (tcgen05.commit), the TMA thread may refill it.
@@ -87,7 +90,7 @@ __global__ void __launch_bounds__(kFcThreads, 1)
     for (int b = 0; b < 2; ++b) { mbar_init(acc_full + 8u * b, 1); mbar_init(acc_empty + 8u * b, kFcEpiWarps); }
     fence_mbar_init();
   }
-  if (warp == 0) tmem_alloc(tmem_slot, 512);
+  if (warp == 0) tmem_alloc(tmem_slot, (uint32_t)P.tmem_cols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -112,10 +115,23 @@ __global__ void __launch_bounds__(kFcThreads, 1)
       for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
         int mt, nt, split, kb0, kb1;
         tile_of(t, mt, nt, split, kb0, kb1);
+        // The A operand (the layer's weights) streams from HBM: its tiles are requested into L2 kFcPrefetch k-blocks
+        // ahead of the loads proper, which then find them a short hop away.
+        auto prefetch_a = [&](int kb) {
+          if (kb >= kb1) return;
+          if (P.a_mn) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) tma_prefetch_2d(&a_map, mt * kTileM + j * 32, kb * kBlockK);
+          } else {
+            tma_prefetch_2d(&a_map, kb * kBlockK, mt * kTileM);
+          }
+        };
+        for (int kb = kb0; kb < kb0 + kFcPrefetch; ++kb) prefetch_a(kb);
         for (int kb = kb0; kb < kb1; ++kb, ring.advance(P.stages)) {
           const int s = ring.idx;
+          prefetch_a(kb + kFcPrefetch);
           if (ring.use > 0) mbar_wait<false>(empty_bar + 8u * s, (uint32_t)(ring.use - 1) & 1u, failed, P.status, 0x1100);
-          const uint32_t st = base + (uint32_t)s * L.stage_bytes, a_raw = st, b_raw = st + 2u * kFcATile;
+          const uint32_t st = base + (uint32_t)s * L.stage_bytes, a_raw = st, b_raw = st + L.b_off;
           const uint32_t bar = raw_bar + 8u * s;
           mbar_expect_tx(bar, kFcATile + L.b_tile_bytes);
           if (P.a_mn) {
@@ -152,7 +168,7 @@ __global__ void __launch_bounds__(kFcThreads, 1)
           mbar_wait<false>(lo_bar + 8u * s, (uint32_t)ring.use & 1u, failed, P.status, 0x1400);
           tc_fence_after();
           const uint32_t st = base + (uint32_t)s * L.stage_bytes;
-          const uint32_t a_raw = st, a_lo = st + kFcATile, b_raw = st + 2u * kFcATile, b_lo = b_raw + L.b_tile_bytes;
+          const uint32_t a_raw = st, a_lo = st + kFcATile, b_raw = st + L.b_off, b_lo = b_raw + L.b_tile_bytes;
           if (P.a_tmem) {
             const uint32_t t_hi = tmem_base + a_col0 + (uint32_t)(s * 64), t_lo = t_hi + 32u;
 #pragma unroll
@@ -235,7 +251,7 @@ __global__ void __launch_bounds__(kFcThreads, 1)
         }
         for (int i = P.a_tmem ? a_vec + xt : xt; i < a_vec + b_vec; i += kXThreads) {
           const bool in_a = i < a_vec;
-          uint8_t* src = in_a ? st + (size_t)i * 16 : st + 2u * kFcATile + (size_t)(i - a_vec) * 16;
+          uint8_t* src = in_a ? st + (size_t)i * 16 : st + L.b_off + (size_t)(i - a_vec) * 16;
           const float4 x = *reinterpret_cast<const float4*>(src);
           float4 l;
           l.x = x.x - __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u);
@@ -284,7 +300,7 @@ __global__ void __launch_bounds__(kFcThreads, 1)
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem_base, 512);
+  if (warp == 0) tmem_dealloc(tmem_base, (uint32_t)P.tmem_cols);
 }
 
 // Y[b][o] = act(bias[o] + sum over splits of partial[s][b][o]), act = optional ReLU then optional dropout
@@ -384,25 +400,37 @@ struct cct_fc_plan {
 namespace {
 
 // Splits of a reduction of `kblocks` k-blocks over `tiles` output tiles: about one CTA per SM, chains bounded.
-void fc_pick_splits(cct_ctx* ctx, int tiles, int kblocks, int* splits, int* kps) {
-  int s = std::max(1, ctx->sm_count / std::max(1, tiles));
+void fc_pick_splits(int slots, int tiles, int kblocks, int* splits, int* kps) {
+  int s = std::max(1, slots / std::max(1, tiles));
   s = std::max(s, (kblocks + kFcMaxChainKblocks - 1) / kFcMaxChainKblocks);
   s = std::min(s, std::max(1, kblocks / 4));
   *kps = (kblocks + s - 1) / s;
   *splits = (kblocks + *kps - 1) / *kps;
 }
 
+// Accumulator width of the forward pass and the data gradient (N = batch): at most 128 columns, so that two CTAs fit on
+// an SM (256 tensor-memory columns and half the shared memory each) - two pipelines of TMA, transform and MMA issue per
+// SM hide each other's latencies, which one CTA with two 96 KB stages cannot.
+int fc_batch_tile(int batch) { return fc_round_up(std::min(batch, 128), 16); }
+
 int fc_launch(cct_ctx* ctx, FcGemmParams& P, const CUtensorMap& a_map, const CUtensorMap& b_map) {
-  const uint32_t stage = fc_smem(P.n_pad, 1).stage_bytes;
-  P.stages = std::max(2, std::min(kFcMaxStages, (int)((kSmemLimit - 2048) / stage)));
-  // Tensor memory: 512 columns = accumulator buffers (+ 64 columns per stage for an A operand kept there).
+  const bool pair = P.a_tmem && P.n_pad <= 128;  // two CTAs per SM
+  const uint32_t stage = fc_smem(P.n_pad, 1, P.a_tmem).stage_bytes;
+  const uint32_t budget = pair ? 113u * 1024u : (uint32_t)kSmemLimit;
+  P.stages = std::min(kFcMaxStages, (int)((budget - 2048) / stage));
+  if (P.stages < 2) {
+    ctx->last_error = "fully connected tile does not fit in shared memory twice";
+    return CCT_ERR_UNSUPPORTED;
+  }
+  // Tensor memory = accumulator buffers (+ 64 columns per stage for an A operand kept there).
+  P.tmem_cols = pair ? 256 : 512;
+  if (P.a_tmem) P.stages = std::min(P.stages, (P.tmem_cols - P.n_pad) / 64);
   const int a_cols = P.a_tmem ? P.stages * 64 : 0;
-  if (P.n_pad + a_cols > 512) { P.a_tmem = 0; }
-  P.acc_bufs = 2 * P.n_pad + (P.a_tmem ? a_cols : 0) <= 512 ? 2 : 1;
-  const size_t smem = fc_smem(P.n_pad, P.stages).total + 1024;
+  P.acc_bufs = 2 * P.n_pad + a_cols <= P.tmem_cols ? 2 : 1;
+  const size_t smem = fc_smem(P.n_pad, P.stages, P.a_tmem).total + 1024;
   P.status = ctx->status_dev;
   const int tiles = P.m_tiles * P.n_tiles * P.splits;
-  fc_gemm_kernel<<<std::min(tiles, ctx->sm_count), kFcThreads, smem, ctx->stream>>>(P, a_map, b_map);
+  fc_gemm_kernel<<<std::min(tiles, (pair ? 2 : 1) * ctx->sm_count), kFcThreads, smem, ctx->stream>>>(P, a_map, b_map);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }
@@ -429,10 +457,10 @@ int cct_fc_plan_create(cct_ctx* ctx, int batch, int in_features, int out_feature
   cct_fc_plan* p = new (std::nothrow) cct_fc_plan();
   if (!p) return CCT_ERR_NOMEM;
   p->ctx = ctx; p->B = batch; p->K = in_features; p->O = out_features; p->bias = bias_term != 0;
-  const int n_tiles = (batch + 255) / 256;
-  fc_pick_splits(ctx, ((out_features + kTileM - 1) / kTileM) * n_tiles, (in_features + kBlockK - 1) / kBlockK,
+  const int n_tiles = (batch + fc_batch_tile(batch) - 1) / fc_batch_tile(batch);
+  fc_pick_splits(2 * ctx->sm_count, ((out_features + kTileM - 1) / kTileM) * n_tiles, (in_features + kBlockK - 1) / kBlockK,
                  &p->f_splits, &p->f_kps);
-  fc_pick_splits(ctx, ((in_features + kTileM - 1) / kTileM) * n_tiles, (out_features + kBlockK - 1) / kBlockK,
+  fc_pick_splits(2 * ctx->sm_count, ((in_features + kTileM - 1) / kTileM) * n_tiles, (out_features + kBlockK - 1) / kBlockK,
                  &p->d_splits, &p->d_kps);
   p->partial_elems = std::max((size_t)p->f_splits * batch * out_features, (size_t)p->d_splits * batch * in_features);
   if (cudaMalloc((void**)&p->partial, p->partial_elems * sizeof(float)) != cudaSuccess) {
@@ -478,7 +506,7 @@ int cct_fc_forward(cct_fc_plan* plan, const float* X, const float* W, const floa
   const int B = plan->B, K = plan->K, O = plan->O;
   FcGemmParams P{};
   P.M = O; P.N = B;
-  P.n_pad = fc_round_up(std::min(B, 256), 16);
+  P.n_pad = fc_batch_tile(B);
   P.m_tiles = (O + kTileM - 1) / kTileM; P.n_tiles = (B + P.n_pad - 1) / P.n_pad;
   P.kblocks_total = (K + kBlockK - 1) / kBlockK; P.splits = plan->f_splits; P.kblocks_per_split = plan->f_kps;
   P.a_mn = 0; P.b_mn = 0; P.a_tmem = 1;
@@ -531,7 +559,7 @@ int cct_fc_backward(cct_fc_plan* plan, const float* X, const float* W, const flo
   if (dX) {
     FcGemmParams P{};
     P.M = K; P.N = B;
-    P.n_pad = fc_round_up(std::min(B, 256), 16);
+    P.n_pad = fc_batch_tile(B);
     P.m_tiles = (K + kTileM - 1) / kTileM; P.n_tiles = (B + P.n_pad - 1) / P.n_pad;
     P.kblocks_total = (O + kBlockK - 1) / kBlockK; P.splits = plan->d_splits; P.kblocks_per_split = plan->d_kps;
     P.a_mn = 1; P.b_mn = 0; P.a_tmem = 1;
