@@ -30,7 +30,6 @@ namespace {
 constexpr int kFcEpiWarps = 4, kFcTmaWarp = 4, kFcMmaWarp = 5, kFcXformWarp0 = 6, kFcXformWarps = 8;
 constexpr int kFcThreads = (kFcXformWarp0 + kFcXformWarps) * 32;  // 448
 constexpr int kFcMaxStages = 4;
-constexpr int kFcPrefetch = 6;  // k-blocks of A requested into L2 ahead of their loads
 constexpr int kFcMaxChainKblocks = 96;  // k-blocks of 32 per partial sum: the tensor core's fp32 accumulate truncates
 constexpr uint32_t kFcATile = kTileM * 128u;  // bytes of one 128 x 32 fp32 tile
 
@@ -115,21 +114,8 @@ __global__ void __launch_bounds__(kFcThreads, 2)
       for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
         int mt, nt, split, kb0, kb1;
         tile_of(t, mt, nt, split, kb0, kb1);
-        // The A operand (the layer's weights) streams from HBM: its tiles are requested into L2 kFcPrefetch k-blocks
-        // ahead of the loads proper, which then find them a short hop away.
-        auto prefetch_a = [&](int kb) {
-          if (kb >= kb1) return;
-          if (P.a_mn) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) tma_prefetch_2d(&a_map, mt * kTileM + j * 32, kb * kBlockK);
-          } else {
-            tma_prefetch_2d(&a_map, kb * kBlockK, mt * kTileM);
-          }
-        };
-        for (int kb = kb0; kb < kb0 + kFcPrefetch; ++kb) prefetch_a(kb);
         for (int kb = kb0; kb < kb1; ++kb, ring.advance(P.stages)) {
           const int s = ring.idx;
-          prefetch_a(kb + kFcPrefetch);
           if (ring.use > 0) mbar_wait<false>(empty_bar + 8u * s, (uint32_t)(ring.use - 1) & 1u, failed, P.status, 0x1100);
           const uint32_t st = base + (uint32_t)s * L.stage_bytes, a_raw = st, b_raw = st + L.b_off;
           const uint32_t bar = raw_bar + 8u * s;

@@ -142,10 +142,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int 
       "l"(tmap), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
-// Asks for the tile to be brought into L2; nothing is written to shared memory and nothing waits for it.
-__device__ __forceinline__ void tma_prefetch_2d(const void* tmap, int x, int y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(tmap), "r"(x), "r"(y) : "memory");
-}
 // D[tmem] (+)= A[tmem] * B[smem]^T.
 __device__ __forceinline__ void umma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
                                              uint32_t accumulate) {
