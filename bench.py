@@ -690,31 +690,51 @@ def run_caffenet(args, rank, world, local_rank):
     up_done = [torch.cuda.Event(), torch.cuda.Event()]
     used = [torch.cuda.Event(), torch.cuda.Event()]
 
+    up_begin = [torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)]
+    up_end = [torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)]
+
     def upload(slot):  # next batch -> staging buffer `slot`, on the copy stream
         copy_stream.wait_event(used[slot])
+        up_begin[slot].record(copy_stream)
         capi.check(lib.cct_memcpy_h2d(cctx.h, vp(stage[slot].ptr), vp(hX.data_ptr()), X.nbytes), "h2d", cctx.h)
         capi.check(lib.cct_memcpy_h2d(cctx.h, vp(stage_l[slot].ptr), vp(hL.data_ptr()), labels.nbytes), "h2d", cctx.h)
+        up_end[slot].record(copy_stream)
         up_done[slot].record(copy_stream)
 
-    def e2e_step(slot):
+    # The loss of every step is read back into pinned host memory by a copy queued behind the step; the host looks at it
+    # one step later (after that copy's event), so it keeps queueing the next iteration's launches meanwhile.
+    loss_host = C.c_void_p()
+    capi.check(lib.cct_malloc_host(ctx.h, 8, C.byref(loss_host)), "cct_malloc_host", ctx.h)
+    loss_view = (C.c_float * 2).from_address(loss_host.value)
+    loss_done = [torch.cuda.Event(), torch.cuda.Event()]
+    e2e_losses = []
+
+    def e2e_step(slot, prev):
         stream.wait_event(up_done[slot])
         net.input.p_data_cube.ptr, net.labels.ptr = stage[slot].ptr, stage_l[slot].ptr
         net.loss_bridge.p_data_labels = net.labels
         net.step()
         used[slot].record(stream)
+        net.read_loss_into(loss_host.value + 4 * slot)  # device -> host read of the step's result
+        loss_done[slot].record(stream)
         upload(slot ^ 1)  # the next step's batch travels while this step computes
-        return net.get_loss()  # device -> host read of the step's result
+        if prev is not None:
+            loss_done[prev].synchronize()
+            e2e_losses.append(float(loss_view[prev]))
 
     for e in used:
         e.record(stream)
     upload(0)
-    e2e_step(0)
+    e2e_step(0, None)
     barrier()
     t0 = time.perf_counter()
     for it in range(args.e2e_steps):
-        e2e_step((it + 1) & 1)
+        e2e_step((it + 1) & 1, it & 1)
     torch.cuda.synchronize()
+    e2e_losses.append(float(loss_view[args.e2e_steps & 1]))  # the last step's loss: its copy has completed
     e2e_s = max_over_ranks((time.perf_counter() - t0) / args.e2e_steps)
+    h2d_ms = max(up_begin[i].elapsed_time(up_end[i]) for i in (0, 1))  # the last two uploads, device-timed
+    capi.check(lib.cct_free_host(ctx.h, loss_host), "cct_free_host", ctx.h)
     net.input.p_data_cube.ptr, net.labels.ptr = main_ptr, main_labels_ptr
     torch.cuda.synchronize()
 
@@ -760,7 +780,9 @@ def run_caffenet(args, rank, world, local_rank):
             "e2e": {"value": world * B / e2e_s, "unit": "images/s", "h2d_bytes_per_step": int(X.nbytes + labels.nbytes),
                     "d2h_bytes_per_step": 4, "ms_per_step": e2e_s * 1e3, "steps": args.e2e_steps,
                     "how": "each step: images and labels copied from pinned host memory (double-buffered on a copy stream), "
-                           "the iteration, the loss read back"},
+                           "the iteration, the loss copied back to pinned host memory and read by the host one step later",
+                    "last_loss": e2e_losses[-1] if e2e_losses else None, "h2d_ms_per_upload": h2d_ms,
+                    "h2d_gbs": X.nbytes / (h2d_ms * 1e-3) / 1e9 if h2d_ms > 0 else None},
             "clocks": clocks, "gpu_launches": net.launches_per_step() * args.steps,
             "allreduce_bytes_per_step": 4 * net.num_parameters() if world > 1 else 0,
         }
@@ -784,9 +806,13 @@ def run_caffenet(args, rank, world, local_rank):
 def run_caffenet_reference_arm(args, rank, world):
     if rank != 0:
         return
-    B = args.batch or 256
+    # A step of this arm is a bounded sample of the workload: one forward + backward pass of every layer over B images,
+    # B = 256 cut down (in multiples of 16, the reference's partition count) until `steps` of them fit in about 150 s at
+    # the ~45 images/s these host cores deliver; images/s barely depends on the batch on the CPU.
+    steps = max(1, args.steps)
+    B = args.batch or max(16, min(256, (150 * 45 // steps) // 16 * 16))
     log = lambda m: print(m, file=sys.stderr, flush=True)
-    total, per = caffenet_reference_seconds(B, max(1, args.steps), log)
+    total, per = caffenet_reference_seconds(B, steps, log)
     if total is None:
         print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libcct_ref.so (the reference's CPU code) is not built"}))
         return
@@ -828,7 +854,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="caffenet", choices=["caffenet"] + sorted(WORKLOADS) + ["caffenet_convs"])
     ap.add_argument("--algo", type=int, default=0, help="0 auto, 1 SIMT fp32, 2 tcgen05 3xTF32")
-    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--preheat-s", type=float, default=1.0,
                     help="untimed warm-up runs until at least this much device time has passed (and --warmup steps)")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -183,6 +183,12 @@ class SoftmaxLossBridge(_Bridge):
         """Summed loss of this partition's images (a device-to-host read: synchronises the stream)."""
         return float(self.loss_cube.download().reshape(-1)[0])
 
+    def read_loss_into(self, host_ptr):
+        """Queues the copy of the summed loss (one float) into pinned host memory at `host_ptr`, behind the kernels already
+        on the stream, without waiting for it: a training loop reads the value once the stream has passed that point
+        (an event, or the next synchronisation) and so never stalls the launches of the following iteration."""
+        capi.check(self.lib.cct_memcpy_d2h(self.ctx.h, _vp(host_ptr), _vp(self.loss_cube.ptr), 4), "cct_memcpy_d2h", self.ctx.h)
+
     def close(self):
         self.image_loss.free()
         self.loss_cube.free()

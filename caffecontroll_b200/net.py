@@ -348,6 +348,10 @@ class Net:
     def get_loss(self):
         return self.loss_bridge.get_loss() if self.loss_bridge else None
 
+    def read_loss_into(self, host_ptr):
+        """Asynchronous form of get_loss(): see SoftmaxLossBridge.read_loss_into."""
+        self.loss_bridge.read_loss_into(host_ptr)
+
     def param_bridges(self):
         return [(self.names[i], self.pbridges[i]) for i in sorted(self.pbridges)]
 
