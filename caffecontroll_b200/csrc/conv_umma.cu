@@ -1332,9 +1332,11 @@ int finish_problem(cct_ctx* ctx, UmmaPlan* p, GatherProblem& gp, int vgroups, in
   };
   gp.b_stages = slots_that_fit(kSmemLimit);
   // Accumulators of at most 128 columns leave room for two CTAs per SM: 256 columns each (accumulator + two A
-  // slots) and half the shared memory (the SM holds 228 KB, 1 KB of it reserved per resident CTA).
+  // slots) and half the shared memory (the SM holds 228 KB, 1 KB of it reserved per resident CTA).  Three weight slots
+  // per CTA, or two when the accumulator is the full 128 columns (each MMA then lasts long enough to cover the refill:
+  // CaffeNet conv5 forward 0.189 -> 0.153 ms).
   const int b_two = slots_that_fit(113 * 1024);
-  if (gp.acc_cols <= 128 && b_two >= 3) {
+  if (gp.acc_cols <= 128 && (b_two >= 3 || (b_two == 2 && gp.acc_cols == 128))) {
     gp.sets = 2; gp.tmem_cols = 256; gp.acc_bufs = 1; gp.a_stages = 2; gp.b_stages = b_two;
   }
   gp.smem = gather_smem(gp.n_pad, taps_smem, gp.b_stages, n_bias, gp.taps_smem == 0 ? 4 * gp.sets : 0).total + 1024;

@@ -15,7 +15,9 @@ from tests.parity import TOL, assert_close, maxnorm_rel
 pytestmark = pytest.mark.gpu
 
 # (B, D, n, num_output): ragged small cases, then fc6's input geometry (256 x 6 x 6) at reduced batch and width
-SHAPES = [(4, 3, 5, 10), (8, 16, 4, 40), (16, 64, 3, 96), (32, 256, 6, 512), (5, 7, 2, 12), (40, 33, 4, 200)]
+# and batches around the 128-column accumulator tile of the forward pass and the data gradient (1, 130, 200 images)
+SHAPES = [(4, 3, 5, 10), (8, 16, 4, 40), (16, 64, 3, 96), (32, 256, 6, 512), (5, 7, 2, 12), (40, 33, 4, 200),
+          (1, 64, 2, 20), (130, 8, 2, 260), (200, 32, 2, 136)]
 
 
 def _oracle(X, W, b, dY):

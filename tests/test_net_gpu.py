@@ -185,3 +185,43 @@ def test_snapshot_round_trip_resumes_the_same_trajectory(ctx, tmp_path):
         assert np.array_equal(pa.history_host()[0], pb.history_host()[0]), name
     a.close()
     b.close()
+
+
+def test_l1_solver_and_asynchronous_loss_read(ctx, port):
+    """regularization_type "L1" from the solver text reaches the update (g += lambda * sign(w), DeviceDriver::L1_update),
+    and read_loss_into() delivers the same number as get_loss() without a stream synchronisation of its own."""
+    import ctypes as C
+    from caffecontroll_b200 import capi
+    net_param = parse_prototxt(NET)
+    rng = np.random.default_rng(78)
+    X = rng.standard_normal((B, 3, 67, 67), dtype=np.float32)
+    labels = rng.integers(0, 12, B).astype(np.float32)
+    mask = (rng.random((B, 64, 1, 1)) < 0.5).astype(np.uint32)
+    nets = []
+    for reg in ("L2", "L1"):
+        net = Net(ctx, net_param, solver_from_message(parse_prototxt(SOLVER + ' regularization_type: "%s"' % reg)), B)
+        for i, br in enumerate(net.bridges):
+            if net.types[i] == "Dropout":
+                br.set_mask(mask)
+        net.set_input(X, labels)
+        nets.append(net)
+    l2, l1 = nets
+    w0 = {n: pb.get_model_cube().download().copy() for n, pb in l1.param_bridges()}
+    host = C.c_void_p()
+    capi.check(ctx.lib.cct_malloc_host(ctx.h, 4, C.byref(host)), "cct_malloc_host", ctx.h)
+    for net in nets:
+        net.step()
+    l1.read_loss_into(host.value)
+    ctx.sync()
+    assert C.c_float.from_address(host.value).value == np.float32(l1.get_loss())
+    capi.check(ctx.lib.cct_free_host(ctx.h, host), "cct_free_host", ctx.h)
+    # same gradients in both nets (same weights, inputs, masks); the weight updates differ by the regulariser alone:
+    # first step, zero history: w1 = w0 - lr * (g + lambda * r(w0)), r = w0 (L2) or sign(w0) with sign(0) = -1 (L1)
+    lr, lam = np.float32(0.01), np.float32(0.0005)
+    for (name, p1), (_, p2) in zip(l1.param_bridges(), l2.param_bridges()):
+        w = w0[name]
+        sign = np.where(w > 0, np.float32(1), np.float32(-1))
+        want = p2.get_model_cube().download() + lr * lam * (w - sign)
+        assert maxnorm_rel(p1.get_model_cube().download(), want) < 1e-6, name
+    for net in nets:
+        net.close()
