@@ -477,7 +477,7 @@ def caffenet_layer_table():
     ]
 
 
-def caffenet_reference_seconds(B, iters, log=None):
+def caffenet_reference_seconds(B, iters, log=None, kinds=None):
     """Seconds of one CaffeNet iteration (forward + backward of every layer) on the host cores through the reference's
     own CPU bridges, one bridge at a time on synthetic tensors of the layer's shapes: convolutions through its
     ParallelizedBridge with the partition count DeepNet uses (grouped layers as one bridge per channel slice - the
@@ -492,6 +492,8 @@ def caffenet_reference_seconds(B, iters, log=None):
     hc = ref.hardware_concurrency()
     per = {}
     for name, kind, g in caffenet_layer_table():
+        if kinds is not None and kind not in kinds:
+            continue
         D, n = g["D"], g["n"]
         X = np.maximum(rng.standard_normal((B, D, n, n), dtype=np.float32), 0) if name != "conv1" else \
             rng.standard_normal((B, D, n, n), dtype=np.float32)
@@ -870,7 +872,26 @@ def main():
         return
     if args.workload == "caffenet_convs":
         if args.impl == "reference":
-            print(json.dumps({"impl": "reference", "unavailable": "the reference arm is timed per layer workload, not for the conv stack"}))
+            if int(os.environ.get("RANK", "0")) == 0:  # the five convolution bridges of the reference, one at a time
+                steps = max(1, args.steps)
+                B = args.batch or max(16, min(256, (150 * 60 // steps) // 16 * 16))
+                total, per = caffenet_reference_seconds(B, steps, lambda m: print(m, file=sys.stderr, flush=True), kinds=("conv",))
+                if total is None:
+                    print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libcct_ref.so (the reference's CPU code) is not built"}))
+                    return
+                from oracle import pyoracle
+                ref = pyoracle.reference()
+                print(json.dumps({
+                    "impl": "reference", "metric": METRIC, "value": B / total, "unit": "images/s", "n_gpus": args.gpus,
+                    "steps": args.steps, "warmup": args.warmup, "ms_per_step": total * 1e3, "higher_is_better": True,
+                    "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                    "config": {"workload": "caffenet_convs (conv1-conv5, batch %d per GPU)" % B, "batch_per_gpu": B},
+                    "layers_ms": {k: v * 1e3 for k, v in per.items()},
+                    "cpu_baseline": {"value": B / total, "unit": "images/s", "cores": ref.hardware_concurrency(), "kind": "reference",
+                                     "sample": "each step = forward + backward of the five convolution layers over one %d-image "
+                                               "batch through the reference's ParallelizedBridge, one layer at a time" % B},
+                    "e2e": {"value": B / total, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                    "gpu_launches": 0}), flush=True)
             return
         run_conv_stack(args, int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")),
                        int(os.environ.get("LOCAL_RANK", "0")))
