@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <string>
+#include <utility>
 
 #include "../../include/cct_b200.h"
 
@@ -27,6 +28,31 @@ struct cct_ctx {
       return e__ == cudaErrorMemoryAllocation ? CCT_ERR_NOMEM : CCT_ERR_CUDA;                 \
     }                                                                                         \
   } while (0)
+
+// Programmatic dependent launch: every kernel of the library starts with pdl_wait() (griddepcontrol.wait: returns once
+// the kernel before it in the stream has completed and its writes are visible) and is launched with the programmatic
+// stream-serialisation attribute, so the launch itself - grid set-up, parameter upload - overlaps the tail of its
+// predecessor instead of following it.  No kernel signals its dependents early: the order of execution stays the
+// stream's order.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+#endif
 
 #define CCT_CHECK_LAUNCH(ctx) CCT_CUDA(ctx, cudaGetLastError())
 

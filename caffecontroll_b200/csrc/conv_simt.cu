@@ -12,6 +12,7 @@ constexpr int kOcPerThread = 4;
 // Y[b][o][r][c]: one thread per output pixel and kOcPerThread consecutive filters.
 __global__ void simt_forward_kernel(const float* __restrict__ X, const float* __restrict__ W,
                                     const float* __restrict__ bias, float* __restrict__ Y, ConvGeom G, int relu) {
+  pdl_wait();
   const int mm = G.m * G.m;
   const int ocb_per_group = (G.og + kOcPerThread - 1) / kOcPerThread;
   const long long total = (long long)G.B * G.g * ocb_per_group * mm;
@@ -59,6 +60,7 @@ __global__ void simt_forward_kernel(const float* __restrict__ X, const float* __
 // two threads add to the same address.
 __global__ void simt_dgrad_kernel(const float* __restrict__ W, const float* __restrict__ dY, float* __restrict__ dX,
                                   ConvGeom G) {
+  pdl_wait();
   const int nn = G.n * G.n, mm = G.m * G.m, kk = G.k * G.k;
   const long long total = (long long)G.B * G.D * nn;
   for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total;
@@ -103,6 +105,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // dW[o][d][kr][kc]: one block per element, fixed reduction tree.
 __global__ void simt_wgrad_kernel(const float* __restrict__ X, const float* __restrict__ dY, float* __restrict__ dW,
                                   ConvGeom G) {
+  pdl_wait();
   __shared__ float red[32];
   const int kk = G.k * G.k, mm = G.m * G.m;
   const size_t e = blockIdx.x;  // index into [o][Dg][k][k]
@@ -126,6 +129,7 @@ __global__ void simt_wgrad_kernel(const float* __restrict__ X, const float* __re
 }
 
 __global__ void simt_bgrad_kernel(const float* __restrict__ dY, float* __restrict__ db, ConvGeom G) {
+  pdl_wait();
   __shared__ float red[32];
   const int mm = G.m * G.m;
   const int o = blockIdx.x;
@@ -155,7 +159,7 @@ int simt_conv_forward(cct_ctx* ctx, const ConvGeom& G, const float* X, const flo
   const int ocb = (G.og + kOcPerThread - 1) / kOcPerThread;
   const long long work = (long long)G.B * G.g * ocb * G.m * G.m;
   t->begin(0, ctx->stream);
-  simt_forward_kernel<<<grid_for(work, 256, ctx->sm_count), 256, 0, ctx->stream>>>(X, W, G.bias ? bias : nullptr, Y,
+  launch_pdl(simt_forward_kernel, dim3(grid_for(work, 256, ctx->sm_count)), dim3(256), 0, ctx->stream, X, W, G.bias ? bias : nullptr, Y,
                                                                                   G, relu);
   t->end(0, ctx->stream);
   CCT_CHECK_LAUNCH(ctx);
@@ -165,19 +169,19 @@ int simt_conv_forward(cct_ctx* ctx, const ConvGeom& G, const float* X, const flo
 int simt_conv_backward(cct_ctx* ctx, const ConvGeom& G, const float* X, const float* W, const float* dY, float* dX,
                        float* dW, float* db, PhaseTimer* t) {
   if (G.bias && db) {
-    simt_bgrad_kernel<<<G.o, 256, 0, ctx->stream>>>(dY, db, G);
+    launch_pdl(simt_bgrad_kernel, dim3(G.o), dim3(256), 0, ctx->stream, dY, db, G);
     CCT_CHECK_LAUNCH(ctx);
   }
   if (dX) {
     const long long work = (long long)G.B * G.D * G.n * G.n;
     t->begin(3, ctx->stream);
-    simt_dgrad_kernel<<<grid_for(work, 256, ctx->sm_count), 256, 0, ctx->stream>>>(W, dY, dX, G);
+    launch_pdl(simt_dgrad_kernel, dim3(grid_for(work, 256, ctx->sm_count)), dim3(256), 0, ctx->stream, W, dY, dX, G);
     t->end(3, ctx->stream);
     CCT_CHECK_LAUNCH(ctx);
   }
   const size_t nw = (size_t)G.o * G.Dg * G.k * G.k;
   t->begin(1, ctx->stream);
-  simt_wgrad_kernel<<<(unsigned)nw, 256, 0, ctx->stream>>>(X, dY, dW, G);
+  launch_pdl(simt_wgrad_kernel, dim3((unsigned)nw), dim3(256), 0, ctx->stream, X, dY, dW, G);
   t->end(1, ctx->stream);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;

@@ -207,6 +207,7 @@ __host__ __device__ inline GatherSmem gather_smem(int n_pad, int k_pad, int b_st
 template <int SETS>
 __global__ void __launch_bounds__(gather_threads(SETS), SETS == 2 ? 2 : 1)
     gather_conv_kernel(const __grid_constant__ GatherParams P, const __grid_constant__ CUtensorMap w_map) {
+  pdl_wait();
   constexpr int kProducerWarps = 4 * SETS, kMmaWarp = kProducerWarps, kTmaWarp = kMmaWarp + 1;
   constexpr int kGatherThreads = gather_threads(SETS);
   extern __shared__ uint8_t smem_raw[];
@@ -603,6 +604,7 @@ __host__ __device__ inline WgSmem wg_smem(int n_pad, int subs, int stages) {
 // 128-byte-swizzled tile has the same swizzle phase ((warp+16*i) & 7 == warp & 7) for every i.
 template <int SUBS, int NB>
 __global__ void __launch_bounds__(kWgThreads, 1) wgrad_kernel(const __grid_constant__ WgradParams P) {
+  pdl_wait();
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -836,6 +838,7 @@ constexpr uint32_t kTsTapsOff = kTsStages * kTsStage, kTsTurnOff = kTsTapsOff + 
                    kTsBarsOff = kTsTurnOff + kTsDyWarps * 32u * 33u * 4u, kTsSmem = kTsBarsOff + 8u * (2 * kTsStages + 1) + 16u;
 
 __global__ void __launch_bounds__(kTsThreads, 1) wgrad_ts_kernel(const __grid_constant__ WgradParams P) {
+  pdl_wait();
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -1041,6 +1044,7 @@ __global__ void __launch_bounds__(256) wgrad_reduce_kernel(const float* __restri
                                                            float* __restrict__ db, int splits, int vgroups,
                                                            int tiles_per_group, int rows_pad, int n_real, int n_pad,
                                                            int k_real, int og, int accumulate) {
+  pdl_wait();
   __shared__ float tile[32][33];
   const int vg = blockIdx.z;
   const int kk0 = blockIdx.x * 32, j0 = blockIdx.y * 32;
@@ -1078,6 +1082,7 @@ __global__ void __launch_bounds__(256) wgrad_reduce_rows_kernel(const float* __r
                                                                 float* __restrict__ db, int splits, int vgroups,
                                                                 int tiles_per_group, int rows_pad, int n_real,
                                                                 int n_pad, int k_real, int og, int accumulate) {
+  pdl_wait();
   __shared__ float part[8][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int rows = vgroups * (k_real + 1);
@@ -1116,6 +1121,7 @@ __global__ void __launch_bounds__(256) split_dy_kernel(const float* __restrict__
                                                        float* __restrict__ lo, float* __restrict__ plane_sums,
                                                        int planes, int channels, int mm, int og, int ch_tile,
                                                        int tiles_per_group, int n_pad, size_t row_len) {
+  pdl_wait();
   // One warp per plane at a time, eight loads in flight per lane; no block-wide synchronisation.
   const int lane = threadIdx.x & 31;
   const int warp0 = (int)((blockIdx.x * blockDim.x + threadIdx.x) >> 5), nwarps = (int)((gridDim.x * blockDim.x) >> 5);
@@ -1157,6 +1163,7 @@ __global__ void __launch_bounds__(256) split_dy_kernel(const float* __restrict__
 
 // db[c] = sum over the batch of the plane sums (ConvolutionBridge_impl.hxx:575-599), in a fixed order.
 __global__ void bias_grad_kernel(const float* __restrict__ plane_sums, float* __restrict__ db, int batch, int channels) {
+  pdl_wait();
   // one warp per channel: lane l adds images l, l + 32, ... in order, then a fixed shuffle tree
   const int c = (int)((blockIdx.x * blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
   if (c >= channels) return;
@@ -1171,6 +1178,7 @@ __global__ void bias_grad_kernel(const float* __restrict__ plane_sums, float* __
 // Forward B operand: [2 (hi, lo)][vg][n_pad][k_pad] <- W[o][Dg*k*k], zero padded.
 __global__ void pack_fwd_kernel(const float* __restrict__ W, float* __restrict__ hi, float* __restrict__ lo, int vgroups,
                                 int tiles_per_group, int og, int n_real, int n_pad, int k_real, int k_pad) {
+  pdl_wait();
   const size_t total = (size_t)vgroups * n_pad * k_pad;
   for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
     const int kk = (int)(t % k_pad);
@@ -1194,6 +1202,7 @@ __global__ void pack_fwd_kernel(const float* __restrict__ W, float* __restrict__
 __global__ void pack_dgrad_kernel(const float* __restrict__ W, float* __restrict__ hi, float* __restrict__ lo,
                                   int vgroups, int tiles_per_group, int og, int Dg, int k, int s, int taps, int d_tile,
                                   int n_real, int n_pad, int k_real, int k_pad) {
+  pdl_wait();
   const size_t total = (size_t)vgroups * n_pad * k_pad;
   for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
     const int kk = (int)(t % k_pad);
@@ -1300,10 +1309,10 @@ void launch_wgrad_reduce(cct_ctx* ctx, const float* partial, float* dW, float* d
                          int accumulate = 0) {
   const dim3 tiles((k_real + 1 + 31) / 32, (n_real + 31) / 32, vgroups);
   if ((int)(tiles.x * tiles.y * tiles.z) >= ctx->sm_count)
-    wgrad_reduce_kernel<<<tiles, 256, 0, ctx->stream>>>(partial, dW, db, splits, vgroups, tiles_per_group, rows_pad,
+    launch_pdl(wgrad_reduce_kernel, dim3(tiles), dim3(256), 0, ctx->stream, partial, dW, db, splits, vgroups, tiles_per_group, rows_pad,
                                                        n_real, n_pad, k_real, og, accumulate);
   else
-    wgrad_reduce_rows_kernel<<<std::max(1, std::min(vgroups * (k_real + 1), ctx->sm_count * 8)), 256, 0, ctx->stream>>>(
+    launch_pdl(wgrad_reduce_rows_kernel, dim3(std::max(1, std::min(vgroups * (k_real + 1), ctx->sm_count * 8))), dim3(256), 0, ctx->stream, 
         partial, dW, db, splits, vgroups, tiles_per_group, rows_pad, n_real, n_pad, k_real, og, accumulate);
 }
 
@@ -1570,10 +1579,10 @@ void fill_common(GatherParams& P, const GatherProblem& gp, cct_ctx* ctx, int vgr
 void launch_gather(cct_ctx* ctx, const GatherParams& P, const GatherProblem& gp) {
   if (gp.sets == 2) {
     const int grid = std::min(P.total_tiles, 2 * ctx->sm_count);
-    gather_conv_kernel<2><<<grid, gather_threads(2), gp.smem, ctx->stream>>>(P, gp.map);
+    launch_pdl(gather_conv_kernel<2>, dim3(grid), dim3(gather_threads(2)), gp.smem, ctx->stream, P, gp.map);
   } else {
     const int grid = std::min(P.total_tiles, ctx->sm_count);
-    gather_conv_kernel<4><<<grid, gather_threads(4), gp.smem, ctx->stream>>>(P, gp.map);
+    launch_pdl(gather_conv_kernel<4>, dim3(grid), dim3(gather_threads(4)), gp.smem, ctx->stream, P, gp.map);
   }
 }
 
@@ -1588,7 +1597,7 @@ int umma_conv_forward(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* W,
   const int B = batch > 0 ? batch : G.B;  // a leading slice of the batch (host-buffer calls pipeline over slices)
   if (repack) {
     t->begin(4, ctx->stream);
-    pack_fwd_kernel<<<pack_grid(ctx, f.w_half), 256, 0, ctx->stream>>>(W, f.w, f.w + f.w_half, vgroups, f.tiles, G.og,
+    launch_pdl(pack_fwd_kernel, dim3(pack_grid(ctx, f.w_half)), dim3(256), 0, ctx->stream, W, f.w, f.w + f.w_half, vgroups, f.tiles, G.og,
                                                                      f.n, f.n_pad, f.k_real, f.k_pad);
     t->end(4, ctx->stream);
     CCT_CHECK_LAUNCH(ctx);
@@ -1632,7 +1641,7 @@ int umma_conv_wgrad(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* dY, 
     GatherProblem& w = p->wgp;
     const int vgroups = G.g * f.tiles, mm = G.m * G.m;
     t->begin(1, ctx->stream);
-    split_dy_kernel<<<std::min((G.B * G.o + 7) / 8, ctx->sm_count * 8), 256, 0, ctx->stream>>>(
+    launch_pdl(split_dy_kernel, dim3(std::min((G.B * G.o + 7) / 8, ctx->sm_count * 8)), dim3(256), 0, ctx->stream, 
         dY, w.w, w.w + w.w_half, G.bias ? p->wg_plane_sums : nullptr, G.B * G.o, G.o, mm, G.og, f.ch_tile, f.tiles,
         f.n_pad, w.map_k);
     CCT_CHECK_LAUNCH(ctx);
@@ -1652,7 +1661,7 @@ int umma_conv_wgrad(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* dY, 
     t->begin(2, ctx->stream);
     launch_wgrad_reduce(ctx, p->w_partial, dW, nullptr, p->wg_splits, vgroups, f.tiles, p->wg_mtiles * kTileM, f.n,
                         f.n_pad, f.k_real, G.og);
-    if (G.bias) bias_grad_kernel<<<(G.o + 7) / 8, 256, 0, ctx->stream>>>(p->wg_plane_sums, db, G.B, G.o);
+    if (G.bias) launch_pdl(bias_grad_kernel, dim3((G.o + 7) / 8), dim3(256), 0, ctx->stream, p->wg_plane_sums, db, G.B, G.o);
     t->end(2, ctx->stream);
     CCT_CHECK_LAUNCH(ctx);
   } else {
@@ -1674,9 +1683,9 @@ int umma_conv_wgrad(cct_ctx* ctx, UmmaPlan* p, const float* X, const float* dY, 
     dim3 grid(p->w_mgroups, p->w_splits, vgroups);
     t->begin(1, ctx->stream);
     if (p->w_ts)
-      wgrad_ts_kernel<<<grid, kTsThreads, p->w_smem, ctx->stream>>>(P);
+      launch_pdl(wgrad_ts_kernel, dim3(grid), dim3(kTsThreads), p->w_smem, ctx->stream, P);
     else
-      wgrad_pick(p->w_subs, f.n_pad)<<<grid, kWgThreads, p->w_smem, ctx->stream>>>(P);
+      launch_pdl(wgrad_pick(p->w_subs, f.n_pad), dim3(grid), dim3(kWgThreads), p->w_smem, ctx->stream, P);
     t->end(1, ctx->stream);
     CCT_CHECK_LAUNCH(ctx);
     t->begin(2, ctx->stream);
@@ -1699,7 +1708,7 @@ int umma_conv_dgrad(cct_ctx* ctx, UmmaPlan* p, const float* W, const float* dY, 
     const int vgroups = G.g * d.tiles;
     t->begin(3, ctx->stream);
     if (repack) {
-      pack_dgrad_kernel<<<pack_grid(ctx, d.w_half), 256, 0, ctx->stream>>>(W, d.w, d.w + d.w_half, vgroups, d.tiles, G.og,
+      launch_pdl(pack_dgrad_kernel, dim3(pack_grid(ctx, d.w_half)), dim3(256), 0, ctx->stream, W, d.w, d.w + d.w_half, vgroups, d.tiles, G.og,
                                                                          G.Dg, G.k, G.s, p->dgr_taps, d.ch_tile, d.n,
                                                                          d.n_pad, d.k_real, d.k_pad);
       CCT_CHECK_LAUNCH(ctx);
@@ -1739,6 +1748,7 @@ namespace {
 
 // Fills the weight-gradient row table on the device (the plan-based path builds it on the host and uploads it).
 __global__ void noalloc_taps_kernel(MaskTap* taps, int rows, int k_real, int k, int n) {
+  pdl_wait();
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < rows; i += gridDim.x * blockDim.x) {
     MaskTap t;
     if (i < k_real) {
@@ -1826,7 +1836,7 @@ extern "C" int cct_conv_weight_grad_noalloc(cct_ctx* ctx, const cct_conv_desc* d
   float* partial = reinterpret_cast<float*>(scratch + taps_bytes);
   WgradKernel kernel = wgrad_pick(subs, n_pad);
   CCT_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
-  noalloc_taps_kernel<<<8, 256, 0, ctx->stream>>>(taps, m_tiles * kTileM, k_real, G.k, G.n);
+  launch_pdl(noalloc_taps_kernel, dim3(8), dim3(256), 0, ctx->stream, taps, m_tiles * kTileM, k_real, G.k, G.n);
   CCT_CHECK_LAUNCH(ctx);
   WgradParams P{};
   P.x = X; P.dy = dY; P.partial = partial; P.taps = taps;
@@ -1845,7 +1855,7 @@ extern "C" int cct_conv_weight_grad_noalloc(cct_ctx* ctx, const cct_conv_desc* d
     const int here = std::min(slots, total_splits - first);
     P.kb_first = first * kblocks_per_split;
     P.kblocks_total = std::min(kblocks_total, P.kb_first + here * kblocks_per_split);
-    kernel<<<dim3(mgroups, here, vgroups), kWgThreads, smem, ctx->stream>>>(P);
+    launch_pdl(kernel, dim3(dim3(mgroups, here, vgroups)), dim3(kWgThreads), smem, ctx->stream, P);
     CCT_CHECK_LAUNCH(ctx);
     launch_wgrad_reduce(ctx, partial, dW, G.bias ? db : nullptr, here, vgroups, tiles, m_tiles * kTileM, n_real, n_pad,
                         k_real, G.og, round > 0);
@@ -1860,6 +1870,7 @@ namespace {
 // complete, with a short limit.  The wait gives up, records `code` in the status word and the kernel returns
 // normally: no trap, no fault, the context stays usable.
 __global__ void bounded_wait_selftest_kernel(int* status, long long limit_cycles, int code) {
+  pdl_wait();
   __shared__ __align__(8) unsigned long long bar_storage;
   const uint32_t bar = smem_u32(&bar_storage);
   if (threadIdx.x == 0) {
@@ -1875,7 +1886,7 @@ __global__ void bounded_wait_selftest_kernel(int* status, long long limit_cycles
 extern "C" int cct_selftest_bounded_wait(cct_ctx* ctx, long long limit_cycles) {
   if (!ctx || limit_cycles <= 0 || limit_cycles > kWaitLimitCycles) return CCT_ERR_INVALID;
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
-  bounded_wait_selftest_kernel<<<1, 32, 0, ctx->stream>>>(ctx->status_dev, limit_cycles, 0x7e57);
+  launch_pdl(bounded_wait_selftest_kernel, dim3(1), dim3(32), 0, ctx->stream, ctx->status_dev, limit_cycles, 0x7e57);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }

@@ -28,6 +28,7 @@ inline int plane_grid(cct_ctx* ctx, int planes) { return std::max(1, std::min(pl
 
 // 4 B written per element.
 __global__ void fill_kernel(float* __restrict__ p, size_t count, float v) {
+  pdl_wait();
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x)
     p[i] = v;
 }
@@ -45,6 +46,7 @@ __device__ __forceinline__ float sgd_one(float& gi, float wi, float& hi_io, floa
 // the decay term into the gradient buffer itself).
 __global__ void sgd_kernel(size_t count, size_t vec, float* __restrict__ w, float* __restrict__ g, float* __restrict__ h,
                            float lr, float momentum, float lambda) {
+  pdl_wait();
   const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, nthreads = (size_t)gridDim.x * blockDim.x;
   float4* w4 = reinterpret_cast<float4*>(w);
   float4* g4 = reinterpret_cast<float4*>(g);
@@ -73,6 +75,7 @@ __global__ void sgd_kernel(size_t count, size_t vec, float* __restrict__ w, floa
 // y = alpha x + beta y (12 B moved per element): the saxpy / saxpby calls of the reference's SGD updater
 // (src/algorithms/GradientUpdater.h:163-181), for callers that keep its three-call update.
 __global__ void saxpby_kernel(size_t count, float alpha, const float* __restrict__ x, float beta, float* __restrict__ y) {
+  pdl_wait();
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x)
     y[i] = __fadd_rn(__fmul_rn(alpha, x[i]), __fmul_rn(beta, y[i]));
 }
@@ -80,11 +83,13 @@ __global__ void saxpby_kernel(size_t count, float alpha, const float* __restrict
 // g += lambda * sign(w) with sign(0) = -1: DeviceDriver::L1_update as the host driver computes it
 // (src/sched/DeviceDriver_CPU.cpp:111-117), the L1 branch of the SGD updater.
 __global__ void l1_update_kernel(size_t count, float* __restrict__ g, float lambda, const float* __restrict__ w) {
+  pdl_wait();
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x)
     g[i] = __fadd_rn(g[i], w[i] > 0.f ? lambda : -lambda);
 }
 
 __global__ void relu_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, size_t count, size_t vec) {
+  pdl_wait();
   const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, nthreads = (size_t)gridDim.x * blockDim.x;
   for (size_t i = tid; i < vec; i += nthreads) {
     const float4 v = reinterpret_cast<const float4*>(x)[i];
@@ -95,6 +100,7 @@ __global__ void relu_fwd_kernel(const float* __restrict__ x, float* __restrict__
 
 // dy and dx may be the same buffer (in-place use by the fused backward of the SIMT path).
 __global__ void relu_bwd_kernel(const float* __restrict__ x, const float* dy, float* dx, size_t count, size_t vec) {
+  pdl_wait();
   const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, nthreads = (size_t)gridDim.x * blockDim.x;
   for (size_t i = tid; i < vec; i += nthreads) {
     const float4 v = reinterpret_cast<const float4*>(x)[i];
@@ -116,6 +122,7 @@ inline size_t vec_groups(size_t count, std::initializer_list<const void*> ptrs) 
 // plane offset is the only 64-bit product.  Rows then columns, strict '>' so the first maximum wins.
 __global__ void maxpool_fwd_kernel(const float* __restrict__ X, float* __restrict__ Y, int32_t* __restrict__ idx,
                                    int planes, int n, int m, int k, int s) {
+  pdl_wait();
   const int mm = m * m;
   for (int plane = blockIdx.x; plane < planes; plane += gridDim.x) {
     const float* in = X + (size_t)plane * n * n;
@@ -162,6 +169,7 @@ __global__ void __launch_bounds__(kPoolWarps * 32, 5) maxpool_bwd_kernel(const f
                                                                       const float* __restrict__ P,
                                                                       float* __restrict__ dA, int planes, int n, int m,
                                                                       int k, int s, uint32_t inv_s, int mm_pad) {
+  pdl_wait();
   extern __shared__ uint32_t pool_smem[];
   const int mm = m * m, nn = n * n;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -266,6 +274,7 @@ __global__ void __launch_bounds__(kSlotThreads) maxpool_bwd_slots_kernel(
     const float* __restrict__ A, const int32_t* __restrict__ idx, const float* __restrict__ dP,
     const float* __restrict__ P, float* __restrict__ dA, int planes, int n, int m, int k, int s, int group,
     uint32_t inv_mm, uint32_t inv_m, uint32_t inv_n) {
+  pdl_wait();
   extern __shared__ float slot_smem[];
   const int mm = m * m, nn = n * n, tid = threadIdx.x;
   const int span = group * nn;
@@ -337,6 +346,7 @@ __global__ void __launch_bounds__(256) maxpool_bwd_3x3s2_kernel(const float* __r
                                                                 const float* __restrict__ dP, const float* __restrict__ P,
                                                                 float* __restrict__ dA, uint32_t items, int n, int m,
                                                                 int half, uint32_t inv_half) {
+  pdl_wait();
   const int nn = n * n, mm = m * m;
   for (uint32_t t = blockIdx.x * blockDim.x + threadIdx.x; t < items; t += gridDim.x * blockDim.x) {
     const uint32_t row = fast_div(t, (uint32_t)half, inv_half);  // = plane * half + a
@@ -400,7 +410,7 @@ int launch_maxpool_bwd(cct_ctx* ctx, const float* A, const int32_t* idx, const f
   if (k == 3 && s == 2 && (size_t)planes * half * half < (1ull << 31)) {
     const size_t items = (size_t)planes * half * half;
     const int blocks = (int)std::max<size_t>(1, std::min<size_t>((items + 255) / 256, (size_t)ctx->sm_count * 16));
-    maxpool_bwd_3x3s2_kernel<RELU><<<blocks, 256, 0, ctx->stream>>>(A, idx, dP, P, dA, (uint32_t)items, n, m, half,
+    launch_pdl(maxpool_bwd_3x3s2_kernel<RELU>, dim3(blocks), dim3(256), 0, ctx->stream, A, idx, dP, P, dA, (uint32_t)items, n, m, half,
                                                                     fast_div_magic(items, (uint32_t)half));
     return CCT_OK;
   }
@@ -414,7 +424,7 @@ int launch_maxpool_bwd(cct_ctx* ctx, const float* A, const int32_t* idx, const f
       CCT_CUDA(ctx, cudaFuncSetAttribute(maxpool_bwd_slots_kernel<RELU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int ngroups = (planes + group - 1) / group;
     const int blocks = std::max(1, std::min(ngroups, ctx->sm_count * 4));
-    maxpool_bwd_slots_kernel<RELU><<<blocks, kSlotThreads, smem, ctx->stream>>>(
+    launch_pdl(maxpool_bwd_slots_kernel<RELU>, dim3(blocks), dim3(kSlotThreads), smem, ctx->stream, 
         A, idx, dP, P, dA, planes, n, m, k, s, group, fast_div_magic((uint64_t)kSlotThreads * kSlotWin, (uint32_t)mm),
         fast_div_magic((uint64_t)mm, (uint32_t)m), fast_div_magic((uint64_t)nn, (uint32_t)n));
     return CCT_OK;
@@ -428,7 +438,7 @@ int launch_maxpool_bwd(cct_ctx* ctx, const float* A, const int32_t* idx, const f
   auto kernel = taps == 1 ? maxpool_bwd_kernel<1, RELU> : taps == 2 ? maxpool_bwd_kernel<2, RELU>
               : taps == 3 ? maxpool_bwd_kernel<3, RELU> : maxpool_bwd_kernel<0, RELU>;
   if (smem > 48 * 1024) CCT_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kernel<<<grid, kPoolWarps * 32, smem, ctx->stream>>>(A, idx, dP, P, dA, planes, n, m, k, s, inv_s, mm_pad);
+  launch_pdl(kernel, dim3(grid), dim3(kPoolWarps * 32), smem, ctx->stream, A, idx, dP, P, dA, planes, n, m, k, s, inv_s, mm_pad);
   return CCT_OK;
 }
 
@@ -455,7 +465,7 @@ int cct_fill_f32(cct_ctx* ctx, float* dptr, size_t count, float value) {
   if (!ctx || (!dptr && count)) return CCT_ERR_INVALID;
   if (!count) return CCT_OK;
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
-  fill_kernel<<<grid_for(ctx, count, 256), 256, 0, ctx->stream>>>(dptr, count, value);
+  launch_pdl(fill_kernel, dim3(grid_for(ctx, count, 256)), dim3(256), 0, ctx->stream, dptr, count, value);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }
@@ -464,7 +474,7 @@ int cct_sgd_step(cct_ctx* ctx, size_t count, float* w, float* g, float* h, float
   if (!ctx || !w || !g || !h) return CCT_ERR_INVALID;
   if (!count) return CCT_OK;
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
-  sgd_kernel<<<grid_for(ctx, (count + 3) / 4, 256), 256, 0, ctx->stream>>>(count, vec_groups(count, {w, g, h}), w, g, h, lr,
+  launch_pdl(sgd_kernel, dim3(grid_for(ctx, (count + 3) / 4, 256)), dim3(256), 0, ctx->stream, count, vec_groups(count, {w, g, h}), w, g, h, lr,
                                                                         momentum, lambda);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
@@ -474,7 +484,7 @@ int cct_saxpby(cct_ctx* ctx, size_t count, float alpha, const float* x, float be
   if (!ctx || ((!x || !y) && count)) return CCT_ERR_INVALID;
   if (!count) return CCT_OK;
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
-  saxpby_kernel<<<grid_for(ctx, count, 256), 256, 0, ctx->stream>>>(count, alpha, x, beta, y);
+  launch_pdl(saxpby_kernel, dim3(grid_for(ctx, count, 256)), dim3(256), 0, ctx->stream, count, alpha, x, beta, y);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }
@@ -483,7 +493,7 @@ int cct_l1_update(cct_ctx* ctx, size_t count, float* g, float lambda, const floa
   if (!ctx || ((!g || !w) && count)) return CCT_ERR_INVALID;
   if (!count) return CCT_OK;
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
-  l1_update_kernel<<<grid_for(ctx, count, 256), 256, 0, ctx->stream>>>(count, g, lambda, w);
+  launch_pdl(l1_update_kernel, dim3(grid_for(ctx, count, 256)), dim3(256), 0, ctx->stream, count, g, lambda, w);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }
@@ -491,7 +501,7 @@ int cct_l1_update(cct_ctx* ctx, size_t count, float* g, float lambda, const floa
 int cct_relu_forward(cct_ctx* ctx, const float* X, float* Y, size_t count) {
   if (!ctx || !X || !Y) return CCT_ERR_INVALID;
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
-  relu_fwd_kernel<<<grid_for(ctx, (count + 3) / 4, 256), 256, 0, ctx->stream>>>(X, Y, count, vec_groups(count, {X, Y}));
+  launch_pdl(relu_fwd_kernel, dim3(grid_for(ctx, (count + 3) / 4, 256)), dim3(256), 0, ctx->stream, X, Y, count, vec_groups(count, {X, Y}));
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }
@@ -499,7 +509,7 @@ int cct_relu_forward(cct_ctx* ctx, const float* X, float* Y, size_t count) {
 int cct_relu_backward(cct_ctx* ctx, const float* X, const float* dY, float* dX, size_t count) {
   if (!ctx || !X || !dY || !dX) return CCT_ERR_INVALID;
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
-  relu_bwd_kernel<<<grid_for(ctx, (count + 3) / 4, 256), 256, 0, ctx->stream>>>(X, dY, dX, count,
+  launch_pdl(relu_bwd_kernel, dim3(grid_for(ctx, (count + 3) / 4, 256)), dim3(256), 0, ctx->stream, X, dY, dX, count,
                                                                                 vec_groups(count, {X, dY, dX}));
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
@@ -512,7 +522,7 @@ int cct_maxpool_forward(cct_ctx* ctx, const float* X, float* Y, int32_t* idx, in
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
   // planes that fit in shared memory are staged there (one HBM read per element); larger ones read through L1
   if ((size_t)n * n * sizeof(float) <= 200 * 1024) return maxpool_forward_staged(ctx, X, Y, idx, planes, n, m, k, s);
-  maxpool_fwd_kernel<<<plane_grid(ctx, planes), 256, 0, ctx->stream>>>(X, Y, idx, planes, n, m, k, s);
+  launch_pdl(maxpool_fwd_kernel, dim3(plane_grid(ctx, planes)), dim3(256), 0, ctx->stream, X, Y, idx, planes, n, m, k, s);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }

@@ -70,6 +70,7 @@ __device__ __forceinline__ uint64_t make_desc_mn(uint32_t smem_addr) {
 __global__ void __launch_bounds__(kFcThreads, 2)
     fc_gemm_kernel(const __grid_constant__ FcGemmParams P, const __grid_constant__ CUtensorMap a_map,
                    const __grid_constant__ CUtensorMap b_map) {
+  pdl_wait();
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -294,6 +295,7 @@ __global__ void __launch_bounds__(kFcThreads, 2)
 __global__ void fc_reduce_fwd_kernel(const float* __restrict__ partial, int splits, size_t split_stride,
                                      const float* __restrict__ bias, float* __restrict__ Y, size_t total, int O, int relu,
                                      const uint32_t* __restrict__ drop_mask, float drop_scale) {
+  pdl_wait();
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     float acc = 0.f;
     for (int s = 0; s < splits; ++s) acc += partial[(size_t)s * split_stride + i];
@@ -309,6 +311,7 @@ __global__ void fc_reduce_fwd_kernel(const float* __restrict__ partial, int spli
 __global__ void fc_reduce_dgrad_kernel(const float* __restrict__ partial, int splits, size_t split_stride,
                                        float* __restrict__ dX, size_t total, const float* __restrict__ X, int in_relu,
                                        const uint32_t* __restrict__ drop_mask, float drop_scale) {
+  pdl_wait();
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     float acc = 0.f;
     for (int s = 0; s < splits; ++s) acc += partial[(size_t)s * split_stride + i];
@@ -322,6 +325,7 @@ __global__ void fc_reduce_dgrad_kernel(const float* __restrict__ partial, int sp
 // outputs: thread (x, y) adds the images y, y + 8, ... in order with sixteen loads in flight, then the eight partial sums
 // of an output are added in a fixed order - deterministic, and two memory round trips instead of B.
 __global__ void __launch_bounds__(256) fc_bias_grad_kernel(const float* __restrict__ dY, float* __restrict__ db, int B, int O) {
+  pdl_wait();
   __shared__ float part[8][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int o = blockIdx.x * 32 + tx;
@@ -416,7 +420,7 @@ int fc_launch(cct_ctx* ctx, FcGemmParams& P, const CUtensorMap& a_map, const CUt
   const size_t smem = fc_smem(P.n_pad, P.stages, P.a_tmem).total + 1024;
   P.status = ctx->status_dev;
   const int tiles = P.m_tiles * P.n_tiles * P.splits;
-  fc_gemm_kernel<<<std::min(tiles, (pair ? 2 : 1) * ctx->sm_count), kFcThreads, smem, ctx->stream>>>(P, a_map, b_map);
+  launch_pdl(fc_gemm_kernel, dim3(std::min(tiles, (pair ? 2 : 1) * ctx->sm_count)), dim3(kFcThreads), smem, ctx->stream, P, a_map, b_map);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }
@@ -505,7 +509,7 @@ int cct_fc_forward(cct_fc_plan* plan, const float* X, const float* W, const floa
   rc = fc_launch(ctx, P, a_map, b_map);
   if (rc != CCT_OK) return rc;
   const size_t total = (size_t)B * O;
-  fc_reduce_fwd_kernel<<<fc_ew_grid(ctx, total), 256, 0, ctx->stream>>>(plan->partial, P.splits, (size_t)P.split_stride,
+  launch_pdl(fc_reduce_fwd_kernel, dim3(fc_ew_grid(ctx, total)), dim3(256), 0, ctx->stream, plan->partial, P.splits, (size_t)P.split_stride,
                                                                       plan->bias ? bias : nullptr, Y, total, O, relu,
                                                                       drop_mask, drop_scale);
   plan->timer.end(0, ctx->stream);
@@ -537,7 +541,7 @@ int cct_fc_backward(cct_fc_plan* plan, const float* X, const float* W, const flo
     plan->timer.begin(1, ctx->stream);
     rc = fc_launch(ctx, P, a_map, b_map);
     if (rc != CCT_OK) return rc;
-    if (plan->bias) fc_bias_grad_kernel<<<(O + 31) / 32, 256, 0, ctx->stream>>>(dY, db, B, O);
+    if (plan->bias) launch_pdl(fc_bias_grad_kernel, dim3((O + 31) / 32), dim3(256), 0, ctx->stream, dY, db, B, O);
     plan->timer.end(1, ctx->stream);
     CCT_CHECK_LAUNCH(ctx);
   }
@@ -558,7 +562,7 @@ int cct_fc_backward(cct_fc_plan* plan, const float* X, const float* W, const flo
     rc = fc_launch(ctx, P, a_map, b_map);
     if (rc != CCT_OK) return rc;
     const size_t total = (size_t)B * K;
-    fc_reduce_dgrad_kernel<<<fc_ew_grid(ctx, total), 256, 0, ctx->stream>>>(plan->partial, P.splits, (size_t)P.split_stride,
+    launch_pdl(fc_reduce_dgrad_kernel, dim3(fc_ew_grid(ctx, total)), dim3(256), 0, ctx->stream, plan->partial, P.splits, (size_t)P.split_stride,
                                                                           dX, total, X, in_relu, in_drop_mask, in_drop_scale);
     plan->timer.end(3, ctx->stream);
     CCT_CHECK_LAUNCH(ctx);

@@ -34,6 +34,7 @@ template <int LOCAL>
 __global__ void __launch_bounds__(128) lrn_fwd_kernel(const float* __restrict__ X, float* __restrict__ Y,
                                                       float* __restrict__ scale, size_t items, int D, int chunks, int plane,
                                                       float alpha_over_size, float beta) {
+  pdl_wait();
   constexpr int W = LOCAL / 2, SPAN = kLrnChunk + 2 * W;
   for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < items; t += (size_t)gridDim.x * blockDim.x) {
     const size_t bc = t / plane, p = t - bc * plane;
@@ -67,6 +68,7 @@ __global__ void __launch_bounds__(128) lrn_fwd_kernel(const float* __restrict__ 
 __global__ void lrn_fwd_generic_kernel(const float* __restrict__ X, float* __restrict__ Y, float* __restrict__ scale,
                                        size_t items, int D, int chunks, int plane, int local, float alpha_over_size,
                                        float beta) {
+  pdl_wait();
   const int w = local / 2;
   for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < items; t += (size_t)gridDim.x * blockDim.x) {
     const size_t bc = t / plane, p = t - bc * plane;
@@ -98,6 +100,7 @@ __global__ void __launch_bounds__(128) lrn_bwd_kernel(const float* __restrict__ 
                                                       const float* __restrict__ scale, const float* __restrict__ dY,
                                                       float* __restrict__ dX, size_t items, int D, int chunks, int plane,
                                                       float alpha_over_size, float beta) {
+  pdl_wait();
   constexpr int kLrnChunk = kLrnBwdChunk;  // four arrays are read here: a shorter chunk keeps the registers in check
   constexpr int W = LOCAL / 2, SPAN = kLrnChunk + 2 * W;
   const float coef = 2.f * beta * alpha_over_size;
@@ -137,6 +140,7 @@ __global__ void lrn_bwd_generic_kernel(const float* __restrict__ X, const float*
                                        const float* __restrict__ scale, const float* __restrict__ dY,
                                        float* __restrict__ dX, size_t items, int D, int chunks, int plane, int local,
                                        float alpha_over_size, float beta) {
+  pdl_wait();
   const int w = local / 2;
   const float coef = 2.f * beta * alpha_over_size;
   for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < items; t += (size_t)gridDim.x * blockDim.x) {
@@ -161,6 +165,7 @@ __global__ void lrn_bwd_generic_kernel(const float* __restrict__ X, const float*
 // element-wise product with the mask (one unsigned int per element, non-zero = keep) and the scale 1 / (1 - ratio).
 __global__ void dropout_kernel(const float* __restrict__ in, const uint32_t* __restrict__ mask, float scale,
                                float* __restrict__ out, size_t count) {
+  pdl_wait();
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x)
     out[i] = in[i] * (float)(mask[i] != 0u) * scale;
 }
@@ -171,6 +176,7 @@ __global__ void dropout_kernel(const float* __restrict__ in, const uint32_t* __r
 // (src/bridges/DropoutBridge_impl.hxx:100-104); its CPU path draws from boost::bernoulli on mt19937 - masks differ
 // between the two there as well, which is why parity runs inject the CPU oracle's mask instead.
 __global__ void dropout_mask_kernel(uint32_t* __restrict__ mask, size_t count, uint32_t threshold, uint64_t key) {
+  pdl_wait();
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x) {
     uint64_t z = key + (uint64_t)i * 0x9E3779B97F4A7C15ull;  // splitmix64 finaliser
     z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
@@ -186,6 +192,7 @@ __global__ void dropout_mask_kernel(uint32_t* __restrict__ mask, size_t count, u
 // result does not depend on the grid.  Labels are floats, as in the reference's label cube.
 __global__ void softmax_fwd_kernel(const float* __restrict__ X, const float* __restrict__ labels, float* __restrict__ prob,
                                    float* __restrict__ image_loss, int B, int C) {
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int img = (int)((blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5);
   if (img >= B) return;
@@ -209,6 +216,7 @@ __global__ void softmax_fwd_kernel(const float* __restrict__ X, const float* __r
 }
 
 __global__ void sum_in_order_kernel(const float* __restrict__ v, float* __restrict__ out, int n) {
+  pdl_wait();
   if (blockIdx.x == 0 && threadIdx.x == 0) {
     float acc = 0.f;
     for (int i = 0; i < n; ++i) acc += v[i];
@@ -220,6 +228,7 @@ __global__ void sum_in_order_kernel(const float* __restrict__ v, float* __restri
 // dX = (prob - onehot(label)) * scale, scale = 1 / (batch the loss is averaged over).
 __global__ void softmax_bwd_kernel(const float* __restrict__ prob, const float* __restrict__ labels,
                                    float* __restrict__ dX, size_t total, int C, float scale) {
+  pdl_wait();
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const size_t img = i / C;
     const int c = (int)(i - img * C);
@@ -239,6 +248,7 @@ template <int K, int S>
 __global__ void __launch_bounds__(256) maxpool_fwd_staged_kernel(const float* __restrict__ X, float* __restrict__ Y,
                                                                  int32_t* __restrict__ idx, int planes, int n, int m,
                                                                  int k_rt, int s_rt, int group) {
+  pdl_wait();
   // `group` consecutive planes (contiguous in memory) are staged and pooled together, so that small planes (13 x 13)
   // still give every thread of the block work.
   extern __shared__ float plane_smem[];
@@ -324,7 +334,7 @@ int maxpool_forward_staged(cct_ctx* ctx, const float* X, float* Y, int32_t* idx,
   const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(8, (200 * 1024) / std::max<size_t>(smem, 1)));
   const int blocks_needed = (planes + group - 1) / group;
   const int grid = std::max(1, std::min(blocks_needed, ctx->sm_count * per_sm));
-  kernel<<<grid, 256, smem, ctx->stream>>>(X, Y, idx, planes, n, m, k, s, group);
+  launch_pdl(kernel, dim3(grid), dim3(256), smem, ctx->stream, X, Y, idx, planes, n, m, k, s, group);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }
@@ -341,11 +351,11 @@ int cct_lrn_forward(cct_ctx* ctx, const float* X, float* Y, float* scale, int ba
   const int grid = ew_grid(ctx, items, 128);
   const float aos = alpha / (float)local_size;
   if (local_size == 5)
-    lrn_fwd_kernel<5><<<grid, 128, 0, ctx->stream>>>(X, Y, scale, items, depth, chunks, plane, aos, beta);
+    launch_pdl(lrn_fwd_kernel<5>, dim3(grid), dim3(128), 0, ctx->stream, X, Y, scale, items, depth, chunks, plane, aos, beta);
   else if (local_size == 3)
-    lrn_fwd_kernel<3><<<grid, 128, 0, ctx->stream>>>(X, Y, scale, items, depth, chunks, plane, aos, beta);
+    launch_pdl(lrn_fwd_kernel<3>, dim3(grid), dim3(128), 0, ctx->stream, X, Y, scale, items, depth, chunks, plane, aos, beta);
   else
-    lrn_fwd_generic_kernel<<<grid, 128, 0, ctx->stream>>>(X, Y, scale, items, depth, chunks, plane, local_size, aos, beta);
+    launch_pdl(lrn_fwd_generic_kernel, dim3(grid), dim3(128), 0, ctx->stream, X, Y, scale, items, depth, chunks, plane, local_size, aos, beta);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }
@@ -363,11 +373,11 @@ int cct_lrn_backward(cct_ctx* ctx, const float* X, const float* Y, const float* 
   const int grid = ew_grid(ctx, items, 128);
   const float aos = alpha / (float)local_size;
   if (local_size == 5)
-    lrn_bwd_kernel<5><<<grid, 128, 0, ctx->stream>>>(X, Y, scale, dY, dX, items, depth, chunks, plane, aos, beta);
+    launch_pdl(lrn_bwd_kernel<5>, dim3(grid), dim3(128), 0, ctx->stream, X, Y, scale, dY, dX, items, depth, chunks, plane, aos, beta);
   else if (local_size == 3)
-    lrn_bwd_kernel<3><<<grid, 128, 0, ctx->stream>>>(X, Y, scale, dY, dX, items, depth, chunks, plane, aos, beta);
+    launch_pdl(lrn_bwd_kernel<3>, dim3(grid), dim3(128), 0, ctx->stream, X, Y, scale, dY, dX, items, depth, chunks, plane, aos, beta);
   else
-    lrn_bwd_generic_kernel<<<grid, 128, 0, ctx->stream>>>(X, Y, scale, dY, dX, items, depth, chunks, plane, local_size, aos,
+    launch_pdl(lrn_bwd_generic_kernel, dim3(grid), dim3(128), 0, ctx->stream, X, Y, scale, dY, dX, items, depth, chunks, plane, local_size, aos,
                                                         beta);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
@@ -377,7 +387,7 @@ int cct_dropout_apply(cct_ctx* ctx, const float* in, const uint32_t* mask, float
   if (!ctx || !in || !mask || !out) return CCT_ERR_INVALID;
   if (!count) return CCT_OK;
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
-  dropout_kernel<<<ew_grid(ctx, count, 256), 256, 0, ctx->stream>>>(in, mask, scale, out, count);
+  launch_pdl(dropout_kernel, dim3(ew_grid(ctx, count, 256)), dim3(256), 0, ctx->stream, in, mask, scale, out, count);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }
@@ -388,7 +398,7 @@ int cct_dropout_mask(cct_ctx* ctx, uint32_t* mask, size_t count, float ratio, ui
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
   const uint32_t threshold = (uint32_t)std::min(4294967295.0, (double)ratio * 4294967296.0);
   const uint64_t key = (seed * 0xD1342543DE82EF95ull + 0x632BE59BD9B4E019ull) ^ (call * 0xDA942042E4DD58B5ull);
-  dropout_mask_kernel<<<ew_grid(ctx, count, 256), 256, 0, ctx->stream>>>(mask, count, threshold, key);
+  launch_pdl(dropout_mask_kernel, dim3(ew_grid(ctx, count, 256)), dim3(256), 0, ctx->stream, mask, count, threshold, key);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }
@@ -397,9 +407,9 @@ int cct_softmax_loss_forward(cct_ctx* ctx, const float* X, const float* labels, 
                              float* loss, int batch, int classes) {
   if (!ctx || !X || !labels || !prob || !image_loss || !loss || batch <= 0 || classes <= 0) return CCT_ERR_INVALID;
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
-  softmax_fwd_kernel<<<(batch + 3) / 4, 128, 0, ctx->stream>>>(X, labels, prob, image_loss, batch, classes);
+  launch_pdl(softmax_fwd_kernel, dim3((batch + 3) / 4), dim3(128), 0, ctx->stream, X, labels, prob, image_loss, batch, classes);
   CCT_CHECK_LAUNCH(ctx);
-  sum_in_order_kernel<<<1, 32, 0, ctx->stream>>>(image_loss, loss, batch);
+  launch_pdl(sum_in_order_kernel, dim3(1), dim3(32), 0, ctx->stream, image_loss, loss, batch);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }
@@ -409,7 +419,7 @@ int cct_softmax_loss_backward(cct_ctx* ctx, const float* prob, const float* labe
   if (!ctx || !prob || !labels || !dX || batch <= 0 || classes <= 0) return CCT_ERR_INVALID;
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
   const size_t total = (size_t)batch * classes;
-  softmax_bwd_kernel<<<ew_grid(ctx, total, 256), 256, 0, ctx->stream>>>(prob, labels, dX, total, classes, scale);
+  launch_pdl(softmax_bwd_kernel, dim3(ew_grid(ctx, total, 256)), dim3(256), 0, ctx->stream, prob, labels, dX, total, classes, scale);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }
