@@ -16,8 +16,10 @@
 //
 // gather_conv_kernel serves the forward pass, the data gradient and (lanes = rows of the lowered matrix, dY as the
 // pre-split TMA operand) the weight gradient of larger layers: gathered operand in tensor memory, the other operand
-// streamed by TMA into swizzled shared memory, warp-specialised roles.  wgrad_kernel is the weight gradient of small
-// layers with both operands staged in shared memory.  Every mbarrier wait is bounded: when it runs out the thread
+// streamed by TMA into swizzled shared memory, warp-specialised roles.  Shorter lowered matrices have their own weight-
+// gradient kernels: wgrad_ts_kernel (257 .. 384 rows: dY through tensor memory, the lowered rows staged in shared memory)
+// and wgrad_kernel (anything shorter, and the allocation-free entry point: both operands staged in shared memory).
+// Every kernel starts with pdl_wait() and is launched with launch_pdl (cct_internal.h).  Every mbarrier wait is bounded: when it runs out the thread
 // sets the context's status word, stops waiting on anything else, and the kernel still frees its tensor memory.
 #include <algorithm>
 #include <cstdio>
