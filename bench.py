@@ -651,6 +651,19 @@ def run_caffenet(args, rank, world, local_rank):
                 continue
             plan_ms[i] = plan_ms.get(i, np.zeros(5)) + np.array(list(t5))
     fwd_ms /= prof_steps; bwd_ms /= prof_steps; upd_ms /= prof_steps
+    # N > 1: the step's gradient reductions on their own (nothing beside them), to compare with the backward pass they
+    # hide behind: every layer's flat gradient buffer, begun back to back, one wait.
+    ar_alone_ms = None
+    if world > 1:
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        a.record(stream)
+        for _, pb in reversed(net.param_bridges()):
+            pb.begin_allreduce()
+        net.ops.allreduce_wait()
+        b.record(stream)
+        torch.cuda.synchronize()
+        ar_alone_ms = max_over_ranks(a.elapsed_time(b))
     layers, contraction = {}, []
     hbm = load_peaks()["hbm_gbs"]
     for i, name in enumerate(names):
@@ -787,6 +800,7 @@ def run_caffenet(args, rank, world, local_rank):
                     "h2d_gbs": X.nbytes / (h2d_ms * 1e-3) / 1e9 if h2d_ms > 0 else None},
             "clocks": clocks, "gpu_launches": net.launches_per_step() * args.steps,
             "allreduce_bytes_per_step": 4 * net.num_parameters() if world > 1 else 0,
+            "allreduce_ms_alone": ar_alone_ms,
         }
         if cpu:
             cpu.pop("seconds_per_step", None)

@@ -14,6 +14,11 @@ struct cct_ctx {
   // Side streams of the host-buffer entry points: uploads and downloads overlap each other and the kernels.
   cudaStream_t copy_in = nullptr, copy_out = nullptr;
   int sm_count = 148;
+  // SMs the persistent kernels leave free while gradient reductions are in flight on the communicator's stream
+  // (set by cct_allreduce_sum_begin, cleared by cct_comm_wait): NCCL's CTAs take whole SMs, and a persistent grid
+  // sized for every SM would otherwise run its displaced CTAs as a second wave.
+  int reserved_sms = 0;
+  int launch_sms() const { return sm_count - reserved_sms > 0 ? sm_count - reserved_sms : 1; }
   // One word in mapped pinned host memory that kernels set when a bounded wait runs out; read by cct_sync().
   volatile int* status_host = nullptr;
   int* status_dev = nullptr;

@@ -7,6 +7,7 @@
 // it overlaps whatever the context's stream is given next), and cct_comm_wait orders the context's stream behind it.
 #include <dlfcn.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -78,6 +79,9 @@ struct cct_comm {
   bool pending = false;               // reductions issued since the last cct_comm_wait
 };
 
+constexpr int kCommSms = 8;           // SMs left to NCCL while reductions are in flight
+const char* const kCommCtas = "8";    // NCCL_MAX_CTAS unless the environment already has one
+
 extern "C" {
 
 int cct_comm_unique_id(unsigned char id[CCT_COMM_ID_BYTES]) {
@@ -104,6 +108,10 @@ int cct_comm_init_rank(cct_ctx* ctx, int nranks, int rank, const unsigned char i
       delete c;
       return CCT_ERR_UNSUPPORTED;
     }
+    // The reductions run beside the backward kernels: a few CTAs carry them at NVLink speed, and every SM NCCL does not
+    // take stays with the persistent kernels (which leave kCommSms free while a reduction is in flight).  A value the
+    // caller has set in the environment wins.
+    setenv("NCCL_MAX_CTAS", kCommCtas, 0);
     NcclUniqueId u;
     std::memcpy(u.internal, id, CCT_COMM_ID_BYTES);
     const ncclResult_t r = api->CommInitRank(&c->comm, nranks, u, rank);
@@ -162,6 +170,7 @@ int cct_allreduce_sum_begin(cct_comm* c, float* buf, size_t count) {
     return CCT_ERR_CUDA;
   }
   c->pending = true;
+  ctx->reserved_sms = kCommSms;
   return CCT_OK;
 }
 
@@ -173,6 +182,7 @@ int cct_comm_wait(cct_comm* c) {
   CCT_CUDA(ctx, cudaEventRecord(c->done, c->stream));
   CCT_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, c->done, 0));
   c->pending = false;
+  ctx->reserved_sms = 0;
   if (c->comm) {
     NcclApi* api = nccl_api();
     ncclResult_t async = 0;

@@ -1580,10 +1580,10 @@ void fill_common(GatherParams& P, const GatherProblem& gp, cct_ctx* ctx, int vgr
 // Persistent grid: one CTA per SM (4 producer sets) or two (2 sets).
 void launch_gather(cct_ctx* ctx, const GatherParams& P, const GatherProblem& gp) {
   if (gp.sets == 2) {
-    const int grid = std::min(P.total_tiles, 2 * ctx->sm_count);
+    const int grid = std::min(P.total_tiles, 2 * ctx->launch_sms());
     launch_pdl(gather_conv_kernel<2>, dim3(grid), dim3(gather_threads(2)), gp.smem, ctx->stream, P, gp.map);
   } else {
-    const int grid = std::min(P.total_tiles, ctx->sm_count);
+    const int grid = std::min(P.total_tiles, ctx->launch_sms());
     launch_pdl(gather_conv_kernel<4>, dim3(grid), dim3(gather_threads(4)), gp.smem, ctx->stream, P, gp.map);
   }
 }

@@ -420,7 +420,7 @@ int fc_launch(cct_ctx* ctx, FcGemmParams& P, const CUtensorMap& a_map, const CUt
   const size_t smem = fc_smem(P.n_pad, P.stages, P.a_tmem).total + 1024;
   P.status = ctx->status_dev;
   const int tiles = P.m_tiles * P.n_tiles * P.splits;
-  launch_pdl(fc_gemm_kernel, dim3(std::min(tiles, (pair ? 2 : 1) * ctx->sm_count)), dim3(kFcThreads), smem, ctx->stream, P, a_map, b_map);
+  launch_pdl(fc_gemm_kernel, dim3(std::min(tiles, (pair ? 2 : 1) * ctx->launch_sms())), dim3(kFcThreads), smem, ctx->stream, P, a_map, b_map);
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }

@@ -9,12 +9,15 @@
 
 template <typename InputLayerDataType, LayoutType InputLayerLayout, typename OutputLayerDataType, LayoutType OutputLayerLayout>
 class AbstractBridge<InputLayerDataType, InputLayerLayout, OutputLayerDataType, OutputLayerLayout, B200Driver> : public PhysicalOperator {
+  public:
+    typedef LogicalCube<InputLayerDataType, InputLayerLayout> InputCube;
+    typedef LogicalCube<OutputLayerDataType, OutputLayerLayout> OutputCube;
+
   protected:
     size_t curr_B;
-    LogicalCube<InputLayerDataType, InputLayerLayout> * input_d_cube;
-    LogicalCube<InputLayerDataType, InputLayerLayout> * input_g_cube;
-    LogicalCube<OutputLayerDataType, OutputLayerLayout> * output_d_cube;
-    LogicalCube<OutputLayerDataType, OutputLayerLayout> * output_g_cube;
+    // views (no memory of their own) of the layers' device cubes, re-pointed in every pass
+    InputCube * input_d_cube, * input_g_cube;
+    OutputCube * output_d_cube, * output_g_cube;
 
   public:
     std::string name;

@@ -361,12 +361,26 @@ class Net:
             br.forward()
 
     def backward(self):
+        # Gradient sums are begun per layer and run on the communicator's stream beside the layers below.  The fully
+        # connected layers' sums (most of the bytes) are held back until the first convolution's backward pass is next:
+        # the inner-product kernels are single-wave grids that lose a whole wave when NCCL takes SMs away from them,
+        # the convolution kernels are many-round persistent grids that only slow down in proportion.
+        held = []
         for i in range(len(self.bridges) - 1, -1, -1):
             pb = self.pbridges.get(i)
             if pb is not None:
-                pb.backward()   # sub-bridge backward, then the gradient all-reduce is begun (not waited for)
+                if self.types[i] == "InnerProduct":
+                    pb.backward(begin_allreduce=False)
+                    held.append(pb)
+                else:
+                    for h in held:
+                        h.begin_allreduce()
+                    held = []
+                    pb.backward()   # sub-bridge backward, then the gradient all-reduce is begun (not waited for)
             else:
                 self.bridges[i].backward()
+        for h in held:
+            h.begin_allreduce()
         self.ops.allreduce_wait()
         for i in sorted(self.pbridges, reverse=True):
             self.pbridges[i].apply_update()

@@ -242,18 +242,25 @@ class ParallelizedBridge:
     def forward(self):
         self.bridge.forward()
 
-    def backward(self):
+    def backward(self, begin_allreduce=True):
+        """The sub-bridge's backward pass, then the gradient sum is begun (not waited for).  A caller that wants the sum
+        to start later - behind further kernels - passes begin_allreduce=False and calls begin_allreduce() itself."""
         self.bridge.backward()
+        if not begin_allreduce and self.defer_update and hasattr(self.ops, "allreduce_begin"):
+            return
+        self.begin_allreduce()
+        if not self.defer_update:
+            wait = getattr(self.ops, "allreduce_wait", None)
+            if hasattr(self.ops, "allreduce_begin") and wait is not None:
+                wait()
+            self.apply_update()
+
+    def begin_allreduce(self):
         begin = getattr(self.ops, "allreduce_begin", None)
         if begin is None:  # an ops object with the blocking form only
             self.ops.allreduce_sum(self.grads, self.count)
         else:
             begin(self.grads, self.count)  # gradients are summed, not averaged (:916-955)
-        if not self.defer_update:
-            wait = getattr(self.ops, "allreduce_wait", None)
-            if begin is not None and wait is not None:
-                wait()
-            self.apply_update()
 
     def apply_update(self):
         """The SGD step on the summed gradients (the caller has waited for the sum when updates are deferred)."""

@@ -244,7 +244,10 @@ int cct_pool_relu_backward(cct_ctx* ctx, const float* A, const int32_t* idx, con
  *      cct_allreduce_sum_begin orders the reduction behind the work already queued on the context's stream and runs it
  *      on the communicator's own stream, so that kernels enqueued afterwards (the backward pass of the layers below)
  *      overlap it; cct_comm_wait makes the context's stream wait for every reduction begun so far - call it before the
- *      SGD step that reads the buffers.  cct_allreduce_sum = begin + wait.  nranks == 1 makes all of them no-ops. ---- */
+ *      SGD step that reads the buffers.  cct_allreduce_sum = begin + wait.  nranks == 1 makes all of them no-ops.
+ *      Between the first begin and the wait the library's persistent kernels size their grids for eight SMs fewer,
+ *      the ones NCCL's CTAs occupy; cct_comm_init_rank sets NCCL_MAX_CTAS=8 in the process environment for that unless
+ *      the variable is already set (a few CTAs carry a reduction at NVLink speed). ---- */
 #define CCT_COMM_ID_BYTES 128
 typedef struct cct_comm cct_comm;
 int cct_comm_unique_id(unsigned char id[CCT_COMM_ID_BYTES]);
