@@ -1136,19 +1136,23 @@ __global__ void __launch_bounds__(256) split_dy_kernel(const float* __restrict__
     float* dh = hi + row * row_len + (size_t)b * mm;
     float* dl = lo + row * row_len + (size_t)b * mm;
     float sum = 0.f;
-    for (int i0 = 0; i0 < mm; i0 += 256) {
+    // Lane l takes the plane's elements whose DESTINATION is l floats into a 128-byte line (rows of the operand are
+    // multiples of 32 floats, so only the image's offset b * mm matters): every warp-wide store then fills whole lines.
+    // Stores that straddle lines run at about two thirds of the bandwidth on this part; loads do not care.
+    const int skew = (int)(((size_t)b * mm) & 31);
+    for (int i0 = -skew; i0 < mm; i0 += 256) {
       float x[8];
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
         const int i = i0 + u * 32 + lane;
-        x[u] = i < mm ? __ldg(src + i) : 0.f;
+        x[u] = (i >= 0 && i < mm) ? __ldg(src + i) : 0.f;
       }
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
         const int i = i0 + u * 32 + lane;
         uint32_t h, l;
         split_tf32_trunc(x[u], h, l);
-        if (i < mm) {
+        if (i >= 0 && i < mm) {
           dh[i] = __uint_as_float(h);
           dl[i] = __uint_as_float(l);
         }
