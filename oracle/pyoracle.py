@@ -244,6 +244,15 @@ class Reference:
                                       _p(dY), _p(dX), time_iters)
         return Y, mask, dX, sec
 
+    def fill(self, kind, count, a=0.0, b=1.0, seed=1, n_batch=1):
+        """`count` values from the reference's own filler: kind 0 gaussian(mean a, std b), 1 xavier over n_batch filters,
+        2 bernoulli(p = a) (CPUDriver::s*_initialize, src/sched/DeviceDriver_CPU.cpp:661-699)."""
+        out = np.empty(count, _f)
+        self.lib.cctref_fill.argtypes = [C.c_int, C.POINTER(C.c_float), C.c_long, C.c_float, C.c_float, C.c_int, C.c_long]
+        self.lib.cctref_fill.restype = None
+        self.lib.cctref_fill(kind, _p(out), count, a, b, seed, n_batch)
+        return out
+
     def fc(self, X, W, bias, dY=None, blas_threads=1, time_iters=0):
         """Y, dX, dW, db, seconds through the reference's FullyConnectedBridge."""
         B, D, n, _ = X.shape

@@ -332,5 +332,16 @@ double cctref_softmax_loss(int B, int C, const float* X, const float* labels, fl
   return time_iters > 0 ? run_and_time(br, dX != NULL, time_iters, NULL, NULL) : 0.0;
 }
 
+// The reference's parameter fillers (CPUDriver::sgaussian_initialize / sinitialize_xavier / sbernoulli_initialize,
+// src/sched/DeviceDriver_CPU.cpp:661-699) on a host buffer.  kind: 0 gaussian(a = mean, b = std), 1 xavier over
+// n_batch filters, 2 bernoulli(a = p).
+void cctref_fill(int kind, float* out, long n, float a, float b, int seed, long n_batch) {
+  CPUDriver drv;
+  DeviceMemoryPointer_Local_RAM ptr(out, sizeof(float) * (size_t)n);
+  if (kind == 0) drv.sgaussian_initialize(&ptr, a, b, seed);
+  else if (kind == 1) drv.sinitialize_xavier(&ptr, (size_t)n_batch, seed);
+  else drv.sbernoulli_initialize(&ptr, a, seed);
+}
+
 }  // extern "C"
 

@@ -114,3 +114,26 @@ def test_fill_and_empty_sizes(ctx):
     assert ctx.lib.cct_fill_f32(ctx.h, None, 0, 1.0) == capi.CCT_OK
     assert ctx.lib.cct_memset(ctx.h, None, 0, 0) == capi.CCT_OK
     c.free()
+
+
+@pytest.mark.parametrize("kind,a,b,n_batch", [(0, 0.0, 0.01, 1), (0, 0.5, 2.0, 1), (1, 363.0, 0.0, 96), (2, 0.3, 0.0, 1)])
+def test_fillers_reproduce_the_reference_fillers(ctx, reference, kind, a, b, n_batch):
+    """cct_fill_random against CPUDriver::sgaussian_initialize / sinitialize_xavier / sbernoulli_initialize
+    (src/sched/DeviceDriver_CPU.cpp:661-699) with the same seed: the same generator and distributions, so the same
+    sequence - bit for bit for the Bernoulli draws, to the last unit or two for the floating-point ones (the checker is
+    built with -march=native, whose fused multiply-adds round the distributions' affine maps once instead of twice).
+    Xavier: a = fan-in = elements per filter."""
+    from caffecontroll_b200 import capi
+    count = 96 * 363 if kind == 1 else 50021
+    seed = 17
+    cube = LogicalCube(ctx, 1, 1, count, 1)
+    capi.check(ctx.lib.cct_fill_random(ctx.h, C.c_void_p(cube.ptr), count, kind, a, b, seed), "cct_fill_random", ctx.h)
+    got = cube.download().ravel()
+    want = reference.fill(kind, count, a=a, b=b, seed=seed, n_batch=n_batch)
+    if kind == 2:
+        assert np.array_equal(got, want)
+    else:
+        scale = np.abs(want).max()
+        assert np.abs(got - want).max() <= 4e-6 * scale
+        assert np.mean(got == want) > 0.5   # the same draws: most values agree exactly, the rest differ in the last place
+    cube.free()
