@@ -1500,13 +1500,31 @@ int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out) {
     const int vgroups = G.g * f.tiles;
     w.tiles = f.tiles; w.ch_tile = f.ch_tile; w.n = f.n; w.n_pad = f.n_pad;
     w.k_real = n_pix;
-    // about two tiles per persistent CTA, at least 16 k-blocks each
     p->wg_mtiles = (f.k_real + kTileM - 1) / kTileM;  // no all-ones row here: the bias gradient comes from the dY pass
     const int base_tiles = vgroups * p->wg_mtiles;
-    int splits = std::max(1, (4 * ctx->sm_count + base_tiles - 1) / base_tiles);
-    splits = std::min(splits, std::max(1, kb_total / 16));
-    splits = std::max(splits, (kb_total + kMaxChainKblocks - 1) / kMaxChainKblocks);  // bounded accumulation chains
-    p->wg_kps = (kb_total + splits - 1) / splits;
+    // Splits of the pixel range: all work units (base tiles x splits) cost the same, so the kernel's time is
+    // (rounds of units over the resident CTAs) x (k-blocks per unit) - pick the split count that minimises it, plus the
+    // traffic of the partial sums it creates (written once, read once by the reduction).  Chains stay bounded
+    // (kMaxChainKblocks) and units no shorter than 16 k-blocks.  A last round that fills at most half of the slots of
+    // the two-CTAs-per-SM shape costs about half a round: its CTAs have their SM's tensor pipe to themselves.
+    {
+      const bool two_per_sm = f.n_pad <= 128;  // the shape finish_problem() will pick for this accumulator width
+      const int slots = ctx->sm_count * (two_per_sm ? 2 : 1);
+      const double us_per_kblock = 12.0 * (f.n_pad / 2.0) / 1900.0 * (two_per_sm ? 2.0 : 1.0);
+      double best = 0.0;
+      int best_kps = 0;
+      for (int s = std::max(1, (kb_total + kMaxChainKblocks - 1) / kMaxChainKblocks); s <= 8 * slots / base_tiles + 1; ++s) {
+        const int kps = (kb_total + s - 1) / s;
+        if (kps < 16 && best_kps) break;
+        const int units = base_tiles * ((kb_total + kps - 1) / kps);
+        const int tail = units % slots;
+        const double rounds = units / slots + (tail == 0 ? 0.0 : (two_per_sm && 2 * tail <= slots) ? 0.55 : 1.0);
+        const double reduce = 1.5 * units * (double)kTileM * f.n_pad * 8.0 / 6.5e6 / us_per_kblock;
+        const double cost = rounds * kps + reduce;
+        if (!best_kps || cost < best - 1e-9) { best = cost; best_kps = kps; }
+      }
+      p->wg_kps = best_kps;
+    }
     p->wg_splits = (kb_total + p->wg_kps - 1) / p->wg_kps;
     w.k_pad = p->wg_kps * kBlockK;
     w.taps_smem = 0;
