@@ -1239,6 +1239,36 @@ int channel_tiles(int channels, int cols_per_channel) {
   return 0;
 }
 
+// Channel tiles of the data gradient.  The widest accumulator is not always the fastest: work units (pixel tile x
+// channel tile) are spread over the resident CTAs in whole rounds, and accumulators of at most 128 columns run as two
+// CTAs per SM, whose last, half-empty round costs about half a round.  Estimated cycles = rounds x k-blocks x cycles per
+// k-block (MMA issue: 75 cycles each; MMA execution: half a cycle per column, shared by the SM's CTAs; gather: about
+// 2 500 cycles per k-block and producer set), for the widest tiling and for the next narrower ones down to 64 columns.
+int dgrad_channel_tiles(int sm_count, int channels, int cols_per_channel, long long pixel_tiles, int groups, int kblocks) {
+  const int t0 = channel_tiles(channels, cols_per_channel);
+  if (t0 == 0) return 0;
+  int best_t = t0;
+  double best = 0.0;
+  for (int t = t0; t <= channels; ++t) {
+    if (channels % t) continue;
+    const int n_pad = round_up((channels / t) * cols_per_channel, 16);
+    if (t > t0 && n_pad < 64) break;
+    const bool dual = n_pad <= 64, two_per_sm = (dual ? 2 * n_pad : n_pad) <= 128;
+    const int mmas = dual ? 8 : 12;
+    const double exec = mmas * (dual ? n_pad : n_pad / 2.0);
+    const double per_kb = two_per_sm ? std::max({mmas * 75.0, 2.0 * exec, 2500.0 / 2}) : std::max({mmas * 75.0, exec, 2500.0 / 4});
+    const long long units = pixel_tiles * groups * t, slots = (long long)sm_count * (two_per_sm ? 2 : 1);
+    const long long tail = units % slots;
+    const double rounds = (double)(units / slots) + (tail == 0 ? 0.0 : (two_per_sm && 2 * tail <= slots) ? 0.55 : 1.0);
+    const double cost = rounds * kblocks * per_kb;
+    if (t == t0 || cost < 0.97 * best) {  // a narrower tiling gathers every pixel once more: it has to win clearly
+      best = cost;
+      best_t = t;
+    }
+  }
+  return best_t;
+}
+
 }  // namespace
 
 // One gather problem (forward, or the data gradient): tables, packed weights and their tensor map.
@@ -1415,7 +1445,11 @@ int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out) {
     p->dgr_taps = (G.k + G.s - 1) / G.s;
     p->dgr_q0 = G.p / G.s;
     p->dgr_q = (G.n - 1 + G.p) / G.s + 1 - p->dgr_q0;
-    d.tiles = channel_tiles(G.Dg, ss);
+    {
+      const int J0 = (G.k + G.s - 1) / G.s, q0 = G.p / G.s, q = (G.n - 1 + G.p) / G.s + 1 - q0;
+      d.tiles = dgrad_channel_tiles(ctx->sm_count, G.Dg, ss, ((long long)G.B * q * q + kTileM - 1) / kTileM, G.g,
+                                    (G.og * J0 * J0 + kBlockK - 1) / kBlockK);
+    }
     d.ch_tile = G.Dg / d.tiles;
     d.n = d.ch_tile * ss;
     d.n_pad = round_up(d.n, 16);
