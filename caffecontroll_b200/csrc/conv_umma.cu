@@ -1547,7 +1547,8 @@ int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out) {
       const double us_per_kblock = 12.0 * (f.n_pad / 2.0) / 1900.0 * (two_per_sm ? 2.0 : 1.0);
       double best = 0.0;
       int best_kps = 0;
-      for (int s = std::max(1, (kb_total + kMaxChainKblocks - 1) / kMaxChainKblocks); s <= 8 * slots / base_tiles + 1; ++s) {
+      const int s_min = std::max(1, (kb_total + kMaxChainKblocks - 1) / kMaxChainKblocks);
+      for (int s = s_min; s <= std::max(s_min, 8 * slots / base_tiles + 1); ++s) {
         const int kps = (kb_total + s - 1) / s;
         if (kps < 16 && best_kps) break;
         const int units = base_tiles * ((kb_total + kps - 1) / kps);
