@@ -19,6 +19,11 @@ struct cct_ctx {
   // sized for every SM would otherwise run its displaced CTAs as a second wave.
   int reserved_sms = 0;
   int launch_sms() const { return sm_count - reserved_sms > 0 ? sm_count - reserved_sms : 1; }
+  // Set when a communicator of more than one rank is created on this context: plans created afterwards size their
+  // work-unit counts (split counts, channel tilings) for the SMs that remain while reductions are in flight, because
+  // that is when the backward kernels of a multi-GPU job run.
+  int comm_sms = 0;
+  int planning_sms() const { return sm_count - comm_sms > 0 ? sm_count - comm_sms : 1; }
   // One word in mapped pinned host memory that kernels set when a bounded wait runs out; read by cct_sync().
   volatile int* status_host = nullptr;
   int* status_dev = nullptr;

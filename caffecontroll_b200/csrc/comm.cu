@@ -112,6 +112,7 @@ int cct_comm_init_rank(cct_ctx* ctx, int nranks, int rank, const unsigned char i
     // take stays with the persistent kernels (which leave kCommSms free while a reduction is in flight).  A value the
     // caller has set in the environment wins.
     setenv("NCCL_MAX_CTAS", kCommCtas, 0);
+    ctx->comm_sms = kCommSms;  // plans created from now on count on that many SMs fewer during the backward pass
     NcclUniqueId u;
     std::memcpy(u.internal, id, CCT_COMM_ID_BYTES);
     const ncclResult_t r = api->CommInitRank(&c->comm, nranks, u, rank);

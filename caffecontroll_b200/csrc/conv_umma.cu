@@ -1447,7 +1447,7 @@ int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out) {
     p->dgr_q = (G.n - 1 + G.p) / G.s + 1 - p->dgr_q0;
     {
       const int J0 = (G.k + G.s - 1) / G.s, q0 = G.p / G.s, q = (G.n - 1 + G.p) / G.s + 1 - q0;
-      d.tiles = dgrad_channel_tiles(ctx->sm_count, G.Dg, ss, ((long long)G.B * q * q + kTileM - 1) / kTileM, G.g,
+      d.tiles = dgrad_channel_tiles(ctx->planning_sms(), G.Dg, ss, ((long long)G.B * q * q + kTileM - 1) / kTileM, G.g,
                                     (G.og * J0 * J0 + kBlockK - 1) / kBlockK);
     }
     d.ch_tile = G.Dg / d.tiles;
@@ -1543,7 +1543,7 @@ int umma_plan_create(cct_ctx* ctx, const ConvGeom& G, UmmaPlan** out) {
     // the two-CTAs-per-SM shape costs about half a round: its CTAs have their SM's tensor pipe to themselves.
     {
       const bool two_per_sm = f.n_pad <= 128;  // the shape finish_problem() will pick for this accumulator width
-      const int slots = ctx->sm_count * (two_per_sm ? 2 : 1);
+      const int slots = ctx->planning_sms() * (two_per_sm ? 2 : 1);
       const double us_per_kblock = 12.0 * (f.n_pad / 2.0) / 1900.0 * (two_per_sm ? 2.0 : 1.0);
       double best = 0.0;
       int best_kps = 0;

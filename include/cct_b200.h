@@ -247,7 +247,8 @@ int cct_pool_relu_backward(cct_ctx* ctx, const float* A, const int32_t* idx, con
  *      SGD step that reads the buffers.  cct_allreduce_sum = begin + wait.  nranks == 1 makes all of them no-ops.
  *      Between the first begin and the wait the library's persistent kernels size their grids for eight SMs fewer,
  *      the ones NCCL's CTAs occupy; cct_comm_init_rank sets NCCL_MAX_CTAS=8 in the process environment for that unless
- *      the variable is already set (a few CTAs carry a reduction at NVLink speed). ---- */
+ *      the variable is already set (a few CTAs carry a reduction at NVLink speed).  Create the communicator before the
+ *      layer plans: plans made afterwards choose their split counts and tilings for the SMs that remain. ---- */
 #define CCT_COMM_ID_BYTES 128
 typedef struct cct_comm cct_comm;
 int cct_comm_unique_id(unsigned char id[CCT_COMM_ID_BYTES]);
