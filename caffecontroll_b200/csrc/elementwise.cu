@@ -336,67 +336,104 @@ __global__ void __launch_bounds__(kSlotThreads) maxpool_bwd_slots_kernel(
   }
 }
 
-// 3x3 windows with stride 2 (the pooling layers of AlexNet / CaffeNet) without shared memory or synchronisation: one
-// thread owns a 2 x 2 block of elements (rows 2a, 2a+1; columns 2b, 2b+1).  Only the windows (a-1 .. a) x (b-1 .. b) can
-// point into it - four index / gradient pairs for four outputs, read through L1, which neighbouring threads share -
-// and each element visits its windows in (ph, pw) order like the reference's scatter:
+// 3x3 windows with stride 2 (the pooling layers of AlexNet / CaffeNet).  A block owns `group` consecutive planes: it
+// brings their pooled indices and gradients (with the P-based ReLU mask already applied) into shared memory with aligned
+// 16-byte loads, then one thread owns a 2 x 2 block of elements (rows 2a, 2a+1; columns 2b, 2b+1).  Only the windows
+// (a-1 .. a) x (b-1 .. b) can point into it - four index / gradient pairs for four outputs - and each element visits its
+// windows in (ph, pw) order like the reference's scatter:
 //   (2a, 2b): all four;  (2a, 2b+1): (a-1, b), (a, b);  (2a+1, 2b): (a, b-1), (a, b);  (2a+1, 2b+1): (a, b).
+// Reading the windows from global memory instead (each is wanted by four threads) ran at 3.7 TB/s, this at 4.9 TB/s;
+// building the result in shared memory as well, to store it in 16-byte pieces, was slower than either.
+constexpr int kPool32Threads = 256;
+constexpr int kPool32Items = 12 * kPool32Threads;  // 2 x 2 blocks a thread block takes on per group
+constexpr size_t kPool32SmemCap = 64 * 1024;
+
 template <bool RELU>
-__global__ void __launch_bounds__(256) maxpool_bwd_3x3s2_kernel(const float* __restrict__ A, const int32_t* __restrict__ idx,
-                                                                const float* __restrict__ dP, const float* __restrict__ P,
-                                                                float* __restrict__ dA, uint32_t items, int n, int m,
-                                                                int half, uint32_t inv_half) {
+__global__ void __launch_bounds__(kPool32Threads) maxpool_bwd_3x3s2_kernel(
+    const float* __restrict__ A, const int32_t* __restrict__ idx, const float* __restrict__ dP, const float* __restrict__ P,
+    float* __restrict__ dA, int planes, int n, int m, int half, uint32_t inv_half, int group, int vec_ok) {
+  extern __shared__ __align__(16) float pool32_smem[];
   pdl_wait();
   const int nn = n * n, mm = m * m;
-  for (uint32_t t = blockIdx.x * blockDim.x + threadIdx.x; t < items; t += gridDim.x * blockDim.x) {
-    const uint32_t row = fast_div(t, (uint32_t)half, inv_half);  // = plane * half + a
-    const int b = (int)(t - row * half);
-    const size_t plane = fast_div(row, (uint32_t)half, inv_half);
-    const int a = (int)(row - (uint32_t)plane * half);
-    const int32_t* ip = idx + plane * mm;
-    const float* gp = dP + plane * mm;
-    const float* pp = P ? P + plane * mm : nullptr;
-    int32_t wi[2][2];
-    float wg[2][2];
-#pragma unroll
-    for (int i = 0; i < 2; ++i)
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const int ph = a - 1 + i, pw = b - 1 + j;
-        const bool ok = ph >= 0 && ph < m && pw >= 0 && pw < m;
-        const int at = ok ? ph * m + pw : 0;
-        wi[i][j] = ok ? __ldg(ip + at) : -1;
-        float g = ok ? __ldg(gp + at) : 0.f;
-        // With the pooled tensor P given, the ReLU mask is applied here: the element a window points at holds exactly
-        // that window's maximum, so [A > 0] at the element equals [P > 0] at the window.
-        if (pp != nullptr && ok && !(__ldg(pp + at) > 0.f)) g = 0.f;
-        wg[i][j] = g;
+  const int in_pad = (group * mm + 3) & ~3;
+  int32_t* s_idx = reinterpret_cast<int32_t*>(pool32_smem);
+  float* s_g = pool32_smem + in_pad;
+  for (int g0 = blockIdx.x * group; g0 < planes; g0 += gridDim.x * group) {
+    const int cnt = min(group, planes - g0);
+    const size_t in_base = (size_t)g0 * mm;
+    const size_t out_base = (size_t)g0 * nn;
+    const int tot = cnt * mm;
+    // With the pooled tensor P given, the ReLU mask is applied here: the element a window points at holds exactly that
+    // window's maximum, so [A > 0] at the element equals [P > 0] at the window.
+    const int v = (vec_ok && (in_base & 3) == 0) ? tot >> 2 : 0;
+    const int4* i4 = reinterpret_cast<const int4*>(idx + in_base);
+    const float4* g4 = reinterpret_cast<const float4*>(dP + in_base);
+    const float4* p4 = reinterpret_cast<const float4*>(P ? P + in_base : dP + in_base);
+    for (int q = threadIdx.x; q < v; q += kPool32Threads) {
+      const int4 iv = __ldg(i4 + q);
+      float4 gv = __ldg(g4 + q);
+      if (P != nullptr) {
+        const float4 pv = __ldg(p4 + q);
+        gv.x = pv.x > 0.f ? gv.x : 0.f;
+        gv.y = pv.y > 0.f ? gv.y : 0.f;
+        gv.z = pv.z > 0.f ? gv.z : 0.f;
+        gv.w = pv.w > 0.f ? gv.w : 0.f;
       }
-    const int h0 = 2 * a, w0 = 2 * b;
-    const int e00 = h0 * n + w0, e01 = e00 + 1, e10 = e00 + n, e11 = e10 + 1;
-    float r00 = 0.f, r01 = 0.f, r10 = 0.f, r11 = 0.f;
-    r00 += wi[0][0] == e00 ? wg[0][0] : 0.f;
-    r00 += wi[0][1] == e00 ? wg[0][1] : 0.f;
-    r00 += wi[1][0] == e00 ? wg[1][0] : 0.f;
-    r00 += wi[1][1] == e00 ? wg[1][1] : 0.f;
-    r01 += wi[0][1] == e01 ? wg[0][1] : 0.f;
-    r01 += wi[1][1] == e01 ? wg[1][1] : 0.f;
-    r10 += wi[1][0] == e10 ? wg[1][0] : 0.f;
-    r10 += wi[1][1] == e10 ? wg[1][1] : 0.f;
-    r11 += wi[1][1] == e11 ? wg[1][1] : 0.f;
-    const bool wide = w0 + 1 < n, tall = h0 + 1 < n;
-    float* out = dA + plane * nn;
-    if (RELU) {
-      const float* ap = A + plane * nn;
-      r00 = __ldg(ap + e00) > 0.f ? r00 : 0.f;
-      if (wide) r01 = __ldg(ap + e01) > 0.f ? r01 : 0.f;
-      if (tall) r10 = __ldg(ap + e10) > 0.f ? r10 : 0.f;
-      if (wide && tall) r11 = __ldg(ap + e11) > 0.f ? r11 : 0.f;
+      reinterpret_cast<int4*>(s_idx)[q] = iv;
+      reinterpret_cast<float4*>(s_g)[q] = gv;
     }
-    out[e00] = r00;
-    if (wide) out[e01] = r01;
-    if (tall) out[e10] = r10;
-    if (wide && tall) out[e11] = r11;
+    for (int q = (v << 2) + threadIdx.x; q < tot; q += kPool32Threads) {
+      s_idx[q] = __ldg(idx + in_base + q);
+      const float gq = __ldg(dP + in_base + q);
+      s_g[q] = (P == nullptr || __ldg(P + in_base + q) > 0.f) ? gq : 0.f;
+    }
+    __syncthreads();
+    const uint32_t items = (uint32_t)cnt * half * half;
+    for (uint32_t t = threadIdx.x; t < items; t += kPool32Threads) {
+      const uint32_t row = fast_div(t, (uint32_t)half, inv_half);  // = plane in group * half + a
+      const int b = (int)(t - row * half);
+      const uint32_t pl = fast_div(row, (uint32_t)half, inv_half);
+      const int a = (int)(row - pl * half);
+      int32_t wi[2][2];
+      float wg[2][2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int ph = a - 1 + i, pw = b - 1 + j;
+          const bool ok = ph >= 0 && ph < m && pw >= 0 && pw < m;
+          const int at = ok ? (int)pl * mm + ph * m + pw : 0;
+          wi[i][j] = ok ? s_idx[at] : -1;
+          wg[i][j] = ok ? s_g[at] : 0.f;
+        }
+      const int h0 = 2 * a, w0 = 2 * b;
+      const int e00 = h0 * n + w0, e01 = e00 + 1, e10 = e00 + n, e11 = e10 + 1;
+      float r00 = 0.f, r01 = 0.f, r10 = 0.f, r11 = 0.f;
+      r00 += wi[0][0] == e00 ? wg[0][0] : 0.f;
+      r00 += wi[0][1] == e00 ? wg[0][1] : 0.f;
+      r00 += wi[1][0] == e00 ? wg[1][0] : 0.f;
+      r00 += wi[1][1] == e00 ? wg[1][1] : 0.f;
+      r01 += wi[0][1] == e01 ? wg[0][1] : 0.f;
+      r01 += wi[1][1] == e01 ? wg[1][1] : 0.f;
+      r10 += wi[1][0] == e10 ? wg[1][0] : 0.f;
+      r10 += wi[1][1] == e10 ? wg[1][1] : 0.f;
+      r11 += wi[1][1] == e11 ? wg[1][1] : 0.f;
+      const bool wide = w0 + 1 < n, tall = h0 + 1 < n;
+      const size_t plane_at = out_base + (size_t)pl * nn;
+      float* out = dA + plane_at;
+      if (RELU) {
+        const float* ap = A + plane_at;
+        r00 = __ldg(ap + e00) > 0.f ? r00 : 0.f;
+        if (wide) r01 = __ldg(ap + e01) > 0.f ? r01 : 0.f;
+        if (tall) r10 = __ldg(ap + e10) > 0.f ? r10 : 0.f;
+        if (wide && tall) r11 = __ldg(ap + e11) > 0.f ? r11 : 0.f;
+      }
+      out[e00] = r00;
+      if (wide) out[e01] = r01;
+      if (tall) out[e10] = r10;
+      if (wide && tall) out[e11] = r11;
+    }
+    __syncthreads();
   }
 }
 
@@ -407,12 +444,20 @@ int launch_maxpool_bwd(cct_ctx* ctx, const float* A, const int32_t* idx, const f
   const uint32_t inv_s = fast_div_magic((uint64_t)n, (uint32_t)s);
   const int taps = (k + s - 1) / s;
   const int half = (n + 1) / 2;
-  if (k == 3 && s == 2 && (size_t)planes * half * half < (1ull << 31)) {
-    const size_t items = (size_t)planes * half * half;
-    const int blocks = (int)std::max<size_t>(1, std::min<size_t>((items + 255) / 256, (size_t)ctx->sm_count * 16));
-    launch_pdl(maxpool_bwd_3x3s2_kernel<RELU>, dim3(blocks), dim3(256), 0, ctx->stream, A, idx, dP, P, dA, (uint32_t)items, n, m, half,
-                                                                    fast_div_magic(items, (uint32_t)half));
-    return CCT_OK;
+  if (k == 3 && s == 2) {
+    // Planes per block: a multiple of four, so that every group starts on a 16-byte boundary of the pooled tensors.
+    const int group = std::max(4, (kPool32Items / (half * half) + 3) & ~3);
+    const size_t smem = (size_t)2 * ((group * m * m + 3) & ~3) * 4;
+    if (smem <= kPool32SmemCap) {
+      const int vec_ok = ((reinterpret_cast<uintptr_t>(idx) | reinterpret_cast<uintptr_t>(dP) |
+                           reinterpret_cast<uintptr_t>(P)) & 15) == 0;
+      if (smem > 48 * 1024)
+        CCT_CUDA(ctx, cudaFuncSetAttribute(maxpool_bwd_3x3s2_kernel<RELU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      const int blocks = std::max(1, std::min((planes + group - 1) / group, ctx->sm_count * 64));
+      launch_pdl(maxpool_bwd_3x3s2_kernel<RELU>, dim3(blocks), dim3(kPool32Threads), smem, ctx->stream, A, idx, dP, P, dA,
+                 planes, n, m, half, fast_div_magic((uint64_t)group * half * half, (uint32_t)half), group, vec_ok);
+      return CCT_OK;
+    }
   }
   constexpr int kSlotSmemCap = 56 * 1024;  // four blocks per SM
   if (taps <= 2 && m * m <= kSlotThreads * kSlotWin && (size_t)n * n * 16 + (size_t)n * 4 <= kSlotSmemCap) {

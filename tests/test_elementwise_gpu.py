@@ -16,9 +16,10 @@ def _cube(ctx, arr):
     return LogicalCube.from_numpy(ctx, arr)
 
 
-# the last two have three and five windows per axis over an element: the kernels for overlapping pooling beyond 2x2
+# (2, 2, 9, 3, 1) and (1, 2, 11, 5, 1) have three and five windows per axis over an element: the kernels for overlapping
+# pooling beyond 2x2; the last two are 3x3 stride-2 cases with several plane groups and a ragged last one, and an even size
 @pytest.mark.parametrize("shape", [(2, 3, 13, 3, 2), (2, 3, 10, 4, 2), (1, 2, 27, 3, 2), (3, 1, 7, 2, 1), (1, 1, 9, 3, 3),
-                                   (2, 2, 9, 3, 1), (1, 2, 11, 5, 1)])
+                                   (2, 2, 9, 3, 1), (1, 2, 11, 5, 1), (5, 7, 55, 3, 2), (2, 5, 12, 3, 2)])
 def test_pool_and_relu_masks_match_oracle_bitwise(ctx, port, shape):
     from caffecontroll_b200 import capi
     B, D, n, k, s = shape
@@ -48,6 +49,31 @@ def test_pool_and_relu_masks_match_oracle_bitwise(ctx, port, shape):
     assert np.array_equal(cdR.download(), port.relu_backward(A, dAr))
     assert np.array_equal(cdA2.download(), port.relu_backward(A, dAr))
     for c in (cA, cdP, cY, cidx, cdA, cdA2, cR, cdR):
+        c.free()
+
+
+def test_pool_backward_takes_pointers_that_are_not_16_byte_aligned(ctx, port):
+    """The 3x3 stride-2 kernel reads the pooled tensors in 16-byte pieces only where the caller's pointers allow it."""
+    from caffecontroll_b200 import capi
+    B, D, n, k, s = 3, 5, 27, 3, 2
+    m = (n - k) // s + 1
+    rng = np.random.default_rng(5)
+    A = rng.standard_normal((B, D, n, n), dtype=np.float32)
+    dP = rng.standard_normal((B, D, m, m), dtype=np.float32)
+    _, idxr = port.maxpool_forward(A, k, s)
+    dAr = port.maxpool_backward(dP, idxr, n)
+    pad = lambda a: np.concatenate([np.zeros(1, a.dtype), a.ravel()]).reshape(1, 1, 1, -1)
+    cA, cdP, cidx = _cube(ctx, A), _cube(ctx, pad(dP)), _cube(ctx, pad(idxr.astype(np.int32)))
+    cdA = LogicalCube(ctx, n, n, D, B)
+    lib, vp = ctx.lib, C.c_void_p
+    capi.check(lib.cct_maxpool_backward(ctx.h, vp(cdP.ptr + 4), vp(cidx.ptr + 4), vp(cdA.ptr), B * D, n, k, s), "pool bwd", ctx.h)
+    ctx.sync()
+    assert np.array_equal(cdA.download(), dAr)
+    capi.check(lib.cct_pool_relu_backward(ctx.h, vp(cA.ptr), vp(cidx.ptr + 4), vp(cdP.ptr + 4), vp(cdA.ptr), B * D, n, k, s),
+               "pool+relu bwd", ctx.h)
+    ctx.sync()
+    assert np.array_equal(cdA.download(), port.relu_backward(A, dAr))
+    for c in (cA, cdP, cidx, cdA):
         c.free()
 
 
