@@ -694,8 +694,9 @@ def run_caffenet(args, rank, world, local_rank):
         if t == "Pooling":
             hbm_passes[name + " forward"] = (4.0 * n_in + 8.0 * n_out, fwd_ms[i])
         elif t == "LRN":
-            hbm_passes[name + " forward"] = (12.0 * n_in, fwd_ms[i])
-            hbm_passes[name + " backward"] = (20.0 * n_in, bwd_ms[i])
+            kept = 4.0 if br.denoms is not None else 0.0  # the denominator cube: written forward, read backward
+            hbm_passes[name + " forward"] = ((8.0 + kept) * n_in, fwd_ms[i])
+            hbm_passes[name + " backward"] = ((12.0 + kept) * n_in, bwd_ms[i])  # X, dY (, scale) in, dX out
     hbm_table = {k: {"ms": float(ms), "bytes": b, "achieved_gbs": b / ms / 1e6, "frac": b / ms / 1e6 / hbm}
                  for k, (b, ms) in hbm_passes.items() if ms > 0}
 

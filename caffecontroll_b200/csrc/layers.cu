@@ -25,6 +25,11 @@ inline int ew_grid(cct_ctx* ctx, size_t work, int threads) {
 constexpr int kLrnChunk = 16;
 constexpr int kLrnBwdChunk = 8;
 
+// One short-lived block of 128 threads per 128 items (the kernels' loops then run once): a thread's item is some sixty
+// loads and stores long, and with a grid of a few blocks per SM looping over the items the last round left a third of
+// the SMs idle (5 - 7 % of the kernel).
+inline int lrn_grid(size_t items) { return (int)std::max<size_t>(1, std::min<size_t>((items + 127) / 128, 1u << 30)); }
+
 // s^(-beta) for s >= 1: exp2(-beta log2 s) on the special-function units (ex2.approx / lg2.approx, each within ~2 ulp:
 // relative error below 1e-6 for the scales and exponents of a normalisation layer, two orders under the path's tolerance;
 // powf costs some thirty instructions and made these kernels compute-bound).
@@ -57,7 +62,7 @@ __global__ void __launch_bounds__(128) lrn_fwd_kernel(const float* __restrict__ 
         for (int i = 0; i < LOCAL; ++i) sum += x[j + i] * x[j + i];
         const float s = alpha_over_size * sum + 1.f;
         const size_t at = base + (size_t)d * plane;
-        scale[at] = s;
+        if (scale != nullptr) scale[at] = s;
         Y[at] = x[j + W] * inv_pow(s, beta);
       }
     }
@@ -82,7 +87,7 @@ __global__ void lrn_fwd_generic_kernel(const float* __restrict__ X, float* __res
         sum += v * v;
       }
       const float s = alpha_over_size * sum + 1.f;
-      scale[base + (size_t)d * plane] = s;
+      if (scale != nullptr) scale[base + (size_t)d * plane] = s;
       Y[base + (size_t)d * plane] = X[base + (size_t)d * plane] / powf(s, beta);
     }
   }
@@ -91,18 +96,20 @@ __global__ void lrn_fwd_generic_kernel(const float* __restrict__ X, float* __res
 // LRNBridge::backward (src/kernels/lrn.hxx:134-180) as a gather: the reference scatters, for every output channel o,
 //   dX[c] += dY[o] * ([c == o] / scale[o]^beta - 2 beta (alpha / size) X[o] X[c] / scale[o]^(beta + 1))   for |c - o| <= w;
 // collected per input channel c:
-//   dX[c] = dY[c] / scale[c]^beta - 2 beta (alpha / size) X[c] * sum_{|o - c| <= w} dY[o] Y[o] / scale[o]
-// (Y[o] = X[o] / scale[o]^beta, so no power is needed inside the window, and dY[c] / scale[c]^beta = dY[c] Y[c] / X[c]
-// needs none either - but X may be 0, so the power is taken once per element).  Same decomposition as the forward
-// kernel, the window terms t[o] = dY[o] Y[o] / scale[o] held in registers.  16 B read + 4 B written per element.
-template <int LOCAL>
-__global__ void __launch_bounds__(128) lrn_bwd_kernel(const float* __restrict__ X, const float* __restrict__ Y,
-                                                      const float* __restrict__ scale, const float* __restrict__ dY,
-                                                      float* __restrict__ dX, size_t items, int D, int chunks, int plane,
-                                                      float alpha_over_size, float beta) {
+//   dX[c] = dY[c] / scale[c]^beta - 2 beta (alpha / size) X[c] * sum_{|o - c| <= w} dY[o] Y[o] / scale[o].
+// Same decomposition as the forward kernel, the window terms t[o] = dY[o] Y[o] / scale[o] held in registers.  Y is not
+// read: Y[o] = X[o] * scale[o]^-beta is formed again with the forward kernel's own expression (one power per element of
+// the chunk and its halo, on the special-function units), which costs less than a fourth stream from HBM.  HAVE_SCALE =
+// false forms the scales again as well, from X with a halo twice as wide and the forward kernel's summation order, for
+// callers that did not keep them: 8 B read + 4 B written per element against 12 + 4 with the scale cube.
+template <int LOCAL, bool HAVE_SCALE>
+__global__ void __launch_bounds__(128) lrn_bwd_kernel(const float* __restrict__ X, const float* __restrict__ scale,
+                                                      const float* __restrict__ dY, float* __restrict__ dX, size_t items,
+                                                      int D, int chunks, int plane, float alpha_over_size, float beta) {
   pdl_wait();
-  constexpr int kLrnChunk = kLrnBwdChunk;  // four arrays are read here: a shorter chunk keeps the registers in check
+  constexpr int kLrnChunk = kLrnBwdChunk;  // several arrays are read here: a shorter chunk keeps the registers in check
   constexpr int W = LOCAL / 2, SPAN = kLrnChunk + 2 * W;
+  constexpr int XW = HAVE_SCALE ? 0 : W, XSPAN = SPAN + 2 * XW;  // channels of X a thread reads: d0 - W - XW ...
   const float coef = 2.f * beta * alpha_over_size;
   for (size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x; t < items; t += (size_t)gridDim.x * blockDim.x) {
     const size_t bc = t / plane, p = t - bc * plane;
@@ -110,27 +117,42 @@ __global__ void __launch_bounds__(128) lrn_bwd_kernel(const float* __restrict__ 
     const int d0 = (int)(bc - b * chunks) * kLrnChunk;
     const size_t base = b * (size_t)D * plane + p;
     // every load of the chunk and its halo is issued before the first use
-    float gy[SPAN], yy[SPAN], sc[SPAN], xx[kLrnChunk];
+    float gy[SPAN], sc[SPAN], xx[XSPAN];
 #pragma unroll
     for (int i = 0; i < SPAN; ++i) {
       const int c = d0 + i - W;
       const bool in = c >= 0 && c < D;
       const size_t at = base + (size_t)(in ? c : 0) * plane;
       gy[i] = in ? __ldg(dY + at) : 0.f;
-      yy[i] = in ? __ldg(Y + at) : 0.f;
-      sc[i] = in ? __ldg(scale + at) : 1.f;
+      if (HAVE_SCALE) sc[i] = in ? __ldg(scale + at) : 1.f;
     }
 #pragma unroll
-    for (int j = 0; j < kLrnChunk; ++j) xx[j] = d0 + j < D ? __ldg(X + base + (size_t)(d0 + j) * plane) : 0.f;
+    for (int i = 0; i < XSPAN; ++i) {
+      const int c = d0 + i - W - XW;
+      xx[i] = (c >= 0 && c < D) ? __ldg(X + base + (size_t)c * plane) : 0.f;
+    }
+    if (!HAVE_SCALE) {
 #pragma unroll
-    for (int i = 0; i < SPAN; ++i) yy[i] = __fdividef(gy[i] * yy[i], sc[i]);  // the window terms
+      for (int i = 0; i < SPAN; ++i) {
+        float sum = 0.f;
+#pragma unroll
+        for (int q = 0; q < LOCAL; ++q) sum += xx[i + q] * xx[i + q];
+        sc[i] = alpha_over_size * sum + 1.f;
+      }
+    }
+    float pw[SPAN], tt[SPAN];
+#pragma unroll
+    for (int i = 0; i < SPAN; ++i) {
+      pw[i] = inv_pow(sc[i], beta);
+      tt[i] = __fdividef(gy[i] * (xx[i + XW] * pw[i]), sc[i]);  // the window terms; xx * pw is Y as the forward pass wrote it
+    }
 #pragma unroll
     for (int j = 0; j < kLrnChunk; ++j) {
       if (d0 + j < D) {
         float acc = 0.f;
 #pragma unroll
-        for (int i = 0; i < LOCAL; ++i) acc += yy[j + i];
-        dX[base + (size_t)(d0 + j) * plane] = gy[j + W] * inv_pow(sc[j + W], beta) - coef * xx[j] * acc;
+        for (int i = 0; i < LOCAL; ++i) acc += tt[j + i];
+        dX[base + (size_t)(d0 + j) * plane] = gy[j + W] * pw[j + W] - coef * xx[j + W + XW] * acc;
       }
     }
   }
@@ -343,12 +365,12 @@ extern "C" {
 
 int cct_lrn_forward(cct_ctx* ctx, const float* X, float* Y, float* scale, int batch, int depth, int plane, int local_size,
                     float alpha, float beta) {
-  if (!ctx || !X || !Y || !scale || batch <= 0 || depth <= 0 || plane <= 0 || local_size <= 0 || !(local_size & 1))
+  if (!ctx || !X || !Y || batch <= 0 || depth <= 0 || plane <= 0 || local_size <= 0 || !(local_size & 1))
     return CCT_ERR_INVALID;
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
   const int chunks = (depth + kLrnChunk - 1) / kLrnChunk;
   const size_t items = (size_t)batch * chunks * plane;
-  const int grid = ew_grid(ctx, items, 128);
+  const int grid = lrn_grid(items);
   const float aos = alpha / (float)local_size;
   if (local_size == 5)
     launch_pdl(lrn_fwd_kernel<5>, dim3(grid), dim3(128), 0, ctx->stream, X, Y, scale, items, depth, chunks, plane, aos, beta);
@@ -362,23 +384,30 @@ int cct_lrn_forward(cct_ctx* ctx, const float* X, float* Y, float* scale, int ba
 
 int cct_lrn_backward(cct_ctx* ctx, const float* X, const float* Y, const float* scale, const float* dY, float* dX,
                      int batch, int depth, int plane, int local_size, float alpha, float beta) {
-  if (!ctx || !X || !Y || !scale || !dY || !dX || batch <= 0 || depth <= 0 || plane <= 0 || local_size <= 0 ||
-      !(local_size & 1))
+  if (!ctx || !X || !dY || !dX || batch <= 0 || depth <= 0 || plane <= 0 || local_size <= 0 || !(local_size & 1))
     return CCT_ERR_INVALID;
   CCT_CUDA(ctx, cudaSetDevice(ctx->device));
   const bool fixed = local_size == 5 || local_size == 3;
+  if (!fixed && (!Y || !scale)) {
+    ctx->last_error = "windows other than 3 and 5 channels need the output and the scale cube of the forward pass";
+    return CCT_ERR_UNSUPPORTED;
+  }
   const int chunk = fixed ? kLrnBwdChunk : kLrnChunk;
   const int chunks = (depth + chunk - 1) / chunk;
   const size_t items = (size_t)batch * chunks * plane;
-  const int grid = ew_grid(ctx, items, 128);
+  const int grid = lrn_grid(items);
   const float aos = alpha / (float)local_size;
-  if (local_size == 5)
-    launch_pdl(lrn_bwd_kernel<5>, dim3(grid), dim3(128), 0, ctx->stream, X, Y, scale, dY, dX, items, depth, chunks, plane, aos, beta);
-  else if (local_size == 3)
-    launch_pdl(lrn_bwd_kernel<3>, dim3(grid), dim3(128), 0, ctx->stream, X, Y, scale, dY, dX, items, depth, chunks, plane, aos, beta);
-  else
+  auto go = [&](auto kernel) {
+    launch_pdl(kernel, dim3(grid), dim3(128), 0, ctx->stream, X, scale, dY, dX, items, depth, chunks, plane, aos, beta);
+  };
+  if (local_size == 5) {
+    if (scale) go(lrn_bwd_kernel<5, true>); else go(lrn_bwd_kernel<5, false>);
+  } else if (local_size == 3) {
+    if (scale) go(lrn_bwd_kernel<3, true>); else go(lrn_bwd_kernel<3, false>);
+  } else {
     launch_pdl(lrn_bwd_generic_kernel, dim3(grid), dim3(128), 0, ctx->stream, X, Y, scale, dY, dX, items, depth, chunks, plane, local_size, aos,
                                                         beta);
+  }
   CCT_CHECK_LAUNCH(ctx);
   return CCT_OK;
 }

@@ -80,19 +80,23 @@ class MaxPoolingBridge(_Bridge):
 
 
 class LRNBridge(_Bridge):
-    """src/bridges/LRNBridge_impl.hxx:46-190 (across channels)."""
+    """src/bridges/LRNBridge_impl.hxx:46-190 (across channels).  The reference's bridge keeps a cube of denominators
+    (`denoms`) from its forward pass for its backward pass; here that cube is optional (keep_denoms): for windows of 3 and
+    5 channels the backward kernel forms the denominators again from the input, which costs less than writing and
+    reading them (8 B per element of HBM traffic in each pass).  Other windows always keep it."""
 
-    def __init__(self, p_input_layer, p_output_layer, local_size=5, alpha=1.0, beta=0.75, ctx=None):
+    def __init__(self, p_input_layer, p_output_layer, local_size=5, alpha=1.0, beta=0.75, ctx=None, keep_denoms=False):
         super().__init__(p_input_layer, p_output_layer, ctx)
         if local_size % 2 != 1:
             raise ValueError("local_size must be odd")
         self.local_size, self.alpha, self.beta = local_size, alpha, beta
-        self.denoms = LogicalCube(self.ctx, self.iR, self.iC, self.iD, self.iB)
+        keep = keep_denoms or local_size not in (3, 5)
+        self.denoms = LogicalCube(self.ctx, self.iR, self.iC, self.iD, self.iB) if keep else None
 
     def forward(self):
         x, y = self.p_input_layer.p_data_cube, self.p_output_layer.p_data_cube
-        capi.check(self.lib.cct_lrn_forward(self.ctx.h, _vp(x.ptr), _vp(y.ptr), _vp(self.denoms.ptr), self.iB, self.iD,
-                                            self.iR * self.iC, self.local_size, self.alpha, self.beta),
+        capi.check(self.lib.cct_lrn_forward(self.ctx.h, _vp(x.ptr), _vp(y.ptr), _vp(self.denoms.ptr if self.denoms else None),
+                                            self.iB, self.iD, self.iR * self.iC, self.local_size, self.alpha, self.beta),
                    "cct_lrn_forward", self.ctx.h)
 
     def backward(self):
@@ -100,12 +104,13 @@ class LRNBridge(_Bridge):
             return
         x, y = self.p_input_layer.p_data_cube, self.p_output_layer.p_data_cube
         dy, dx = self.p_output_layer.p_gradient_cube, self.p_input_layer.p_gradient_cube
-        capi.check(self.lib.cct_lrn_backward(self.ctx.h, _vp(x.ptr), _vp(y.ptr), _vp(self.denoms.ptr), _vp(dy.ptr),
-                                             _vp(dx.ptr), self.iB, self.iD, self.iR * self.iC, self.local_size,
+        capi.check(self.lib.cct_lrn_backward(self.ctx.h, _vp(x.ptr), _vp(y.ptr), _vp(self.denoms.ptr if self.denoms else None),
+                                             _vp(dy.ptr), _vp(dx.ptr), self.iB, self.iD, self.iR * self.iC, self.local_size,
                                              self.alpha, self.beta), "cct_lrn_backward", self.ctx.h)
 
     def close(self):
-        self.denoms.free()
+        if self.denoms is not None:
+            self.denoms.free()
 
 
 class DropoutBridge(_Bridge):

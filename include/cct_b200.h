@@ -263,7 +263,10 @@ int cct_allreduce_sum(cct_comm* comm, float* buf, size_t count);
 /* LRNBridge (across channels; src/bridges/LRNBridge_impl.hxx:46-190, src/kernels/lrn.hxx:38-180, exact pow as in the
  * reference's test build): scale = 1 + (alpha / local_size) * sum over the local_size channels around d of X^2,
  * Y = X / scale^beta.  X, Y, scale, dY, dX are [batch][depth][plane] with plane = R * C; local_size is odd.
- * The backward pass needs X, Y and scale of the forward pass. */
+ * `scale` is the bridge's denominator cube.  It may be NULL in both calls: the forward pass then does not store it and
+ * the backward pass forms it again from X (windows of 3 and 5 channels; other windows need Y and scale of the forward
+ * pass and answer CCT_ERR_UNSUPPORTED without them).  For windows of 3 and 5 channels the backward pass does not read
+ * Y (it may be NULL): Y = X / scale^beta is formed again as the forward pass formed it. */
 int cct_lrn_forward(cct_ctx* ctx, const float* X, float* Y, float* scale, int batch, int depth, int plane, int local_size,
                     float alpha, float beta);
 int cct_lrn_backward(cct_ctx* ctx, const float* X, const float* Y, const float* scale, const float* dY, float* dX,

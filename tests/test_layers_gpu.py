@@ -41,7 +41,18 @@ def test_lrn_forward_backward(ctx, shape):
         Yb, dXb, _ = ref.lrn(X, local, alpha, beta, dY=dY)
         assert_close(cY.download(), Yb, "LRN Y vs the reference bridge")
         assert_close(cdX.download(), dXb, "LRN dX vs the reference bridge")
-    for c in (cX, cdY, cY, cS, cdX):
+    # without the denominator cube: the forward pass does not store it, the backward pass forms it again from X
+    cY2, cdX2 = LogicalCube(ctx, n, n, D, B), LogicalCube(ctx, n, n, D, B)
+    capi.check(lib.cct_lrn_forward(ctx.h, vp(cX.ptr), vp(cY2.ptr), vp(None), B, D, n * n, local, alpha, beta), "lrn fwd", ctx.h)
+    rc = lib.cct_lrn_backward(ctx.h, vp(cX.ptr), vp(None), vp(None), vp(cdY.ptr), vp(cdX2.ptr), B, D, n * n, local, alpha, beta)
+    ctx.sync()
+    assert np.array_equal(cY2.download(), cY.download())
+    if local in (3, 5):
+        capi.check(rc, "lrn bwd without scale", ctx.h)
+        assert np.array_equal(cdX2.download(), cdX.download())
+    else:
+        assert rc == capi.CCT_ERR_UNSUPPORTED
+    for c in (cX, cdY, cY, cS, cdX, cY2, cdX2):
         c.free()
 
 
