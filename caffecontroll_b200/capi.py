@@ -20,7 +20,7 @@ _ERR_NAMES = {1: "CCT_ERR_INVALID", 2: "CCT_ERR_CUDA", 3: "CCT_ERR_NOMEM", 4: "C
 EXPORTS = [
     "cct_ctx_create", "cct_ctx_create_on_stream", "cct_ctx_destroy", "cct_sync", "cct_last_error_string",
     "cct_device_count", "cct_malloc", "cct_free", "cct_malloc_host", "cct_free_host", "cct_memcpy_h2d",
-    "cct_memcpy_d2h", "cct_memcpy_d2d", "cct_memset", "cct_fill_f32", "cct_fill_random", "cct_conv_plan_create",
+    "cct_memcpy_d2h", "cct_memcpy_d2d", "cct_memcpy2d_d2d", "cct_memset", "cct_fill_f32", "cct_fill_random", "cct_conv_plan_create",
     "cct_conv_plan_destroy", "cct_conv_out_size", "cct_conv_plan_algo", "cct_conv_plan_workspace_bytes",
     "cct_conv_plan_enable_timing", "cct_conv_plan_last_timings", "cct_conv_forward", "cct_conv_backward", "cct_conv_backward_fused",
     "cct_conv_plan_reserve_fusion", "cct_selftest_bounded_wait", "cct_conv_forward_host", "cct_conv_backward_host", "cct_conv_weight_grad_noalloc",
@@ -29,7 +29,7 @@ EXPORTS = [
     "cct_fc_plan_create", "cct_fc_plan_destroy", "cct_fc_plan_workspace_bytes", "cct_fc_forward", "cct_fc_backward",
     "cct_fc_plan_enable_timing", "cct_fc_plan_last_timings",
     "cct_comm_unique_id", "cct_comm_init_rank", "cct_comm_destroy", "cct_comm_size", "cct_allreduce_sum_begin",
-    "cct_comm_wait", "cct_allreduce_sum",
+    "cct_comm_wait", "cct_allreduce_sum", "cct_allgather", "cct_reduce_scatter_sum",
     "cct_lrn_forward", "cct_lrn_backward", "cct_dropout_apply", "cct_dropout_mask", "cct_softmax_loss_forward", "cct_softmax_loss_backward",
 ]
 
@@ -78,6 +78,7 @@ def load():
         "cct_memcpy_h2d": [_vp, _vp, _vp, sz],
         "cct_memcpy_d2h": [_vp, _vp, _vp, sz],
         "cct_memcpy_d2d": [_vp, _vp, _vp, sz],
+        "cct_memcpy2d_d2d": [_vp, _vp, sz, _vp, sz, sz, sz],
         "cct_memset": [_vp, _vp, i, sz],
         "cct_fill_f32": [_vp, _vp, sz, f],
         "cct_fill_random": [_vp, _vp, sz, i, f, f, C.c_long],
@@ -111,6 +112,8 @@ def load():
         "cct_allreduce_sum_begin": [_vp, _vp, sz],
         "cct_comm_wait": [_vp],
         "cct_allreduce_sum": [_vp, _vp, sz],
+        "cct_allgather": [_vp, _vp, _vp, sz],
+        "cct_reduce_scatter_sum": [_vp, _vp, _vp, sz],
         "cct_lrn_forward": [_vp, _vp, _vp, _vp, i, i, i, i, f, f],
         "cct_lrn_backward": [_vp, _vp, _vp, _vp, _vp, _vp, i, i, i, i, f, f],
         "cct_dropout_apply": [_vp, _vp, _vp, f, _vp, sz],

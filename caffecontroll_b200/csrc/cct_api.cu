@@ -241,6 +241,16 @@ int cct_memcpy_d2d(cct_ctx* ctx, void* dst, const void* src, size_t bytes) {
   return copy_common(ctx, dst, src, bytes, cudaMemcpyDeviceToDevice);
 }
 
+int cct_memcpy2d_d2d(cct_ctx* ctx, void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes,
+                     size_t rows) {
+  if (!ctx || ((!dst || !src) && width_bytes && rows) || dst_pitch < width_bytes || src_pitch < width_bytes)
+    return CCT_ERR_INVALID;
+  if (!width_bytes || !rows) return CCT_OK;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  CCT_CUDA(ctx, cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows, cudaMemcpyDeviceToDevice, ctx->stream));
+  return CCT_OK;
+}
+
 int cct_memset(cct_ctx* ctx, void* dptr, int byte_value, size_t bytes) {
   if (!ctx || (!dptr && bytes)) return CCT_ERR_INVALID;
   if (!bytes) return CCT_OK;

@@ -27,6 +27,8 @@ struct NcclApi {
   ncclResult_t (*GetUniqueId)(NcclUniqueId*) = nullptr;
   ncclResult_t (*CommInitRank)(ncclComm_t*, int, NcclUniqueId, int) = nullptr;
   ncclResult_t (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*AllGather)(const void*, void*, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*ReduceScatter)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
   ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
   ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t*) = nullptr;
   const char* (*GetErrorString)(ncclResult_t) = nullptr;
@@ -56,6 +58,9 @@ NcclApi* nccl_api() {
   api.GetUniqueId = (ncclResult_t(*)(NcclUniqueId*))sym("ncclGetUniqueId");
   api.CommInitRank = (ncclResult_t(*)(ncclComm_t*, int, NcclUniqueId, int))sym("ncclCommInitRank");
   api.AllReduce = (ncclResult_t(*)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t))sym("ncclAllReduce");
+  api.AllGather = (ncclResult_t(*)(const void*, void*, size_t, int, ncclComm_t, cudaStream_t))sym("ncclAllGather");
+  api.ReduceScatter =
+      (ncclResult_t(*)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t))sym("ncclReduceScatter");
   api.CommDestroy = (ncclResult_t(*)(ncclComm_t))sym("ncclCommDestroy");
   api.CommGetAsyncError = (ncclResult_t(*)(ncclComm_t, ncclResult_t*))sym("ncclCommGetAsyncError");
   api.GetErrorString = (const char* (*)(ncclResult_t))sym("ncclGetErrorString");
@@ -198,6 +203,40 @@ int cct_comm_wait(cct_comm* c) {
 int cct_allreduce_sum(cct_comm* c, float* buf, size_t count) {
   const int rc = cct_allreduce_sum_begin(c, buf, count);
   return rc != CCT_OK ? rc : cct_comm_wait(c);
+}
+
+// The two exchanges of a model-parallel fully connected layer (the split and concat bridges DeepNet puts around one,
+// src/DeepNet.h:1213-1357): every rank's block to every rank, and the sum over ranks of the block a rank owns.  Both
+// are ordered behind the work queued on the context's stream, and the context's stream behind them.
+static int exchange(cct_comm* c, const float* send, float* recv, size_t count, bool gather) {
+  if (!c || ((!send || !recv) && count)) return CCT_ERR_INVALID;
+  cct_ctx* ctx = c->ctx;
+  if (count == 0) return CCT_OK;
+  CCT_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (c->nranks == 1) {
+    if (send != recv) CCT_CUDA(ctx, cudaMemcpyAsync(recv, send, count * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+    return CCT_OK;
+  }
+  NcclApi* api = nccl_api();
+  if (!api) return CCT_ERR_UNSUPPORTED;
+  CCT_CUDA(ctx, cudaEventRecord(c->ready, ctx->stream));
+  CCT_CUDA(ctx, cudaStreamWaitEvent(c->stream, c->ready, 0));
+  const ncclResult_t r = gather ? api->AllGather(send, recv, count, kNcclFloat, c->comm, c->stream)
+                                : api->ReduceScatter(send, recv, count, kNcclFloat, kNcclSum, c->comm, c->stream);
+  if (r != 0) {
+    ctx->last_error = std::string(gather ? "ncclAllGather: " : "ncclReduceScatter: ") + api->GetErrorString(r);
+    return CCT_ERR_CUDA;
+  }
+  c->pending = true;
+  return cct_comm_wait(c);
+}
+
+int cct_allgather(cct_comm* c, const float* send, float* recv, size_t count_per_rank) {
+  return exchange(c, send, recv, count_per_rank, true);
+}
+
+int cct_reduce_scatter_sum(cct_comm* c, const float* send, float* recv, size_t count_per_rank) {
+  return exchange(c, send, recv, count_per_rank, false);
 }
 
 }  // extern "C"

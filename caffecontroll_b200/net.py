@@ -15,7 +15,8 @@ import numpy as np
 from . import capi
 from .bridge import ConvolutionBridge, FullyConnectedBridge, Layer, LogicalCube
 from .layers import DropoutBridge, LRNBridge, MaxPoolingBridge, ReLUBridge, SoftmaxLossBridge
-from .parallel import DeviceOps, ParallelizedBridge, SolverParameter
+from .parallel import (DeviceOps, ModelParallelFullyConnectedBridge, ModelParallelizedBridge, ParallelizedBridge,
+                       SolverParameter, model_parallel_gpus)
 
 # ------------------------------------------------------------------------------------- protobuf text format
 
@@ -178,7 +179,9 @@ class Net:
     """
 
     def __init__(self, ctx, net_param, solver, batch, input_shape=None, ops=None, fuse=True, loss_batch=None,
-                 algo=capi.ALGO_AUTO, phase="TRAIN"):
+                 algo=capi.ALGO_AUTO, phase="TRAIN", model_parallel=()):
+        """model_parallel: names of InnerProduct layers to split over all ranks by output depth, beside those whose
+        placement fields (gpu_N_depth_proportion) ask for it - the fields only reach four GPUs."""
         self.ctx, self.solver, self.batch = ctx, solver, batch
         self.ops = ops or DeviceOps(ctx)
         self.blobs, self.bridges, self.names, self.types = {}, [], [], []
@@ -225,10 +228,34 @@ class Net:
                 ip = layer.msg("inner_product_param")
                 o = int(ip.get1("num_output"))
                 dst = self._top(tops[0], bottoms[0], 1, 1, o)
-                br = FullyConnectedBridge(src, dst, bool(ip.get1("bias_term", True)), algo, ctx)
-                _fill(ctx, br.p_model_cube, ip.msg("weight_filler"), seed, o)
-                if br.bias_term:
-                    _fill(ctx, br.p_bias_cube, ip.msg("bias_filler"), seed, 1)
+                comm = getattr(self.ops, "comm", None)
+                shares = [float(layer.get1("gpu_%d_depth_proportion" % g, 0.0)) for g in range(4)]
+                gpus = model_parallel_gpus(shares, o)  # src/DeepNet.h:728-790
+                if gpus and (comm is None or comm.nranks != len(gpus)):
+                    raise ValueError("layer %r asks for model parallelism over %d GPUs; the job has %d rank(s)" %
+                                     (name, len(gpus), comm.nranks if comm is not None else 1))
+                if name in model_parallel and (comm is None or comm.nranks < 2):
+                    raise ValueError("layer %r: model parallelism needs a communicator of two or more ranks" % name)
+                if gpus or name in model_parallel:
+                    # src/DeepNet.h:1213-1357.  The slices are cut from the matrix the fillers give the whole layer, so
+                    # the net starts from the same parameters as its data-parallel form with the same seed (the
+                    # reference fills every slice bridge from the same seed, which makes the slices copies of each other).
+                    br = ModelParallelFullyConnectedBridge(src, dst, comm, bool(ip.get1("bias_term", True)), algo, ctx)
+                    whole = LogicalCube(ctx, x.R, x.C, x.D, o)
+                    _fill(ctx, whole, ip.msg("weight_filler"), seed, o)
+                    n = br.p_model_cube.n_elements
+                    self.ops.copy(br.p_model_cube.ptr, whole.ptr + 4 * comm.rank * n, n)
+                    whole.free()
+                    if br.bias_term:
+                        whole = LogicalCube(ctx, 1, 1, o, 1)
+                        _fill(ctx, whole, ip.msg("bias_filler"), seed, 1)
+                        self.ops.copy(br.p_bias_cube.ptr, whole.ptr + 4 * comm.rank * br.slice_depth, br.slice_depth)
+                        whole.free()
+                else:
+                    br = FullyConnectedBridge(src, dst, bool(ip.get1("bias_term", True)), algo, ctx)
+                    _fill(ctx, br.p_model_cube, ip.msg("weight_filler"), seed, o)
+                    if br.bias_term:
+                        _fill(ctx, br.p_bias_cube, ip.msg("bias_filler"), seed, 1)
                 F = 2.0 * o * (x.R * x.C * x.D) * batch
             elif typ == "ReLU":
                 br = ReLUBridge(src, self._top(tops[0], bottoms[0], x.R, x.C, x.D), ctx)
@@ -260,7 +287,11 @@ class Net:
                     br.needs_to_calc_backward_grad = False  # nothing below the first layer wants dX (src/DeepNet.h:1108-1110)
                     first_param_layer = False
                 lr_mult, decay_mult = _multipliers(layer)
-                self.pbridges[len(self.bridges)] = ParallelizedBridge(br, solver, self.ops, lr_mult, decay_mult, defer_update=True)
+                if isinstance(br, ModelParallelFullyConnectedBridge):
+                    pb = ModelParallelizedBridge(br, solver, ctx, lr_mult, decay_mult, defer_update=True)
+                else:
+                    pb = ParallelizedBridge(br, solver, self.ops, lr_mult, decay_mult, defer_update=True)
+                self.pbridges[len(self.bridges)] = pb
                 self.flops_forward += F
                 self.flops_backward += (2.0 if br.needs_to_calc_backward_grad else 1.0) * F
             self.bridges.append(br)
@@ -398,6 +429,12 @@ class Net:
         self.ctx.sync()
         with open(path, "wb") as f:
             for _, pb in self.param_bridges():
+                if hasattr(pb, "model_host"):  # a layer split over the ranks: the whole matrix, gathered (a collective)
+                    w, b = pb.model_host()
+                    w.astype(np.float32).tofile(f)
+                    if b is not None:
+                        b.astype(np.float32).tofile(f)
+                    continue
                 pb.get_model_cube().download().astype(np.float32).tofile(f)
                 if pb.get_bias_cube() is not None:
                     pb.get_bias_cube().download().astype(np.float32).tofile(f)
@@ -405,6 +442,13 @@ class Net:
     def read_model_from_file(self, path):
         with open(path, "rb") as f:
             for name, pb in self.param_bridges():
+                if hasattr(pb, "set_model_host"):  # a layer split over the ranks keeps its own rows
+                    n_w, n_b = pb.full_counts
+                    w, b = np.fromfile(f, np.float32, n_w), (np.fromfile(f, np.float32, n_b) if n_b else None)
+                    if w.size != n_w or (b is not None and b.size != n_b):
+                        raise ValueError("model file ends inside layer %r" % name)
+                    pb.set_model_host(w, b)
+                    continue
                 for cube in (pb.get_model_cube(), pb.get_bias_cube()):
                     if cube is None:
                         continue
@@ -433,9 +477,10 @@ class Net:
         self.read_model_from_file(prefix + ".MODEL")
         with open(prefix + ".HISTORY", "rb") as f:
             for name, pb in self.param_bridges():
-                w = np.fromfile(f, np.float32, pb.n_w)
-                b = np.fromfile(f, np.float32, pb.n_b) if pb.n_b else None
-                if w.size != pb.n_w or (b is not None and b.size != pb.n_b):
+                n_w, n_b = getattr(pb, "full_counts", (pb.n_w, pb.n_b))
+                w = np.fromfile(f, np.float32, n_w)
+                b = np.fromfile(f, np.float32, n_b) if n_b else None
+                if w.size != n_w or (b is not None and b.size != n_b):
                     raise ValueError("history file ends inside layer %r" % name)
                 pb.set_history_host(w, b)
         with open(prefix + ".ITER") as f:

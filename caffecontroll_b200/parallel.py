@@ -106,10 +106,44 @@ class Communicator:
         capi.check(capi.load().cct_comm_unique_id(buf), "cct_comm_unique_id")
         return buf.raw
 
+    def allgather(self, send_ptr, recv_ptr, count_per_rank):
+        """recv[r * count_per_rank ...] = rank r's block of count_per_rank floats, on every rank."""
+        capi.check(self.ctx.lib.cct_allgather(self.h, C.c_void_p(send_ptr), C.c_void_p(recv_ptr), count_per_rank),
+                   "cct_allgather", self.ctx.h)
+
+    def reduce_scatter_sum(self, send_ptr, recv_ptr, count_per_rank):
+        """recv = the sum over ranks of their send[rank * count_per_rank ...] blocks."""
+        capi.check(self.ctx.lib.cct_reduce_scatter_sum(self.h, C.c_void_p(send_ptr), C.c_void_p(recv_ptr), count_per_rank),
+                   "cct_reduce_scatter_sum", self.ctx.h)
+
     def close(self):
         if self.h:
             self.ctx.lib.cct_comm_destroy(self.h)
             self.h = None
+
+
+def model_parallel_gpus(depth_proportions, output_depth):
+    """The GPUs of a model-parallel layer from its placement fields gpu_{0..3}_depth_proportion, with the checks of
+    DeepNet::get_model_parallelism_info (src/DeepNet.h:728-790): every share divides the output depth exactly, all
+    non-zero shares are equal, they add up to 1 over two or more GPUs - or are all zero (no model parallelism: [])."""
+    used, share = [], 0.0
+    for i, p in enumerate(depth_proportions):
+        if p == 1.0:
+            raise ValueError("a depth proportion of 1.0: model parallelism needs two or more GPUs (use batch proportions)")
+        if p < 0 or float(output_depth) * p != int(float(output_depth) * p):
+            raise ValueError("model parallelism must divide the output depth exactly (depth %d, proportion %g)" %
+                             (output_depth, p))
+        if p > 0:
+            if share and p != share:
+                raise ValueError("every GPU of a model-parallel layer must have the same depth proportion")
+            share = p
+            used.append(i)
+    total = sum(depth_proportions)
+    if not used:
+        return []
+    if abs(total - 1.0) > 1e-6:
+        raise ValueError("depth proportions must add up to 1 (model parallelism is all on the GPUs)")
+    return used
 
 
 class DeviceOps:
@@ -186,6 +220,134 @@ class DeviceOps:
         capi.check(self.ctx.lib.cct_memcpy_d2d(self.ctx.h, C.c_void_p(dst), C.c_void_p(src), 4 * count), "cct_memcpy_d2d",
                    self.ctx.h)
         self.ctx.sync()  # the source is freed right after
+
+
+class SliceOps(DeviceOps):
+    """DeviceOps for parameters that only this rank holds (a slice of a model-parallel layer): its gradients are already
+    those of the whole mini-batch, so there is nothing to sum."""
+
+    def __init__(self, ctx):
+        super().__init__(ctx, comm=None)
+
+    def world_size(self):
+        return 1
+
+    def allreduce_begin(self, ptr, count):
+        pass
+
+    def allreduce_wait(self):
+        pass
+
+
+class ModelParallelFullyConnectedBridge:
+    """A fully connected layer split over the ranks by output depth: what DeepNet builds as split bridge -> one
+    FullyConnectedBridge per GPU over output_depth / n_gpus outputs, each on the whole mini-batch -> concat bridge
+    (src/DeepNet.h:1213-1357), with the host round trips of those two bridges replaced by NCCL exchanges.
+
+    The layers around it stay data parallel, so its input and output layers hold this rank's batch slice:
+      forward   all-gather of the input slices (every rank sees the whole mini-batch, as behind the reference's split
+                bridge) -> this rank's output slice for the whole batch -> all-gather of the slices, of which the rows of
+                this rank's images are copied side by side into its output cube (the concat bridge);
+      backward  all-gather of the output gradients, this rank's columns of it -> weight / bias gradient of the slice (over
+                the whole mini-batch: no gradient sum is needed) and its share of the input gradient for every image ->
+                reduce-scatter: each rank receives the sum over the slices for its own images (SplitBridge::backward,
+                src/bridges/SplitBridge_impl.hxx:51-90).
+    Model and bias cubes are this rank's slice (rows rank * O / n ... of the [num_output][in_features] matrix)."""
+
+    algo = capi.ALGO_SIMT_FP32  # keeps the network's fusion pass away: the ReLU / dropout bridges around it run as bridges
+
+    def __init__(self, p_input_layer, p_output_layer, comm, bias_term=True, algo=capi.ALGO_AUTO, ctx=None):
+        from .bridge import FullyConnectedBridge, Layer, LogicalCube
+        x, y = p_input_layer.p_data_cube, p_output_layer.p_data_cube
+        self.p_input_layer, self.p_output_layer = p_input_layer, p_output_layer
+        self.ctx = ctx or x.ctx
+        self.lib, self.comm = self.ctx.lib, comm
+        self.world, self.rank = comm.nranks, comm.rank
+        self.iR, self.iC, self.iD, self.iB = x.R, x.C, x.D, x.B
+        self.oR, self.oC, self.oD, self.oB = y.R, y.C, y.D, y.B
+        if (self.oR, self.oC, self.oB) != (1, 1, self.iB):
+            raise ValueError("output layer must be B x num_output x 1 x 1")
+        if self.oD % self.world:
+            raise ValueError("model parallelism must divide the output depth exactly (%d outputs, %d GPUs)" %
+                             (self.oD, self.world))
+        self.slice_depth = self.oD // self.world
+        self.in_features = x.D * x.R * x.C
+        self.global_batch = self.iB * self.world
+        self.bias_term = bias_term
+        self.needs_to_calc_backward_grad = True
+        c, Bg = self.ctx, self.global_batch
+        self.all_in = Layer(LogicalCube(c, x.R, x.C, x.D, Bg), LogicalCube(c, x.R, x.C, x.D, Bg))
+        self.slice_out = Layer(LogicalCube(c, 1, 1, self.slice_depth, Bg), LogicalCube(c, 1, 1, self.slice_depth, Bg))
+        self.staging = LogicalCube(c, 1, 1, self.oD, Bg)  # gathered output slices / gathered output gradients
+        self.inner = FullyConnectedBridge(self.all_in, self.slice_out, bias_term, algo, c)
+        i = self.inner
+        self.p_model_cube, self.p_model_gradient_cube = i.p_model_cube, i.p_model_gradient_cube
+        self.p_bias_cube, self.p_bias_gradient_cube = i.p_bias_cube, i.p_bias_gradient_cube
+
+    def get_model_cube(self):
+        return self.p_model_cube
+
+    def get_bias_cube(self):
+        return self.p_bias_cube
+
+    def get_model_grad_cube(self):
+        return self.p_model_gradient_cube
+
+    def get_bias_grad_cube(self):
+        return self.p_bias_gradient_cube
+
+    def _copy2d(self, dst, dst_pitch, src, src_pitch, width, rows):
+        capi.check(self.lib.cct_memcpy2d_d2d(self.ctx.h, C.c_void_p(dst), 4 * dst_pitch, C.c_void_p(src), 4 * src_pitch,
+                                             4 * width, rows), "cct_memcpy2d_d2d", self.ctx.h)
+
+    def forward(self):
+        B, Bg, K, O, Os = self.iB, self.global_batch, self.in_features, self.oD, self.slice_depth
+        self.comm.allgather(self.p_input_layer.p_data_cube.ptr, self.all_in.p_data_cube.ptr, B * K)
+        self.inner.forward()
+        self.comm.allgather(self.slice_out.p_data_cube.ptr, self.staging.ptr, Bg * Os)
+        y = self.p_output_layer.p_data_cube.ptr
+        for q in range(self.world):  # rank q's slice for this rank's images -> columns q * Os ... of the output cube
+            self._copy2d(y + 4 * q * Os, O, self.staging.ptr + 4 * (q * Bg + self.rank * B) * Os, Os, Os, B)
+
+    def backward(self):
+        B, Bg, K, O, Os = self.iB, self.global_batch, self.in_features, self.oD, self.slice_depth
+        self.comm.allgather(self.p_output_layer.p_gradient_cube.ptr, self.staging.ptr, B * O)
+        self._copy2d(self.slice_out.p_gradient_cube.ptr, Os, self.staging.ptr + 4 * self.rank * Os, O, Os, Bg)
+        self.inner.needs_to_calc_backward_grad = self.needs_to_calc_backward_grad
+        self.inner.backward()
+        if self.needs_to_calc_backward_grad:
+            self.comm.reduce_scatter_sum(self.all_in.p_gradient_cube.ptr, self.p_input_layer.p_gradient_cube.ptr, B * K)
+
+    # the whole layer's parameters to / from the host (every rank calls these: they gather over the ranks)
+    def gather_host(self, ptr, n):
+        """n floats at `ptr` of every rank, in rank order, as one host array (a collective: every rank calls it)."""
+        from .bridge import LogicalCube
+        full = LogicalCube(self.ctx, 1, 1, n, self.world)
+        self.comm.allgather(ptr, full.ptr, n)
+        self.ctx.sync()
+        out = full.download().ravel()
+        full.free()
+        return out
+
+    def model_host(self):
+        w = self.gather_host(self.p_model_cube.ptr, self.p_model_cube.n_elements).reshape(self.oD, self.iD, self.iR, self.iC)
+        b = self.gather_host(self.p_bias_cube.ptr, self.slice_depth).reshape(1, self.oD, 1, 1) if self.bias_term else None
+        return w, b
+
+    def set_model_host(self, w, b=None):
+        Os = self.slice_depth
+        w = np.ascontiguousarray(w, np.float32).reshape(self.oD, -1)
+        self.p_model_cube.upload(w[self.rank * Os:(self.rank + 1) * Os].reshape(self.p_model_cube.shape))
+        if self.bias_term and b is not None:
+            b = np.ascontiguousarray(b, np.float32).ravel()
+            self.p_bias_cube.upload(b[self.rank * Os:(self.rank + 1) * Os].reshape(self.p_bias_cube.shape))
+
+    def close(self):
+        self.inner.close()
+        for layer in (self.all_in, self.slice_out):
+            layer.p_data_cube.free()
+            layer.p_gradient_cube.free()
+        self.staging.free()
 
 
 class ParallelizedBridge:
@@ -304,3 +466,35 @@ class ParallelizedBridge:
             for p in (self.params, self.grads, self.hist):
                 free(p)
         self.params = self.grads = self.hist = None
+
+
+class ModelParallelizedBridge(ParallelizedBridge):
+    """The updater around a ModelParallelFullyConnectedBridge: this rank's slice of the parameters, their gradients over
+    the whole mini-batch (so no sum over ranks) and their momentum history.  The host-side views (model files,
+    snapshots) are those of the whole layer: reading gathers the slices in rank order - the rows of the
+    [num_output][in_features] matrix in order - and is a collective every rank takes part in."""
+
+    def __init__(self, bridge, solver, ctx, lr_mult=(1.0, 2.0), decay_mult=(1.0, 0.0), defer_update=False):
+        super().__init__(bridge, solver, SliceOps(ctx), lr_mult, decay_mult, defer_update)
+
+    def model_host(self):
+        return self.bridge.model_host()
+
+    def set_model_host(self, w, b=None):
+        self.bridge.set_model_host(w, b)
+
+    @property
+    def full_counts(self):
+        return self.n_w * self.bridge.world, self.n_b * self.bridge.world
+
+    def history_host(self):
+        w = self.bridge.gather_host(self.hist, self.n_w)
+        b = self.bridge.gather_host(self.hist + 4 * self.n_w, self.n_b) if self.n_b else None
+        return w, b
+
+    def set_history_host(self, w_hist, b_hist=None):
+        r = self.bridge.rank
+        w = np.ascontiguousarray(w_hist, np.float32).ravel()[r * self.n_w:(r + 1) * self.n_w]
+        b = np.ascontiguousarray(b_hist, np.float32).ravel()[r * self.n_b:(r + 1) * self.n_b] if self.n_b else None
+        super().set_history_host(w, b)
+

@@ -59,6 +59,11 @@ int cct_free_host(cct_ctx* ctx, void* hptr);
 int cct_memcpy_h2d(cct_ctx* ctx, void* dst, const void* src, size_t bytes); /* stream-ordered */
 int cct_memcpy_d2h(cct_ctx* ctx, void* dst, const void* src, size_t bytes); /* stream-ordered */
 int cct_memcpy_d2d(cct_ctx* ctx, void* dst, const void* src, size_t bytes);
+/* `rows` runs of width_bytes each, the runs dst_pitch / src_pitch bytes apart (stream-ordered, device to device): the
+ * column blocks a model-parallel layer's concat and split bridges move (src/bridges/ConcatBridge_impl.hxx,
+ * src/bridges/SplitBridge_impl.hxx copy whole cubes; here the slices sit side by side in one row-major cube). */
+int cct_memcpy2d_d2d(cct_ctx* ctx, void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes,
+                     size_t rows);
 int cct_memset(cct_ctx* ctx, void* dptr, int byte_value, size_t bytes);
 /* DeviceDriver::sconstant_initialize (src/sched/DeviceDriver.h:236, DeviceDriver_GPU.cu:1189-1200). */
 int cct_fill_f32(cct_ctx* ctx, float* dptr, size_t count, float value);
@@ -258,6 +263,15 @@ int cct_comm_size(const cct_comm* comm, int* nranks, int* rank);
 int cct_allreduce_sum_begin(cct_comm* comm, float* buf, size_t count);
 int cct_comm_wait(cct_comm* comm);
 int cct_allreduce_sum(cct_comm* comm, float* buf, size_t count);
+/* The exchanges of a model-parallel fully connected layer (DeepNet builds it as split bridge -> one fully connected
+ * bridge per GPU over an equal slice of the output depth -> concat bridge, with the whole mini-batch copied to every
+ * GPU through the host: src/DeepNet.h:1213-1357).  cct_allgather: recv[r * count_per_rank ...] = rank r's send block,
+ * for every rank r (ncclAllGather).  cct_reduce_scatter_sum: recv = the sum over ranks of their
+ * send[rank * count_per_rank ...] blocks (ncclReduceScatter) - the sum the split bridge's backward pass forms of the
+ * slices' input gradients.  Both are ordered behind the work queued on the context's stream and the context's stream
+ * waits for them; with one rank they are copies. */
+int cct_allgather(cct_comm* comm, const float* send, float* recv, size_t count_per_rank);
+int cct_reduce_scatter_sum(cct_comm* comm, const float* send, float* recv, size_t count_per_rank);
 
 /* ---- the other bridges of a CaffeNet iteration, as HBM-bound kernels ---- */
 /* LRNBridge (across channels; src/bridges/LRNBridge_impl.hxx:46-190, src/kernels/lrn.hxx:38-180, exact pow as in the

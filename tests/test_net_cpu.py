@@ -82,3 +82,19 @@ def test_every_prototxt_of_the_reference_parses():
         layers = [l for l in parse_prototxt(fh.read()).all("layer") if _in_phase(l, "TRAIN")]
     assert [_layer_type(l) for l in layers].count("Convolution") == 5
     assert _multipliers(layers[1]) == ((1.0, 2.0), (1.0, 0.0))  # the older blobs_lr / weight_decay notation
+
+
+def test_model_parallel_placement_fields_follow_the_reference_rules():
+    """DeepNet::get_model_parallelism_info (src/DeepNet.h:728-790)."""
+    import pytest
+    from caffecontroll_b200.parallel import model_parallel_gpus
+    assert model_parallel_gpus([0.0, 0.0, 0.0, 0.0], 4096) == []
+    assert model_parallel_gpus([0.5, 0.5, 0.0, 0.0], 4096) == [0, 1]
+    assert model_parallel_gpus([0.25, 0.25, 0.25, 0.25], 4096) == [0, 1, 2, 3]
+    for bad, depth in (([1.0, 0.0, 0.0, 0.0], 4096),      # one GPU: use batch proportions
+                       ([0.5, 0.25, 0.25, 0.0], 4096),     # unequal shares
+                       ([0.5, 0.0, 0.0, 0.0], 4096),       # does not add up to 1
+                       ([0.5, 0.5, 0.0, 0.0], 1001)):      # does not divide the depth
+        with pytest.raises(ValueError):
+            model_parallel_gpus(bad, depth)
+
