@@ -570,7 +570,8 @@ def run_caffenet(args, rank, world, local_rank):
         net_param = parse_prototxt(f.read())
     with open(os.path.join(nets_dir, "caffenet_solver.prototxt")) as f:
         solver = solver_from_message(parse_prototxt(f.read()))
-    net = Net(ctx, net_param, solver, B, ops=ops, loss_batch=B * world, algo=args.algo)
+    split = tuple(n for n in args.model_parallel.split(",") if n) if world > 1 else ()
+    net = Net(ctx, net_param, solver, B, ops=ops, loss_batch=B * world, algo=args.algo, model_parallel=split)
     rng = np.random.default_rng(5000 + rank)
     X = rng.standard_normal((B, 3, 227, 227), dtype=np.float32)
     labels = rng.integers(0, 1000, B).astype(np.float32)
@@ -792,7 +793,8 @@ def run_caffenet(args, rank, world, local_rank):
                        "step": "forward + backward of all 23 layers + NCCL all-reduce of the %.1f M parameter gradients (N>1, "
                                "begun per layer, overlapping the layers below) + SGD momentum step" % (net.num_parameters() / 1e6),
                        "fusions": net.fused, "l2": "inputs larger than L2 (%.1f GB of activations and gradients per step)" %
-                       (sum(c.n_elements * 4 for c in net._cubes) / 1e9), "parallelism": "dp%d" % world},
+                       (sum(c.n_elements * 4 for c in net._cubes) / 1e9),
+                       "parallelism": "dp%d" % world + (" + %s split by output depth" % "/".join(split) if split else "")},
             "tflops": tf, "flops_per_step": flops,
             "roofline": {"bound": "tensor", "kernel": dom_name, "achieved": ach, "peak": roof["peak"], "unit": "TFLOP/s",
                          "frac": ach / roof["peak"] if roof["peak"] else None, "traffic": dom_traffic,
@@ -889,6 +891,8 @@ def main():
                     help="untimed warm-up runs until at least this much device time has passed (and --warmup steps)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (profiling on a small case)")
+    ap.add_argument("--model-parallel", default="", help="comma-separated InnerProduct layers to split over the ranks by "
+                    "output depth instead of by batch (N > 1 only; the default and the BASELINE configs are data parallel)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.workload == "caffenet":

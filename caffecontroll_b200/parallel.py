@@ -255,6 +255,7 @@ class ModelParallelFullyConnectedBridge:
     Model and bias cubes are this rank's slice (rows rank * O / n ... of the [num_output][in_features] matrix)."""
 
     algo = capi.ALGO_SIMT_FP32  # keeps the network's fusion pass away: the ReLU / dropout bridges around it run as bridges
+    plan = None                 # the plan belongs to the inner bridge
 
     def __init__(self, p_input_layer, p_output_layer, comm, bias_term=True, algo=capi.ALGO_AUTO, ctx=None):
         from .bridge import FullyConnectedBridge, Layer, LogicalCube
