@@ -334,17 +334,103 @@ class Communicator {
     if (cct_comm_unique_id(id.data()) != CCT_OK) { std::fprintf(stderr, "cct_b200: NCCL is not available\n"); std::abort(); }
     return id;
   }
-  Communicator(B200Driver* driver, int nranks, int rank, const unsigned char* id) : driver_(driver) {
+  Communicator(B200Driver* driver, int nranks, int rank, const unsigned char* id)
+      : driver_(driver), nranks_(nranks), rank_(rank) {
     driver->check(cct_comm_init_rank(driver->ctx(), nranks, rank, id, &comm_), "cct_comm_init_rank");
   }
   ~Communicator() { if (comm_) cct_comm_destroy(comm_); }
   Communicator(const Communicator&) = delete;
+  int nranks() const { return nranks_; }
+  int rank() const { return rank_; }
   void allreduce_sum_begin(float* buf, size_t count) { driver_->check(cct_allreduce_sum_begin(comm_, buf, count), "cct_allreduce_sum_begin"); }
   void wait() { driver_->check(cct_comm_wait(comm_), "cct_comm_wait"); }
+  // recv[r * count ...] = rank r's block, on every rank / recv = the sum over ranks of their send[rank * count ...] blocks
+  void allgather(const float* send, float* recv, size_t count) { driver_->check(cct_allgather(comm_, send, recv, count), "cct_allgather"); }
+  void reduce_scatter_sum(const float* send, float* recv, size_t count) {
+    driver_->check(cct_reduce_scatter_sum(comm_, send, recv, count), "cct_reduce_scatter_sum");
+  }
 
  private:
   B200Driver* driver_;
+  int nranks_, rank_;
   cct_comm* comm_ = nullptr;
+};
+
+// A fully connected layer split over the ranks by output depth: what DeepNet builds as split bridge -> one
+// FullyConnectedBridge per GPU over num_output / n outputs, each on the whole mini-batch -> concat bridge
+// (src/DeepNet.h:1213-1357), the host round trips of those two bridges replaced by NCCL exchanges.  The layers around
+// it stay data parallel: its input and output layers hold this rank's batch slice.
+//   forward   all-gather of the input slices -> this rank's output columns for the whole mini-batch -> all-gather of the
+//             column slices, of which the rows of this rank's images are put side by side into the output cube;
+//   backward  all-gather of the output gradients, this rank's columns of them -> weight / bias gradient of the slice
+//             over the whole mini-batch (no sum over ranks is needed: wrap it in a ParallelizedBridgeT without a
+//             communicator) and a partial input gradient for every image -> reduce-scatter: each rank receives the sum
+//             for its own images (SplitBridge::backward, src/bridges/SplitBridge_impl.hxx:51-90).
+// Model and bias cubes are this rank's slice: rows rank * num_output / n ... of the [num_output][in_features] matrix.
+class ModelParallelFullyConnectedBridge : public PhysicalOperator {
+ public:
+  Layer* const p_input_layer;
+  Layer* const p_output_layer;
+  B200Driver* const p_driver;
+  const bool bias_term;
+  bool needs_to_calc_backward_grad = true;
+
+  ModelParallelFullyConnectedBridge(Layer* in, Layer* out, int num_output, bool bias, B200Driver* driver, Communicator* comm)
+      : p_input_layer(in), p_output_layer(out), p_driver(driver), bias_term(bias), comm_(comm),
+        batch_(in->p_data_cube->B), global_batch_(batch_ * comm->nranks()),
+        in_features_(in->p_data_cube->R * in->p_data_cube->C * in->p_data_cube->D), outputs_(num_output),
+        slice_(check_slice(num_output, comm->nranks(), driver)),
+        all_x_(in->p_data_cube->R, in->p_data_cube->C, in->p_data_cube->D, global_batch_, driver),
+        all_dx_(in->p_data_cube->R, in->p_data_cube->C, in->p_data_cube->D, global_batch_, driver),
+        slice_y_(1, 1, slice_, global_batch_, driver), slice_dy_(1, 1, slice_, global_batch_, driver),
+        staging_(1, 1, num_output, global_batch_, driver), all_in_(&all_x_, &all_dx_), slice_out_(&slice_y_, &slice_dy_),
+        inner_(&all_in_, &slice_out_, (int)slice_, bias, driver) {
+    if (out->p_data_cube->B != batch_ || out->p_data_cube->n_elements / batch_ != outputs_)
+      driver->check(CCT_ERR_INVALID, "ModelParallelFullyConnectedBridge: output layer must be B x num_output x 1 x 1");
+  }
+  LogicalCube<float>* get_model_cube() { return inner_.get_model_cube(); }
+  LogicalCube<float>* get_bias_cube() { return inner_.get_bias_cube(); }
+  LogicalCube<float>* get_model_grad_cube() { return inner_.get_model_grad_cube(); }
+  LogicalCube<float>* get_bias_grad_cube() { return inner_.get_bias_grad_cube(); }
+  void set_model_cube(float* p) { inner_.set_model_cube(p); }
+  void set_bias_cube(float* p) { inner_.set_bias_cube(p); }
+  void set_model_grad_cube(float* p) { inner_.set_model_grad_cube(p); }
+  void set_bias_grad_cube(float* p) { inner_.set_bias_grad_cube(p); }
+  size_t slice_depth() const { return slice_; }
+
+  void forward() override {
+    comm_->allgather(p_input_layer->p_data_cube->get_p_data(), all_x_.get_p_data(), batch_ * in_features_);
+    inner_.forward();
+    comm_->allgather(slice_y_.get_p_data(), staging_.get_p_data(), global_batch_ * slice_);
+    float* y = p_output_layer->p_data_cube->get_p_data();
+    for (int q = 0; q < comm_->nranks(); ++q)  // rank q's columns for this rank's images
+      copy2d(y + q * slice_, outputs_, staging_.get_p_data() + ((size_t)q * global_batch_ + comm_->rank() * batch_) * slice_,
+             slice_, slice_, batch_);
+  }
+  void backward() override {
+    comm_->allgather(p_output_layer->p_gradient_cube->get_p_data(), staging_.get_p_data(), batch_ * outputs_);
+    copy2d(slice_dy_.get_p_data(), slice_, staging_.get_p_data() + comm_->rank() * slice_, outputs_, slice_, global_batch_);
+    inner_.needs_to_calc_backward_grad = needs_to_calc_backward_grad;
+    inner_.backward();
+    if (needs_to_calc_backward_grad)
+      comm_->reduce_scatter_sum(all_dx_.get_p_data(), p_input_layer->p_gradient_cube->get_p_data(), batch_ * in_features_);
+  }
+
+ private:
+  static size_t check_slice(int num_output, int nranks, B200Driver* driver) {
+    if (nranks < 1 || num_output % nranks)  // "model parallelism must divide depth exactly" (src/DeepNet.h:744-750)
+      driver->check(CCT_ERR_INVALID, "ModelParallelFullyConnectedBridge: the ranks must divide num_output");
+    return (size_t)(num_output / nranks);
+  }
+  void copy2d(float* dst, size_t dst_pitch, const float* src, size_t src_pitch, size_t width, size_t rows) {
+    p_driver->check(cct_memcpy2d_d2d(p_driver->ctx(), dst, dst_pitch * sizeof(float), src, src_pitch * sizeof(float),
+                                     width * sizeof(float), rows), "cct_memcpy2d_d2d");
+  }
+  Communicator* comm_;
+  size_t batch_, global_batch_, in_features_, outputs_, slice_;
+  LogicalCube<float> all_x_, all_dx_, slice_y_, slice_dy_, staging_;
+  Layer all_in_, slice_out_;
+  FullyConnectedBridge inner_;
 };
 
 // One batch partition on one GPU.  forward()/backward() run the sub-bridge; backward() then sums the model and bias

@@ -101,6 +101,40 @@ int main(int argc, char** argv) {
       });
     for (auto& t : threads) t.join();
   }
+  if (mode.compare(0, 5, "mpfc=") == 0) {
+    // kernel == input: the layer as a fully connected one split over `ranks` GPUs by output depth, one host thread each
+    const int ranks = atoi(mode.c_str() + 5);
+    if (ranks < 2 || B % ranks || o % ranks) { std::cerr << "ranks must be >= 2 and divide batch and outputs" << std::endl; return 2; }
+    const std::vector<unsigned char> id = Communicator::unique_id();
+    const std::vector<float> hX = load(dir + "/X.bin", x.n_elements), hdY = load(dir + "/dY.bin", dy.n_elements),
+                             hW = load(dir + "/W.bin", hdw.size()), hb0 = load(dir + "/b.bin", o);
+    const int Bp = B / ranks, os = o / ranks;
+    std::vector<std::thread> threads;
+    for (int r = 0; r < ranks; ++r)
+      threads.emplace_back([&, r]() {
+        B200Driver drv(r);
+        Communicator comm(&drv, ranks, r, id.data());
+        LogicalCube<float> px(n, n, D, Bp, &drv), pdx(n, n, D, Bp, &drv), py(1, 1, o, Bp, &drv), pdy(1, 1, o, Bp, &drv);
+        Layer pin(&px, &pdx), pout(&py, &pdy);
+        ModelParallelFullyConnectedBridge sub(&pin, &pout, o, true, &drv, &comm);
+        ParallelizedBridgeT<ModelParallelFullyConnectedBridge> pb(&sub, &solver, &drv, nullptr);  // slice gradients need no sum
+        pb.set_update_model_gradients(false);
+        px.copy_from_host(hX.data() + (size_t)r * px.n_elements);
+        pdy.copy_from_host(hdY.data() + (size_t)r * pdy.n_elements);
+        const size_t nw = sub.get_model_cube()->n_elements;  // rows r * os ... of the [o][D n n] matrix
+        sub.get_model_cube()->copy_from_host(hW.data() + (size_t)r * nw);
+        sub.get_bias_cube()->copy_from_host(hb0.data() + (size_t)r * os);
+        pb.forward();
+        pb.backward();
+        drv.device_sync();
+        std::vector<float> vy(py.n_elements), vdx(pdx.n_elements), vdw(nw), vdb(os);
+        py.copy_to_host(vy.data()); pdx.copy_to_host(vdx.data());
+        sub.get_model_grad_cube()->copy_to_host(vdw.data()); sub.get_bias_grad_cube()->copy_to_host(vdb.data());
+        const std::string tag = "_mp" + std::to_string(r) + ".bin";
+        save(dir + "/Y" + tag, vy); save(dir + "/dX" + tag, vdx); save(dir + "/dW" + tag, vdw); save(dir + "/db" + tag, vdb);
+      });
+    for (auto& t : threads) t.join();
+  }
   std::cout << "host_selftest ok" << std::endl;
   return 0;
 }

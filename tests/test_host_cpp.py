@@ -99,3 +99,32 @@ def test_host_mirror_two_gpus_one_thread_each(port, tmp_path):
         assert maxnorm_rel(rd("Wnew_r%d" % r, W.shape), W1) <= TOL
         assert maxnorm_rel(rd("bnew_r%d" % r, (o,)), b1) <= TOL
     assert np.array_equal(rd("Wnew_r0", W.shape), rd("Wnew_r1", W.shape))
+
+
+@pytest.mark.gpu
+def test_host_mirror_model_parallel_fc_two_gpus(port, tmp_path):
+    """The C++ ModelParallelFullyConnectedBridge (output depth split over two GPUs, one host thread each, NCCL exchanges
+    through the C ABI): every rank's output rows, input-gradient rows and its slice of the weight and bias gradients
+    against the oracle's product over the whole batch."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    exe = _build()
+    B, D, n, o, k, s, p, g = 8, 5, 4, 24, 4, 1, 0, 1
+    X, W, b, dY = make_inputs(58, B, D, n, o, k, s, p, g)
+    for name, arr in (("X", X), ("W", W), ("b", b), ("dY", dY)):
+        arr.tofile(os.path.join(str(tmp_path), name + ".bin"))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    subprocess.run([exe, str(tmp_path)] + [str(v) for v in (B, D, n, o, k, s, p, g, 0)] + ["mpfc=2"], check=True, env=env,
+                   timeout=300)
+    rd = lambda name, shape: np.fromfile(os.path.join(str(tmp_path), name + ".bin"), np.float32).reshape(shape)
+    Yr = port.conv_forward(X, W, b, k, s, p, g)
+    dXr, dWr, dbr = port.conv_backward(X, W, dY, k, s, p, g)
+    Bp, os_ = B // 2, o // 2
+    for r in (0, 1):
+        rows, cols = slice(r * Bp, (r + 1) * Bp), slice(r * os_, (r + 1) * os_)
+        assert_close(rd("Y_mp%d" % r, (Bp, o, 1, 1)), Yr[rows], "Y rank %d" % r)
+        assert_close(rd("dX_mp%d" % r, (Bp,) + X.shape[1:]), dXr[rows], "dX rank %d" % r)
+        assert_close(rd("dW_mp%d" % r, (os_,) + W.shape[1:]), dWr[cols], "dW rank %d" % r)
+        assert_close(rd("db_mp%d" % r, (os_,)), dbr[cols], "db rank %d" % r)
+
